@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the convolution-layer hot path: the 13 conv layers of VGG-16 (3x3, stride 1, pad 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode fp32|3xtf32|tf32] [--batch B]
+    python bench.py --impl reference ...      # the reference's own CPU algorithm on the host cores
+
+A step is one Forward() of every layer of the stack on this rank's own images (each layer has its
+own seeded synthetic input and weights: the reference benchmarks single layers, it does not chain
+them).  With N GPUs every rank runs the same stack on different images, no collective in the data
+path (weak scaling).  The metric is direct-convolution-equivalent GFLOP/s,
+sum(2*N*K*C*9*OH*OW) / time, whole job.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# C, K, H(=W) of the 13 VGG-16 conv layers at 224x224 input
+VGG16 = [(3, 64, 224), (64, 64, 224), (64, 128, 112), (128, 128, 112), (128, 256, 56), (256, 256, 56), (256, 256, 56),
+         (256, 512, 28), (512, 512, 28), (512, 512, 28), (512, 512, 14), (512, 512, 14), (512, 512, 14)]
+
+HBM_FALLBACK_GBS = 6650.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return HBM_FALLBACK_GBS, 1590.0, "fallback"
+
+
+def layer_flops(n, c, k, h):
+    return 2.0 * n * k * c * 9 * h * h
+
+
+def wino_geometry(n, c, k, h):
+    t = n * ((h + 5) // 6) ** 2
+    return t, (t + 7) // 8 * 8, (c + 7) // 8 * 8
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_cpu_pass(layers, batch, threads, seeds_base=0):
+    """One pass of the reference's own Winograd driver (oracle/_ref, compiled from the reference sources
+    through the NEON stand-in header) over the layer stack, all host threads.  Returns seconds."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    from _oracle import Reference
+    from fastconv_b200 import synth
+
+    ref = Reference.try_load()
+    if ref is None:
+        return None, "oracle/_ref/libfastconv_ref.so is not built"
+    total = 0.0
+    for idx, (c, k, h) in enumerate(layers):
+        x = synth.conv_input(1, c, h, h, 1000 + idx + seeds_base)
+        w = synth.conv_weights(k, c, 3, 3, 2000 + idx)
+        t0 = time.perf_counter()
+        for _ in range(batch):
+            ref.wino_forward(x, w, 1, threads=threads)
+        total += time.perf_counter() - t0
+    return total, None
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    layers = VGG16
+    flops = sum(layer_flops(args.batch, c, k, h) for c, k, h in layers)
+    for _ in range(min(args.warmup, 1)):
+        reference_cpu_pass(layers, args.batch, threads)
+    times = []
+    for _ in range(args.steps):
+        t, err = reference_cpu_pass(layers, args.batch, threads)
+        if t is None:
+            print(json.dumps({"impl": "reference", "unavailable": err}))
+            return
+        times.append(t)
+    sec = sum(times) / len(times)
+    value = flops / sec / 1e9
+    line = {
+        "impl": "reference", "metric": "conv GFLOP/s (direct-equiv), VGG-16 conv stack", "value": value,
+        "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"VGG-16 13 conv layers, batch {args.batch}, 224x224, 3x3 s1 p1, fp32 NCHW",
+                   "algorithm": "reference winoF63_v1_multi (tileReg 5), online filter transform"},
+        "cpu_baseline": {"value": value, "unit": "GFLOP/s", "cores": threads, "kind": "reference",
+                         "sample": "all 13 layers, every step; NEON emulated through a vector-type stand-in header"},
+        "e2e": {"value": value, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="fastconv", choices=["fastconv", "reference"])
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32"])
+    ap.add_argument("--batch", type=int, default=1, help="images per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "fastconv":
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import fastconv_b200 as fc
+    from fastconv_b200 import _lib, synth
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    lib = fc.load()
+    mode = _lib.MODE_NAMES[args.mode]
+    n = args.batch
+    layers = VGG16
+    # arena: weights (U is 64/9 of the raw filter), Winograd-domain V and M, activations
+    need = 0
+    for c, k, h in layers:
+        t, tp, icp = wino_geometry(n, c, k, h)
+        need += 4 * (64 * k * icp + 64 * tp * icp + 64 * k * tp + k * c * 9 + n * c * h * h + n * k * h * h) + 8 * 4096
+    ctx = fc.Context(local_rank, arena_bytes=int(need * 1.05) + (64 << 20))
+
+    convs, flops, h2d, d2h, footprint = [], 0.0, 0, 0, 0
+    host_in, host_out = [], []
+    for idx, (c, k, h) in enumerate(layers):
+        desc = fc.make_desc(n, c, h, h, k)
+        w = synth.conv_weights(k, c, 3, 3, 2000 + idx)
+        x = synth.conv_input(n, c, h, h, 1000 + idx + 100 * rank)
+        hdl = C.c_void_p()
+        _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, mode, C.c_void_p(w.ctypes.data),
+                                      C.byref(hdl)), "fc_conv_create")
+        d_in, d_out = C.c_void_p(), C.c_void_p()
+        _lib.check(lib.fc_conv_device_buffers(hdl, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
+        ctx.upload(x, d_in.value)
+        px = ctx.pinned(x.shape)
+        px[...] = x
+        po = ctx.pinned((n, k, h, h))
+        host_in.append(px)
+        host_out.append(po)
+        convs.append((hdl, d_in, d_out, desc))
+        flops += layer_flops(n, c, k, h)
+        h2d += x.nbytes
+        d2h += po.nbytes
+        t, tp, icp = wino_geometry(n, c, k, h)
+        footprint += 4 * (64 * k * icp + 64 * tp * icp + 64 * k * tp + n * c * h * h + n * k * h * h)
+
+    def step_device():
+        for hdl, d_in, d_out, _ in convs:
+            _lib.check(lib.fc_conv_forward_device(hdl, d_in, d_out), "fc_conv_forward_device")
+
+    def step_host():
+        for (hdl, _, _, _), px, po in zip(convs, host_in, host_out):
+            _lib.check(lib.fc_conv_forward_host(hdl, C.c_void_p(px.ctypes.data), C.c_void_p(po.ctypes.data)),
+                       "fc_conv_forward_host")
+
+    def barrier():
+        ctx.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def reduce_max(v: float) -> float:
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput (`value`) -----------------------------------------------------
+    for _ in range(args.warmup):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ctx.timer_record(0)
+    for _ in range(args.steps):
+        step_device()
+    ctx.timer_record(1)
+    ms_total = ctx.timer_elapsed_ms(0, 1)
+    barrier()
+    clocks = sampler.stop()
+    ms_step = reduce_max(ms_total) / args.steps
+
+    # ---- end to end through the host-pointer entry point (pinned host buffers) ----------------------
+    for _ in range(3):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    ctx.synchronize()
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / args.steps
+    barrier()
+
+    # ---- per-layer and per-kernel device times (CUDA events around each stage, same inputs) ----------
+    per_layer, stage_tot = [], [0.0] * 5
+    launches_per_step = 0
+    gemm_bytes = gemm_ms = gemm_flops = 0.0
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    for (hdl, d_in, d_out, desc), (c, k, h) in zip(convs, layers):
+        ms = (C.c_float * 5)()
+        _lib.check(lib.fc_conv_profile(hdl, d_in, d_out, max(3, args.steps), ms), "fc_conv_profile")
+        one = C.c_float()
+        _lib.check(lib.fc_conv_time_device(hdl, d_in, d_out, 3, max(3, args.steps), C.byref(one)), "fc_conv_time_device")
+        nl = C.c_int()
+        lib.fc_conv_launches_per_forward(hdl, C.byref(nl))
+        launches_per_step += nl.value
+        t, tp, icp = wino_geometry(n, c, k, h)
+        bytes_wino = 4.0 * (n * c * h * h + 64 * c * k + n * k * h * h)
+        wino_flops = 2.0 * 64 * t * c * k
+        per_layer.append({
+            "layer": f"{c}->{k}@{h}", "ms": round(one.value, 5),
+            "gflops_direct_equiv": round(layer_flops(n, c, k, h) / one.value / 1e6, 1),
+            "stage_ms": [round(float(v), 5) for v in ms],
+            "hbm_roofline_ms": round(bytes_wino / hbm_peak / 1e6, 5),
+            "frac_of_hbm_roofline": round(bytes_wino / hbm_peak / 1e6 / one.value, 4),
+        })
+        for i in range(5):
+            stage_tot[i] += ms[i]
+        gemm_bytes += 4.0 * (64 * k * icp + 64 * tp * icp + 64 * k * tp)
+        gemm_ms += ms[2]
+        gemm_flops += wino_flops
+
+    nl = len(layers)
+    achieved_gbs = gemm_bytes / (gemm_ms / 1e3) / 1e9
+    roofline = {
+        "kernel": "TensorGEMM (64 batched U*V products, one launch per layer)",
+        "bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
+        "frac": round(achieved_gbs / hbm_peak, 4), "peak_source": f"of {peak_kind}",
+        "traffic": None,
+        "algorithmic_bytes_per_launch": gemm_bytes / nl, "avg_launch_ms": gemm_ms / nl,
+        "winograd_domain_tflops": round(gemm_flops / (gemm_ms / 1e3) / 1e12, 2),
+        "share_of_step": {"InputTran": round(stage_tot[0] / stage_tot[4], 3), "TensorGEMM": round(stage_tot[2] / stage_tot[4], 3),
+                          "OutputTran": round(stage_tot[3] / stage_tot[4], 3)},
+    }
+
+    line = None
+    if rank == 0:
+        value = world * flops / (ms_step / 1e3) / 1e9
+        e2e_value = world * flops / (e2e_ms / 1e3) / 1e9
+        line = {
+            "metric": "conv GFLOP/s (direct-equiv), VGG-16 conv stack", "value": round(value, 1), "unit": "GFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32"}[args.mode], "data": "synthetic",
+            "config": {"workload": f"VGG-16 13 conv layers, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
+                       "algorithm": "winograd F(6x6,3x3)", "math_mode": args.mode,
+                       "parallelism": f"images sharded over {world} GPU(s), no collective",
+                       "l2": f"inputs larger than L2: the stack touches {footprint / 1e6:.0f} MB per step"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e_ms, 4)},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "roofline": roofline,
+            "layers": per_layer,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            sec, err = reference_cpu_pass(layers, n, threads)
+            if sec is not None:
+                line["cpu_baseline"] = {"value": round(flops / sec / 1e9, 2), "unit": "GFLOP/s", "cores": threads,
+                                        "kind": "reference",
+                                        "sample": "one pass over all 13 layers with the reference's winoF63_v1_multi "
+                                                  "(NEON emulated via a vector-type stand-in header), all host threads"}
+            else:
+                line["cpu_baseline"] = {"value": None, "unit": "GFLOP/s", "cores": threads, "kind": "reference",
+                                        "sample": err}
+    for hdl, _, _, _ in convs:
+        lib.fc_conv_destroy(hdl)
+    ctx.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

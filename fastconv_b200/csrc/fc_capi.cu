@@ -1,0 +1,641 @@
+// C ABI of libfastconv_b200: context + device arena, stage-level entry points, planned layers.
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "fc_internal.h"
+
+namespace fc {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+static int check_desc(const fc_conv_desc *d) {
+    FC_REQUIRE(d != nullptr, FC_ERR_INVALID_ARG, "descriptor is NULL");
+    FC_REQUIRE(d->batch > 0 && d->ic > 0 && d->oc > 0 && d->ih > 0 && d->iw > 0 && d->kh > 0 && d->kw > 0,
+               FC_ERR_INVALID_ARG, "descriptor has a non-positive extent");
+    FC_REQUIRE(d->sh > 0 && d->sw > 0, FC_ERR_INVALID_ARG, "stride must be positive (conv_layer.h:62-63)");
+    FC_REQUIRE(d->pad_left >= 0 && d->pad_right >= 0 && d->pad_top >= 0 && d->pad_bottom >= 0, FC_ERR_INVALID_ARG,
+               "negative padding");
+    FC_REQUIRE(d->group == 1, FC_ERR_UNSUPPORTED, "group=%d: only group 1 is computed (as in the reference)",
+               d->group);
+    FC_REQUIRE(d->iw + d->pad_left + d->pad_right >= d->kw && d->ih + d->pad_top + d->pad_bottom >= d->kh,
+               FC_ERR_INVALID_ARG, "kernel larger than the padded input");
+    return FC_OK;
+}
+
+int wino_geom(const fc_conv_desc *d, WinoGeom *g) {
+    FC_PROPAGATE(check_desc(d));
+    // The reference driver ignores kh/kw/stride and assumes 3x3 s1 with one symmetric pad
+    // (winoF63ZC/winoF63ZC.cpp:334-338); anything else is refused here instead of computed wrongly.
+    FC_REQUIRE(d->kh == 3 && d->kw == 3, FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) needs a 3x3 kernel, got %dx%d",
+               d->kh, d->kw);
+    FC_REQUIRE(d->sh == 1 && d->sw == 1, FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) needs stride 1, got %dx%d", d->sh,
+               d->sw);
+    FC_REQUIRE(d->pad_left == d->pad_right && d->pad_left == d->pad_top && d->pad_left == d->pad_bottom,
+               FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) needs one symmetric padding value");
+    g->n = d->batch; g->ic = d->ic; g->oc = d->oc; g->ih = d->ih; g->iw = d->iw; g->pad = d->pad_left;
+    g->oh = d->ih + 2 * g->pad - 2;
+    g->ow = d->iw + 2 * g->pad - 2;
+    FC_REQUIRE(g->oh >= 1 && g->ow >= 1, FC_ERR_INVALID_ARG, "empty output");
+    g->th = (g->oh + 5) / 6;
+    g->tw = (g->ow + 5) / 6;
+    const long long tiles = (long long)g->n * g->th * g->tw;
+    FC_REQUIRE(tiles < (1ll << 30), FC_ERR_UNSUPPORTED, "too many tiles (%lld)", tiles);
+    g->tiles = (int)tiles;
+    g->icp = round_up(g->ic, 8);
+    g->tp = round_up(g->tiles, 8);
+    return FC_OK;
+}
+
+}  // namespace fc
+
+using namespace fc;
+
+struct fc_conv {
+    fc_context *ctx;
+    fc_conv_desc desc;
+    int algo, mode;
+    int oh, ow;
+    WinoGeom geom;
+    float *d_kernel;  // raw [oc][ic*kh*kw]
+    float *d_U, *d_V, *d_M;
+    float *d_in, *d_out;  // staging for forward_host
+    float kernel_tran_ms;
+    float stage_ms[5];
+};
+
+extern "C" {
+
+int fc_abi_version(void) { return FC_ABI_VERSION; }
+
+const char *fc_status_string(int s) {
+    switch (s) {
+        case FC_OK: return "ok";
+        case FC_ERR_INVALID_ARG: return "invalid argument";
+        case FC_ERR_UNSUPPORTED: return "unsupported shape or mode";
+        case FC_ERR_OUT_OF_MEMORY: return "out of device memory";
+        case FC_ERR_CUDA: return "CUDA error";
+        case FC_ERR_NO_DEVICE: return "no usable CUDA device";
+        case FC_ERR_TIMEOUT: return "device-side wait timed out";
+        case FC_ERR_COMM: return "multi-GPU communication error";
+        default: return "unknown status";
+    }
+}
+
+const char *fc_last_error(void) { return fc::g_err; }
+
+int fc_device_count(int *count) {
+    FC_REQUIRE(count != nullptr, FC_ERR_INVALID_ARG, "count is NULL");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    *count = n;
+    return FC_OK;
+}
+
+// ---- context + arena -----------------------------------------------------------------------
+
+int fc_context_create(int device, size_t arena_bytes, fc_context **out) {
+    FC_REQUIRE(out != nullptr, FC_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device is visible; this library has no CPU path");
+        return FC_ERR_NO_DEVICE;
+    }
+    FC_REQUIRE(device >= 0 && device < n, FC_ERR_INVALID_ARG, "device %d out of range (0..%d)", device, n - 1);
+    cudaDeviceProp prop;
+    FC_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
+    FC_REQUIRE(prop.major == 10, FC_ERR_NO_DEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only",
+               device, prop.major, prop.minor);
+    FC_CHECK_CUDA(cudaSetDevice(device));
+    fc_context *ctx = new (std::nothrow) fc_context();
+    FC_REQUIRE(ctx != nullptr, FC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->slab = nullptr;
+    ctx->stream = nullptr;
+    ctx->d_status = nullptr;
+    for (auto &e : ctx->ev) e = nullptr;
+    for (auto &e : ctx->user_ev) e = nullptr;
+    if (arena_bytes < (1u << 20)) arena_bytes = 1u << 20;
+    cudaError_t e = cudaMalloc(&ctx->slab, arena_bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error("cudaMalloc of the %zu-byte arena failed: %s", arena_bytes, cudaGetErrorString(e));
+        delete ctx;
+        return FC_ERR_OUT_OF_MEMORY;
+    }
+    ctx->arena.reset((uintptr_t)ctx->slab, arena_bytes);
+    FC_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+    for (auto &ev : ctx->ev) FC_CHECK_CUDA(cudaEventCreate(&ev));
+    for (auto &ev : ctx->user_ev) FC_CHECK_CUDA(cudaEventCreate(&ev));
+    ctx->d_status = (int *)ctx->arena.alloc(256);
+    FC_CHECK_CUDA(cudaMemsetAsync(ctx->d_status, 0, 256, ctx->stream));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    *out = ctx;
+    return FC_OK;
+}
+
+int fc_context_destroy(fc_context *ctx) {
+    if (!ctx) return FC_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    for (auto &ev : ctx->ev)
+        if (ev) cudaEventDestroy(ev);
+    for (auto &ev : ctx->user_ev)
+        if (ev) cudaEventDestroy(ev);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->slab) cudaFree(ctx->slab);
+    delete ctx;
+    return FC_OK;
+}
+
+int fc_context_synchronize(fc_context *ctx) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return FC_OK;
+}
+
+int fc_context_device(const fc_context *ctx, int *device) {
+    FC_REQUIRE(ctx != nullptr && device != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    *device = ctx->device;
+    return FC_OK;
+}
+
+int fc_arena_alloc(fc_context *ctx, size_t bytes, void **dptr) {
+    FC_REQUIRE(ctx != nullptr && dptr != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    const uintptr_t p = ctx->arena.alloc(bytes);
+    *dptr = (void *)p;
+    FC_REQUIRE(p != 0, FC_ERR_OUT_OF_MEMORY,
+               "arena exhausted: %zu bytes requested, %zu in use of %zu, largest free block %zu", bytes,
+               ctx->arena.in_use(), ctx->arena.capacity(), ctx->arena.largest_free());
+    return FC_OK;
+}
+
+int fc_arena_size_of(fc_context *ctx, const void *dptr, size_t *bytes) {
+    FC_REQUIRE(ctx != nullptr && bytes != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    *bytes = ctx->arena.size_of((uintptr_t)dptr);
+    FC_REQUIRE(*bytes != 0, FC_ERR_INVALID_ARG, "pointer %p was not allocated from this arena", dptr);
+    return FC_OK;
+}
+
+int fc_arena_free(fc_context *ctx, void *dptr) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    if (dptr == nullptr) return FC_OK;
+    FC_REQUIRE(ctx->arena.release((uintptr_t)dptr), FC_ERR_INVALID_ARG,
+               "pointer %p was not allocated from this arena (or was freed twice)", dptr);
+    return FC_OK;
+}
+
+int fc_arena_free_all(fc_context *ctx) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    ctx->arena.release_all();
+    ctx->common.clear();
+    ctx->d_status = (int *)ctx->arena.alloc(256);
+    return FC_OK;
+}
+
+int fc_arena_stats(fc_context *ctx, size_t *capacity, size_t *in_use, size_t *peak, size_t *blocks) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    if (capacity) *capacity = ctx->arena.capacity();
+    if (in_use) *in_use = ctx->arena.in_use();
+    if (peak) *peak = ctx->arena.peak();
+    if (blocks) *blocks = ctx->arena.blocks();
+    return FC_OK;
+}
+
+int fc_arena_common_request(fc_context *ctx, size_t bytes, size_t id) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    CommonSlot &s = ctx->common[id];  // value-initialised on first use
+    FC_REQUIRE(s.ptr == nullptr || bytes <= s.bytes, FC_ERR_INVALID_ARG,
+               "common pool %zu is already committed with %zu bytes; free it before requesting %zu", id, s.bytes,
+               bytes);
+    if (bytes > s.bytes) s.bytes = bytes;
+    return FC_OK;
+}
+
+int fc_arena_common_commit(fc_context *ctx) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    for (auto &kv : ctx->common) {
+        if (kv.second.ptr != nullptr || kv.second.bytes == 0) continue;
+        void *p = nullptr;
+        FC_PROPAGATE(fc_arena_alloc(ctx, kv.second.bytes, &p));
+        kv.second.ptr = p;
+    }
+    return FC_OK;
+}
+
+int fc_arena_common_ptr(fc_context *ctx, size_t id, void **dptr) {
+    FC_REQUIRE(ctx != nullptr && dptr != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    auto it = ctx->common.find(id);
+    FC_REQUIRE(it != ctx->common.end() && it->second.ptr != nullptr, FC_ERR_INVALID_ARG,
+               "common pool %zu has not been requested and committed", id);
+    *dptr = it->second.ptr;
+    return FC_OK;
+}
+
+int fc_arena_common_free(fc_context *ctx, size_t id) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    auto it = ctx->common.find(id);
+    FC_REQUIRE(it != ctx->common.end(), FC_ERR_INVALID_ARG, "common pool %zu does not exist", id);
+    if (it->second.ptr) ctx->arena.release((uintptr_t)it->second.ptr);
+    ctx->common.erase(it);
+    return FC_OK;
+}
+
+int fc_memcpy_h2d(fc_context *ctx, void *dst, const void *src, size_t bytes) {
+    FC_REQUIRE(ctx != nullptr && dst != nullptr && src != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return FC_OK;
+}
+
+int fc_memcpy_d2h(fc_context *ctx, void *dst, const void *src, size_t bytes) {
+    FC_REQUIRE(ctx != nullptr && dst != nullptr && src != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return FC_OK;
+}
+
+int fc_memset_device(fc_context *ctx, void *dst, int value, size_t bytes) {
+    FC_REQUIRE(ctx != nullptr && dst != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_CHECK_CUDA(cudaMemsetAsync(dst, value, bytes, ctx->stream));
+    return FC_OK;
+}
+
+int fc_host_alloc_pinned(size_t bytes, void **hptr) {
+    FC_REQUIRE(hptr != nullptr, FC_ERR_INVALID_ARG, "hptr is NULL");
+    FC_CHECK_CUDA(cudaMallocHost(hptr, bytes));
+    return FC_OK;
+}
+
+int fc_host_free_pinned(void *hptr) {
+    if (hptr) FC_CHECK_CUDA(cudaFreeHost(hptr));
+    return FC_OK;
+}
+
+int fc_timer_record(fc_context *ctx, int slot) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    FC_REQUIRE(slot >= 0 && slot < FC_TIMER_SLOTS, FC_ERR_INVALID_ARG, "timer slot %d out of range", slot);
+    FC_CHECK_CUDA(cudaEventRecord(ctx->user_ev[slot], ctx->stream));
+    return FC_OK;
+}
+
+int fc_timer_elapsed_ms(fc_context *ctx, int a, int b, float *ms) {
+    FC_REQUIRE(ctx != nullptr && ms != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(a >= 0 && a < FC_TIMER_SLOTS && b >= 0 && b < FC_TIMER_SLOTS, FC_ERR_INVALID_ARG,
+               "timer slot out of range");
+    FC_CHECK_CUDA(cudaEventSynchronize(ctx->user_ev[b]));
+    FC_CHECK_CUDA(cudaEventElapsedTime(ms, ctx->user_ev[a], ctx->user_ev[b]));
+    return FC_OK;
+}
+
+// ---- shape helpers -------------------------------------------------------------------------
+
+int fc_conv_output_size(const fc_conv_desc *d, int *oh, int *ow) {
+    FC_PROPAGATE(check_desc(d));
+    FC_REQUIRE(oh != nullptr && ow != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    *ow = (d->iw + d->pad_left + d->pad_right - d->kw) / d->sw + 1;
+    *oh = (d->ih + d->pad_top + d->pad_bottom - d->kh) / d->sh + 1;
+    return FC_OK;
+}
+
+int fc_select_algorithm(const fc_conv_desc *d, int *algo) {
+    FC_PROPAGATE(check_desc(d));
+    FC_REQUIRE(algo != nullptr, FC_ERR_INVALID_ARG, "algo is NULL");
+    int a = FC_ALGO_IM2COL;  // fall-back, ConvTest.cpp:329-330
+    if ((d->sh > d->sw ? d->sh : d->sw) == 1) {
+        if ((d->kh > d->kw ? d->kh : d->kw) == 1) {
+            a = FC_ALGO_IM2COL;  // "direct" in the reference, whose case body is empty
+        } else if (d->kh == 3 && d->kw == 3 && d->pad_left == d->pad_right && d->pad_left == d->pad_top &&
+                   d->pad_left == d->pad_bottom) {
+            a = FC_ALGO_WINOGRAD;
+        }
+    }
+    *algo = a;
+    return FC_OK;
+}
+
+int fc_wino_buffer_elems(const fc_conv_desc *d, int mode, size_t *u, size_t *v, size_t *m) {
+    (void)mode;
+    WinoGeom g;
+    FC_PROPAGATE(wino_geom(d, &g));
+    if (u) *u = (size_t)64 * g.oc * g.icp;
+    if (v) *v = (size_t)64 * g.tp * g.icp;
+    if (m) *m = (size_t)64 * g.oc * g.tp;
+    return FC_OK;
+}
+
+// ---- Winograd stages -----------------------------------------------------------------------
+
+int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic) {
+    FC_REQUIRE(ctx && d_kernel && d_U, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(oc > 0 && ic > 0, FC_ERR_INVALID_ARG, "non-positive channel count");
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return launch_filter_transform(ctx, d_kernel, d_U, oc, ic, round_up(ic, 8));
+}
+
+int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc) {
+    FC_REQUIRE(ctx && d_in && d_V, FC_ERR_INVALID_ARG, "NULL argument");
+    WinoGeom g;
+    FC_PROPAGATE(wino_geom(desc, &g));
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return launch_input_transform(ctx, d_in, d_V, g);
+}
+
+static int wino_gemm_dispatch(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
+                              int mode) {
+    switch (mode) {
+        case FC_MATH_FP32_MIRRORED: return launch_wino_gemm_ffma(ctx, d_U, d_V, d_M, g);
+        case FC_MATH_3XTF32:
+        case FC_MATH_TF32: return launch_wino_gemm_tc(ctx, d_U, d_V, d_M, g, mode);
+        default: set_error("unknown math mode %d", mode); return FC_ERR_INVALID_ARG;
+    }
+}
+
+int fc_wino_tensor_gemm(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const fc_conv_desc *desc,
+                        int mode) {
+    FC_REQUIRE(ctx && d_U && d_V && d_M, FC_ERR_INVALID_ARG, "NULL argument");
+    WinoGeom g;
+    FC_PROPAGATE(wino_geom(desc, &g));
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return wino_gemm_dispatch(ctx, d_U, d_V, d_M, g, mode);
+}
+
+int fc_wino_output_transform(fc_context *ctx, const float *d_M, float *d_out, const fc_conv_desc *desc) {
+    FC_REQUIRE(ctx && d_M && d_out, FC_ERR_INVALID_ARG, "NULL argument");
+    WinoGeom g;
+    FC_PROPAGATE(wino_geom(desc, &g));
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return launch_output_transform(ctx, d_M, d_out, g);
+}
+
+int fc_wino_forward(fc_context *ctx, const float *d_in, const float *d_U, float *d_V, float *d_M, float *d_out,
+                    const fc_conv_desc *desc, int mode, float *stage_ms) {
+    FC_REQUIRE(ctx && d_in && d_U && d_V && d_M && d_out, FC_ERR_INVALID_ARG, "NULL argument");
+    WinoGeom g;
+    FC_PROPAGATE(wino_geom(desc, &g));
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
+    FC_PROPAGATE(launch_input_transform(ctx, d_in, d_V, g));
+    if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
+    FC_PROPAGATE(wino_gemm_dispatch(ctx, d_U, d_V, d_M, g, mode));
+    if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+    FC_PROPAGATE(launch_output_transform(ctx, d_M, d_out, g));
+    if (stage_ms) {
+        FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+        FC_CHECK_CUDA(cudaEventSynchronize(ctx->ev[3]));
+        FC_CHECK_CUDA(cudaEventElapsedTime(&stage_ms[0], ctx->ev[0], ctx->ev[1]));
+        stage_ms[1] = 0.0f;
+        FC_CHECK_CUDA(cudaEventElapsedTime(&stage_ms[2], ctx->ev[1], ctx->ev[2]));
+        FC_CHECK_CUDA(cudaEventElapsedTime(&stage_ms[3], ctx->ev[2], ctx->ev[3]));
+    }
+    return FC_OK;
+}
+
+// ---- im2col / implicit GEMM ----------------------------------------------------------------
+
+int fc_im2col_gather(fc_context *ctx, const float *d_in, float *d_gathered, const fc_conv_desc *desc, int image) {
+    FC_REQUIRE(ctx && d_in && d_gathered, FC_ERR_INVALID_ARG, "NULL argument");
+    int oh, ow;
+    FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
+    FC_REQUIRE(image >= 0 && image < desc->batch, FC_ERR_INVALID_ARG, "image %d outside the batch of %d", image,
+               desc->batch);
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return launch_im2col_gather(ctx, d_in, d_gathered, *desc, oh, ow, image);
+}
+
+int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out,
+                     const fc_conv_desc *desc, int mode) {
+    FC_REQUIRE(ctx && d_in && d_kernel && d_out, FC_ERR_INVALID_ARG, "NULL argument");
+    int oh, ow;
+    FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
+    FC_REQUIRE((long long)desc->batch * oh * ow < (1ll << 31) && (long long)desc->ic * desc->kh * desc->kw < (1ll << 31),
+               FC_ERR_UNSUPPORTED, "GEMM extent exceeds 32-bit indexing");
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    switch (mode) {
+        case FC_MATH_FP32_MIRRORED: return launch_igemm_ffma(ctx, d_in, d_kernel, d_out, *desc, oh, ow);
+        case FC_MATH_3XTF32:
+        case FC_MATH_TF32: return launch_igemm_tc(ctx, d_in, d_kernel, d_out, *desc, oh, ow, mode);
+        default: set_error("unknown math mode %d", mode); return FC_ERR_INVALID_ARG;
+    }
+}
+
+// ---- planned layer --------------------------------------------------------------------------
+
+static void conv_release(fc_conv *c) {
+    fc_context *ctx = c->ctx;
+    float *bufs[] = {c->d_kernel, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    for (float *b : bufs)
+        if (b) ctx->arena.release((uintptr_t)b);
+    delete c;
+}
+
+int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode, const float *h_kernel,
+                   fc_conv **out) {
+    FC_REQUIRE(ctx && desc && h_kernel && out, FC_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32, FC_ERR_INVALID_ARG, "unknown math mode %d",
+               mode);
+    FC_REQUIRE(algo >= FC_ALGO_AUTO && algo <= FC_ALGO_WINOGRAD, FC_ERR_INVALID_ARG, "unknown algorithm %d", algo);
+    int oh, ow;
+    FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
+    if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
+    if (algo == FC_ALGO_DIRECT) algo = FC_ALGO_IM2COL;
+    WinoGeom g;
+    memset(&g, 0, sizeof g);
+    if (algo == FC_ALGO_WINOGRAD) FC_PROPAGATE(wino_geom(desc, &g));
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+
+    fc_conv *c = new (std::nothrow) fc_conv();
+    FC_REQUIRE(c != nullptr, FC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    memset(c, 0, sizeof *c);
+    c->ctx = ctx; c->desc = *desc; c->algo = algo; c->mode = mode; c->oh = oh; c->ow = ow; c->geom = g;
+
+    const size_t k_elems = (size_t)desc->oc * desc->ic * desc->kh * desc->kw;
+    const size_t in_elems = (size_t)desc->batch * desc->ic * desc->ih * desc->iw;
+    const size_t out_elems = (size_t)desc->batch * desc->oc * oh * ow;
+    auto grab = [&](float **p, size_t elems) -> int {
+        void *q = nullptr;
+        int st = fc_arena_alloc(ctx, elems * sizeof(float), &q);
+        *p = (float *)q;
+        return st;
+    };
+    int st = grab(&c->d_kernel, k_elems);
+    if (st == FC_OK) st = grab(&c->d_in, in_elems);
+    if (st == FC_OK) st = grab(&c->d_out, out_elems);
+    if (st == FC_OK && algo == FC_ALGO_WINOGRAD) {
+        st = grab(&c->d_U, (size_t)64 * g.oc * g.icp);
+        if (st == FC_OK) st = grab(&c->d_V, (size_t)64 * g.tp * g.icp);
+        if (st == FC_OK) st = grab(&c->d_M, (size_t)64 * g.oc * g.tp);
+    }
+    if (st != FC_OK) {
+        conv_release(c);
+        return st;
+    }
+    cudaError_t e = cudaMemcpyAsync(c->d_kernel, h_kernel, k_elems * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess && algo == FC_ALGO_WINOGRAD) {
+        cudaEventRecord(ctx->ev[0], ctx->stream);
+        st = launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic, g.icp);
+        cudaEventRecord(ctx->ev[1], ctx->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess || st != FC_OK) {
+        if (e != cudaSuccess) set_error("kernel upload / filter transform failed: %s", cudaGetErrorString(e));
+        conv_release(c);
+        return e != cudaSuccess ? FC_ERR_CUDA : st;
+    }
+    if (algo == FC_ALGO_WINOGRAD) cudaEventElapsedTime(&c->kernel_tran_ms, ctx->ev[0], ctx->ev[1]);
+    *out = c;
+    return FC_OK;
+}
+
+int fc_conv_destroy(fc_conv *c) {
+    if (!c) return FC_OK;
+    cudaSetDevice(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);
+    conv_release(c);
+    return FC_OK;
+}
+
+int fc_conv_algorithm(const fc_conv *c, int *algo) {
+    FC_REQUIRE(c && algo, FC_ERR_INVALID_ARG, "NULL argument");
+    *algo = c->algo;
+    return FC_OK;
+}
+
+static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed) {
+    fc_context *ctx = c->ctx;
+    if (c->algo == FC_ALGO_WINOGRAD) {
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
+        FC_PROPAGATE(launch_input_transform(ctx, d_in, c->d_V, c->geom));
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
+        FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, c->geom, c->mode));
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+        FC_PROPAGATE(launch_output_transform(ctx, c->d_M, d_out, c->geom));
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+        return FC_OK;
+    }
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
+    int st;
+    if (c->mode == FC_MATH_FP32_MIRRORED)
+        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow);
+    else
+        st = launch_igemm_tc(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, c->mode);
+    FC_PROPAGATE(st);
+    if (timed) {
+        FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+        FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+    }
+    return FC_OK;
+}
+
+int fc_conv_forward_device(fc_conv *c, const float *d_in, float *d_out) {
+    FC_REQUIRE(c && d_in && d_out, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_CHECK_CUDA(cudaSetDevice(c->ctx->device));
+    return conv_enqueue(c, d_in, d_out, false);
+}
+
+int fc_conv_forward_host(fc_conv *c, const float *h_in, float *h_out) {
+    FC_REQUIRE(c && h_in && h_out, FC_ERR_INVALID_ARG, "NULL argument");
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    const size_t in_bytes = (size_t)c->desc.batch * c->desc.ic * c->desc.ih * c->desc.iw * sizeof(float);
+    const size_t out_bytes = (size_t)c->desc.batch * c->desc.oc * c->oh * c->ow * sizeof(float);
+    FC_CHECK_CUDA(cudaMemcpyAsync(c->d_in, h_in, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
+    FC_CHECK_CUDA(cudaMemcpyAsync(h_out, c->d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return FC_OK;
+}
+
+int fc_conv_device_buffers(fc_conv *c, float **d_in, float **d_out) {
+    FC_REQUIRE(c != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    if (d_in) *d_in = c->d_in;
+    if (d_out) *d_out = c->d_out;
+    return FC_OK;
+}
+
+int fc_conv_time_device(fc_conv *c, const float *d_in, float *d_out, int warmup, int iters, float *ms_per_iter) {
+    FC_REQUIRE(c && d_in && d_out && ms_per_iter, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(iters > 0 && warmup >= 0, FC_ERR_INVALID_ARG, "iters must be positive");
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    for (int i = 0; i < warmup; ++i) FC_PROPAGATE(conv_enqueue(c, d_in, d_out, false));
+    FC_CHECK_CUDA(cudaEventRecord(ctx->ev[4], ctx->stream));
+    for (int i = 0; i < iters; ++i) FC_PROPAGATE(conv_enqueue(c, d_in, d_out, false));
+    FC_CHECK_CUDA(cudaEventRecord(ctx->ev[5], ctx->stream));
+    FC_CHECK_CUDA(cudaEventSynchronize(ctx->ev[5]));
+    float ms = 0.f;
+    FC_CHECK_CUDA(cudaEventElapsedTime(&ms, ctx->ev[4], ctx->ev[5]));
+    *ms_per_iter = ms / iters;
+    return FC_OK;
+}
+
+int fc_conv_profile(fc_conv *c, const float *d_in, float *d_out, int iters, float stage_ms[5]) {
+    FC_REQUIRE(c && d_in && d_out && stage_ms, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(iters > 0, FC_ERR_INVALID_ARG, "iters must be positive");
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    double acc[5] = {0, 0, 0, 0, 0};
+    for (int i = 0; i < iters; ++i) {
+        FC_PROPAGATE(conv_enqueue(c, d_in, d_out, true));
+        FC_CHECK_CUDA(cudaEventSynchronize(ctx->ev[3]));
+        float a = 0, b = 0, d = 0, t = 0;
+        FC_CHECK_CUDA(cudaEventElapsedTime(&a, ctx->ev[0], ctx->ev[1]));
+        FC_CHECK_CUDA(cudaEventElapsedTime(&b, ctx->ev[1], ctx->ev[2]));
+        FC_CHECK_CUDA(cudaEventElapsedTime(&d, ctx->ev[2], ctx->ev[3]));
+        FC_CHECK_CUDA(cudaEventElapsedTime(&t, ctx->ev[0], ctx->ev[3]));
+        acc[0] += a; acc[2] += b; acc[3] += d; acc[4] += t;
+    }
+    stage_ms[0] = (float)(acc[0] / iters);
+    stage_ms[1] = c->kernel_tran_ms;
+    stage_ms[2] = (float)(acc[2] / iters);
+    stage_ms[3] = (float)(acc[3] / iters);
+    stage_ms[4] = (float)(acc[4] / iters);
+    memcpy(c->stage_ms, stage_ms, sizeof c->stage_ms);
+    return FC_OK;
+}
+
+int fc_conv_tune(fc_conv *c, int iters, int verbose) {
+    FC_REQUIRE(c != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    (void)iters;
+    (void)verbose;
+    return FC_OK;
+}
+
+int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
+    FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 : 1;
+    return FC_OK;
+}
+
+float fc_diff(const float *a, const float *b, int len) {
+    int num = 0;
+    double dif = 0.0;
+    for (int i = 0; i < len; ++i) {
+        const float err = fabsf(a[i] - b[i]);
+        if (err > 1e-5f) {
+            dif += err;
+            ++num;
+        }
+    }
+    return num == 0 ? 0.0f : (float)(dif / num);
+}
+
+}  // extern "C"

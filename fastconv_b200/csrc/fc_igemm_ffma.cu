@@ -1,0 +1,198 @@
+// im2col path: gather dump + implicit-GEMM convolution on the FP32 pipes ("mirrored" mode).
+//
+// The reference materialises B[(ic*kh+u)*kw+v][i*ow+j] (ConvIm2colLayer::im2col,
+// convLayer/im2colConv.cpp:285-309) and multiplies A[oc][K] * B with packed register kernels whose
+// accumulation per output element is one fused multiply-add per k, k ascending
+// (im2col/gemm_kernel.cpp:350-420; kc blocks continue through C, convLayer/im2colConv.cpp:465-557).
+// Here the matrix is never built: the CTA's operand loader computes the same index map on the fly
+// and zero-fills the padding, and each output element keeps one accumulator fed in ascending k.
+#include "fc_internal.h"
+
+namespace fc {
+
+namespace {
+
+// ---- gather dump (debug / parity): exactly the reference's index map ---------------------------
+__global__ void im2col_gather_kernel(const float *__restrict__ in, float *__restrict__ B, int ic, int ih, int iw,
+                                     int kh, int kw, int sh, int sw, int pad_l, int pad_t, int oh, int ow) {
+    const size_t total = (size_t)ic * kh * kw * oh * ow;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(idx % ow);
+        size_t r = idx / ow;
+        const int i = (int)(r % oh);
+        r /= oh;
+        const int v = (int)(r % kw);
+        r /= kw;
+        const int u = (int)(r % kh);
+        const int c = (int)(r / kh);
+        const int row = u - pad_t + i * sh, col = v - pad_l + j * sw;
+        B[idx] = (row < 0 || row >= ih || col < 0 || col >= iw) ? 0.0f : in[((size_t)c * ih + row) * iw + col];
+    }
+}
+
+constexpr int BK = 16;
+constexpr int THREADS = 256;
+
+struct IgemmParams {
+    int n, ic, ih, iw, oc, kh, kw, sh, sw, pad_l, pad_t, oh, ow;
+    int K;        // ic*kh*kw
+    int npix;     // n*oh*ow
+};
+
+template <int BM, int BN>
+__global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__restrict__ in,
+                                                             const float *__restrict__ A, float *__restrict__ out,
+                                                             IgemmParams P) {
+    constexpr int TM = BM / 16, TN = BN / 16;
+    constexpr int LDA = BM + 4, LDB = BN + 4;
+    constexpr int A_PER = BM * BK / THREADS;  // scalar A loads per thread per slab
+    constexpr int B_PER = BN * BK / THREADS;  // gathered B loads per thread per slab
+    constexpr int B_KSTEP = THREADS / BN;     // k rows covered per pass of the loader
+    __shared__ __align__(16) float As[2][BK][LDA];
+    __shared__ __align__(16) float Bs[2][BK][LDB];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const int oc0 = blockIdx.y * BM;
+    const int pix0 = blockIdx.x * BN;
+
+    // the pixel this thread gathers for is fixed for the whole K loop
+    const int bn = tid % BN, bk0 = tid / BN;
+    const int pix = pix0 + bn;
+    const bool pix_ok = pix < P.npix;
+    int img = 0, oi = 0, oj = 0;
+    if (pix_ok) {
+        img = pix / (P.oh * P.ow);
+        const int rem = pix - img * P.oh * P.ow;
+        oi = rem / P.ow;
+        oj = rem - oi * P.ow;
+    }
+    const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
+    const float *img_ptr = in + (size_t)img * P.ic * P.ih * P.iw;
+    const int khw = P.kh * P.kw;
+
+    float a_stage[A_PER], b_stage[B_PER];
+
+    auto load_slab = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < A_PER; ++i) {
+            const int idx = tid + i * THREADS;
+            const int row = idx / BK, kk = idx % BK;
+            const int r = oc0 + row, k = k0 + kk;
+            a_stage[i] = (r < P.oc && k < P.K) ? __ldg(A + (size_t)r * P.K + k) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; ++i) {
+            const int k = k0 + bk0 + i * B_KSTEP;
+            float val = 0.0f;
+            if (pix_ok && k < P.K) {
+                const int c = k / khw;
+                const int r2 = k - c * khw;
+                const int u = r2 / P.kw;
+                const int v = r2 - u * P.kw;
+                const int row = base_row + u, col = base_col + v;
+                if (row >= 0 && row < P.ih && col >= 0 && col < P.iw)
+                    val = __ldg(img_ptr + ((size_t)c * P.ih + row) * P.iw + col);
+            }
+            b_stage[i] = val;
+        }
+    };
+    auto store_slab = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_PER; ++i) {
+            const int idx = tid + i * THREADS;
+            As[buf][idx % BK][idx / BK] = a_stage[i];
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; ++i) Bs[buf][bk0 + i * B_KSTEP][bn] = b_stage[i];
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    load_slab(0);
+    store_slab(0);
+    __syncthreads();
+
+    const int n_slabs = (P.K + BK - 1) / BK;
+    for (int s = 0; s < n_slabs; ++s) {
+        const int buf = s & 1;
+        if (s + 1 < n_slabs) load_slab((s + 1) * BK);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int g = 0; g < TM / 4; ++g) {
+                const float4 v = *reinterpret_cast<const float4 *>(&As[buf][k][g * 64 + ty * 4]);
+                a[g * 4 + 0] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int g = 0; g < TN / 4; ++g) {
+                const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][k][g * 64 + tx * 4]);
+                b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+        }
+        if (s + 1 < n_slabs) {
+            store_slab(buf ^ 1);
+            __syncthreads();
+        }
+    }
+
+    const int ohw = P.oh * P.ow;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = oc0 + (i / 4) * 64 + ty * 4 + (i % 4);
+        if (r >= P.oc) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int px = pix0 + (j / 4) * 64 + tx * 4 + (j % 4);
+            if (px >= P.npix) continue;
+            const int im = px / ohw;
+            out[((size_t)im * P.oc + r) * ohw + (px - im * ohw)] = acc[i][j];
+        }
+    }
+}
+
+}  // namespace
+
+int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
+                         int image) {
+    const size_t total = (size_t)d.ic * d.kh * d.kw * oh * ow;
+    const unsigned blocks = (unsigned)(ceil_div(total, 256) > 148 * 32 ? 148 * 32 : ceil_div(total, 256));
+    const float *src = d_in + (size_t)image * d.ic * d.ih * d.iw;
+    im2col_gather_kernel<<<blocks, 256, 0, ctx->stream>>>(src, d_B, d.ic, d.ih, d.iw, d.kh, d.kw, d.sh, d.sw,
+                                                          d.pad_left, d.pad_top, oh, ow);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+                      int oh, int ow) {
+    IgemmParams P;
+    P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
+    P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
+    P.K = d.ic * d.kh * d.kw;
+    P.npix = d.batch * oh * ow;
+    const bool wide_m = d.oc > 64, wide_n = P.npix > 64;
+    dim3 grid((unsigned)ceil_div(P.npix, wide_n ? 128 : 64), (unsigned)ceil_div(d.oc, wide_m ? 128 : 64)), block(THREADS);
+    if (wide_m && wide_n)
+        igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+    else if (wide_m)
+        igemm_ffma_kernel<128, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+    else if (wide_n)
+        igemm_ffma_kernel<64, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+    else
+        igemm_ffma_kernel<64, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+}  // namespace fc

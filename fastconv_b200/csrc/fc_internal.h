@@ -1,0 +1,88 @@
+// Internal declarations shared by the translation units of libfastconv_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+
+#include "../../include/fastconv_b200.h"
+#include "fc_arena.h"
+
+namespace fc {
+
+void set_error(const char *fmt, ...);
+
+#define FC_CHECK_CUDA(call)                                                                             \
+    do {                                                                                                \
+        cudaError_t fc_err__ = (call);                                                                  \
+        if (fc_err__ != cudaSuccess) {                                                                  \
+            fc::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(fc_err__), __FILE__, __LINE__); \
+            return FC_ERR_CUDA;                                                                         \
+        }                                                                                               \
+    } while (0)
+
+#define FC_REQUIRE(cond, status, ...)     \
+    do {                                  \
+        if (!(cond)) {                    \
+            fc::set_error(__VA_ARGS__);   \
+            return (status);              \
+        }                                 \
+    } while (0)
+
+#define FC_PROPAGATE(call)               \
+    do {                                 \
+        int fc_st__ = (call);            \
+        if (fc_st__ != FC_OK) return fc_st__; \
+    } while (0)
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Geometry of one Winograd F(6x6,3x3) layer (3x3, stride 1, symmetric padding):
+// output size as the reference driver derives it (winoF63ZC/winoF63ZC.cpp:334-338).
+struct WinoGeom {
+    int n, ic, oc, ih, iw, pad, oh, ow, th, tw, tiles, icp, tp;
+};
+
+int wino_geom(const fc_conv_desc *d, WinoGeom *g);  // validates and fills
+
+struct CommonSlot {
+    size_t bytes;
+    void *ptr;
+};
+
+}  // namespace fc
+
+struct fc_context {
+    int device;
+    int sm_count;
+    cudaStream_t stream;
+    void *slab;
+    fc::Arena arena;
+    std::map<size_t, fc::CommonSlot> common;
+    cudaEvent_t ev[6];
+    cudaEvent_t user_ev[FC_TIMER_SLOTS];
+    int *d_status;  // device word kernels with bounded waits report into
+};
+
+// kernel launchers (device pointers, context stream) ------------------------------------------
+namespace fc {
+
+int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int icp);
+int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
+int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g);
+int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g);
+int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
+                        int mode);
+int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
+                         int image);
+int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+                      int oh, int ow);
+int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+                    int oh, int ow, int mode);
+
+}  // namespace fc

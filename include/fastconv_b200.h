@@ -1,0 +1,184 @@
+/*
+ * fastconv_b200 -- C ABI of the B200 (sm_100a) convolution-layer hot path.
+ *
+ * This is the drop-in boundary: everything FastConv's operator classes
+ * (ConvWinoF63ZCLayer, ConvIm2colLayer) call below their Init()/Forward()
+ * is replaced by the entry points declared here.  Plain C types only; device
+ * buffers are raw pointers obtained from the arena functions (or any CUDA
+ * allocation of the caller's).  Each declaration cites the reference
+ * interface it replaces as path:line inside the FastConv tree.
+ *
+ * Conventions
+ *   - every function returns FC_OK (0) or a negative fc_status; on failure
+ *     fc_last_error() holds a message for the calling thread.
+ *   - tensors are fp32 NCHW: input [n][ic][ih][iw], kernel [oc][ic][kh][kw],
+ *     output [n][oc][oh][ow]; oh/ow follow conv_layer.h:68-69.
+ *   - a context is bound to one GPU and one stream; it is not re-entrant
+ *     (the reference layers are not either: shared workspaces).
+ *   - there is no CPU fallback: without a usable GPU fc_context_create fails.
+ */
+#ifndef FASTCONV_B200_H_
+#define FASTCONV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FC_ABI_VERSION 1
+
+typedef enum fc_status {
+    FC_OK = 0,
+    FC_ERR_INVALID_ARG = -1,   /* NULL operand, non-positive size, bad enum            */
+    FC_ERR_UNSUPPORTED = -2,   /* shape the requested algorithm cannot compute          */
+    FC_ERR_OUT_OF_MEMORY = -3, /* arena exhausted or cudaMalloc failed                   */
+    FC_ERR_CUDA = -4,          /* a CUDA runtime / driver call failed                    */
+    FC_ERR_NO_DEVICE = -5,     /* no CUDA device, or not compute capability 10.x         */
+    FC_ERR_TIMEOUT = -6,       /* a bounded device-side wait gave up (kernel reported)   */
+    FC_ERR_COMM = -7           /* multi-GPU setup / exchange failed                      */
+} fc_status;
+
+/* Same numbering as nnp_convolution_algorithm, utility/helper.h:94-103. */
+typedef enum fc_algorithm {
+    FC_ALGO_AUTO = 0,
+    FC_ALGO_DIRECT = 1, /* routed to the implicit-GEMM kernel (the reference's case is empty, ConvTest.cpp:369-371) */
+    FC_ALGO_IM2COL = 2,
+    FC_ALGO_WINOGRAD = 3
+} fc_algorithm;
+
+/* Arithmetic of the multiply-accumulate stage. */
+typedef enum fc_math_mode {
+    FC_MATH_FP32_MIRRORED = 0, /* FFMA, one fused multiply-add per reduction step in ascending order:
+                                  bit-identical to the reference's accumulation chain            */
+    FC_MATH_3XTF32 = 1,        /* tcgen05 tensor cores, hi/lo TF32 split, fp32 accumulate         */
+    FC_MATH_TF32 = 2           /* tcgen05 tensor cores, single TF32 pass                          */
+} fc_math_mode;
+
+typedef struct fc_conv_desc {
+    int32_t batch; /* images; the reference is batch 1 (no N anywhere in conv_layer.h:121-148) */
+    int32_t ic, ih, iw;
+    int32_t oc, kh, kw;
+    int32_t sh, sw;
+    int32_t pad_left, pad_right, pad_top, pad_bottom;
+    int32_t group; /* must be 1: parsed but unused by every reference fast path */
+} fc_conv_desc;
+
+typedef struct fc_context fc_context; /* one GPU + stream + device arena */
+typedef struct fc_conv fc_conv;       /* one planned layer: weights, workspaces, kernels */
+
+/* ---- library ------------------------------------------------------------- */
+int fc_abi_version(void);
+const char *fc_status_string(int status);
+const char *fc_last_error(void);
+int fc_device_count(int *count);
+
+/* ---- context + device arena ----------------------------------------------
+ * Replaces the host allocators of utility/mempool.h:23-71 (CommonMemPool::
+ * Request/Alloc/GetPtr/Free, PrivateMemPool::Alloc/GetSize/Free/FreeAll/
+ * PrintStats) and _mm_malloc/_mm_free (utility/common.cpp:26-49): one
+ * cudaMalloc'd slab per context, sub-allocated with 256-byte alignment. */
+int fc_context_create(int device, size_t arena_bytes, fc_context **out);
+int fc_context_destroy(fc_context *ctx);
+int fc_context_synchronize(fc_context *ctx);
+int fc_context_device(const fc_context *ctx, int *device);
+/* PrivateMemPool::Alloc / GetSize / Free / FreeAll / PrintStats */
+int fc_arena_alloc(fc_context *ctx, size_t bytes, void **dptr);
+int fc_arena_size_of(fc_context *ctx, const void *dptr, size_t *bytes);
+int fc_arena_free(fc_context *ctx, void *dptr);
+int fc_arena_free_all(fc_context *ctx);
+int fc_arena_stats(fc_context *ctx, size_t *capacity, size_t *in_use, size_t *peak, size_t *blocks);
+/* CommonMemPool::Request(size,id) / Alloc() / GetPtr(ptr,id) / Free(id): shared scratch, the
+ * requests under one id are max-reduced and materialised by commit. */
+int fc_arena_common_request(fc_context *ctx, size_t bytes, size_t id);
+int fc_arena_common_commit(fc_context *ctx);
+int fc_arena_common_ptr(fc_context *ctx, size_t id, void **dptr);
+int fc_arena_common_free(fc_context *ctx, size_t id);
+/* host<->device copies on the context's stream (synchronous on return) and pinned host memory */
+int fc_memcpy_h2d(fc_context *ctx, void *dst_device, const void *src_host, size_t bytes);
+int fc_memcpy_d2h(fc_context *ctx, void *dst_host, const void *src_device, size_t bytes);
+int fc_memset_device(fc_context *ctx, void *dst_device, int value, size_t bytes);
+int fc_host_alloc_pinned(size_t bytes, void **hptr);
+int fc_host_free_pinned(void *hptr);
+
+/* device-time stopwatch on the context stream: what the reference's Timer (utility/helper.h:66-80,
+ * CLOCK_MONOTONIC around each stage) becomes on a GPU.  `slot` is 0..FC_TIMER_SLOTS-1. */
+#define FC_TIMER_SLOTS 16
+int fc_timer_record(fc_context *ctx, int slot);
+int fc_timer_elapsed_ms(fc_context *ctx, int start_slot, int stop_slot, float *ms);
+
+/* ---- shape helpers -------------------------------------------------------- */
+/* oh/ow as conv_layer.h:68-69 / ConvTest.cpp:344-347 */
+int fc_conv_output_size(const fc_conv_desc *desc, int *oh, int *ow);
+/* select_algorithm, ConvTest.cpp:318-331 -- except that 1x1 stride-1 ("direct", an empty case in
+ * the reference) resolves to FC_ALGO_IM2COL so that something runs. */
+int fc_select_algorithm(const fc_conv_desc *desc, int *algo);
+/* element counts (floats) of the Winograd-domain buffers for a descriptor */
+int fc_wino_buffer_elems(const fc_conv_desc *desc, int mode, size_t *u_elems, size_t *v_elems, size_t *m_elems);
+
+/* ---- Winograd F(6x6,3x3) stages -------------------------------------------
+ * Device-pointer entry points, one per stage of winoF63_v1_single / _multi
+ * (winoF63ZC/winoF63ZC.h:5-9).  Layouts: U[64][oc][icp], V[64][tp][icp],
+ * M[64][oc][tp] with icp = ic rounded up to 8 and tp = tiles rounded up to 8
+ * (padding is zero); position p = col*8 + row of the 8x8 transformed tile. */
+/* offline_kernel_transform_v1, winoF63ZC/winoF63ZC.h:14 (winoF63ZC.cpp:242-322) */
+int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
+/* input transform stage, winoF63ZC/winoF63ZC.cpp:512-813 */
+int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc);
+/* TensorGEMM stage, winoF63ZC/winoF63ZC.cpp:818-860 + winoF63ZC/TensorGEMMZC.cpp */
+int fc_wino_tensor_gemm(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const fc_conv_desc *desc,
+                        int mode);
+/* output transform stage, winoF63ZC/winoF63ZC.cpp:869-973 */
+int fc_wino_output_transform(fc_context *ctx, const float *d_M, float *d_out, const fc_conv_desc *desc);
+/* whole forward with a pre-transformed filter: winoF63_v1_single(...), winoF63ZC/winoF63ZC.h:5-6.
+ * stage_ms (may be NULL) receives InputTran, KernelTran (0: one-time), TensorGEMM, OutputTran
+ * device milliseconds -- the four Timer& of the reference signature. */
+int fc_wino_forward(fc_context *ctx, const float *d_in, const float *d_U, float *d_V, float *d_M, float *d_out,
+                    const fc_conv_desc *desc, int mode, float *stage_ms);
+
+/* ---- im2col / implicit GEMM ------------------------------------------------ */
+/* ConvIm2colLayer::im2col(), convLayer/im2colConv.cpp:285-309: materialises the gathered matrix
+ * [ic*kh*kw][oh*ow] of image `image` for inspection; the forward path never builds it. */
+int fc_im2col_gather(fc_context *ctx, const float *d_in, float *d_gathered, const fc_conv_desc *desc, int image);
+/* ConvIm2colLayer::im2col_v1() + sgemm(), convLayer/im2colConv.cpp:311-398: gather fused into the
+ * GEMM's operand producer.  d_kernel is the raw [oc][ic*kh*kw] matrix (A, lda = K). */
+int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out,
+                     const fc_conv_desc *desc, int mode);
+
+/* ---- planned layer ---------------------------------------------------------
+ * What ConvLayer's constructor + Init() do (conv_layer.h:27-80,
+ * convLayer/winoF63ConvZC.cpp:176-213, convLayer/im2colConv.cpp:224-235):
+ * deep-copies the kernel to the device, sizes and allocates workspaces from
+ * the context's arena, runs the one-time filter transform. */
+int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode, const float *h_kernel,
+                   fc_conv **out);
+int fc_conv_destroy(fc_conv *conv);
+int fc_conv_algorithm(const fc_conv *conv, int *algo);
+/* Forward() on device-resident tensors, asynchronous on the context stream */
+int fc_conv_forward_device(fc_conv *conv, const float *d_in, float *d_out);
+/* Forward() from / to host memory: H2D copy, kernels, D2H copy, synchronous */
+int fc_conv_forward_host(fc_conv *conv, const float *h_in, float *h_out);
+/* device buffers owned by the layer (input / output staging used by forward_host) */
+int fc_conv_device_buffers(fc_conv *conv, float **d_in, float **d_out);
+/* `iters` back-to-back forwards timed with CUDA events on the context stream (the reference's
+ * `-i` loop, convLayer/winoF63ConvZC.cpp:227-247); ms_per_iter is the mean. */
+int fc_conv_time_device(fc_conv *conv, const float *d_in, float *d_out, int warmup, int iters, float *ms_per_iter);
+/* per-stage device milliseconds of the most recent fc_conv_profile call:
+ * [0] InputTran / Im2colTran, [1] KernelTran (one-time, measured at create), [2] TensorGEMM / Gemm,
+ * [3] OutputTran, [4] Total  (labels of convLayer/winoF63ConvZC.cpp:249-253, im2colConv.cpp:254-256) */
+int fc_conv_profile(fc_conv *conv, const float *d_in, float *d_out, int iters, float stage_ms[5]);
+/* Tuning(): picks the kernel configuration (and, for FC_ALGO_AUTO, the algorithm) from measured
+ * device time (convLayer/winoF63ConvZC.cpp:25-174, convLayer/im2colConv.cpp:261-283). */
+int fc_conv_tune(fc_conv *conv, int iters, int verbose);
+/* number of kernel launches one forward issues (for launch accounting) */
+int fc_conv_launches_per_forward(const fc_conv *conv, int *launches);
+
+/* ---- error metrics on the host ---------------------------------------------- */
+/* diff(), utility/helper.cpp:74-89: mean |a-b| over the elements with |a-b| > 1e-5 */
+float fc_diff(const float *a, const float *b, int len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTCONV_B200_H_ */

@@ -1,0 +1,106 @@
+"""Parity of the im2col / implicit-GEMM path: the gathered matrix is bit-exact with the reference's
+index map; the mirrored fp32 GEMM is bit-exact with the oracle's one-FMA-per-k chain."""
+import hashlib
+
+import numpy as np
+import pytest
+
+import fastconv_b200 as fc
+from _oracle import max_abs_rel, rel_l2
+from fastconv_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+CASES = [  # n, ic, oc, ih, iw, kh, kw, sh, sw, pad
+    (1, 3, 8, 30, 30, 7, 7, 2, 2, 3), (1, 16, 12, 14, 14, 1, 1, 1, 1, 0), (1, 8, 8, 15, 15, 3, 3, 2, 2, 1),
+    (1, 12, 6, 14, 14, 1, 1, 2, 2, 0), (2, 5, 7, 9, 11, 3, 3, 1, 1, 1), (1, 4, 4, 8, 8, 5, 3, 1, 2, 2),
+    (3, 64, 130, 7, 7, 1, 1, 1, 1, 0), (1, 70, 65, 9, 9, 3, 3, 1, 1, 1), (1, 1, 1, 1, 1, 1, 1, 1, 1, 0),
+    (2, 33, 17, 12, 10, 3, 3, 2, 2, 1), (1, 256, 64, 14, 14, 1, 1, 1, 1, 0),
+]
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def make(ctx, x, w, sh, sw, pad, mode="fp32", ref=None, iters=1):
+    n, ic, ih, iw = x.shape
+    oc, _, kh, kw = w.shape
+    return fc.ConvIm2colLayer(x, w, None, ref, ic, ih, iw, oc, kh, kw, sh, sw, pad, pad, pad, pad, 1, False, 1, iters,
+                              batch=n, mode=mode, ctx=ctx)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_gather_bit_exact(ctx, oracle, case):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 5)
+    w = synth.conv_weights(oc, ic, kh, kw, 6)
+    layer = make(ctx, x, w, sh, sw, pad)
+    for img in range(n):
+        want = oracle.im2col(x[img], kh, kw, sh, sw, pad, pad, pad, pad)
+        assert np.array_equal(layer.im2col(img), want)
+
+
+def test_gather_matches_reference_digests(ctx, golden):
+    meta, _ = golden
+    for rec in meta["general"]:
+        x = synth.conv_input(1, rec["ic"], rec["ih"], rec["iw"], rec["seed_in"])
+        w = synth.conv_weights(rec["oc"], rec["ic"], rec["kh"], rec["kw"], rec["seed_w"])
+        layer = make(ctx, x, w, rec["sh"], rec["sw"], rec["pad"])
+        assert sha(layer.im2col(0)) == rec["sha_gather"], rec
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_mirrored_gemm_bit_exact(ctx, oracle, case):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 15)
+    w = synth.conv_weights(oc, ic, kh, kw, 16)
+    layer = make(ctx, x, w, sh, sw, pad)
+    assert layer.Init() == 1 and layer.Forward() == 1  # return values of im2colConv.cpp:234, :258
+    want = oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad)
+    assert np.array_equal(layer.output_data, want)
+    layer.release()
+
+
+def test_against_reference_naive_layer(ctx, golden):
+    meta, z = golden
+    for rec in meta["general"]:
+        x = synth.conv_input(1, rec["ic"], rec["ih"], rec["iw"], rec["seed_in"])
+        w = synth.conv_weights(rec["oc"], rec["ic"], rec["kh"], rec["kw"], rec["seed_w"])
+        layer = make(ctx, x, w, rec["sh"], rec["sw"], rec["pad"])
+        layer.Init()
+        layer.Forward()
+        assert rel_l2(layer.output_data[0], z[f"general_naive_{rec['idx']}"]) < 2e-6
+        layer.release()
+
+
+def test_auto_dispatch_and_labels(ctx, oracle, capsys):
+    x = synth.conv_input(1, 16, 14, 14, 25)
+    w = synth.conv_weights(32, 16, 1, 1, 26)
+    layer = fc.make_layer("auto", x, w, None, None, 16, 14, 14, 32, 1, 1, 1, 1, 0, 0, 0, 0, ctx=ctx)
+    assert isinstance(layer, fc.ConvIm2colLayer)  # 1x1 s1: "direct" in the reference, which runs nothing
+    layer.Init()
+    layer.Forward()
+    text = capsys.readouterr().out
+    for label in ("Algorithm: im2col", "Im2colTran time:", "Gemm time:", "Total time:"):
+        assert label in text
+    assert np.array_equal(layer.output_data, oracle.im2col_gemm_forward(x, w))
+    w3 = synth.conv_weights(32, 16, 3, 3, 27)
+    assert isinstance(fc.make_layer("auto", x, w3, None, None, 16, 14, 14, 32, ctx=ctx), fc.ConvWinoF63ZCLayer)
+
+
+@pytest.mark.parametrize("mode, tol_l2, tol_max", [("3xtf32", 1e-5, 1e-4), ("tf32", 3e-3, 3e-2)])
+@pytest.mark.parametrize("case", [(1, 3, 64, 64, 64, 7, 7, 2, 2, 3), (1, 64, 256, 56, 56, 1, 1, 1, 1, 0),
+                                  (2, 128, 128, 28, 28, 3, 3, 2, 2, 1), (1, 1024, 256, 14, 14, 1, 1, 1, 1, 0),
+                                  (1, 20, 36, 9, 9, 3, 3, 1, 1, 1)])
+def test_tensor_core_modes_within_tolerance(ctx, oracle, mode, tol_l2, tol_max, case):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 35)
+    w = synth.conv_weights(oc, ic, kh, kw, 36)
+    want = oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad)
+    layer = make(ctx, x, w, sh, sw, pad, mode=mode)
+    layer.Init()
+    layer.Forward()
+    assert rel_l2(layer.output_data, want) <= tol_l2, f"{mode} rel-L2 {rel_l2(layer.output_data, want):.3e}"
+    assert max_abs_rel(layer.output_data, want) <= tol_max
+    layer.release()

@@ -1,0 +1,172 @@
+"""Parity of the CUDA Winograd F(6x6,3x3) path with the CPU oracle, through the C ABI.
+
+fp32 "mirrored" mode is held to BIT equality with the oracle (which is itself bit-equal to the
+reference build).  Tensor-core modes are held to the tolerances the task states: 3xTF32
+rel-L2 <= 1e-5 and max-abs <= 1e-4*||out||inf for the sizes checked here, TF32 rel-L2 <= 3e-3.
+"""
+import ctypes as C
+import hashlib
+
+import numpy as np
+import pytest
+
+import fastconv_b200 as fc
+from _oracle import max_abs_rel, rel_l2
+from fastconv_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+SMALL = [  # n, ic, oc, ih, iw, pad -- every OH mod 6 residue, channel counts around the 4/8 padding
+    (1, 1, 1, 6, 6, 1), (1, 3, 5, 7, 9, 1), (1, 4, 4, 1, 1, 1), (1, 8, 8, 12, 12, 1), (1, 5, 3, 6, 6, 0),
+    (1, 17, 6, 23, 20, 1), (1, 6, 7, 13, 8, 2), (2, 3, 4, 10, 11, 1), (3, 9, 65, 5, 31, 1), (1, 64, 64, 14, 14, 1),
+    (1, 33, 129, 8, 8, 1), (2, 70, 40, 19, 7, 1), (1, 5, 8, 2, 2, 1), (1, 4, 4, 3, 3, 1), (1, 8, 4, 4, 4, 1),
+    (1, 12, 20, 5, 5, 1), (1, 16, 16, 16, 16, 0), (1, 130, 66, 15, 15, 1),
+]
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def run_layer(ctx, x, w, pad, mode="fp32"):
+    n, ic, ih, iw = x.shape
+    oc = w.shape[0]
+    layer = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, ih, iw, oc, 3, 3, 1, 1, pad, pad, pad, pad, 1, False, 1, 1,
+                                  batch=n, mode=mode, ctx=ctx)
+    assert layer.Init() == -1  # the reference's Init returns -1 (winoF63ConvZC.cpp:212)
+    assert layer.Forward() == 1
+    out = layer.output_data.copy()
+    layer.release()
+    return out
+
+
+@pytest.mark.parametrize("shape", SMALL)
+def test_mirrored_mode_is_bit_exact(ctx, oracle, shape):
+    n, ic, oc, ih, iw, pad = shape
+    x = synth.conv_input(n, ic, ih, iw, 41)
+    w = synth.conv_weights(oc, ic, 3, 3, 42)
+    assert np.array_equal(run_layer(ctx, x, w, pad), oracle.wino_forward(x, w, pad))
+
+
+def test_golden_vectors_small(ctx, golden):
+    meta, z = golden
+    for rec in meta["wino"]:
+        x = synth.conv_input(1, rec["ic"], rec["ih"], rec["iw"], rec["seed_in"])
+        w = synth.conv_weights(rec["oc"], rec["ic"], 3, 3, rec["seed_w"])
+        got = run_layer(ctx, x, w, rec["pad"])[0]
+        assert np.array_equal(got, z[f"wino_{rec['idx']}"]), rec
+
+
+def test_golden_vectors_full_size(ctx, golden):
+    meta, z = golden
+    for rec in meta["wino_large"]:
+        x = synth.conv_input(1, rec["ic"], rec["ih"], rec["iw"], rec["seed_in"])
+        w = synth.conv_weights(rec["oc"], rec["ic"], 3, 3, rec["seed_w"])
+        got = run_layer(ctx, x, w, rec["pad"])[0]
+        assert sha(got) == rec["sha_wino"], f"{rec['ic']}->{rec['oc']}@{rec['ih']} differs from the reference output"
+
+
+def _dev(ctx, a):
+    return C.c_void_p(ctx.upload(a))
+
+
+def test_each_stage_bit_exact(ctx, oracle):
+    lib = fc.load()
+    n, ic, oc, ih, iw, pad = 2, 13, 21, 17, 11, 1
+    x = synth.conv_input(n, ic, ih, iw, 51)
+    w = synth.conv_weights(oc, ic, 3, 3, 52)
+    d = fc.make_desc(n, ic, ih, iw, oc, 3, 3, 1, 1, pad, pad, pad, pad)
+    u, v, m = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    fc._lib.check(lib.fc_wino_buffer_elems(C.byref(d), 0, C.byref(u), C.byref(v), C.byref(m)), "elems")
+    icp, tiles = 16, 2 * 3 * 2
+    tp = 16
+    assert (u.value, v.value, m.value) == (64 * oc * icp, 64 * tp * icp, 64 * oc * tp)
+    dU, dV, dM = (C.c_void_p(ctx.alloc(4 * e.value)) for e in (u, v, m))
+    d_out = C.c_void_p(ctx.alloc(4 * n * oc * ih * iw))
+    dk, dx = _dev(ctx, w), _dev(ctx, x)
+    h = ctx.handle
+    fc._lib.check(lib.fc_wino_filter_transform(h, dk, dU, oc, ic), "filter")
+    fc._lib.check(lib.fc_wino_input_transform(h, dx, dV, C.byref(d)), "input")
+    fc._lib.check(lib.fc_wino_tensor_gemm(h, dU, dV, dM, C.byref(d), 0), "gemm")
+    fc._lib.check(lib.fc_wino_output_transform(h, dM, d_out, C.byref(d)), "output")
+    U = ctx.download(dU.value, (64, oc, icp))
+    V = ctx.download(dV.value, (64, tp, icp))
+    M = ctx.download(dM.value, (64, oc, tp))
+    out = ctx.download(d_out.value, (n, oc, ih, iw))
+    Uo = oracle.filter_transform(w, icp=icp)
+    Vo = oracle.input_transform(x, pad, tp=tp, icp=icp)
+    assert np.array_equal(U, Uo), "filter transform"
+    assert np.array_equal(V, Vo), "input transform (padding rows/channels must be zero)"
+    Mo = oracle.wino_gemm(Uo, Vo, oc, icp, tp)
+    assert np.array_equal(M[:, :, :tiles], Mo[:, :, :tiles]), "TensorGEMM"
+    assert np.array_equal(out, oracle.output_transform(Mo, n, oc, ih, iw)), "output transform"
+    # the fused entry point gives the same bits and reports stage times
+    ms = (C.c_float * 4)()
+    fc._lib.check(lib.fc_wino_forward(h, dx, dU, dV, dM, d_out, C.byref(d), 0, ms), "forward")
+    assert np.array_equal(ctx.download(d_out.value, (n, oc, ih, iw)), out)
+    assert ms[0] > 0 and ms[2] > 0 and ms[3] > 0 and ms[1] == 0
+    for p in (dU, dV, dM, d_out, dk, dx):
+        ctx.free(p.value)
+
+
+def test_unsupported_shapes_are_refused(ctx):
+    x = synth.conv_input(1, 4, 8, 8, 1)
+    for kw in (dict(kh=5, kw=5), dict(sh=2, sw=2), dict(pad_left=0)):
+        args = dict(kh=3, kw=3, sh=1, sw=1, pad_left=1, pad_right=1, pad_top=1, pad_bottom=1)
+        args.update(kw)
+        w = synth.conv_weights(4, 4, args["kh"], args["kw"], 2)
+        layer = fc.ConvWinoF63ZCLayer(x, w, None, None, 4, 8, 8, 4, ctx=ctx, **args)
+        with pytest.raises(fc.FastConvError) as e:
+            layer.Init()
+        assert e.value.status == -2
+
+
+def test_batch_is_independent_images(ctx, oracle):
+    """Tiles of all images are concatenated on the GEMM's tile axis; each image must come out as if alone."""
+    n, ic, oc, ih, iw = 5, 16, 24, 14, 14
+    x = synth.conv_input(n, ic, ih, iw, 61)
+    w = synth.conv_weights(oc, ic, 3, 3, 62)
+    whole = run_layer(ctx, x, w, 1)
+    for i in range(n):
+        assert np.array_equal(whole[i:i + 1], run_layer(ctx, x[i:i + 1], w, 1))
+
+
+def test_linearity_at_full_size(ctx):
+    """conv(x, a+b) == conv(x, a) + conv(x, b) up to fp32 rounding, on conv3_2's full shape."""
+    ic = oc = 256
+    x = synth.conv_input(1, ic, 56, 56, 71)
+    a = synth.conv_weights(oc, ic, 3, 3, 72)
+    b = synth.conv_weights(oc, ic, 3, 3, 73)
+    lhs = run_layer(ctx, x, a + b, 1)
+    rhs = run_layer(ctx, x, a, 1) + run_layer(ctx, x, b, 1)
+    assert rel_l2(lhs, rhs) < 2e-5
+
+
+def test_reference_self_check_line(ctx, oracle, capsys):
+    """Forward() prints the reference's labels and the `diff` against output_ref (winoF63ConvZC.cpp:249-256)."""
+    ic, oc, hw = 32, 32, 28
+    x = synth.conv_input(1, ic, hw, hw, 81)
+    w = synth.conv_weights(oc, ic, 3, 3, 82)
+    naive = oracle.naive_conv(x, w, 1, 1, 1, 1, 1, 1)
+    layer = fc.ConvWinoF63ZCLayer(x, w, None, naive, ic, hw, hw, oc, iter=3, ctx=ctx)
+    layer.Init()
+    layer.Forward()
+    text = capsys.readouterr().out
+    for label in ("Algorithm: winograd F63", "InputTran time:", "KernelTran time:", "TensorGEMM time:",
+                  "OutputTran time:", "Total time:", "The difference is"):
+        assert label in text
+    assert rel_l2(layer.output_data, naive) < 1e-5
+    layer.release()
+
+
+@pytest.mark.parametrize("mode, tol_l2, tol_max", [("3xtf32", 1e-5, 1e-4), ("tf32", 3e-3, 3e-2)])
+@pytest.mark.parametrize("shape", [(1, 64, 64, 56, 56, 1), (1, 256, 256, 56, 56, 1), (2, 37, 70, 20, 23, 1),
+                                   (1, 3, 64, 40, 40, 1), (1, 128, 128, 14, 14, 1), (1, 8, 8, 6, 6, 1)])
+def test_tensor_core_modes_within_tolerance(ctx, oracle, mode, tol_l2, tol_max, shape):
+    n, ic, oc, ih, iw, pad = shape
+    x = synth.conv_input(n, ic, ih, iw, 91)
+    w = synth.conv_weights(oc, ic, 3, 3, 92)
+    want = oracle.wino_forward(x, w, pad)
+    got = run_layer(ctx, x, w, pad, mode=mode)
+    assert rel_l2(got, want) <= tol_l2, f"{mode} rel-L2 {rel_l2(got, want):.3e}"
+    assert max_abs_rel(got, want) <= tol_max, f"{mode} max-abs/||out||inf {max_abs_rel(got, want):.3e}"
