@@ -59,13 +59,17 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu, self.proc, self.lines = gpu_index, None, []
+        self.gpu, self.proc, self.lines, self.marks = gpu_index, None, [], []
+
+    def mark(self):
+        """Remembers how many samples had arrived: the first two marks bracket the device-timed region."""
+        self.marks.append(len(self.lines))
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -85,7 +89,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = "device-timed region"
+        lines = self.lines[self.marks[0]:self.marks[1]] if len(self.marks) >= 2 else []
+        if len(lines) < 2:  # region shorter than the sampling period: use every sample taken under load
+            lines, window = self.lines[self.marks[0] if self.marks else 0:], "timed + end-to-end regions"
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -98,7 +106,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def reference_cpu_pass(layers, batch, threads, seeds_base=0):
@@ -162,11 +170,18 @@ def main():
     ap.add_argument("--impl", default="fastconv", choices=["fastconv", "reference"])
     ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32"])
     ap.add_argument("--batch", type=int, default=1, help="images per GPU")
+    ap.add_argument("--layers", default="vgg16",
+                    help="'vgg16' (the 13-layer stack) or a list 'C,K,H;C,K,H;...' of 3x3 s1 p1 layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "fastconv":
         args.warmup = 3
 
+    global VGG16
+    workload_name = "VGG-16 13 conv layers"
+    if args.layers != "vgg16":
+        VGG16 = [tuple(int(v) for v in item.split(",")) for item in args.layers.split(";") if item]
+        workload_name = "layers " + args.layers
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -245,18 +260,19 @@ def main():
         return float(t.item())
 
     # ---- device-resident throughput (`value`) -----------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step_device()
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    sampler.mark()
     ctx.timer_record(0)
     for _ in range(args.steps):
         step_device()
     ctx.timer_record(1)
     ms_total = ctx.timer_elapsed_ms(0, 1)
     barrier()
-    clocks = sampler.stop()
+    sampler.mark()
     ms_step = reduce_max(ms_total) / args.steps
 
     # ---- end to end through the host-pointer entry point (pinned host buffers) ----------------------
@@ -269,6 +285,7 @@ def main():
     ctx.synchronize()
     e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / args.steps
     barrier()
+    clocks = sampler.stop()
 
     # ---- per-layer and per-kernel device times (CUDA events around each stage, same inputs) ----------
     per_layer, stage_tot = [], [0.0] * 5
@@ -321,7 +338,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32"}[args.mode], "data": "synthetic",
-            "config": {"workload": f"VGG-16 13 conv layers, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
+            "config": {"workload": f"{workload_name}, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
                        "algorithm": "winograd F(6x6,3x3)", "math_mode": args.mode,
                        "parallelism": f"images sharded over {world} GPU(s), no collective",
                        "l2": f"inputs larger than L2: the stack touches {footprint / 1e6:.0f} MB per step"},

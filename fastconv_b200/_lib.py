@@ -47,6 +47,7 @@ SIGNATURES = {
     "fc_context_destroy": (C.c_int, [_vp]),
     "fc_context_synchronize": (C.c_int, [_vp]),
     "fc_context_device": (C.c_int, [_vp, _ip]),
+    "fc_context_stream": (C.c_int, [_vp, C.POINTER(_vp)]),
     "fc_arena_alloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "fc_arena_size_of": (C.c_int, [_vp, _vp, _szp]),
     "fc_arena_free": (C.c_int, [_vp, _vp]),

@@ -176,6 +176,12 @@ int fc_context_device(const fc_context *ctx, int *device) {
     return FC_OK;
 }
 
+int fc_context_stream(const fc_context *ctx, void **stream) {
+    FC_REQUIRE(ctx != nullptr && stream != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
+    *stream = (void *)ctx->stream;
+    return FC_OK;
+}
+
 int fc_arena_alloc(fc_context *ctx, size_t bytes, void **dptr) {
     FC_REQUIRE(ctx != nullptr && dptr != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
     const uintptr_t p = ctx->arena.alloc(bytes);

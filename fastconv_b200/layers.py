@@ -71,6 +71,13 @@ class Context:
             raise RuntimeError("context is closed")
         return self._h
 
+    @property
+    def stream(self) -> C.c_void_p:
+        """The context's cudaStream_t as an opaque pointer."""
+        s = C.c_void_p()
+        check(self._lib.fc_context_stream(self.handle, C.byref(s)), "fc_context_stream")
+        return s
+
     # -- arena (PrivateMemPool / CommonMemPool of utility/mempool.h) -----------------------------
     def alloc(self, nbytes: int) -> int:
         p = C.c_void_p()

@@ -83,6 +83,8 @@ int fc_context_create(int device, size_t arena_bytes, fc_context **out);
 int fc_context_destroy(fc_context *ctx);
 int fc_context_synchronize(fc_context *ctx);
 int fc_context_device(const fc_context *ctx, int *device);
+/* the context's cudaStream_t, for callers that enqueue their own work in order with the library's */
+int fc_context_stream(const fc_context *ctx, void **stream);
 /* PrivateMemPool::Alloc / GetSize / Free / FreeAll / PrintStats */
 int fc_arena_alloc(fc_context *ctx, size_t bytes, void **dptr);
 int fc_arena_size_of(fc_context *ctx, const void *dptr, size_t *bytes);
