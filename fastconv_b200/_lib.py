@@ -72,6 +72,7 @@ SIGNATURES = {
     "fc_wino_tensor_gemm": (C.c_int, [_vp, _vp, _vp, _vp, _dp, C.c_int]),
     "fc_wino_output_transform": (C.c_int, [_vp, _vp, _vp, _dp]),
     "fc_wino_forward": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _dp, C.c_int, _fp]),
+    "fc_wino_forward_static_scratch": (C.c_int, [_vp, _vp, _vp, _dp, _vp]),
     "fc_im2col_gather": (C.c_int, [_vp, _vp, _vp, _dp, C.c_int]),
     "fc_igemm_forward": (C.c_int, [_vp, _vp, _vp, _vp, _dp, C.c_int]),
     "fc_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),

@@ -139,6 +139,25 @@ int fc_wino_output_transform(fc_context *ctx, const float *d_M, float *d_out, co
 int fc_wino_forward(fc_context *ctx, const float *d_in, const float *d_U, float *d_V, float *d_M, float *d_out,
                     const fc_conv_desc *desc, int mode, float *stage_ms);
 
+/* No counterpart in the reference (its layers malloc their workspaces in Init,
+ * convLayer/winoF63ConvZC.cpp:193-201).  Same computation as fc_wino_forward in
+ * FC_MATH_FP32_MIRRORED mode, for callers that may not allocate device memory -- a plugin inside
+ * an engine with a fixed memory budget, a loop that must not synchronise the device after start-up,
+ * a process whose allocator belongs to another framework.  The V and M workspaces live in a
+ * FC_STATIC_SCRATCH_FLOATS-float (16 MiB) array built into the library, which every GPU that loads
+ * the library holds until the process exits; the call makes no cudaMalloc / cudaFree and needs no
+ * fc_context.  It runs on the CURRENT device, on `stream` (a cudaStream_t, NULL = default stream),
+ * asynchronously.  Limits and rules:
+ *   - 64*tp*icp + 64*oc*tp floats must fit in the array, else FC_ERR_UNSUPPORTED (e.g. 256->256@56
+ *     and 512->512@28 at batch 1 fit, 128->128@112 does not);
+ *   - the first call on each device looks up the array's device address: make that call before
+ *     starting any stream capture;
+ *   - all calls share the one array: two calls that can overlap on the GPU (different streams,
+ *     or different host threads) race -- serialise them. */
+#define FC_STATIC_SCRATCH_FLOATS (4u << 20)
+int fc_wino_forward_static_scratch(const float *d_in, const float *d_U, float *d_out, const fc_conv_desc *desc,
+                                   void *stream);
+
 /* ---- im2col / implicit GEMM ------------------------------------------------ */
 /* ConvIm2colLayer::im2col(), convLayer/im2colConv.cpp:285-309: materialises the gathered matrix
  * [ic*kh*kw][oh*ow] of image `image` for inspection; the forward path never builds it. */
