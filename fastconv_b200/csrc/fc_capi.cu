@@ -164,10 +164,23 @@ int fc_context_destroy(fc_context *ctx) {
     return FC_OK;
 }
 
+// Waits for the stream, then reads (and clears) the word kernels with bounded waits report into.
+static int sync_and_check_status(fc_context *ctx) {
+    int st = 0;
+    FC_CHECK_CUDA(cudaMemcpyAsync(&st, ctx->d_status, sizeof st, cudaMemcpyDeviceToHost, ctx->stream));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (st != 0) {
+        FC_CHECK_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof st, ctx->stream));
+        FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+        set_error("a kernel gave up a bounded device-side wait (status word %d)", st);
+        return FC_ERR_TIMEOUT;
+    }
+    return FC_OK;
+}
+
 int fc_context_synchronize(fc_context *ctx) {
     FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
-    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
-    return FC_OK;
+    return sync_and_check_status(ctx);
 }
 
 int fc_context_device(const fc_context *ctx, int *device) {
@@ -566,8 +579,11 @@ int fc_conv_forward_host(fc_conv *c, const float *h_in, float *h_out) {
     FC_CHECK_CUDA(cudaMemcpyAsync(c->d_in, h_in, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
     FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
     FC_CHECK_CUDA(cudaMemcpyAsync(h_out, c->d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
-    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
-    return FC_OK;
+    if (c->mode == FC_MATH_FP32_MIRRORED) {  // FFMA kernels have no device-side waits to report
+        FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+        return FC_OK;
+    }
+    return sync_and_check_status(ctx);
 }
 
 int fc_conv_device_buffers(fc_conv *c, float **d_in, float **d_out) {

@@ -1,11 +1,360 @@
-// Tensor-core (tcgen05) GEMM launchers -- placeholder until the kernels land.
+// TensorGEMM on the 5th-generation tensor cores (tcgen05 + TMEM), operands fed by TMA.
+//
+// For every Winograd position p the GEMM  M_p[oc][tile] = sum_ic U_p[oc][ic] * V_p[tile][ic]  has both
+// operands K-major in global memory, which is exactly what a K-major UMMA shared-memory descriptor
+// with 128-byte swizzle and a TMA box of 32 floats x rows want.  One CTA owns one 128(oc) x BN(tile)
+// block of one position:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor 3-D boxes (ic, row, p) of U and V into a ring of
+//               shared-memory stages, completion counted on an mbarrier per stage
+//   warp 1      allocates TMEM, then one elected lane issues tcgen05.mma.cta_group::1.kind::tf32
+//               (M=128, N=BN, K=8) four times per stage; tcgen05.commit releases the stage
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (lane = oc row) and store it to M.
+//               In 3xTF32 mode the same warps first split every landed stage in place into
+//               hi = tf32(x) and lo = x - hi, so each k-step becomes lo*hi + hi*lo + hi*hi with fp32
+//               accumulation: fp32-class accuracy without touching HBM twice.
+//
+// Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
+// context's status word, all roles drain, TMEM is released and the kernel returns.
+#include <cuda.h>
+
 #include "fc_internal.h"
 
 namespace fc {
 
-int launch_wino_gemm_tc(fc_context *, const float *, const float *, float *, const WinoGeom &, int) {
-    set_error("tensor-core TensorGEMM is not built yet");
-    return FC_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int BM = 128;            // oc rows per CTA = TMEM lanes
+constexpr int BK = 32;             // floats per stage row = 128 bytes = one swizzle span
+constexpr int A_BYTES = BM * BK * 4;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct TcParams {
+    float *M;
+    int *status;
+    int oc, tp, bn, num_kb, stages, tmem_cols;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is hit or another
+// role already gave up, so that no role can spin forever on a barrier nobody will complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (i > 128) __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicExch(status, (int)FC_ERR_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], TF32 inputs, fp32 accumulate
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups
+// 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle; 1)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset
+    d |= (uint64_t)1 << 46;                          // version
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D fp32, A/B tf32, both K-major, M=128, N=bn
+__host__ __device__ inline uint32_t umma_idesc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// ---- kernel ---------------------------------------------------------------------------------
+template <bool kSplit>
+__global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
+                                                                  const __grid_constant__ CUtensorMap tmV,
+                                                                  const TcParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    // carve: [barriers + flags | 1024-aligned stage ring]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);      // full[S], empty[S], split[S], tmem_full
+    const int S = P.stages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * 8 + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t ring = (smem_u32(smem_raw) + 512 + 1023) & ~1023u;
+    const uint32_t b_bytes = (uint32_t)P.bn * BK * 4;
+    const uint32_t part_bytes = A_BYTES + b_bytes;                  // one (A,B) pair
+    const uint32_t stage_bytes = part_bytes * (kSplit ? 2 : 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * P.bn;
+
+    auto bar_full = [&](int s) { return smem_u32(bars + s); };
+    auto bar_empty = [&](int s) { return smem_u32(bars + 8 + s); };
+    auto bar_split = [&](int s) { return smem_u32(bars + 16 + s); };
+    const uint32_t bar_tmem_full = smem_u32(bars + 24);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+            mbar_init(bar_split(s), 128);
+        }
+        mbar_init(bar_tmem_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)P.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < P.num_kb; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status)) break;
+                const uint32_t a_dst = ring + s * stage_bytes;
+                mbar_expect_tx(bar_full(s), part_bytes);
+                tma_load_3d(a_dst, &tmU, bar_full(s), kb * BK, oc0, p);
+                tma_load_3d(a_dst + A_BYTES, &tmV, bar_full(s), kb * BK, t0, p);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_tf32(BM, P.bn);
+            bool ok = true;
+            for (int kb = 0; kb < P.num_kb && ok; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+                ok = mbar_wait(kSplit ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_hi = ring + s * stage_bytes, b_hi = a_hi + A_BYTES;
+                const uint32_t a_lo = a_hi + part_bytes, b_lo = a_lo + A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BK / 8; ++ks) {
+                    const uint32_t koff = ks * 32;  // 8 tf32 = 32 bytes further along K inside the swizzle span
+                    const uint32_t first = (kb == 0 && ks == 0) ? 0u : 1u;
+                    if (kSplit) {
+                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_lo + koff), umma_desc_k_sw128(b_hi + koff), idesc, first);
+                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_lo + koff), idesc, 1u);
+                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, 1u);
+                    } else {
+                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, first);
+                    }
+                }
+                tc_commit(bar_empty(s));  // arrives once the MMAs above have finished reading the stage
+            }
+            tc_commit(bar_tmem_full);
+        }
+    } else {
+        // ---------------- splitters (3xTF32) + epilogue ----------------
+        const int et = threadIdx.x - 64;  // 0..127
+        if (kSplit) {
+            const int a_chunks = A_BYTES / 16, all_chunks = (int)(part_bytes / 16);
+            (void)a_chunks;
+            for (int kb = 0; kb < P.num_kb; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+                if (!mbar_wait(bar_full(s), ph, abort_flag, P.status)) break;
+                float4 *hi = reinterpret_cast<float4 *>(smem_raw + (ring - smem_u32(smem_raw)) + s * stage_bytes);
+                float4 *lo = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(hi) + part_bytes);
+                // element-wise at identical offsets: the swizzled placement of hi and lo stays that of TMA
+                for (int i = et; i < all_chunks; i += 128) {
+                    const float4 v = hi[i];
+                    float4 h, l;
+                    h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+                    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
+                mbar_arrive(bar_split(s));
+            }
+        }
+        if (mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
+            tc_fence_after();
+            const int q = warp & 3;  // TMEM lane quarter this warp may read
+            const int row = oc0 + q * 32 + lane;
+            float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
+            for (int c0 = 0; c0 < P.bn; c0 += 16) {
+                float v[16];
+                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (row < P.oc) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4)
+                        if (t0 + c0 + j < P.tp)  // tp is a multiple of 8: a float4 never straddles the end
+                            *reinterpret_cast<float4 *>(dst + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before the CTA's shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.tmem_cols)
+                     : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encoder(EncodeTiledFn *fn) {
+    static EncodeTiledFn cached = nullptr;
+    if (!cached) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        FC_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q));
+        FC_REQUIRE(ptr != nullptr && q == cudaDriverEntryPointSuccess, FC_ERR_CUDA,
+                   "the driver does not export cuTensorMapEncodeTiled");
+        cached = (EncodeTiledFn)ptr;
+    }
+    *fn = cached;
+    return FC_OK;
+}
+
+// 3-D fp32 tensor [planes][rows][cols] (cols contiguous), box = 32 cols x box_rows x 1 plane,
+// 128-byte swizzle, out-of-range elements read as zero.
+int make_map_3d(CUtensorMap *map, const float *base, int cols, int rows, int planes, int box_rows) {
+    EncodeTiledFn enc;
+    FC_PROPAGATE(get_encoder(&enc));
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)cols * rows * 4};
+    cuuint32_t box[3] = {BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (cols %d rows %d planes %d box %d)",
+               (int)r, cols, rows, planes, box_rows);
+    return FC_OK;
+}
+
+int pow2_at_least(int x, int lo) {
+    int v = lo;
+    while (v < x) v <<= 1;
+    return v;
+}
+
+}  // namespace
+
+int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode) {
+    const bool split = mode == FC_MATH_3XTF32;
+    // tile blocks of at most 128 tiles, balanced, multiple of 16 (UMMA N granularity at M=128)
+    const int n_blk = (g.tp + 127) / 128;
+    const int bn = round_up((g.tp + n_blk - 1) / n_blk, 16);
+    TcParams P;
+    P.M = d_M;
+    P.status = ctx->d_status;
+    P.oc = g.oc;
+    P.tp = g.tp;
+    P.bn = bn;
+    P.num_kb = (g.icp + BK - 1) / BK;
+    P.tmem_cols = pow2_at_least(bn, 32);
+    const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
+    int stages = (int)((200 * 1024) / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages > P.num_kb) stages = P.num_kb < 2 ? 2 : P.num_kb;
+    FC_REQUIRE(stages >= 2, FC_ERR_UNSUPPORTED, "tile block of %d does not fit the shared-memory ring", bn);
+    P.stages = stages;
+    const size_t smem = 512 + 1024 + stages * stage_bytes;
+
+    CUtensorMap tmU, tmV;
+    FC_PROPAGATE(make_map_3d(&tmU, d_U, g.icp, g.oc, 64, BM));
+    FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, bn));
+
+    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(g.oc, BM), 64), block(TC_THREADS);
+    if (split) {
+        FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        wino_gemm_tc_kernel<true><<<grid, block, smem, ctx->stream>>>(tmU, tmV, P);
+    } else {
+        FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        wino_gemm_tc_kernel<false><<<grid, block, smem, ctx->stream>>>(tmU, tmV, P);
+    }
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
 }
 
 int launch_igemm_tc(fc_context *, const float *, const float *, float *, const fc_conv_desc &, int, int, int) {
