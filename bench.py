@@ -237,9 +237,11 @@ def main():
         t, tp, icp = wino_geometry(n, c, k, h)
         footprint += 4 * (64 * k * icp + 64 * tp * icp + 64 * k * tp + n * c * h * h + n * k * h * h)
 
+    # the whole stack as one CUDA graph: a step is one graph launch
+    stack = fc.LayerList(ctx, [c[0] for c in convs], [c[1].value for c in convs], [c[2].value for c in convs])
+
     def step_device():
-        for hdl, d_in, d_out, _ in convs:
-            _lib.check(lib.fc_conv_forward_device(hdl, d_in, d_out), "fc_conv_forward_device")
+        stack.forward()
 
     def step_host():
         for (hdl, _, _, _), px, po in zip(convs, host_in, host_out):
@@ -340,6 +342,7 @@ def main():
             "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32"}[args.mode], "data": "synthetic",
             "config": {"workload": f"{workload_name}, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
                        "algorithm": "winograd F(6x6,3x3)", "math_mode": args.mode,
+                       "launch": "all layers of a step replayed as one CUDA graph",
                        "parallelism": f"images sharded over {world} GPU(s), no collective",
                        "l2": f"inputs larger than L2: the stack touches {footprint / 1e6:.0f} MB per step"},
             "e2e": {"value": round(e2e_value, 1), "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -360,6 +363,7 @@ def main():
             else:
                 line["cpu_baseline"] = {"value": None, "unit": "GFLOP/s", "cores": threads, "kind": "reference",
                                         "sample": err}
+    stack.close()
     for hdl, _, _, _ in convs:
         lib.fc_conv_destroy(hdl)
     ctx.close()

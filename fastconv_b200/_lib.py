@@ -74,6 +74,8 @@ SIGNATURES = {
     "fc_wino_forward": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _dp, C.c_int, _fp]),
     "fc_wino_forward_static_scratch": (C.c_int, [_vp, _vp, _vp, _dp, _vp]),
     "fc_im2col_gather": (C.c_int, [_vp, _vp, _vp, _dp, C.c_int]),
+    "fc_igemm_packed_elems": (C.c_int, [C.c_int, C.c_int, _szp]),
+    "fc_igemm_pack_weights": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int]),
     "fc_igemm_forward": (C.c_int, [_vp, _vp, _vp, _vp, _dp, C.c_int]),
     "fc_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "fc_conv_destroy": (C.c_int, [_vp]),
@@ -85,6 +87,10 @@ SIGNATURES = {
     "fc_conv_profile": (C.c_int, [_vp, _vp, _vp, C.c_int, _fp]),
     "fc_conv_tune": (C.c_int, [_vp, C.c_int, C.c_int]),
     "fc_conv_launches_per_forward": (C.c_int, [_vp, _ip]),
+    "fc_layer_list_create": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.c_int, C.POINTER(_vp)]),
+    "fc_layer_list_forward": (C.c_int, [_vp]),
+    "fc_layer_list_launches": (C.c_int, [_vp, _ip]),
+    "fc_layer_list_destroy": (C.c_int, [_vp]),
     "fc_diff": (C.c_float, [_vp, _vp, C.c_int]),
 }
 

@@ -22,6 +22,7 @@ SOURCES = [
     "fc_wino_gemm_ffma.cu",
     "fc_igemm_ffma.cu",
     "fc_gemm_tc.cu",
+    "fc_igemm_tc.cu",
     "fc_static_scratch.cu",
 ]
 

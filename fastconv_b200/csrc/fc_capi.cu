@@ -67,6 +67,7 @@ struct fc_conv {
     int oh, ow;
     WinoGeom geom;
     float *d_kernel;  // raw [oc][ic*kh*kw]
+    float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
     float *d_U, *d_V, *d_M;
     float *d_in, *d_out;  // staging for forward_host
     float kernel_tran_ms;
@@ -438,6 +439,19 @@ int fc_im2col_gather(fc_context *ctx, const float *d_in, float *d_gathered, cons
     return launch_im2col_gather(ctx, d_in, d_gathered, *desc, oh, ow, image);
 }
 
+int fc_igemm_packed_elems(int oc, int K, size_t *elems) {
+    FC_REQUIRE(elems != nullptr && oc > 0 && K > 0, FC_ERR_INVALID_ARG, "bad argument");
+    *elems = igemm_packed_elems(oc, K);
+    return FC_OK;
+}
+
+int fc_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K) {
+    FC_REQUIRE(ctx && d_kernel && d_packed, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(oc > 0 && K > 0, FC_ERR_INVALID_ARG, "non-positive matrix extent");
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    return launch_igemm_pack_weights(ctx, d_kernel, d_packed, oc, K);
+}
+
 int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out,
                      const fc_conv_desc *desc, int mode) {
     FC_REQUIRE(ctx && d_in && d_kernel && d_out, FC_ERR_INVALID_ARG, "NULL argument");
@@ -458,7 +472,7 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
 
 static void conv_release(fc_conv *c) {
     fc_context *ctx = c->ctx;
-    float *bufs[] = {c->d_kernel, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    float *bufs[] = {c->d_kernel, c->d_packed, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
     for (float *b : bufs)
         if (b) ctx->arena.release((uintptr_t)b);
     delete c;
@@ -502,6 +516,8 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
         if (st == FC_OK) st = grab(&c->d_V, (size_t)64 * g.tp * g.icp);
         if (st == FC_OK) st = grab(&c->d_M, (size_t)64 * g.oc * g.tp);
     }
+    const bool packed = algo == FC_ALGO_IM2COL && mode != FC_MATH_FP32_MIRRORED;
+    if (st == FC_OK && packed) st = grab(&c->d_packed, igemm_packed_elems(desc->oc, desc->ic * desc->kh * desc->kw));
     if (st != FC_OK) {
         conv_release(c);
         return st;
@@ -512,13 +528,18 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
         st = launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic, g.icp);
         cudaEventRecord(ctx->ev[1], ctx->stream);
     }
+    if (e == cudaSuccess && packed) {
+        cudaEventRecord(ctx->ev[0], ctx->stream);
+        st = launch_igemm_pack_weights(ctx, c->d_kernel, c->d_packed, desc->oc, desc->ic * desc->kh * desc->kw);
+        cudaEventRecord(ctx->ev[1], ctx->stream);
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess || st != FC_OK) {
         if (e != cudaSuccess) set_error("kernel upload / filter transform failed: %s", cudaGetErrorString(e));
         conv_release(c);
         return e != cudaSuccess ? FC_ERR_CUDA : st;
     }
-    if (algo == FC_ALGO_WINOGRAD) cudaEventElapsedTime(&c->kernel_tran_ms, ctx->ev[0], ctx->ev[1]);
+    if (algo == FC_ALGO_WINOGRAD || packed) cudaEventElapsedTime(&c->kernel_tran_ms, ctx->ev[0], ctx->ev[1]);
     *out = c;
     return FC_OK;
 }
@@ -555,7 +576,7 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     if (c->mode == FC_MATH_FP32_MIRRORED)
         st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow);
     else
-        st = launch_igemm_tc(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, c->mode);
+        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode);
     FC_PROPAGATE(st);
     if (timed) {
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
@@ -644,6 +665,76 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
     *launches = c->algo == FC_ALGO_WINOGRAD ? 3 : 1;
+    return FC_OK;
+}
+
+// ---- layer list (CUDA graph over several layers) ----------------------------------------------
+
+struct fc_layer_list {
+    fc_context *ctx;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    int launches;
+};
+
+int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *const *d_ins, float *const *d_outs,
+                         int count, fc_layer_list **out) {
+    FC_REQUIRE(ctx && convs && d_ins && d_outs && out, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(count > 0, FC_ERR_INVALID_ARG, "empty layer list");
+    *out = nullptr;
+    int launches = 0;
+    for (int i = 0; i < count; ++i) {
+        FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
+        FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 : 1;
+    }
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    // one eager pass first: kernel attributes are set and any error shows up outside the capture
+    for (int i = 0; i < count; ++i) FC_PROPAGATE(conv_enqueue(convs[i], d_ins[i], d_outs[i], false));
+    FC_PROPAGATE(sync_and_check_status(ctx));
+
+    fc_layer_list *l = new (std::nothrow) fc_layer_list();
+    FC_REQUIRE(l != nullptr, FC_ERR_OUT_OF_MEMORY, "host allocation failed");
+    l->ctx = ctx;
+    l->graph = nullptr;
+    l->exec = nullptr;
+    l->launches = launches;
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    int st = FC_OK;
+    if (e == cudaSuccess) {
+        for (int i = 0; i < count && st == FC_OK; ++i) st = conv_enqueue(convs[i], d_ins[i], d_outs[i], false);
+        e = cudaStreamEndCapture(ctx->stream, &l->graph);  // always end the capture, even after a failed enqueue
+    }
+    if (e == cudaSuccess && st == FC_OK) e = cudaGraphInstantiate(&l->exec, l->graph, 0);
+    if (e != cudaSuccess || st != FC_OK) {
+        if (e != cudaSuccess) set_error("capturing the layer list failed: %s", cudaGetErrorString(e));
+        if (l->graph) cudaGraphDestroy(l->graph);
+        delete l;
+        cudaGetLastError();
+        return e != cudaSuccess ? FC_ERR_CUDA : st;
+    }
+    *out = l;
+    return FC_OK;
+}
+
+int fc_layer_list_forward(fc_layer_list *l) {
+    FC_REQUIRE(l != nullptr, FC_ERR_INVALID_ARG, "list is NULL");
+    FC_CHECK_CUDA(cudaGraphLaunch(l->exec, l->ctx->stream));
+    return FC_OK;
+}
+
+int fc_layer_list_launches(const fc_layer_list *l, int *n) {
+    FC_REQUIRE(l && n, FC_ERR_INVALID_ARG, "NULL argument");
+    *n = l->launches;
+    return FC_OK;
+}
+
+int fc_layer_list_destroy(fc_layer_list *l) {
+    if (!l) return FC_OK;
+    cudaStreamSynchronize(l->ctx->stream);
+    if (l->exec) cudaGraphExecDestroy(l->exec);
+    if (l->graph) cudaGraphDestroy(l->graph);
+    delete l;
     return FC_OK;
 }
 

@@ -82,7 +82,9 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
                          int image);
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                       int oh, int ow);
-int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
                     int oh, int ow, int mode);
+size_t igemm_packed_elems(int oc, int K);
+int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 
 }  // namespace fc

@@ -32,7 +32,7 @@ struct FfmaCfg {
 };
 
 template <int BM, int BN>
-__global__ void __launch_bounds__(THREADS) wino_gemm_ffma_kernel(const float *__restrict__ U,
+__global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float *__restrict__ U,
                                                                  const float *__restrict__ V, float *__restrict__ M,
                                                                  int oc, int tp, int icp) {
     using C = FfmaCfg<BM, BN>;
@@ -144,9 +144,99 @@ __global__ void __launch_bounds__(THREADS) wino_gemm_ffma_kernel(const float *__
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Few tiles (small feature maps at batch 1: 28x28 -> 25 tiles, 14x14 -> 9, 7x7 -> 4).  The GEMM is a
+// stream over U with a short N, so the blocked kernel above would multiply mostly padding.  Here a
+// thread owns ONE output channel and ALL TN tiles of a position: its row of U goes straight from
+// global memory to registers (each element is used by exactly this thread), V_p is staged transposed
+// in shared memory a K-chunk at a time and read as broadcasts, and the TN accumulators take one FMA
+// per input channel in ascending order -- the same chain as the blocked kernel and the reference.
+// ---------------------------------------------------------------------------------------------
+constexpr int SK_THREADS = 128;
+constexpr int SK_KC = 256;  // input channels staged per chunk
+
+template <int TN>
+__global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const float *__restrict__ U,
+                                                                           const float *__restrict__ V,
+                                                                           float *__restrict__ M, int oc, int tp,
+                                                                           int icp) {
+    constexpr int TNP = (TN + 3) / 4 * 4;
+    __shared__ __align__(16) float Vs[SK_KC * TNP];
+    const int tid = threadIdx.x;
+    const int p = blockIdx.y;
+    const int row = blockIdx.x * SK_THREADS + tid;
+    const int row_ld = row < oc ? row : oc - 1;
+    const float *up = U + ((size_t)p * oc + row_ld) * icp;
+    const float *Vp = V + (size_t)p * tp * icp;
+
+    float acc[TN];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
+
+    for (int k0 = 0; k0 < icp; k0 += SK_KC) {
+        const int kc = min(SK_KC, icp - k0);  // multiple of 8
+        __syncthreads();
+        // stage V_p[t][k0..k0+kc) as Vs[k][t]; consecutive threads take consecutive tiles
+        for (int idx = tid; idx < TNP * (kc / 4); idx += SK_THREADS) {
+            const int t = idx % TNP, k4 = idx / TNP;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < tp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)t * icp + k0 + k4 * 4));
+            Vs[(k4 * 4 + 0) * TNP + t] = v.x;
+            Vs[(k4 * 4 + 1) * TNP + t] = v.y;
+            Vs[(k4 * 4 + 2) * TNP + t] = v.z;
+            Vs[(k4 * 4 + 3) * TNP + t] = v.w;
+        }
+        __syncthreads();
+        float4 u_next = __ldg(reinterpret_cast<const float4 *>(up + k0));
+        for (int k = 0; k < kc; k += 4) {
+            const float4 u = u_next;
+            if (k + 4 < kc) u_next = __ldg(reinterpret_cast<const float4 *>(up + k0 + k + 4));
+            const float uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const float4 *b4 = reinterpret_cast<const float4 *>(&Vs[(k + kk) * TNP]);
+#pragma unroll
+                for (int g = 0; g < TNP / 4; ++g) {
+                    const float4 b = b4[g];
+                    if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(uu[kk], b.x, acc[g * 4 + 0]);
+                    if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(uu[kk], b.y, acc[g * 4 + 1]);
+                    if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(uu[kk], b.z, acc[g * 4 + 2]);
+                    if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(uu[kk], b.w, acc[g * 4 + 3]);
+                }
+            }
+        }
+    }
+    if (row < oc) {
+        float *dst = M + ((size_t)p * oc + row) * tp;
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+            if (j < tp) dst[j] = acc[j];
+    }
+}
+
+template <int TN>
+int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    dim3 grid((unsigned)ceil_div(g.oc, SK_THREADS), 64), block(SK_THREADS);
+    wino_gemm_ffma_skinny_kernel<TN><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
 }  // namespace
 
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    if (g.tiles <= 32) {  // every real tile in one thread's registers
+        const int t = g.tiles;
+        if (t <= 4) return launch_skinny<4>(ctx, d_U, d_V, d_M, g);
+        if (t <= 8) return launch_skinny<8>(ctx, d_U, d_V, d_M, g);
+        if (t <= 9) return launch_skinny<9>(ctx, d_U, d_V, d_M, g);
+        if (t <= 12) return launch_skinny<12>(ctx, d_U, d_V, d_M, g);
+        if (t <= 16) return launch_skinny<16>(ctx, d_U, d_V, d_M, g);
+        if (t <= 20) return launch_skinny<20>(ctx, d_U, d_V, d_M, g);
+        if (t <= 25) return launch_skinny<25>(ctx, d_U, d_V, d_M, g);
+        if (t <= 28) return launch_skinny<28>(ctx, d_U, d_V, d_M, g);
+        return launch_skinny<32>(ctx, d_U, d_V, d_M, g);
+    }
     // 64 is the float4-group stride of the thread mapping, so BM and BN are 64 or 128.
     const bool wide_n = g.tp > 64;
     const bool wide_m = g.oc > 64;

@@ -133,43 +133,66 @@ int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, 
 // ---------------------------------------------------------------------------------------------
 // Input transform: V = B^T d B per 8x8 tile at (6*ty - pad, 6*tx - pad), zero outside the image
 // (winoF63ZC/winoF63ZC.cpp:541-612); B^T over the tile rows first, then the columns (:614-630).
-// Block = 32 channels x 8 tiles; a warp walks ic so every one of the 64 position stores is one
-// coalesced 128-byte line of V[p][tile][ic..ic+31].
+//
+// A block owns 8 consecutive tiles x 32 consecutive channels.  Phase 1 stages the 8x8 windows into
+// shared memory with loads that run along the image rows (8 consecutive floats per lane group, four
+// channels per warp instruction) -- zero-filled outside the image, past the last tile and past the
+// last channel, so the padding of V falls out of the arithmetic.  Phase 2 gives every thread one
+// (tile, channel): it reads its window with the channel as the fastest index (conflict-free), runs
+// the two passes in registers and stores the 64 positions, each warp store being one 128-byte line
+// of V[p][tile][c..c+31].
 // ---------------------------------------------------------------------------------------------
 constexpr int IT_TILES = 8;
+constexpr int IT_CH = 32;
+constexpr int IT_LD = IT_CH + 1;  // padded channel stride in shared memory
 
-__global__ void __launch_bounds__(32 * IT_TILES) input_transform_kernel(const float *__restrict__ in,
-                                                                       float *__restrict__ V, int n_tiles, int ic,
-                                                                       int icp, int tp, int ih, int iw, int pad,
-                                                                       int th, int tw) {
-    const int c = blockIdx.x * 32 + threadIdx.x;
-    const int t = blockIdx.y * IT_TILES + threadIdx.y;
-    if (c >= icp || t >= tp) return;
-    const size_t plane = (size_t)tp * icp;
-    float *dst = V + (size_t)t * icp + c;
-    if (c >= ic || t >= n_tiles) {
-#pragma unroll
-        for (int p = 0; p < 64; ++p) dst[p * plane] = 0.0f;
-        return;
-    }
+__global__ void __launch_bounds__(IT_CH * IT_TILES) input_transform_kernel(const float *__restrict__ in,
+                                                                          float *__restrict__ V, int n_tiles, int ic,
+                                                                          int icp, int tp, int ih, int iw, int pad,
+                                                                          int th, int tw) {
+    extern __shared__ float win[];  // [tile][y*8+x][channel (padded)]
+    const int tid = threadIdx.x;
+    const int c0 = blockIdx.x * IT_CH, t0 = blockIdx.y * IT_TILES;
     const int per_img = th * tw;
-    const int img = t / per_img, tt = t - img * per_img;
-    const int row0 = (tt / tw) * 6 - pad, col0 = (tt % tw) * 6 - pad;
-    const float *src = in + ((size_t)img * ic + c) * ih * iw;
-    float d[8][8];
+
+    {   // phase 1: lane group of 8 walks x, 32 groups walk the channels
+        const int x = tid & 7, cl = tid >> 3;
+        const int c = c0 + cl;
+        const bool c_ok = c < ic;
+#pragma unroll 1
+        for (int t = 0; t < IT_TILES; ++t) {
+            const int tile = t0 + t;
+            const bool t_ok = c_ok && tile < n_tiles;
+            const int img = tile / per_img, tt = tile - img * per_img;
+            const int row0 = (tt / tw) * 6 - pad, col = (tt % tw) * 6 - pad + x;
+            const float *src = in + ((size_t)img * ic + c) * ih * iw + col;
+            const bool x_ok = t_ok && col >= 0 && col < iw;
+            float v[8];
 #pragma unroll
-    for (int y = 0; y < 8; ++y) {
-        const int yy = row0 + y;
-        const bool row_ok = yy >= 0 && yy < ih;
+            for (int y = 0; y < 8; ++y) {
+                const int yy = row0 + y;
+                v[y] = (x_ok && yy >= 0 && yy < ih) ? __ldg(src + (size_t)yy * iw) : 0.0f;
+            }
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-            const int xx = col0 + x;
-            d[y][x] = (row_ok && xx >= 0 && xx < iw) ? __ldg(src + (size_t)yy * iw + xx) : 0.0f;
+            for (int y = 0; y < 8; ++y) win[(t * 64 + y * 8 + x) * IT_LD + cl] = v[y];
         }
     }
+    __syncthreads();
+
+    const int lane = tid & 31, t = tid >> 5;
+    const int c = c0 + lane, tile = t0 + t;
+    if (c >= icp || tile >= tp) return;
+    const float *w = win + (size_t)t * 64 * IT_LD + lane;
+    float d[8][8];
+#pragma unroll
+    for (int y = 0; y < 8; ++y)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) d[y][x] = w[(y * 8 + x) * IT_LD];
 #pragma unroll
     for (int x = 0; x < 8; ++x)
         input_transform_1d(d[0][x], d[1][x], d[2][x], d[3][x], d[4][x], d[5][x], d[6][x], d[7][x]);
+    const size_t plane = (size_t)tp * icp;
+    float *dst = V + (size_t)tile * icp + c;
 #pragma unroll
     for (int y = 0; y < 8; ++y) {
         input_transform_1d(d[y][0], d[y][1], d[y][2], d[y][3], d[y][4], d[y][5], d[y][6], d[y][7]);
@@ -179,9 +202,15 @@ __global__ void __launch_bounds__(32 * IT_TILES) input_transform_kernel(const fl
 }
 
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
-    dim3 block(32, IT_TILES), grid((unsigned)ceil_div(g.icp, 32), (unsigned)ceil_div(g.tp, IT_TILES));
-    input_transform_kernel<<<grid, block, 0, ctx->stream>>>(d_in, d_V, g.tiles, g.ic, g.icp, g.tp, g.ih, g.iw, g.pad,
-                                                            g.th, g.tw);
+    static bool attr_set = false;
+    const size_t smem = (size_t)IT_TILES * 64 * IT_LD * sizeof(float);
+    if (!attr_set) {
+        FC_CHECK_CUDA(cudaFuncSetAttribute(input_transform_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    dim3 block(IT_CH * IT_TILES), grid((unsigned)ceil_div(g.icp, IT_CH), (unsigned)ceil_div(g.tp, IT_TILES));
+    input_transform_kernel<<<grid, block, smem, ctx->stream>>>(d_in, d_V, g.tiles, g.ic, g.icp, g.tp, g.ih, g.iw, g.pad,
+                                                               g.th, g.tw);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -189,46 +218,81 @@ int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const
 // ---------------------------------------------------------------------------------------------
 // Output transform: Y = A^T M A, A^T over the tile columns first (for every row), then over the
 // rows (winoF63ZC/winoF63ZC.cpp:905-912), clipped store at the right/bottom edges (:928-969).
-// One thread per (oc, tile); a warp walks the tile axis so the 64 loads from M[p][oc][tile] are
-// coalesced.
+//
+// One thread per (oc, tile).  A warp covers TPW consecutive tiles of 32/TPW output channels (TPW =
+// 32, 16 or 8, chosen from the tile count so that small feature maps do not idle most lanes); the
+// 64 loads per thread from M[p][oc][tile] are contiguous across the lanes of a channel.  The 6x6
+// results go through shared memory so that the stores run along the output rows: tiles that are
+// neighbours in x are neighbours in memory, so a warp writes runs of 6*TPW consecutive floats.
 // ---------------------------------------------------------------------------------------------
-constexpr int OT_OCS = 4;
+constexpr int OT_WARPS = 4;
 
-__global__ void __launch_bounds__(32 * OT_OCS) output_transform_kernel(const float *__restrict__ M,
-                                                                      float *__restrict__ out, int n_tiles, int oc,
-                                                                      int tp, int oh, int ow, int th, int tw) {
-    const int t = blockIdx.x * 32 + threadIdx.x;
-    const int k = blockIdx.y * OT_OCS + threadIdx.y;
-    if (t >= n_tiles || k >= oc) return;
+template <int TPW>
+__global__ void __launch_bounds__(32 * OT_WARPS) output_transform_kernel(const float *__restrict__ M,
+                                                                        float *__restrict__ out, int n_tiles, int oc,
+                                                                        int tp, int oh, int ow, int th, int tw) {
+    constexpr int OCW = 32 / TPW;            // output channels per warp
+    constexpr int ROW = TPW * 6 + 2;         // floats per staged output row (+2: fewer bank conflicts)
+    __shared__ float stage[OT_WARPS][OCW][6][ROW];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tl = lane % TPW, ol = lane / TPW;
+    const int t_base = blockIdx.x * TPW;
+    const int k_base = (blockIdx.y * OT_WARPS + warp) * OCW;
+    const int t = t_base + tl, k = k_base + ol;
     const size_t plane = (size_t)oc * tp;
-    const float *src = M + (size_t)k * tp + t;
-    float h[8][6];
+    const bool active = t < n_tiles && k < oc;
+    if (active) {
+        const float *src = M + (size_t)k * tp + t;
+        float h[8][6];
 #pragma unroll
-    for (int row = 0; row < 8; ++row) {
-        float m[8];
+        for (int row = 0; row < 8; ++row) {
+            float m[8];
 #pragma unroll
-        for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
-        output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
+            for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
+            output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
+        }
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            float s[6];
+            output_transform_1d(h[0][j], h[1][j], h[2][j], h[3][j], h[4][j], h[5][j], h[6][j], h[7][j], s);
+#pragma unroll
+            for (int i = 0; i < 6; ++i) stage[warp][ol][i][tl * 6 + j] = s[i];
+        }
     }
+    __syncwarp();
     const int per_img = th * tw;
-    const int img = t / per_img, tt = t - img * per_img;
-    const int y0 = (tt / tw) * 6, x0 = (tt % tw) * 6;
-    float *dst = out + ((size_t)img * oc + k) * oh * ow + (size_t)y0 * ow + x0;
-#pragma unroll
-    for (int j = 0; j < 6; ++j) {
-        float s[6];
-        output_transform_1d(h[0][j], h[1][j], h[2][j], h[3][j], h[4][j], h[5][j], h[6][j], h[7][j], s);
-        if (x0 + j < ow) {
+    // each lane now writes elements e = lane, lane+32, ... of every staged row: e -> (tile e/6, column e%6)
+#pragma unroll 1
+    for (int o = 0; o < OCW; ++o) {
+        const int kk = k_base + o;
+        if (kk >= oc) break;
+        for (int e = lane; e < TPW * 6; e += 32) {
+            const int te = e / 6, j = e - te * 6;
+            const int tile = t_base + te;
+            if (tile >= n_tiles) continue;
+            const int img = tile / per_img, tt = tile - img * per_img;
+            const int y0 = (tt / tw) * 6, x = (tt % tw) * 6 + j;
+            if (x >= ow) continue;
+            float *dst = out + ((size_t)img * oc + kk) * oh * ow + (size_t)y0 * ow + x;
 #pragma unroll
             for (int i = 0; i < 6; ++i)
-                if (y0 + i < oh) dst[(size_t)i * ow + j] = s[i];
+                if (y0 + i < oh) dst[(size_t)i * ow] = stage[warp][o][i][e];
         }
     }
 }
 
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g) {
-    dim3 block(32, OT_OCS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OT_OCS));
-    output_transform_kernel<<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+    dim3 block(32 * OT_WARPS);
+    if (g.tiles > 16) {
+        dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OT_WARPS));
+        output_transform_kernel<32><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+    } else if (g.tiles > 8) {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, OT_WARPS * 2));
+        output_transform_kernel<16><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+    } else {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, OT_WARPS * 4));
+        output_transform_kernel<8><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+    }
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }

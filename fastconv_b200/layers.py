@@ -360,6 +360,32 @@ class ConvIm2colLayer(ConvLayer):
             ctx.free(d_in)
 
 
+class LayerList:
+    """Several initialised layers replayed as one CUDA graph (fc_layer_list): the in-process form of the
+    reference's per-network shell loops (run_vgg16.sh:5-13, run_resnet50.sh:10-30)."""
+
+    def __init__(self, ctx: Context, convs, d_ins, d_outs):
+        self._lib = _lib.load()
+        n = len(convs)
+        arr = C.c_void_p * n
+        h = C.c_void_p()
+        check(self._lib.fc_layer_list_create(ctx.handle, arr(*[c.value if isinstance(c, C.c_void_p) else c for c in convs]),
+                                             arr(*[int(p) for p in d_ins]), arr(*[int(p) for p in d_outs]), n,
+                                             C.byref(h)), "fc_layer_list_create")
+        self._h = h
+        k = C.c_int()
+        check(self._lib.fc_layer_list_launches(h, C.byref(k)), "fc_layer_list_launches")
+        self.kernel_launches = k.value
+
+    def forward(self) -> None:
+        check(self._lib.fc_layer_list_forward(self._h), "fc_layer_list_forward")
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.fc_layer_list_destroy(self._h)
+            self._h = None
+
+
 def make_layer(algorithm: str, *args, **kw) -> ConvLayer:
     """The dispatch of ConvTest.cpp:365-413 (`-a auto|direct|im2col|winograd`)."""
     algo = _lib.ALGO_NAMES[algorithm]

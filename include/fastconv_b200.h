@@ -162,8 +162,14 @@ int fc_wino_forward_static_scratch(const float *d_in, const float *d_U, float *d
 /* ConvIm2colLayer::im2col(), convLayer/im2colConv.cpp:285-309: materialises the gathered matrix
  * [ic*kh*kw][oh*ow] of image `image` for inspection; the forward path never builds it. */
 int fc_im2col_gather(fc_context *ctx, const float *d_in, float *d_gathered, const fc_conv_desc *desc, int image);
+/* pack_a_v2, im2col/gemm_pack.cpp:192-238: one-time re-layout of the weight matrix A[oc][K] for the
+ * tensor-core kernel -- rows padded to a multiple of 32 floats, stored as two planes hi = tf32(a) and
+ * lo = a - hi.  fc_igemm_packed_elems gives the float count of the packed buffer. */
+int fc_igemm_packed_elems(int oc, int K, size_t *elems);
+int fc_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 /* ConvIm2colLayer::im2col_v1() + sgemm(), convLayer/im2colConv.cpp:311-398: gather fused into the
- * GEMM's operand producer.  d_kernel is the raw [oc][ic*kh*kw] matrix (A, lda = K). */
+ * GEMM's operand producer.  In FC_MATH_FP32_MIRRORED mode d_kernel is the raw [oc][ic*kh*kw] matrix
+ * (A, lda = K); in the tensor-core modes it is the buffer written by fc_igemm_pack_weights. */
 int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out,
                      const fc_conv_desc *desc, int mode);
 
@@ -194,6 +200,19 @@ int fc_conv_profile(fc_conv *conv, const float *d_in, float *d_out, int iters, f
 int fc_conv_tune(fc_conv *conv, int iters, int verbose);
 /* number of kernel launches one forward issues (for launch accounting) */
 int fc_conv_launches_per_forward(const fc_conv *conv, int *launches);
+
+/* ---- layer list -------------------------------------------------------------
+ * The reference benchmarks a network as a shell loop over its layers (run_vgg16.sh:5-13,
+ * run_resnet50.sh:10-30: one process per layer).  A layer list plays the same list in one
+ * process: the forwards of `count` planned layers, each on its own device input/output, captured
+ * once into a CUDA graph so that one call replays all of their kernels without per-kernel launch
+ * cost.  The layers must belong to `ctx` and outlive the list. */
+typedef struct fc_layer_list fc_layer_list;
+int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *const *d_ins, float *const *d_outs,
+                         int count, fc_layer_list **out);
+int fc_layer_list_forward(fc_layer_list *list);
+int fc_layer_list_launches(const fc_layer_list *list, int *kernel_launches);
+int fc_layer_list_destroy(fc_layer_list *list);
 
 /* ---- error metrics on the host ---------------------------------------------- */
 /* diff(), utility/helper.cpp:74-89: mean |a-b| over the elements with |a-b| > 1e-5 */

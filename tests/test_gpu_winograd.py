@@ -198,3 +198,36 @@ def test_single_pass_tf32_meets_3e_3(ctx, oracle):
 
 def test_tensor_core_kernel_reports_no_timeouts(ctx):
     ctx.synchronize()  # raises FastConvError(FC_ERR_TIMEOUT) if any bounded wait gave up in the tests above
+
+
+def test_layer_list_graph_replays_every_layer(ctx, oracle):
+    """Three layers captured into one CUDA graph give, on replay, the bits of running them one by one."""
+    import ctypes as C
+    lib = fc.load()
+    specs = [(1, 16, 24, 20, 20), (2, 8, 8, 9, 13), (1, 40, 72, 14, 14)]
+    convs, ins, outs, wants = [], [], [], []
+    for i, (n, ic, oc, ih, iw) in enumerate(specs):
+        x = synth.conv_input(n, ic, ih, iw, 300 + i)
+        w = synth.conv_weights(oc, ic, 3, 3, 400 + i)
+        d = fc.make_desc(n, ic, ih, iw, oc)
+        h = C.c_void_p()
+        fc._lib.check(lib.fc_conv_create(ctx.handle, C.byref(d), fc.ALGO_WINOGRAD, 0, C.c_void_p(w.ctypes.data),
+                                         C.byref(h)), "create")
+        convs.append(h)
+        ins.append(ctx.upload(x))
+        outs.append(ctx.zeros(4 * n * oc * ih * iw))
+        wants.append(oracle.wino_forward(x, w, 1))
+    stack = fc.LayerList(ctx, convs, ins, outs)
+    assert stack.kernel_launches == 9
+    for o, want in zip(outs, wants):  # clear what the eager pass inside create() wrote
+        fc._lib.check(lib.fc_memset_device(ctx.handle, C.c_void_p(o), 0, want.nbytes), "memset")
+    stack.forward()
+    stack.forward()
+    ctx.synchronize()
+    for o, want in zip(outs, wants):
+        assert np.array_equal(ctx.download(o, want.shape), want)
+    stack.close()
+    for h in convs:
+        lib.fc_conv_destroy(h)
+    for p in ins + outs:
+        ctx.free(p)
