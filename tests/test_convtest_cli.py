@@ -1,0 +1,82 @@
+"""The ConvTest command-line harness (fastconv_b200/host/ConvTest.cpp): same flags, header and labels as the
+reference's winograd_dev."""
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+HOST = Path(__file__).resolve().parents[1] / "fastconv_b200" / "host"
+BIN = HOST / "winograd_dev"
+
+
+@pytest.fixture(scope="module")
+def binary():
+    import fastconv_b200
+    fastconv_b200.load()  # builds the library if needed
+    subprocess.run(["make", "-C", str(HOST)], check=True, capture_output=True)
+    assert BIN.exists()
+    return str(BIN)
+
+
+def run(binary, *args):
+    return subprocess.run([binary, *args], capture_output=True, text=True, timeout=600)
+
+
+def test_help_lists_the_reference_flags(binary):
+    r = run(binary, "-h")
+    assert r.returncode == 0
+    for flag in ("-ic", "-oc", "-is", "-ks", "-a ", "-ts", "-s ", "-ip", "-tn", "-t ", "-i "):
+        assert flag in r.stdout
+    assert "auto, direct, im2col, or winograd" in r.stdout
+
+
+@pytest.mark.parametrize("args, message", [
+    (["-oc", "4", "-is", "8", "8", "-ks", "3", "3"], "the number of input channels is not specified"),
+    (["-ic", "4", "-is", "8", "8", "-ks", "3", "3"], "the number of output channels is not specified"),
+    (["-ic", "4", "-oc", "4", "-ks", "3", "3"], "the input size is not specified"),
+    (["-ic", "4", "-oc", "4", "-is", "8", "8"], "the kernel size is not specified"),
+    (["-ic", "0", "-oc", "4", "-is", "8", "8", "-ks", "3", "3"], "positive value expected"),
+    (["-ic", "x", "-oc", "4", "-is", "8", "8", "-ks", "3", "3"], "can not parse x as an unsigned integer"),
+    (["-ic", "4", "-oc", "4", "-is", "8", "8", "-ks", "3", "3", "-a", "fft"], "invalid convolution algorithm name fft"),
+    (["-ic", "4", "-oc", "4", "-is", "8", "8", "-ks", "3", "3", "-tn", "maybe"], "invalid tuning name maybe"),
+    (["-ic", "4", "-oc", "4", "-is", "8", "8", "-ks", "3", "3", "--frobnicate", "1"], "unknown argument"),
+    (["-ic", "4", "-oc", "4", "-is", "8"], "expected two values"),
+])
+def test_argument_errors_exit_nonzero(binary, args, message):
+    r = run(binary, *args)
+    assert r.returncode != 0
+    assert message in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("args, algo, labels", [
+    (["-ic", "16", "-oc", "16", "-is", "12", "12", "-ks", "3", "3"], "winograd F63",
+     ["InputTran time:", "KernelTran time:", "TensorGEMM time:", "OutputTran time:", "Total time:"]),
+    (["-ic", "16", "-oc", "24", "-is", "14", "14", "-ks", "1", "1", "-ip", "0"], "im2col",  # `direct` in the reference: ran nothing
+     ["Im2colTran time:", "Gemm time:", "Total time:"]),
+    (["-ic", "3", "-oc", "8", "-is", "30", "30", "-ks", "7", "7", "-s", "2", "2", "-ip", "3", "-a", "im2col"], "im2col",
+     ["Gemm time:"]),
+    (["-ic", "8", "-oc", "8", "-is", "20", "20", "-ks", "3", "3", "-a", "winograd", "-n", "3", "-m", "3xtf32", "-tn", "tuning"],
+     "winograd F63", ["TensorGEMM time:"]),
+])
+def test_runs_and_prints_reference_lines(binary, args, algo, labels):
+    r = run(binary, *args, "-i", "3", "-seed", "7")
+    assert r.returncode == 0, r.stderr
+    out = r.stdout
+    assert re.search(r"Input channels: \d+\nOutput channels: \d+\nInput: \d+x\d+ with implicit padding \d+\nKernel: \d+x\d+\n"
+                     r"Subsampling: \d+x\d+\n", out)
+    assert f"Algorithm: {algo}" in out
+    for label in labels:
+        assert label in out
+    m = re.search(r"The difference is ([0-9.]+)", out)
+    assert m, out
+    # inputs are in [0,256) and kernels in [0,1) as in the reference, so outputs are ~1e4 and an fp32
+    # difference of a few 1e-3 in absolute terms is rounding, not error
+    assert float(m.group(1)) < 0.05
+
+
+@pytest.mark.gpu
+def test_winograd_refuses_shapes_the_reference_computes_wrongly(binary):
+    r = run(binary, "-ic", "8", "-oc", "8", "-is", "16", "16", "-ks", "3", "3", "-s", "2", "2", "-a", "winograd")
+    assert r.returncode != 0 and "stride 1" in r.stderr
