@@ -18,6 +18,16 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
+// FASTCONV_PDL=0 in the environment turns programmatic dependent launch off (plain stream order).
+bool pdl_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_PDL");
+        state = (e && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
 static int check_desc(const fc_conv_desc *d) {
     FC_REQUIRE(d != nullptr, FC_ERR_INVALID_ARG, "descriptor is NULL");
     FC_REQUIRE(d->batch > 0 && d->ic > 0 && d->oc > 0 && d->ih > 0 && d->iw > 0 && d->kh > 0 && d->kw > 0,
@@ -72,6 +82,9 @@ struct fc_conv {
     float *d_in, *d_out;  // staging for forward_host
     float kernel_tran_ms;
     float stage_ms[5];
+    KernelCfg cfg;        // all zero = launcher heuristics; set by fc_conv_tune
+    bool auto_requested;  // created with FC_ALGO_AUTO: Tuning may switch between Winograd and im2col
+    bool wino_eligible;   // 3x3, stride 1, symmetric padding
 };
 
 extern "C" {
@@ -378,11 +391,11 @@ int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, cons
 }
 
 static int wino_gemm_dispatch(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
-                              int mode) {
+                              int mode, const KernelCfg *cfg = nullptr) {
     switch (mode) {
-        case FC_MATH_FP32_MIRRORED: return launch_wino_gemm_ffma(ctx, d_U, d_V, d_M, g);
+        case FC_MATH_FP32_MIRRORED: return launch_wino_gemm_ffma(ctx, d_U, d_V, d_M, g, cfg);
         case FC_MATH_3XTF32:
-        case FC_MATH_TF32: return launch_wino_gemm_tc(ctx, d_U, d_V, d_M, g, mode);
+        case FC_MATH_TF32: return launch_wino_gemm_tc(ctx, d_U, d_V, d_M, g, mode, cfg);
         default: set_error("unknown math mode %d", mode); return FC_ERR_INVALID_ARG;
     }
 }
@@ -478,6 +491,59 @@ static void conv_release(fc_conv *c) {
     delete c;
 }
 
+static int grab(fc_context *ctx, float **p, size_t elems) {
+    if (*p) return FC_OK;
+    void *q = nullptr;
+    int st = fc_arena_alloc(ctx, elems * sizeof(float), &q);
+    *p = (float *)q;
+    return st;
+}
+
+static void drop(fc_context *ctx, float **p) {
+    if (*p) ctx->arena.release((uintptr_t)*p);
+    *p = nullptr;
+}
+
+// Workspaces and one-time weight re-layout of one algorithm (idempotent): Winograd gets U/V/M and the
+// filter transform, the tensor-core implicit GEMM gets the packed hi/lo weight planes.
+static int conv_prepare(fc_conv *c, int algo) {
+    fc_context *ctx = c->ctx;
+    const fc_conv_desc &d = c->desc;
+    int st = FC_OK;
+    bool timed = false;
+    if (algo == FC_ALGO_WINOGRAD) {
+        const WinoGeom &g = c->geom;
+        const bool fresh = c->d_U == nullptr;
+        st = grab(ctx, &c->d_U, (size_t)64 * g.oc * g.icp);
+        if (st == FC_OK) st = grab(ctx, &c->d_V, (size_t)64 * g.tp * g.icp);
+        if (st == FC_OK) st = grab(ctx, &c->d_M, (size_t)64 * g.oc * g.tp);
+        if (st == FC_OK && fresh) {
+            cudaEventRecord(ctx->ev[0], ctx->stream);
+            st = launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic, g.icp);
+            cudaEventRecord(ctx->ev[1], ctx->stream);
+            timed = true;
+        }
+    } else if (c->mode != FC_MATH_FP32_MIRRORED) {
+        const bool fresh = c->d_packed == nullptr;
+        const int K = d.ic * d.kh * d.kw;
+        st = grab(ctx, &c->d_packed, igemm_packed_elems(d.oc, K));
+        if (st == FC_OK && fresh) {
+            cudaEventRecord(ctx->ev[0], ctx->stream);
+            st = launch_igemm_pack_weights(ctx, c->d_kernel, c->d_packed, d.oc, K);
+            cudaEventRecord(ctx->ev[1], ctx->stream);
+            timed = true;
+        }
+    }
+    if (st != FC_OK) return st;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        set_error("weight re-layout failed: %s", cudaGetErrorString(e));
+        return FC_ERR_CUDA;
+    }
+    if (timed) cudaEventElapsedTime(&c->kernel_tran_ms, ctx->ev[0], ctx->ev[1]);
+    return FC_OK;
+}
+
 int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode, const float *h_kernel,
                    fc_conv **out) {
     FC_REQUIRE(ctx && desc && h_kernel && out, FC_ERR_INVALID_ARG, "NULL argument");
@@ -487,59 +553,43 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     FC_REQUIRE(algo >= FC_ALGO_AUTO && algo <= FC_ALGO_WINOGRAD, FC_ERR_INVALID_ARG, "unknown algorithm %d", algo);
     int oh, ow;
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
+    const bool auto_requested = algo == FC_ALGO_AUTO;
     if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
     if (algo == FC_ALGO_DIRECT) algo = FC_ALGO_IM2COL;
+    int auto_pick = FC_ALGO_IM2COL;
+    fc_select_algorithm(desc, &auto_pick);
+    const bool wino_eligible = auto_pick == FC_ALGO_WINOGRAD;
     WinoGeom g;
     memset(&g, 0, sizeof g);
-    if (algo == FC_ALGO_WINOGRAD) FC_PROPAGATE(wino_geom(desc, &g));
+    if (algo == FC_ALGO_WINOGRAD || wino_eligible) FC_PROPAGATE(wino_geom(desc, &g));
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
 
     fc_conv *c = new (std::nothrow) fc_conv();
     FC_REQUIRE(c != nullptr, FC_ERR_OUT_OF_MEMORY, "host allocation failed");
     memset(c, 0, sizeof *c);
     c->ctx = ctx; c->desc = *desc; c->algo = algo; c->mode = mode; c->oh = oh; c->ow = ow; c->geom = g;
+    c->auto_requested = auto_requested;
+    c->wino_eligible = wino_eligible;
 
     const size_t k_elems = (size_t)desc->oc * desc->ic * desc->kh * desc->kw;
     const size_t in_elems = (size_t)desc->batch * desc->ic * desc->ih * desc->iw;
     const size_t out_elems = (size_t)desc->batch * desc->oc * oh * ow;
-    auto grab = [&](float **p, size_t elems) -> int {
-        void *q = nullptr;
-        int st = fc_arena_alloc(ctx, elems * sizeof(float), &q);
-        *p = (float *)q;
-        return st;
-    };
-    int st = grab(&c->d_kernel, k_elems);
-    if (st == FC_OK) st = grab(&c->d_in, in_elems);
-    if (st == FC_OK) st = grab(&c->d_out, out_elems);
-    if (st == FC_OK && algo == FC_ALGO_WINOGRAD) {
-        st = grab(&c->d_U, (size_t)64 * g.oc * g.icp);
-        if (st == FC_OK) st = grab(&c->d_V, (size_t)64 * g.tp * g.icp);
-        if (st == FC_OK) st = grab(&c->d_M, (size_t)64 * g.oc * g.tp);
+    int st = grab(ctx, &c->d_kernel, k_elems);
+    if (st == FC_OK) st = grab(ctx, &c->d_in, in_elems);
+    if (st == FC_OK) st = grab(ctx, &c->d_out, out_elems);
+    if (st == FC_OK) {
+        cudaError_t e = cudaMemcpyAsync(c->d_kernel, h_kernel, k_elems * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) {
+            set_error("kernel upload failed: %s", cudaGetErrorString(e));
+            st = FC_ERR_CUDA;
+        }
     }
-    const bool packed = algo == FC_ALGO_IM2COL && mode != FC_MATH_FP32_MIRRORED;
-    if (st == FC_OK && packed) st = grab(&c->d_packed, igemm_packed_elems(desc->oc, desc->ic * desc->kh * desc->kw));
+    if (st == FC_OK) st = conv_prepare(c, algo);
     if (st != FC_OK) {
+        cudaStreamSynchronize(ctx->stream);
         conv_release(c);
         return st;
     }
-    cudaError_t e = cudaMemcpyAsync(c->d_kernel, h_kernel, k_elems * sizeof(float), cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess && algo == FC_ALGO_WINOGRAD) {
-        cudaEventRecord(ctx->ev[0], ctx->stream);
-        st = launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic, g.icp);
-        cudaEventRecord(ctx->ev[1], ctx->stream);
-    }
-    if (e == cudaSuccess && packed) {
-        cudaEventRecord(ctx->ev[0], ctx->stream);
-        st = launch_igemm_pack_weights(ctx, c->d_kernel, c->d_packed, desc->oc, desc->ic * desc->kh * desc->kw);
-        cudaEventRecord(ctx->ev[1], ctx->stream);
-    }
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess || st != FC_OK) {
-        if (e != cudaSuccess) set_error("kernel upload / filter transform failed: %s", cudaGetErrorString(e));
-        conv_release(c);
-        return e != cudaSuccess ? FC_ERR_CUDA : st;
-    }
-    if (algo == FC_ALGO_WINOGRAD || packed) cudaEventElapsedTime(&c->kernel_tran_ms, ctx->ev[0], ctx->ev[1]);
     *out = c;
     return FC_OK;
 }
@@ -564,7 +614,7 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
         FC_PROPAGATE(launch_input_transform(ctx, d_in, c->d_V, c->geom));
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
-        FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, c->geom, c->mode));
+        FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, c->geom, c->mode, &c->cfg));
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
         FC_PROPAGATE(launch_output_transform(ctx, c->d_M, d_out, c->geom));
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
@@ -574,9 +624,9 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
     int st;
     if (c->mode == FC_MATH_FP32_MIRRORED)
-        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow);
+        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg);
     else
-        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode);
+        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg);
     FC_PROPAGATE(st);
     if (timed) {
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
@@ -655,10 +705,164 @@ int fc_conv_profile(fc_conv *c, const float *d_in, float *d_out, int iters, floa
     return FC_OK;
 }
 
+// ---- Tuning() -------------------------------------------------------------------------------
+// The reference tunes by exhaustive timing: every (ocBlock, tileBlock, icBlock, loop order) point runs
+// `iterations` forwards and the fastest is kept (convLayer/winoF63ConvZC.cpp:25-174); the im2col layer
+// keeps its best (mc, nc, kc, ...) in an append-only text log keyed by the GEMM shape
+// (convLayer/im2colConv.cpp:66-92, 202-222, 261-283).  Same scheme here over the GPU kernels'
+// configurations, timed with CUDA events; with FC_ALGO_AUTO on a Winograd-eligible layer the
+// Winograd-vs-im2col choice itself is made from the measured times.  The log lives at
+// $FASTCONV_TUNING_LOG or ./gemm_log/b200_tuning_log.
+
+struct TuneCandidate {
+    int algo;
+    KernelCfg cfg;
+};
+
+static int time_current(fc_conv *c, int iters, float *ms) {
+    fc_context *ctx = c->ctx;
+    for (int i = 0; i < 2; ++i) FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
+    FC_CHECK_CUDA(cudaEventRecord(ctx->ev[4], ctx->stream));
+    for (int i = 0; i < iters; ++i) FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
+    FC_CHECK_CUDA(cudaEventRecord(ctx->ev[5], ctx->stream));
+    FC_PROPAGATE(sync_and_check_status(ctx));
+    FC_CHECK_CUDA(cudaEventElapsedTime(ms, ctx->ev[4], ctx->ev[5]));
+    *ms /= iters;
+    return FC_OK;
+}
+
+static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCandidate> *out) {
+    auto push = [&](int bm, int bn, int skinny, int smem_kb) {
+        TuneCandidate t;
+        t.algo = algo;
+        t.cfg.bm = bm; t.cfg.bn = bn; t.cfg.skinny = skinny; t.cfg.smem_kb = smem_kb;
+        out->push_back(t);
+    };
+    const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
+    if (c->mode == FC_MATH_FP32_MIRRORED) {
+        if (algo == FC_ALGO_WINOGRAD && c->geom.tiles <= 32) push(0, 0, 1, 0);
+        for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
+    } else {
+        const int widths[5] = {32, 64, 96, 128, 256};
+        const int budgets[3] = {72, 104, 200};
+        for (int w : widths)
+            for (int b : budgets) push(0, w, 0, b);
+    }
+}
+
+static const char *tuning_log_path() {
+    const char *e = getenv("FASTCONV_TUNING_LOG");
+    return e && e[0] ? e : "./gemm_log/b200_tuning_log";
+}
+
+// one log line: 17 key integers, then algo, bm, bn, skinny, smem_kb and the time in microseconds
+static void tuning_key(const fc_conv *c, int key[17]) {
+    const fc_conv_desc &d = c->desc;
+    const int k[17] = {c->ctx->sm_count, c->auto_requested ? FC_ALGO_AUTO : c->algo, c->mode, d.batch, d.ic, d.ih, d.iw,
+                       d.oc, d.kh, d.kw, d.sh, d.sw, d.pad_left, d.pad_right, d.pad_top, d.pad_bottom, d.group};
+    memcpy(key, k, sizeof k);
+}
+
+static bool tuning_log_lookup(const fc_conv *c, TuneCandidate *hit, float *us) {
+    FILE *f = fopen(tuning_log_path(), "r");
+    if (!f) return false;
+    int key[17], row[17], v[5];
+    tuning_key(c, key);
+    bool found = false;
+    char line[512];
+    while (fgets(line, sizeof line, f)) {
+        int n = 0, off = 0, pos = 0;
+        bool ok = true;
+        for (int i = 0; i < 17 && ok; ++i) ok = sscanf(line + pos, "%d,%n", &row[i], &off) == 1 && (pos += off, true);
+        for (int i = 0; i < 5 && ok; ++i) ok = sscanf(line + pos, "%d,%n", &v[i], &off) == 1 && (pos += off, true);
+        float t = 0;
+        if (!ok || sscanf(line + pos, "%f%n", &t, &n) != 1) continue;
+        if (memcmp(row, key, sizeof key) != 0) continue;
+        hit->algo = v[0];
+        hit->cfg.bm = v[1]; hit->cfg.bn = v[2]; hit->cfg.skinny = v[3]; hit->cfg.smem_kb = v[4];
+        *us = t;
+        found = true;  // keep scanning: the last matching line wins
+    }
+    fclose(f);
+    return found;
+}
+
+static void tuning_log_append(const fc_conv *c, const TuneCandidate &best, float us) {
+    const char *path = tuning_log_path();
+    if (strcmp(path, "./gemm_log/b200_tuning_log") == 0) {
+        if (system("mkdir -p ./gemm_log") != 0) return;
+    }
+    FILE *f = fopen(path, "a");
+    if (!f) return;
+    int key[17];
+    tuning_key(c, key);
+    for (int i = 0; i < 17; ++i) fprintf(f, "%d,", key[i]);
+    fprintf(f, "%d,%d,%d,%d,%d,%.3f\n", best.algo, best.cfg.bm, best.cfg.bn, best.cfg.skinny, best.cfg.smem_kb, us);
+    fclose(f);
+}
+
 int fc_conv_tune(fc_conv *c, int iters, int verbose) {
     FC_REQUIRE(c != nullptr, FC_ERR_INVALID_ARG, "NULL argument");
-    (void)iters;
-    (void)verbose;
+    FC_REQUIRE(iters > 0, FC_ERR_INVALID_ARG, "iters must be positive");
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+
+    TuneCandidate cached;
+    float cached_us = 0;
+    if (tuning_log_lookup(c, &cached, &cached_us)) {
+        if (verbose) printf("log entry exists.\n");
+        if (cached.algo != c->algo) FC_PROPAGATE(conv_prepare(c, cached.algo));
+        c->algo = cached.algo;
+        c->cfg = cached.cfg;
+        return FC_OK;
+    }
+    if (verbose) printf("log entry doesn't exist.\n");
+
+    std::vector<TuneCandidate> cands;
+    enumerate_candidates(c, c->algo, &cands);
+    if (c->auto_requested && c->wino_eligible) {
+        const int other = c->algo == FC_ALGO_WINOGRAD ? FC_ALGO_IM2COL : FC_ALGO_WINOGRAD;
+        if (conv_prepare(c, other) == FC_OK) enumerate_candidates(c, other, &cands);
+    }
+    const int start_algo = c->algo;
+    const KernelCfg start_cfg = c->cfg;
+    TuneCandidate best;
+    best.algo = start_algo;
+    best.cfg = start_cfg;
+    float best_ms = 1e30f;
+    FC_CHECK_CUDA(cudaMemsetAsync(c->d_in, 0, (size_t)c->desc.batch * c->desc.ic * c->desc.ih * c->desc.iw * sizeof(float),
+                                  ctx->stream));
+    for (const TuneCandidate &t : cands) {
+        c->algo = t.algo;
+        c->cfg = t.cfg;
+        float ms = 0;
+        const int st = time_current(c, iters, &ms);
+        if (st == FC_ERR_UNSUPPORTED || st == FC_ERR_INVALID_ARG) continue;  // configuration does not fit this shape
+        if (st != FC_OK) {
+            c->algo = start_algo;
+            c->cfg = start_cfg;
+            return st;
+        }
+        if (verbose)
+            printf("algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", t.algo == FC_ALGO_WINOGRAD ? "winograd" : "im2col",
+                   t.cfg.bm, t.cfg.bn, t.cfg.skinny, t.cfg.smem_kb, ms);
+        if (ms < best_ms) {
+            best_ms = ms;
+            best = t;
+        }
+    }
+    c->algo = best.algo;
+    c->cfg = best.cfg;
+    if (best.algo != FC_ALGO_WINOGRAD) {  // the loser's workspaces go back to the arena
+        drop(ctx, &c->d_U); drop(ctx, &c->d_V); drop(ctx, &c->d_M);
+    } else {
+        drop(ctx, &c->d_packed);
+    }
+    if (verbose)
+        printf("Best Config: (%d %d %d) algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", c->desc.ic, c->desc.oc,
+               c->desc.iw, best.algo == FC_ALGO_WINOGRAD ? "winograd" : "im2col", best.cfg.bm, best.cfg.bn,
+               best.cfg.skinny, best.cfg.smem_kb, best_ms);
+    if (best_ms < 1e29f) tuning_log_append(c, best, best_ms * 1e3f);
     return FC_OK;
 }
 

@@ -75,11 +75,21 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < P.num_kb; ++kb) {
+            // U is constant: fill the ring's U halves before waiting for the input transform, then add V
+            const int pre = P.num_kb < S ? P.num_kb : S;
+            for (int kb = 0; kb < pre; ++kb) {
+                mbar_expect_tx(bar_full(kb), part_bytes);
+                tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), kb * BK, oc0, p);
+            }
+            pdl_wait();
+            for (int kb = 0; kb < pre; ++kb)
+                tma_load_3d(ring + kb * stage_bytes + A_BYTES, &tmV, bar_full(kb), kb * BK, t0, p);
+            for (int kb = pre; kb < P.num_kb; ++kb) {
                 const int s = kb % S;
                 const uint32_t ph = (uint32_t)(kb / S) & 1u;
                 if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status)) break;
@@ -143,6 +153,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                 mbar_arrive(bar_split(s));
             }
         }
+        pdl_wait();  // M may still be read by the output transform of the forward before this one
         if (mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
             tc_fence_after();
             const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -175,10 +186,12 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
 
 }  // namespace
 
-int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode) {
+int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode,
+                        const KernelCfg *cfg) {
     const bool split = mode == FC_MATH_3XTF32;
-    // tile blocks of at most 128 tiles, balanced, multiple of 16 (UMMA N granularity at M=128)
-    const int n_blk = (g.tp + 127) / 128;
+    // tile blocks of at most 128 tiles (or the tuned width), balanced, multiple of 16 (UMMA N granularity at M=128)
+    const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
+    const int n_blk = (g.tp + max_bn - 1) / max_bn;
     const int bn = round_up((g.tp + n_blk - 1) / n_blk, 16);
     TcParams P;
     P.M = d_M;
@@ -189,12 +202,18 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.num_kb = (g.icp + BK - 1) / BK;
     P.tmem_cols = pow2_at_least(bn, 32);
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
-    int stages = (int)((200 * 1024) / stage_bytes);
+    // More CTAs than SMs: size the ring so that two CTAs share an SM (the second one's loads and
+    // prologue then overlap the first one's epilogue); otherwise one CTA takes the whole SM.
+    const size_t n_ctas = (size_t)n_blk * ceil_div(g.oc, BM) * 64;
+    const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024
+                                              : (n_ctas > (size_t)ctx->sm_count ? 104 * 1024 : 200 * 1024);
+    int stages = (int)(budget / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages > P.num_kb) stages = P.num_kb < 2 ? 2 : P.num_kb;
-    FC_REQUIRE(stages >= 2, FC_ERR_UNSUPPORTED, "tile block of %d does not fit the shared-memory ring", bn);
+    if (stages > P.num_kb) stages = P.num_kb;
+    if (stages < 2) stages = 2;
     P.stages = stages;
     const size_t smem = 512 + 1024 + stages * stage_bytes;
+    FC_REQUIRE(smem <= 227 * 1024, FC_ERR_UNSUPPORTED, "tile block of %d does not fit the shared-memory ring", bn);
 
     CUtensorMap tmU, tmV;
     FC_PROPAGATE(make_map_3d(&tmU, d_U, g.icp, g.oc, 64, BM));
@@ -203,10 +222,10 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     dim3 grid((unsigned)n_blk, (unsigned)ceil_div(g.oc, BM), 64), block(TC_THREADS);
     if (split) {
         FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        wino_gemm_tc_kernel<true><<<grid, block, smem, ctx->stream>>>(tmU, tmV, P);
+        FC_CHECK_CUDA(launch_pdl(wino_gemm_tc_kernel<true>, grid, block, smem, ctx->stream, tmU, tmV, P));
     } else {
         FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        wino_gemm_tc_kernel<false><<<grid, block, smem, ctx->stream>>>(tmU, tmV, P);
+        FC_CHECK_CUDA(launch_pdl(wino_gemm_tc_kernel<false>, grid, block, smem, ctx->stream, tmU, tmV, P));
     }
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;

@@ -175,13 +175,14 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
 }
 
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow) {
+                      int oh, int ow, const KernelCfg *cfg) {
     IgemmParams P;
     P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
     P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
     P.K = d.ic * d.kh * d.kw;
     P.npix = d.batch * oh * ow;
-    const bool wide_m = d.oc > 64, wide_n = P.npix > 64;
+    const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
+    const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;
     dim3 grid((unsigned)ceil_div(P.npix, wide_n ? 128 : 64), (unsigned)ceil_div(d.oc, wide_m ? 128 : 64)), block(THREADS);
     if (wide_m && wide_n)
         igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);

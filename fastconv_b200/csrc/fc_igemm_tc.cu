@@ -228,12 +228,13 @@ int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_p
 }
 
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode) {
+                    int oh, int ow, int mode, const KernelCfg *cfg) {
     using namespace tc;
     const bool split = mode == FC_MATH_3XTF32;
     const int K = d.ic * d.kh * d.kw, Kp = round_up(K, BK);
     const int ohw = oh * ow;
-    const int n_blk = (ohw + 127) / 128;
+    const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
+    const int n_blk = (ohw + max_bn - 1) / max_bn;
     const int bn = round_up((ohw + n_blk - 1) / n_blk, 16);
     IgemmTcParams P;
     P.in = d_in; P.out = d_out; P.status = ctx->d_status;
@@ -241,11 +242,16 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
     P.K = K; P.num_kb = Kp / BK; P.bn = bn; P.tmem_cols = pow2_at_least(bn, 32);
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
-    int stages = (int)((200 * 1024) / stage_bytes);
+    const size_t n_ctas = (size_t)n_blk * ceil_div(d.oc, BM) * d.batch;
+    const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024
+                                              : (n_ctas > (size_t)ctx->sm_count ? 104 * 1024 : 200 * 1024);
+    int stages = (int)(budget / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages > P.num_kb) stages = P.num_kb < 2 ? 2 : P.num_kb;
+    if (stages > P.num_kb) stages = P.num_kb;
+    if (stages < 2) stages = 2;
     P.stages = stages;
     const size_t smem = 512 + 1024 + stages * stage_bytes;
+    FC_REQUIRE(smem <= 227 * 1024, FC_ERR_UNSUPPORTED, "pixel block of %d does not fit the shared-memory ring", bn);
 
     CUtensorMap tmA;  // [2 planes][oc][Kp]
     FC_PROPAGATE(make_map_3d(&tmA, d_packed, Kp, d.oc, 2, BM));

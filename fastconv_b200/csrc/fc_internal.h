@@ -50,6 +50,14 @@ struct WinoGeom {
 
 int wino_geom(const fc_conv_desc *d, WinoGeom *g);  // validates and fills
 
+// Kernel configuration of the multiply-accumulate stage; every field 0 = let the launcher's heuristic decide.
+// This is what Tuning() searches (the counterpart of the reference's ocBlock/tileBlock/icBlock and mc/nc/kc).
+struct KernelCfg {
+    int bm, bn;     // block rows (output channels) / columns (tiles or pixels): 64 or 128 for FFMA, bn a multiple of 16 for tcgen05
+    int skinny;     // FFMA TensorGEMM with <= 32 tiles: 1 = one-thread-per-channel kernel, 2 = blocked kernel
+    int smem_kb;    // tcgen05 kernels: shared-memory budget of the operand ring (sets the stage count / CTAs per SM)
+};
+
 struct CommonSlot {
     size_t bytes;
     void *ptr;
@@ -69,21 +77,51 @@ struct fc_context {
     int *d_status;  // device word kernels with bounded waits report into
 };
 
+// Programmatic dependent launch.  Every kernel of the forward path is launched with the
+// programmatic-stream-serialization attribute: it may start while its predecessor in the stream is
+// still running, does whatever does not depend on that predecessor (barrier set-up, TMEM allocation,
+// streaming constant weights), and calls pdl_wait() before it touches anything the predecessor reads or
+// writes.  pdl_trigger() lets the successor begin the same way.  Both are no-ops for a plain launch.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+namespace fc {
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+}  // namespace fc
+#endif
+
 // kernel launchers (device pointers, context stream) ------------------------------------------
 namespace fc {
 
 int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int icp);
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g);
-int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g);
+int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
+                          const KernelCfg *cfg = nullptr);
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
-                        int mode);
+                        int mode, const KernelCfg *cfg = nullptr);
 int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
                          int image);
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow);
+                      int oh, int ow, const KernelCfg *cfg = nullptr);
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode);
+                    int oh, int ow, int mode, const KernelCfg *cfg = nullptr);
 size_t igemm_packed_elems(int oc, int K);
 int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 

@@ -10,7 +10,7 @@
 // and a BN x BK slab of V into shared memory transposed ([k][row], padded) so that the inner
 // product reads 128-bit rows without bank conflicts; global loads of the next slab are issued
 // before the math of the current one (register-staged double buffering).
-#include "fc_internal.h"
+#include "fc_tc_common.cuh"
 
 namespace fc {
 
@@ -96,6 +96,9 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
 #pragma unroll
         for (int j = 0; j < C::TN; ++j) acc[i][j] = 0.0f;
 
+    pdl_trigger();
+    pdl_wait();
+
     load_slab(0);
     store_slab(0);
     __syncthreads();
@@ -173,6 +176,9 @@ __global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const
 #pragma unroll
     for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
 
+    pdl_trigger();
+    pdl_wait();
+
     for (int k0 = 0; k0 < icp; k0 += SK_KC) {
         const int kc = min(SK_KC, icp - k0);  // multiple of 8
         __syncthreads();
@@ -214,18 +220,156 @@ __global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const
     }
 }
 
+// Same computation with U streamed by TMA: a producer warp keeps a ring of 128(oc) x 32(ic) boxes of U in
+// flight (128-byte swizzle), so HBM latency is hidden by the ring instead of by each thread's own
+// loads; the 128 consumer threads read their row of the landed box (conflict-free through the swizzle),
+// V_p is staged transposed a 256-channel chunk at a time.  The chain per output element is unchanged:
+// one accumulator, one FMA per input channel, ascending.
+constexpr int ST_STAGES = 5;
+constexpr int ST_KC = 256;
+constexpr int ST_THREADS = 160;  // 4 consumer warps + 1 producer warp
+constexpr int ST_BOX = 128 * 32 * 4;
+
+template <int TN>
+__global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmU,
+                                                                               const float *__restrict__ V,
+                                                                               float *__restrict__ M, int *status,
+                                                                               int oc, int tp, int icp) {
+    using namespace tc;
+    constexpr int TNP = (TN + 3) / 4 * 4;
+    extern __shared__ uint8_t smem_raw[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[ST_STAGES], empty[ST_STAGES]
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * ST_STAGES);
+    const uint32_t ring = (smem_u32(smem_raw) + 128 + 1023) & ~1023u;
+    const uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    float *Vs = reinterpret_cast<float *>(smem_raw + (ring - smem_u32(smem_raw)) + ST_STAGES * ST_BOX);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p = blockIdx.y, oc0 = blockIdx.x * 128;
+    const int num_kb = (icp + 31) / 32;
+    auto bar_full = [&](int s) { return smem_u32(bars + s); };
+    auto bar_empty = [&](int s) { return smem_u32(bars + ST_STAGES + s); };
+
+    if (tid == 0) {
+        for (int s = 0; s < ST_STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_trigger();
+
+    if (warp == 4) {
+        if (lane == 0) {  // U is constant: no need to wait for the input transform
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % ST_STAGES;
+                const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
+                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status)) break;
+                mbar_expect_tx(bar_full(s), ST_BOX);
+                tma_load_3d(ring + s * ST_BOX, &tmU, bar_full(s), kb * 32, oc0, p);
+            }
+        }
+    } else {
+        pdl_wait();  // V comes from the input transform launched just before
+        const int row = oc0 + tid;
+        const float *Vp = V + (size_t)p * tp * icp;
+        float acc[TN];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
+        // `ok` turns false when a bounded wait gives up; the warp then skips the math but still walks the
+        // loop so that all four consumer warps meet at every chunk barrier
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+            if (kb % (ST_KC / 32) == 0) {
+                const int k0 = kb * 32;
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // consumers only: everyone is done with the old chunk
+                for (int idx = tid; idx < TNP * (ST_KC / 4); idx += 128) {
+                    const int t = idx % TNP, k4 = idx / TNP;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (t < tp && k0 + k4 * 4 < icp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)t * icp + k0 + k4 * 4));
+                    Vs[(k4 * 4 + 0) * TNP + t] = v.x;
+                    Vs[(k4 * 4 + 1) * TNP + t] = v.y;
+                    Vs[(k4 * 4 + 2) * TNP + t] = v.z;
+                    Vs[(k4 * 4 + 3) * TNP + t] = v.w;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            const int s = kb % ST_STAGES;
+            const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), ph, abort_flag, status));
+            if (!ok) continue;
+            const uint8_t *a = ring_ptr + s * ST_BOX + tid * 128;  // this thread's oc row: 32 floats, swizzled
+            const float *vk = Vs + (size_t)(kb % (ST_KC / 32)) * 32 * TNP;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float4 u = *reinterpret_cast<const float4 *>(a + ((c ^ (tid & 7)) << 4));
+                const float uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const float4 *b4 = reinterpret_cast<const float4 *>(vk + (c * 4 + kk) * TNP);
+#pragma unroll
+                    for (int g = 0; g < TNP / 4; ++g) {
+                        const float4 b = b4[g];
+                        if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(uu[kk], b.x, acc[g * 4 + 0]);
+                        if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(uu[kk], b.y, acc[g * 4 + 1]);
+                        if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(uu[kk], b.z, acc[g * 4 + 2]);
+                        if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(uu[kk], b.w, acc[g * 4 + 3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(s));  // this warp no longer reads the stage
+        }
+        if (ok && row < oc) {
+            float *dst = M + ((size_t)p * oc + row) * tp;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) dst[j] = acc[j];
+        }
+    }
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let boxes still in flight land before the CTA goes
+    }
+}
+
+bool skinny_uses_tma() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_SKINNY");
+        state = (e && e[0] == 'l') ? 0 : 1;  // FASTCONV_SKINNY=ldg keeps the per-thread global loads
+    }
+    return state == 1;
+}
+
+template <int TN>
+int launch_skinny_tma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    constexpr int TNP = (TN + 3) / 4 * 4;
+    CUtensorMap tmU;
+    FC_PROPAGATE(tc::make_map_3d(&tmU, d_U, g.icp, g.oc, 64, 128));
+    const size_t smem = 128 + 1024 + (size_t)ST_STAGES * ST_BOX + (size_t)ST_KC * TNP * sizeof(float);
+    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_skinny_tma_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    dim3 grid((unsigned)ceil_div(g.oc, 128), 64), block(ST_THREADS);
+    FC_CHECK_CUDA(launch_pdl(wino_gemm_ffma_skinny_tma_kernel<TN>, grid, block, smem, ctx->stream, tmU, d_V, d_M,
+                             ctx->d_status, g.oc, g.tp, g.icp));
+    return FC_OK;
+}
+
 template <int TN>
 int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    if (skinny_uses_tma() && ctx->d_status != nullptr) return launch_skinny_tma<TN>(ctx, d_U, d_V, d_M, g);
     dim3 grid((unsigned)ceil_div(g.oc, SK_THREADS), 64), block(SK_THREADS);
-    wino_gemm_ffma_skinny_kernel<TN><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
-    FC_CHECK_CUDA(cudaGetLastError());
+    FC_CHECK_CUDA(launch_pdl(wino_gemm_ffma_skinny_kernel<TN>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp));
     return FC_OK;
 }
 
 }  // namespace
 
-int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
-    if (g.tiles <= 32) {  // every real tile in one thread's registers
+int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
+                          const KernelCfg *cfg) {
+    const int force = cfg ? cfg->skinny : 0;
+    if (g.tiles <= 32 && force != 2) {  // every real tile in one thread's registers
         const int t = g.tiles;
         if (t <= 4) return launch_skinny<4>(ctx, d_U, d_V, d_M, g);
         if (t <= 8) return launch_skinny<8>(ctx, d_U, d_V, d_M, g);
@@ -238,19 +382,19 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
         return launch_skinny<32>(ctx, d_U, d_V, d_M, g);
     }
     // 64 is the float4-group stride of the thread mapping, so BM and BN are 64 or 128.
-    const bool wide_n = g.tp > 64;
-    const bool wide_m = g.oc > 64;
+    const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : g.tp > 64;
+    const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : g.oc > 64;
     const unsigned gx_n = (unsigned)ceil_div(g.tp, wide_n ? 128 : 64);
     const unsigned gy_m = (unsigned)ceil_div(g.oc, wide_m ? 128 : 64);
     dim3 grid(gx_n, gy_m, 64), block(THREADS);
     if (wide_m && wide_n)
-        wino_gemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
+        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<128, 128>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
     else if (wide_m)
-        wino_gemm_ffma_kernel<128, 64><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
+        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<128, 64>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
     else if (wide_n)
-        wino_gemm_ffma_kernel<64, 128><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
+        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<64, 128>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
     else
-        wino_gemm_ffma_kernel<64, 64><<<grid, block, 0, ctx->stream>>>(d_U, d_V, d_M, g.oc, g.tp, g.icp);
+        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<64, 64>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }

@@ -134,84 +134,71 @@ int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, 
 // Input transform: V = B^T d B per 8x8 tile at (6*ty - pad, 6*tx - pad), zero outside the image
 // (winoF63ZC/winoF63ZC.cpp:541-612); B^T over the tile rows first, then the columns (:614-630).
 //
-// A block owns 8 consecutive tiles x 32 consecutive channels.  Phase 1 stages the 8x8 windows into
-// shared memory with loads that run along the image rows (8 consecutive floats per lane group, four
-// channels per warp instruction) -- zero-filled outside the image, past the last tile and past the
-// last channel, so the padding of V falls out of the arithmetic.  Phase 2 gives every thread one
-// (tile, channel): it reads its window with the channel as the fastest index (conflict-free), runs
-// the two passes in registers and stores the 64 positions, each warp store being one 128-byte line
-// of V[p][tile][c..c+31].
+// The layers this serves at batch 1 are tiny, so the kernel is built for latency: a block owns ONE tile
+// and 32 channels and spreads each (tile, channel) item over 8 threads.
+//   phase 1  256 threads fetch the 32 windows: 8 consecutive floats of an image row per lane group,
+//            zero outside the image / past the last tile / past the last channel (so the padding of V
+//            falls out of the arithmetic);
+//   pass 1   thread (x, channel) transforms column x of its window in place in shared memory;
+//   pass 2   thread (y, channel) transforms row y and stores the 8 positions p = x*8 + y, each warp
+//            store being one 128-byte line of V[p][tile][c..c+31].
+// Shared memory is indexed [y*8+x][channel] with the channel fastest, so every access is conflict-free.
 // ---------------------------------------------------------------------------------------------
-constexpr int IT_TILES = 8;
 constexpr int IT_CH = 32;
-constexpr int IT_LD = IT_CH + 1;  // padded channel stride in shared memory
+constexpr int IT_LD = IT_CH + 1;
 
-__global__ void __launch_bounds__(IT_CH * IT_TILES) input_transform_kernel(const float *__restrict__ in,
-                                                                          float *__restrict__ V, int n_tiles, int ic,
-                                                                          int icp, int tp, int ih, int iw, int pad,
-                                                                          int th, int tw) {
-    extern __shared__ float win[];  // [tile][y*8+x][channel (padded)]
+__global__ void __launch_bounds__(256) input_transform_kernel(const float *__restrict__ in, float *__restrict__ V,
+                                                              int n_tiles, int ic, int icp, int tp, int ih, int iw,
+                                                              int pad, int th, int tw) {
+    __shared__ float win[64 * IT_LD];
     const int tid = threadIdx.x;
-    const int c0 = blockIdx.x * IT_CH, t0 = blockIdx.y * IT_TILES;
-    const int per_img = th * tw;
-
-    {   // phase 1: lane group of 8 walks x, 32 groups walk the channels
+    const int c0 = blockIdx.y * IT_CH, tile = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();  // the input may be the previous layer's output; V may still be read by an earlier GEMM
+    {
         const int x = tid & 7, cl = tid >> 3;
         const int c = c0 + cl;
-        const bool c_ok = c < ic;
-#pragma unroll 1
-        for (int t = 0; t < IT_TILES; ++t) {
-            const int tile = t0 + t;
-            const bool t_ok = c_ok && tile < n_tiles;
-            const int img = tile / per_img, tt = tile - img * per_img;
-            const int row0 = (tt / tw) * 6 - pad, col = (tt % tw) * 6 - pad + x;
-            const float *src = in + ((size_t)img * ic + c) * ih * iw + col;
-            const bool x_ok = t_ok && col >= 0 && col < iw;
-            float v[8];
+        const int per_img = th * tw;
+        const int img = tile / per_img, tt = tile - img * per_img;
+        const int row0 = (tt / tw) * 6 - pad, col = (tt % tw) * 6 - pad + x;
+        const bool ok = c < ic && tile < n_tiles && col >= 0 && col < iw;
+        const float *src = in + ((size_t)img * ic + c) * ih * iw + col;
+        float v[8];
 #pragma unroll
-            for (int y = 0; y < 8; ++y) {
-                const int yy = row0 + y;
-                v[y] = (x_ok && yy >= 0 && yy < ih) ? __ldg(src + (size_t)yy * iw) : 0.0f;
-            }
-#pragma unroll
-            for (int y = 0; y < 8; ++y) win[(t * 64 + y * 8 + x) * IT_LD + cl] = v[y];
+        for (int y = 0; y < 8; ++y) {
+            const int yy = row0 + y;
+            v[y] = (ok && yy >= 0 && yy < ih) ? __ldg(src + (ptrdiff_t)yy * iw) : 0.0f;
         }
+#pragma unroll
+        for (int y = 0; y < 8; ++y) win[(y * 8 + x) * IT_LD + cl] = v[y];
     }
     __syncthreads();
-
-    const int lane = tid & 31, t = tid >> 5;
-    const int c = c0 + lane, tile = t0 + t;
-    if (c >= icp || tile >= tp) return;
-    const float *w = win + (size_t)t * 64 * IT_LD + lane;
-    float d[8][8];
-#pragma unroll
-    for (int y = 0; y < 8; ++y)
-#pragma unroll
-        for (int x = 0; x < 8; ++x) d[y][x] = w[(y * 8 + x) * IT_LD];
-#pragma unroll
-    for (int x = 0; x < 8; ++x)
-        input_transform_1d(d[0][x], d[1][x], d[2][x], d[3][x], d[4][x], d[5][x], d[6][x], d[7][x]);
-    const size_t plane = (size_t)tp * icp;
-    float *dst = V + (size_t)tile * icp + c;
-#pragma unroll
-    for (int y = 0; y < 8; ++y) {
-        input_transform_1d(d[y][0], d[y][1], d[y][2], d[y][3], d[y][4], d[y][5], d[y][6], d[y][7]);
-#pragma unroll
-        for (int x = 0; x < 8; ++x) dst[(size_t)(x * 8 + y) * plane] = d[y][x];
+    const int lane = tid & 31, w = tid >> 5;  // w = column (pass 1) or row (pass 2) of the window
+    {
+        float *q = win + w * IT_LD + lane;  // column w: elements (y*8 + w)
+        float r0 = q[0 * 8 * IT_LD], r1 = q[1 * 8 * IT_LD], r2 = q[2 * 8 * IT_LD], r3 = q[3 * 8 * IT_LD];
+        float r4 = q[4 * 8 * IT_LD], r5 = q[5 * 8 * IT_LD], r6 = q[6 * 8 * IT_LD], r7 = q[7 * 8 * IT_LD];
+        input_transform_1d(r0, r1, r2, r3, r4, r5, r6, r7);
+        q[0 * 8 * IT_LD] = r0; q[1 * 8 * IT_LD] = r1; q[2 * 8 * IT_LD] = r2; q[3 * 8 * IT_LD] = r3;
+        q[4 * 8 * IT_LD] = r4; q[5 * 8 * IT_LD] = r5; q[6 * 8 * IT_LD] = r6; q[7 * 8 * IT_LD] = r7;
     }
+    __syncthreads();
+    const int c = c0 + lane;
+    if (c >= icp) return;
+    const float *q = win + w * 8 * IT_LD + lane;  // row w: elements (w*8 + x)
+    float r0 = q[0 * IT_LD], r1 = q[1 * IT_LD], r2 = q[2 * IT_LD], r3 = q[3 * IT_LD];
+    float r4 = q[4 * IT_LD], r5 = q[5 * IT_LD], r6 = q[6 * IT_LD], r7 = q[7 * IT_LD];
+    input_transform_1d(r0, r1, r2, r3, r4, r5, r6, r7);
+    const size_t plane = (size_t)tp * icp;
+    float *dst = V + (size_t)w * plane + (size_t)tile * icp + c;  // p = x*8 + w
+    dst[0 * 8 * plane] = r0; dst[1 * 8 * plane] = r1; dst[2 * 8 * plane] = r2; dst[3 * 8 * plane] = r3;
+    dst[4 * 8 * plane] = r4; dst[5 * 8 * plane] = r5; dst[6 * 8 * plane] = r6; dst[7 * 8 * plane] = r7;
 }
 
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
-    static bool attr_set = false;
-    const size_t smem = (size_t)IT_TILES * 64 * IT_LD * sizeof(float);
-    if (!attr_set) {
-        FC_CHECK_CUDA(cudaFuncSetAttribute(input_transform_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
-    }
-    dim3 block(IT_CH * IT_TILES), grid((unsigned)ceil_div(g.icp, IT_CH), (unsigned)ceil_div(g.tp, IT_TILES));
-    input_transform_kernel<<<grid, block, smem, ctx->stream>>>(d_in, d_V, g.tiles, g.ic, g.icp, g.tp, g.ih, g.iw, g.pad,
-                                                               g.th, g.tw);
-    FC_CHECK_CUDA(cudaGetLastError());
+    dim3 block(256), grid((unsigned)g.tp, (unsigned)ceil_div(g.icp, IT_CH));
+    FC_CHECK_CUDA(launch_pdl(input_transform_kernel, grid, block, 0, ctx->stream, d_in, d_V, g.tiles, g.ic, g.icp, g.tp,
+                             g.ih, g.iw, g.pad, g.th, g.tw));
     return FC_OK;
 }
 
@@ -219,79 +206,93 @@ int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const
 // Output transform: Y = A^T M A, A^T over the tile columns first (for every row), then over the
 // rows (winoF63ZC/winoF63ZC.cpp:905-912), clipped store at the right/bottom edges (:928-969).
 //
-// One thread per (oc, tile).  A warp covers TPW consecutive tiles of 32/TPW output channels (TPW =
-// 32, 16 or 8, chosen from the tile count so that small feature maps do not idle most lanes); the
-// 64 loads per thread from M[p][oc][tile] are contiguous across the lanes of a channel.  The 6x6
-// results go through shared memory so that the stores run along the output rows: tiles that are
-// neighbours in x are neighbours in memory, so a warp writes runs of 6*TPW consecutive floats.
+// Also built for latency: a block owns TPW consecutive tiles of OCB = 32/TPW output channels and
+// spreads every (oc, tile) item over 8 threads.
+//   pass 1   warp r (0..7) loads row r of M's 8x8 (8 loads per thread, the lanes of a channel run
+//            along the contiguous tile axis of M[p][oc][tile]) and reduces it to 6 values;
+//   pass 2   warp j (0..5) reduces column j over the 8 rows and stages the 6 outputs;
+//   store    the staged 6 x (6*TPW) block of every channel is written along the output rows: tiles
+//            that are neighbours in x are neighbours in memory.
+// TPW is 32, 16 or 8 so that small feature maps (9 or 4 tiles) do not idle most lanes.
 // ---------------------------------------------------------------------------------------------
-constexpr int OT_WARPS = 4;
-
 template <int TPW>
-__global__ void __launch_bounds__(32 * OT_WARPS) output_transform_kernel(const float *__restrict__ M,
-                                                                        float *__restrict__ out, int n_tiles, int oc,
-                                                                        int tp, int oh, int ow, int th, int tw) {
-    constexpr int OCW = 32 / TPW;            // output channels per warp
-    constexpr int ROW = TPW * 6 + 2;         // floats per staged output row (+2: fewer bank conflicts)
-    __shared__ float stage[OT_WARPS][OCW][6][ROW];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__global__ void __launch_bounds__(256) output_transform_kernel(const float *__restrict__ M, float *__restrict__ out,
+                                                               int n_tiles, int oc, int tp, int oh, int ow, int th,
+                                                               int tw) {
+    constexpr int OCB = 32 / TPW;
+    constexpr int ROW = TPW * 6 + 1;
+    __shared__ float hbuf[8][6][33];          // [row][j][lane]
+    __shared__ float stage[OCB][6][ROW];      // [oc][i][tile*6 + j]
+    __shared__ int tile_org[TPW];             // element offset of each tile's top-left output, -1 past the end
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int tl = lane % TPW, ol = lane / TPW;
-    const int t_base = blockIdx.x * TPW;
-    const int k_base = (blockIdx.y * OT_WARPS + warp) * OCW;
+    const int t_base = blockIdx.x * TPW, k_base = blockIdx.y * OCB;
     const int t = t_base + tl, k = k_base + ol;
-    const size_t plane = (size_t)oc * tp;
     const bool active = t < n_tiles && k < oc;
-    if (active) {
-        const float *src = M + (size_t)k * tp + t;
-        float h[8][6];
-#pragma unroll
-        for (int row = 0; row < 8; ++row) {
-            float m[8];
-#pragma unroll
-            for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
-            output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
-        }
-#pragma unroll
-        for (int j = 0; j < 6; ++j) {
-            float s[6];
-            output_transform_1d(h[0][j], h[1][j], h[2][j], h[3][j], h[4][j], h[5][j], h[6][j], h[7][j], s);
-#pragma unroll
-            for (int i = 0; i < 6; ++i) stage[warp][ol][i][tl * 6 + j] = s[i];
+    const size_t plane = (size_t)oc * tp;
+    if (threadIdx.x < TPW) {
+        const int tile = t_base + threadIdx.x;
+        int org = -1;
+        if (tile < n_tiles) {
+            const int per_img = th * tw;
+            const int img = tile / per_img, tt = tile - img * per_img;
+            org = ((tt / tw) * 6) << 16 | ((tt % tw) * 6);  // y0 : x0 (both below 32768)
+            tile_org[threadIdx.x] = org;
+        } else {
+            tile_org[threadIdx.x] = -1;
         }
     }
-    __syncwarp();
-    const int per_img = th * tw;
-    // each lane now writes elements e = lane, lane+32, ... of every staged row: e -> (tile e/6, column e%6)
-#pragma unroll 1
-    for (int o = 0; o < OCW; ++o) {
-        const int kk = k_base + o;
-        if (kk >= oc) break;
-        for (int e = lane; e < TPW * 6; e += 32) {
-            const int te = e / 6, j = e - te * 6;
-            const int tile = t_base + te;
-            if (tile >= n_tiles) continue;
-            const int img = tile / per_img, tt = tile - img * per_img;
-            const int y0 = (tt / tw) * 6, x = (tt % tw) * 6 + j;
-            if (x >= ow) continue;
-            float *dst = out + ((size_t)img * oc + kk) * oh * ow + (size_t)y0 * ow + x;
+    pdl_trigger();
+    pdl_wait();  // M comes from the GEMM launched just before
+    {   // pass 1: row w of the 8x8, positions p = col*8 + w
+        float m[8];
+        const float *src = M + (size_t)w * plane + (size_t)k * tp + t;
 #pragma unroll
-            for (int i = 0; i < 6; ++i)
-                if (y0 + i < oh) dst[(size_t)i * ow] = stage[warp][o][i][e];
-        }
+        for (int col = 0; col < 8; ++col) m[col] = active ? __ldg(src + (size_t)col * 8 * plane) : 0.0f;
+        float h[6];
+        output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h);
+#pragma unroll
+        for (int j = 0; j < 6; ++j) hbuf[w][j][lane] = h[j];
+    }
+    __syncthreads();
+    if (w < 6) {  // pass 2: column w over the 8 rows
+        float s[6];
+        output_transform_1d(hbuf[0][w][lane], hbuf[1][w][lane], hbuf[2][w][lane], hbuf[3][w][lane], hbuf[4][w][lane],
+                            hbuf[5][w][lane], hbuf[6][w][lane], hbuf[7][w][lane], s);
+#pragma unroll
+        for (int i = 0; i < 6; ++i) stage[ol][i][tl * 6 + w] = s[i];
+    }
+    __syncthreads();
+    const int per_img = th * tw;
+    // 6 rows x OCB channels x (6*TPW) floats, one element per thread and step, consecutive threads on
+    // consecutive floats of an output row; the tile origins were decoded once into tile_org
+    constexpr int PER_ROW = TPW * 6;
+    const size_t out_page = (size_t)oh * ow;
+    for (int idx = threadIdx.x; idx < OCB * 6 * PER_ROW; idx += 256) {
+        const int e = idx % PER_ROW, i = (idx / PER_ROW) % 6, o = idx / (PER_ROW * 6);
+        const int te = e / 6, j = e - te * 6;
+        const int org = tile_org[te], kk = k_base + o;
+        if (org < 0 || kk >= oc) continue;
+        const int y = (org >> 16) + i, x = (org & 0xffff) + j;
+        const int img = (t_base + te) / per_img;
+        if (y < oh && x < ow) out[((size_t)img * oc + kk) * out_page + (size_t)y * ow + x] = stage[o][i][e];
     }
 }
 
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g) {
-    dim3 block(32 * OT_WARPS);
+    dim3 block(256);
     if (g.tiles > 16) {
-        dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OT_WARPS));
-        output_transform_kernel<32><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+        dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
+        FC_CHECK_CUDA(launch_pdl(output_transform_kernel<32>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
+                                 g.oh, g.ow, g.th, g.tw));
     } else if (g.tiles > 8) {
-        dim3 grid(1, (unsigned)ceil_div(g.oc, OT_WARPS * 2));
-        output_transform_kernel<16><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 2));
+        FC_CHECK_CUDA(launch_pdl(output_transform_kernel<16>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
+                                 g.oh, g.ow, g.th, g.tw));
     } else {
-        dim3 grid(1, (unsigned)ceil_div(g.oc, OT_WARPS * 4));
-        output_transform_kernel<8><<<grid, block, 0, ctx->stream>>>(d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw);
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
+        FC_CHECK_CUDA(launch_pdl(output_transform_kernel<8>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
+                                 g.oh, g.ow, g.th, g.tw));
     }
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
