@@ -162,6 +162,73 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line))
 
 
+WIDE = [(c, c, h) for c in (512, 1024, 2048) for h in (14, 28, 56)]
+
+
+def run_k_sharded(args, rank, world, local_rank, dist):
+    """Single-image wide layers (C = K in {512,1024,2048} at 14/28/56), output channels split over the ranks:
+    each rank keeps only its slice of the transformed weights, computes its channel slab and one NCCL
+    all-gather per layer reassembles the NCHW output on every rank.  Total work is fixed: strong scaling."""
+    import torch
+
+    import fastconv_b200 as fc
+    from fastconv_b200 import parallel, synth
+
+    if dist is None:  # single rank: a one-member group keeps the code path identical
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        dist_mod.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    layers = WIDE if args.layers == "vgg16" else VGG16
+    need = sum(4 * (64 * (k // world + 8) * c + 2 * 64 * 128 * (c + k) + k * c * 9 + 2 * (c + k) * h * h) for c, k, h in layers)
+    ctx = fc.Context(local_rank, arena_bytes=int(need * 1.1) + (256 << 20))
+    convs, flops = [], 0.0
+    for idx, (c, k, h) in enumerate(layers):
+        w = synth.conv_weights(k, c, 3, 3, 2000 + idx)
+        x = synth.conv_input(1, c, h, h, 1000 + idx)
+        conv = parallel.KShardedConv.gpu(ctx, w, h, h, 1, args.mode)
+        conv.forward(x)  # plans the slice, uploads the input once
+        convs.append(conv)
+        flops += layer_flops(1, c, k, h)
+        del w
+
+    def step():
+        for conv in convs:
+            conv.forward(None)
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ctx.synchronize(); torch.cuda.synchronize(); dist.barrier()
+    sampler.mark()
+    ctx.timer_record(0)
+    for _ in range(args.steps):
+        step()
+    ctx.timer_record(1)
+    ms = ctx.timer_elapsed_ms(0, 1)
+    torch.cuda.synchronize(); dist.barrier()
+    sampler.mark()
+    clocks = sampler.stop()
+    t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "conv GFLOP/s (direct-equiv), wide single-image layers, K-sharded", "value": round(flops / ms_step / 1e6, 1),
+            "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
+            "config": {"workload": "3x3 s1 p1, batch 1, " + ";".join(f"{c}->{k}@{h}" for c, k, h in layers),
+                       "parallelism": f"output channels split over {world} GPU(s), one NCCL all-gather per layer",
+                       "math_mode": args.mode},
+            "gpu_launches": 3 * len(layers) * args.steps, "clocks": clocks}))
+    ctx.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -172,6 +239,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="images per GPU")
     ap.add_argument("--layers", default="vgg16",
                     help="'vgg16' (the 13-layer stack) or a list 'C,K,H;C,K,H;...' of 3x3 s1 p1 layers")
+    ap.add_argument("--shard", default="batch", choices=["batch", "k"],
+                    help="'batch': every rank runs the stack on its own images (no collective, the default); "
+                         "'k': single-image wide layers with output channels split over the ranks + NCCL all-gather")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "fastconv":
@@ -201,6 +271,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
+
+    if args.shard == "k":
+        run_k_sharded(args, rank, world, local_rank, dist)
+        return
 
     lib = fc.load()
     mode = _lib.MODE_NAMES[args.mode]

@@ -1,0 +1,140 @@
+"""Multi-GPU partitioning of the convolution path: one process per GPU, torch.distributed for the plumbing.
+
+The reference has no distributed code (its only parallelism is OpenMP inside one process), so nothing here
+mirrors a reference interface; the two partitionings are the ones the path offers naturally:
+
+* batch sharding  -- images are independent: rank r runs the same layers on images [b0, b1) of the batch;
+  there is NO collective in the data path.
+* K sharding      -- output channels are independent: rank r owns channels [k0, k1) of a single-image
+  wide layer, i.e. transforms and keeps only its slice of the weights (which is what shrinks the
+  dominant 64*C*K weight stream), reads the whole (small) input, and produces the slab
+  out[:, k0:k1] -- contiguous in NCHW for one image -- which one all-gather reassembles on every
+  rank.  The reduction over input channels is never split, so every output element is computed by
+  exactly the arithmetic of the unsharded layer: sharded == unsharded bit for bit.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Optional, Tuple
+
+import numpy as np
+
+
+def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous balanced split of range(total): the first total % world ranks get one extra item."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    if total < 0:
+        raise ValueError("negative extent")
+    base, extra = divmod(total, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def shard_batch(images: int, world: int, rank: int) -> Tuple[int, int]:
+    return shard_range(images, world, rank)
+
+
+def shard_channels(oc: int, world: int, rank: int, multiple: int = 1) -> Tuple[int, int]:
+    """Output-channel slice of a rank; with `multiple` > 1 every slice but the last is a multiple of it."""
+    blocks = -(-oc // multiple)
+    b0, b1 = shard_range(blocks, world, rank)
+    return min(b0 * multiple, oc), min(b1 * multiple, oc)
+
+
+def allgather_channel_slabs(local, oc: int, group=None):
+    """All-gather of per-rank slabs [n][k_r][oh][ow] into [n][oc][oh][ow] on every rank (torch tensors,
+    any backend).  Equal slabs of a single image go through one all_gather_into_tensor (the slab is a
+    contiguous piece of the NCHW output); ragged or batched slabs are gathered as a list and concatenated."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    n, k_local, oh, ow = local.shape
+    sizes = [shard_channels(oc, world, r)[1] - shard_channels(oc, world, r)[0] for r in range(world)]
+    if sum(sizes) != oc or sizes[dist.get_rank(group)] != k_local:
+        raise ValueError(f"slab of {k_local} channels does not match the partition {sizes} of {oc}")
+    local = local.contiguous()
+    if n == 1 and len(set(sizes)) == 1:
+        out = torch.empty((1, oc, oh, ow), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out.view(-1), local.view(-1), group=group)
+        return out
+    # ragged or batched: collectives want equal shapes, so every slab is padded to the widest one
+    widest = max(sizes)
+    padded = torch.zeros((n, widest, oh, ow), dtype=local.dtype, device=local.device)
+    padded[:, :k_local] = local
+    parts = [torch.empty_like(padded) for _ in sizes]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p[:, :s] for p, s in zip(parts, sizes)], dim=1)
+
+
+class KShardedConv:
+    """One single-image layer with its output channels split over the ranks of a process group.
+
+    `forward_slab(x, w_slice) -> ndarray/tensor [n][k_r][oh][ow]` computes this rank's channels; on a GPU
+    it is a planned fastconv layer built from the weight slice (see `gpu`), in CPU tests any convolution.
+    """
+
+    def __init__(self, weights: np.ndarray, forward_slab: Callable, group=None):
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.oc = int(weights.shape[0])
+        self.k0, self.k1 = shard_channels(self.oc, self.world, self.rank)
+        self.w_slice = np.ascontiguousarray(weights[self.k0:self.k1])
+        self._forward_slab = forward_slab
+
+    def forward(self, x):
+        import torch
+
+        slab = self._forward_slab(x, self.w_slice)
+        if not isinstance(slab, torch.Tensor):
+            slab = torch.from_numpy(np.ascontiguousarray(slab))
+        return allgather_channel_slabs(slab, self.oc, self.group)
+
+    @classmethod
+    def gpu(cls, ctx, weights: np.ndarray, ih: int, iw: int, pad: int = 1, mode: str = "fp32", group=None):
+        """K-sharded Winograd layer on this rank's GPU: the slab is written straight into a torch CUDA
+        tensor by the library, then all-gathered over NCCL."""
+        import torch
+
+        from . import _lib
+        from .layers import make_desc
+
+        lib = _lib.load()
+        state = {}
+
+        def forward_slab(x, w_slice):
+            if "conv" not in state:
+                x = np.ascontiguousarray(x, dtype=np.float32)
+                n, ic = x.shape[:2]
+                desc = make_desc(n, ic, ih, iw, w_slice.shape[0], 3, 3, 1, 1, pad, pad, pad, pad)
+                h = C.c_void_p()
+                _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, _lib.MODE_NAMES[mode],
+                                              C.c_void_p(w_slice.ctypes.data), C.byref(h)), "fc_conv_create")
+                d_in, d_out = C.c_void_p(), C.c_void_p()
+                _lib.check(lib.fc_conv_device_buffers(h, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
+                oh, ow = ih + 2 * pad - 2, iw + 2 * pad - 2
+                state.update(conv=h, d_in=d_in, slab=torch.empty((n, w_slice.shape[0], oh, ow), dtype=torch.float32,
+                                                                  device=f"cuda:{ctx.device}"))
+            if x is not None:
+                ctx.upload(x, state["d_in"].value)
+            _lib.check(lib.fc_conv_forward_device(state["conv"], state["d_in"], C.c_void_p(state["slab"].data_ptr())),
+                       "fc_conv_forward_device")
+            return state["slab"]
+
+        obj = cls(weights, forward_slab, group)
+        obj._state = state
+        # torch sees the library's stream as an external stream: with it current, the all-gather is ordered
+        # after the kernels without a host synchronisation, and CUDA events on it time both
+        obj.stream = torch.cuda.ExternalStream(ctx.stream.value, device=f"cuda:{ctx.device}")
+        plain_forward = obj.forward
+
+        def forward_on_library_stream(x):
+            with torch.cuda.stream(obj.stream):
+                return plain_forward(x)
+
+        obj.forward = forward_on_library_stream
+        return obj
