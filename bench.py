@@ -318,9 +318,7 @@ def main():
         stack.forward()
 
     def step_host():
-        for (hdl, _, _, _), px, po in zip(convs, host_in, host_out):
-            _lib.check(lib.fc_conv_forward_host(hdl, C.c_void_p(px.ctypes.data), C.c_void_p(po.ctypes.data)),
-                       "fc_conv_forward_host")
+        stack.forward_host(host_in, host_out)  # pinned host buffers in, pinned host buffers out
 
     def barrier():
         ctx.synchronize()

@@ -89,6 +89,7 @@ SIGNATURES = {
     "fc_conv_launches_per_forward": (C.c_int, [_vp, _ip]),
     "fc_layer_list_create": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.c_int, C.POINTER(_vp)]),
     "fc_layer_list_forward": (C.c_int, [_vp]),
+    "fc_layer_list_forward_host": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "fc_layer_list_launches": (C.c_int, [_vp, _ip]),
     "fc_layer_list_destroy": (C.c_int, [_vp]),
     "fc_diff": (C.c_float, [_vp, _vp, C.c_int]),

@@ -143,6 +143,7 @@ int fc_context_create(int device, size_t arena_bytes, fc_context **out) {
     ctx->slab = nullptr;
     ctx->stream = nullptr;
     ctx->d_status = nullptr;
+    ctx->copy_in = ctx->copy_out = nullptr;
     for (auto &e : ctx->ev) e = nullptr;
     for (auto &e : ctx->user_ev) e = nullptr;
     if (arena_bytes < (1u << 20)) arena_bytes = 1u << 20;
@@ -172,6 +173,8 @@ int fc_context_destroy(fc_context *ctx) {
         if (ev) cudaEventDestroy(ev);
     for (auto &ev : ctx->user_ev)
         if (ev) cudaEventDestroy(ev);
+    if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     if (ctx->slab) cudaFree(ctx->slab);
     delete ctx;
@@ -879,6 +882,8 @@ struct fc_layer_list {
     cudaGraph_t graph;
     cudaGraphExec_t exec;
     int launches;
+    std::vector<fc_conv *> convs;
+    std::vector<cudaEvent_t> uploaded, computed;  // per layer, for the pipelined host forward
 };
 
 int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *const *d_ins, float *const *d_outs,
@@ -903,6 +908,7 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     l->graph = nullptr;
     l->exec = nullptr;
     l->launches = launches;
+    l->convs.assign(convs, convs + count);
     cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
     int st = FC_OK;
     if (e == cudaSuccess) {
@@ -927,6 +933,37 @@ int fc_layer_list_forward(fc_layer_list *l) {
     return FC_OK;
 }
 
+int fc_layer_list_forward_host(fc_layer_list *l, const float *const *h_ins, float *const *h_outs) {
+    FC_REQUIRE(l && h_ins && h_outs, FC_ERR_INVALID_ARG, "NULL argument");
+    fc_context *ctx = l->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    if (!ctx->copy_in) FC_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+    if (!ctx->copy_out) FC_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+    const size_t n = l->convs.size();
+    while (l->uploaded.size() < n) {
+        cudaEvent_t a, b;
+        FC_CHECK_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        FC_CHECK_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        l->uploaded.push_back(a);
+        l->computed.push_back(b);
+    }
+    for (size_t i = 0; i < n; ++i) {
+        fc_conv *c = l->convs[i];
+        FC_REQUIRE(h_ins[i] && h_outs[i], FC_ERR_INVALID_ARG, "layer %zu has a NULL host buffer", i);
+        const size_t in_bytes = (size_t)c->desc.batch * c->desc.ic * c->desc.ih * c->desc.iw * sizeof(float);
+        const size_t out_bytes = (size_t)c->desc.batch * c->desc.oc * c->oh * c->ow * sizeof(float);
+        FC_CHECK_CUDA(cudaMemcpyAsync(c->d_in, h_ins[i], in_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+        FC_CHECK_CUDA(cudaEventRecord(l->uploaded[i], ctx->copy_in));
+        FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, l->uploaded[i], 0));
+        FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
+        FC_CHECK_CUDA(cudaEventRecord(l->computed[i], ctx->stream));
+        FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->copy_out, l->computed[i], 0));
+        FC_CHECK_CUDA(cudaMemcpyAsync(h_outs[i], c->d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->copy_out));
+    return sync_and_check_status(ctx);
+}
+
 int fc_layer_list_launches(const fc_layer_list *l, int *n) {
     FC_REQUIRE(l && n, FC_ERR_INVALID_ARG, "NULL argument");
     *n = l->launches;
@@ -938,6 +975,8 @@ int fc_layer_list_destroy(fc_layer_list *l) {
     cudaStreamSynchronize(l->ctx->stream);
     if (l->exec) cudaGraphExecDestroy(l->exec);
     if (l->graph) cudaGraphDestroy(l->graph);
+    for (cudaEvent_t e : l->uploaded) cudaEventDestroy(e);
+    for (cudaEvent_t e : l->computed) cudaEventDestroy(e);
     delete l;
     return FC_OK;
 }

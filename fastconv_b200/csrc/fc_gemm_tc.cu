@@ -2,18 +2,22 @@
 //
 // For every Winograd position p the GEMM  M_p[oc][tile] = sum_ic U_p[oc][ic] * V_p[tile][ic]  has both
 // operands K-major in global memory, which is exactly what a K-major UMMA shared-memory descriptor
-// with 128-byte swizzle and a TMA box of 32 floats x rows want.  One CTA owns one 128(oc) x BN(tile)
-// block of one position:
+// with 128-byte swizzle and a TMA box of 32 floats x rows want.  A work item is one 128(oc) x BN(tile)
+// block of one position; the kernel is persistent: CTA b handles items b, b + gridDim.x, ... with
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor 3-D boxes (ic, row, p) of U and V into a ring of
-//               shared-memory stages, completion counted on an mbarrier per stage
-//   warp 1      allocates TMEM, then one elected lane issues tcgen05.mma.cta_group::1.kind::tf32
-//               (M=128, N=BN, K=8) four times per stage; tcgen05.commit releases the stage
-//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (lane = oc row) and store it to M.
+//               shared-memory stages that runs on across work items, one mbarrier per stage
+//   warp 1      allocates TMEM (two accumulators of BN columns), then one elected lane issues
+//               tcgen05.mma.cta_group::1.kind::tf32 (M=128, N=BN, K=8) four times per stage;
+//               tcgen05.commit releases the stage and, after the last one, publishes the accumulator
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (lane = oc row), hand the TMEM buffer back,
+//               store to M -- while the MMA warp already fills the other accumulator.
 //               In 3xTF32 mode the same warps first split every landed stage in place into
 //               hi = tf32(x) and lo = x - hi, so each k-step becomes lo*hi + hi*lo + hi*hi with fp32
 //               accumulation: fp32-class accuracy without touching HBM twice.
 //
+// U is constant, so the producer fills the ring's U halves before griddepcontrol.wait (the kernel may
+// have been launched while the input transform is still running) and adds V afterwards.
 // Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
 // context's status word, all roles drain, TMEM is released and the kernel returns.
 #include "fc_tc_common.cuh"
@@ -27,32 +31,41 @@ using namespace tc;
 struct TcParams {
     float *M;
     int *status;
-    int oc, tp, bn, num_kb, stages, tmem_cols;
+    int oc, tp, bn, num_kb, stages, acc_cols;
+    int n_tile_blk, n_oc_blk, n_items;
 };
 
-// ---- kernel ---------------------------------------------------------------------------------
+__device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p, int &oc0, int &t0) {
+    // tile block fastest, then oc block, then position: CTAs next to each other share the same U box
+    const int tb = item % P.n_tile_blk;
+    const int rest = item / P.n_tile_blk;
+    t0 = tb * P.bn;
+    oc0 = (rest % P.n_oc_blk) * BM;
+    p = rest / P.n_oc_blk;
+}
+
 template <bool kSplit>
 __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const TcParams P) {
     extern __shared__ uint8_t smem_raw[];
     // carve: [barriers + flags | 1024-aligned stage ring]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);      // full[S], empty[S], split[S], tmem_full
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[8] empty[8] split[8] acc_full[2] acc_empty[2]
     const int S = P.stages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * 8 + 1);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t ring = (smem_u32(smem_raw) + 512 + 1023) & ~1023u;
     const uint32_t b_bytes = (uint32_t)P.bn * BK * 4;
-    const uint32_t part_bytes = A_BYTES + b_bytes;                  // one (A,B) pair
+    const uint32_t part_bytes = A_BYTES + b_bytes;  // one (A,B) pair
     const uint32_t stage_bytes = part_bytes * (kSplit ? 2 : 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * P.bn;
 
     auto bar_full = [&](int s) { return smem_u32(bars + s); };
     auto bar_empty = [&](int s) { return smem_u32(bars + 8 + s); };
     auto bar_split = [&](int s) { return smem_u32(bars + 16 + s); };
-    const uint32_t bar_tmem_full = smem_u32(bars + 24);
+    auto bar_acc_full = [&](int a) { return smem_u32(bars + 24 + a); };
+    auto bar_acc_empty = [&](int a) { return smem_u32(bars + 26 + a); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -60,14 +73,17 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
             mbar_init(bar_empty(s), 1);
             mbar_init(bar_split(s), 128);
         }
-        mbar_init(bar_tmem_full, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_acc_full(a), 1);
+            mbar_init(bar_acc_empty(a), 128);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)P.tmem_cols)
+                     "r"((uint32_t)(2 * P.acc_cols))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -80,93 +96,140 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            // U is constant: fill the ring's U halves before waiting for the input transform, then add V
-            const int pre = P.num_kb < S ? P.num_kb : S;
-            for (int kb = 0; kb < pre; ++kb) {
-                mbar_expect_tx(bar_full(kb), part_bytes);
-                tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), kb * BK, oc0, p);
-            }
-            pdl_wait();
-            for (int kb = 0; kb < pre; ++kb)
-                tma_load_3d(ring + kb * stage_bytes + A_BYTES, &tmV, bar_full(kb), kb * BK, t0, p);
-            for (int kb = pre; kb < P.num_kb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
-                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status)) break;
-                const uint32_t a_dst = ring + s * stage_bytes;
-                mbar_expect_tx(bar_full(s), part_bytes);
-                tma_load_3d(a_dst, &tmU, bar_full(s), kb * BK, oc0, p);
-                tma_load_3d(a_dst + A_BYTES, &tmV, bar_full(s), kb * BK, t0, p);
+            int g = 0;  // k-blocks issued so far by this CTA, over all its items
+            bool first = true, ok = true;
+            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+                int p, oc0, t0;
+                item_coords(P, item, p, oc0, t0);
+                int kb = 0;
+                if (first) {
+                    // the ring is empty: fill it with U boxes before waiting for the producer of V
+                    const int pre = P.num_kb < S ? P.num_kb : S;
+                    for (; kb < pre; ++kb) {
+                        mbar_expect_tx(bar_full(kb), part_bytes);
+                        tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), kb * BK, oc0, p);
+                    }
+                    pdl_wait();
+                    for (int j = 0; j < pre; ++j)
+                        tma_load_3d(ring + j * stage_bytes + A_BYTES, &tmV, bar_full(j), j * BK, t0, p);
+                    g = pre;
+                    first = false;
+                }
+                for (; kb < P.num_kb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status);
+                    if (!ok) break;
+                    const uint32_t a_dst = ring + s * stage_bytes;
+                    mbar_expect_tx(bar_full(s), part_bytes);
+                    tma_load_3d(a_dst, &tmU, bar_full(s), kb * BK, oc0, p);
+                    tma_load_3d(a_dst + A_BYTES, &tmV, bar_full(s), kb * BK, t0, p);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_tf32(BM, P.bn);
+            int g = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < P.num_kb && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
-                ok = mbar_wait(kSplit ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
+            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                ok = mbar_wait(bar_acc_empty(acc), acc_ph ^ 1u, abort_flag, P.status);  // epilogue drained it
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_hi = ring + s * stage_bytes, b_hi = a_hi + A_BYTES;
-                const uint32_t a_lo = a_hi + part_bytes, b_lo = a_lo + A_BYTES;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.acc_cols);
+                for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(kSplit ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_hi = ring + s * stage_bytes, b_hi = a_hi + A_BYTES;
+                    const uint32_t a_lo = a_hi + part_bytes, b_lo = a_lo + A_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < BK / 8; ++ks) {
-                    const uint32_t koff = ks * 32;  // 8 tf32 = 32 bytes further along K inside the swizzle span
-                    const uint32_t first = (kb == 0 && ks == 0) ? 0u : 1u;
-                    if (kSplit) {
-                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_lo + koff), umma_desc_k_sw128(b_hi + koff), idesc, first);
-                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_lo + koff), idesc, 1u);
-                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, 1u);
-                    } else {
-                        tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, first);
+                    for (int ks = 0; ks < BK / 8; ++ks) {
+                        const uint32_t koff = ks * 32;  // 8 tf32 = 32 bytes further along K inside the swizzle span
+                        const uint32_t accum = (kb == 0 && ks == 0) ? 0u : 1u;
+                        if (kSplit) {
+                            tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_lo + koff), umma_desc_k_sw128(b_hi + koff), idesc, accum);
+                            tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_lo + koff), idesc, 1u);
+                            tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, 1u);
+                        } else {
+                            tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_hi + koff), idesc, accum);
+                        }
                     }
+                    tc_commit(bar_empty(s));  // arrives once the MMAs above have finished reading the stage
                 }
-                tc_commit(bar_empty(s));  // arrives once the MMAs above have finished reading the stage
+                if (ok) tc_commit(bar_acc_full(acc));
             }
-            tc_commit(bar_tmem_full);
         }
     } else {
         // ---------------- splitters (3xTF32) + epilogue ----------------
         const int et = threadIdx.x - 64;  // 0..127
-        if (kSplit) {
-            const int a_chunks = A_BYTES / 16, all_chunks = (int)(part_bytes / 16);
-            (void)a_chunks;
-            for (int kb = 0; kb < P.num_kb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
-                if (!mbar_wait(bar_full(s), ph, abort_flag, P.status)) break;
-                float4 *hi = reinterpret_cast<float4 *>(smem_raw + (ring - smem_u32(smem_raw)) + s * stage_bytes);
-                float4 *lo = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(hi) + part_bytes);
-                // element-wise at identical offsets: the swizzled placement of hi and lo stays that of TMA
-                for (int i = et; i < all_chunks; i += 128) {
-                    const float4 v = hi[i];
-                    float4 h, l;
-                    h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-                    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-                    hi[i] = h;
-                    lo[i] = l;
+        const int q = warp & 3;           // TMEM lane quarter this warp may read
+        int g = 0, it = 0;
+        bool ok = true, waited = false;
+        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+            int p, oc0, t0;
+            item_coords(P, item, p, oc0, t0);
+            if (kSplit) {
+                const int all_chunks = (int)(part_bytes / 16);
+                for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(bar_full(s), ph, abort_flag, P.status);
+                    if (!ok) break;
+                    float4 *hi = reinterpret_cast<float4 *>(smem_raw + (ring - smem_u32(smem_raw)) + s * stage_bytes);
+                    float4 *lo = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(hi) + part_bytes);
+                    // element-wise at identical offsets: the swizzled placement of hi and lo stays that of TMA
+                    for (int i = et; i < all_chunks; i += 128) {
+                        const float4 v = hi[i];
+                        float4 h, l;
+                        h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+                        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+                        hi[i] = h;
+                        lo[i] = l;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
+                    mbar_arrive(bar_split(s));
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
-                mbar_arrive(bar_split(s));
+                if (!ok) break;
             }
-        }
-        pdl_wait();  // M may still be read by the output transform of the forward before this one
-        if (mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
+            if (!waited) {  // M may still be read by the output transform of the forward before this one
+                pdl_wait();
+                waited = true;
+            }
+            const int acc = it & 1;
+            const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+            ok = mbar_wait(bar_acc_full(acc), acc_ph, abort_flag, P.status);
+            if (!ok) break;
             tc_fence_after();
-            const int q = warp & 3;  // TMEM lane quarter this warp may read
             const int row = oc0 + q * 32 + lane;
             float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
-            for (int c0 = 0; c0 < P.bn; c0 += 16) {
-                float v[16];
-                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * P.acc_cols);
+            for (int c0 = 0; c0 < P.bn; c0 += 32) {
+                float va[16], vb[16];
+                tc_ld16(t_addr + (uint32_t)c0, va);
+                const bool second = c0 + 16 < P.bn;
+                if (second) tc_ld16(t_addr + (uint32_t)(c0 + 16), vb);
+                if (c0 + 32 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
+                    tc_fence_before();
+                    mbar_arrive(bar_acc_empty(acc));
+                }
                 if (row < P.oc) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
                         if (t0 + c0 + j < P.tp)  // tp is a multiple of 8: a float4 never straddles the end
-                            *reinterpret_cast<float4 *>(dst + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            *reinterpret_cast<float4 *>(dst + c0 + j) = make_float4(va[j], va[j + 1], va[j + 2], va[j + 3]);
+                    if (second) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            if (t0 + c0 + 16 + j < P.tp)
+                                *reinterpret_cast<float4 *>(dst + c0 + 16 + j) =
+                                    make_float4(vb[j], vb[j + 1], vb[j + 2], vb[j + 3]);
+                    }
                 }
             }
         }
@@ -179,7 +242,8 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.tmem_cols)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)(2 * P.acc_cols))
                      : "memory");
     }
 }
@@ -200,26 +264,30 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.tp = g.tp;
     P.bn = bn;
     P.num_kb = (g.icp + BK - 1) / BK;
-    P.tmem_cols = pow2_at_least(bn, 32);
+    P.acc_cols = pow2_at_least(bn, 32);  // two accumulators: 2 * acc_cols TMEM columns (<= 512)
+    P.n_tile_blk = n_blk;
+    P.n_oc_blk = (int)ceil_div(g.oc, BM);
+    P.n_items = P.n_tile_blk * P.n_oc_blk * 64;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
-    // More CTAs than SMs: size the ring so that two CTAs share an SM (the second one's loads and
-    // prologue then overlap the first one's epilogue); otherwise one CTA takes the whole SM.
-    const size_t n_ctas = (size_t)n_blk * ceil_div(g.oc, BM) * 64;
-    const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024
-                                              : (n_ctas > (size_t)ctx->sm_count ? 104 * 1024 : 200 * 1024);
+    // More work items than SMs: size the ring so that two CTAs share an SM (one CTA's loads then overlap the
+    // other's epilogue); otherwise one CTA takes the whole SM.  512 TMEM columns cannot be shared.
+    const bool two_per_sm = P.n_items > ctx->sm_count && 2 * P.acc_cols <= 256;
+    const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024 : (two_per_sm ? 104 * 1024 : 200 * 1024);
     int stages = (int)(budget / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages > P.num_kb) stages = P.num_kb;
     if (stages < 2) stages = 2;
     P.stages = stages;
     const size_t smem = 512 + 1024 + stages * stage_bytes;
     FC_REQUIRE(smem <= 227 * 1024, FC_ERR_UNSUPPORTED, "tile block of %d does not fit the shared-memory ring", bn);
+    const int per_sm = (2 * P.acc_cols > 256 || smem > 113 * 1024) ? 1 : 2;
+    int ctas = ctx->sm_count * per_sm;
+    if (ctas > P.n_items) ctas = P.n_items;
 
     CUtensorMap tmU, tmV;
     FC_PROPAGATE(make_map_3d(&tmU, d_U, g.icp, g.oc, 64, BM));
     FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, bn));
 
-    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(g.oc, BM), 64), block(TC_THREADS);
+    dim3 grid((unsigned)ctas), block(TC_THREADS);
     if (split) {
         FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FC_CHECK_CUDA(launch_pdl(wino_gemm_tc_kernel<true>, grid, block, smem, ctx->stream, tmU, tmV, P));

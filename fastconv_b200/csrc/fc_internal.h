@@ -75,6 +75,7 @@ struct fc_context {
     cudaEvent_t ev[6];
     cudaEvent_t user_ev[FC_TIMER_SLOTS];
     int *d_status;  // device word kernels with bounded waits report into
+    cudaStream_t copy_in, copy_out;  // created on first use by the pipelined host forward
 };
 
 // Programmatic dependent launch.  Every kernel of the forward path is launched with the

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import sys
+import weakref
 from typing import Optional
 
 import numpy as np
@@ -43,10 +44,17 @@ class Context:
         self._h = h
         self.device = device
         self._pinned = []
+        self._children = weakref.WeakSet()  # layers / layer lists planned on this context
+
+    def adopt(self, child) -> None:
+        """Registers an object with a release()/close() method that must run before the context goes."""
+        self._children.add(child)
 
     # -- lifetime ---------------------------------------------------------------------------
     def close(self) -> None:
         if getattr(self, "_h", None):
+            for child in list(self._children):  # their device buffers live in this context's arena
+                (getattr(child, "release", None) or child.close)()
             for p in self._pinned:
                 self._lib.fc_host_free_pinned(p)
             self._pinned = []
@@ -257,6 +265,7 @@ class ConvLayer:
         check(self._lib.fc_conv_create(self.ctx.handle, C.byref(self.desc), self._algo, self.mode,
                                        _ptr(self.kernel_data), C.byref(h)), "fc_conv_create")
         self._conv = h
+        self.ctx.adopt(self)
 
     def _forward_iterations(self, labels) -> None:
         """`iterations` forwards from host memory; prints the reference's timing lines with device times."""
@@ -373,12 +382,21 @@ class LayerList:
                                              arr(*[int(p) for p in d_ins]), arr(*[int(p) for p in d_outs]), n,
                                              C.byref(h)), "fc_layer_list_create")
         self._h = h
+        ctx.adopt(self)
         k = C.c_int()
         check(self._lib.fc_layer_list_launches(h, C.byref(k)), "fc_layer_list_launches")
         self.kernel_launches = k.value
 
     def forward(self) -> None:
         check(self._lib.fc_layer_list_forward(self._h), "fc_layer_list_forward")
+
+    def forward_host(self, host_ins, host_outs) -> None:
+        """All layers from/to host arrays; uploads, kernels and downloads of neighbouring layers overlap."""
+        n = len(host_ins)
+        arr = C.c_void_p * n
+        check(self._lib.fc_layer_list_forward_host(self._h, arr(*[a.ctypes.data for a in host_ins]),
+                                                   arr(*[a.ctypes.data for a in host_outs])),
+              "fc_layer_list_forward_host")
 
     def close(self) -> None:
         if self._h:

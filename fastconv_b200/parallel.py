@@ -125,8 +125,14 @@ class KShardedConv:
                        "fc_conv_forward_device")
             return state["slab"]
 
+        def release():
+            if "conv" in state:
+                lib.fc_conv_destroy(state.pop("conv"))
+
         obj = cls(weights, forward_slab, group)
         obj._state = state
+        obj.release = release
+        ctx.adopt(obj)
         # torch sees the library's stream as an external stream: with it current, the all-gather is ordered
         # after the kernels without a host synchronisation, and CUDA events on it time both
         obj.stream = torch.cuda.ExternalStream(ctx.stream.value, device=f"cuda:{ctx.device}")

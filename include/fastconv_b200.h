@@ -211,6 +211,10 @@ typedef struct fc_layer_list fc_layer_list;
 int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *const *d_ins, float *const *d_outs,
                          int count, fc_layer_list **out);
 int fc_layer_list_forward(fc_layer_list *list);
+/* The same list from / to HOST memory (pinned buffers recommended): layer i's input upload, its
+ * kernels and its output download run on three streams chained by events, so the PCIe traffic of
+ * neighbouring layers overlaps in both directions with the kernels.  Synchronous on return. */
+int fc_layer_list_forward_host(fc_layer_list *list, const float *const *h_ins, float *const *h_outs);
 int fc_layer_list_launches(const fc_layer_list *list, int *kernel_launches);
 int fc_layer_list_destroy(fc_layer_list *list);
 

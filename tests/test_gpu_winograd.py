@@ -226,6 +226,13 @@ def test_layer_list_graph_replays_every_layer(ctx, oracle):
     ctx.synchronize()
     for o, want in zip(outs, wants):
         assert np.array_equal(ctx.download(o, want.shape), want)
+    # the host-buffer form of the same list (uploads / kernels / downloads pipelined over three streams)
+    xs = [synth.conv_input(n, ic, ih, iw, 600 + i) for i, (n, ic, oc, ih, iw) in enumerate(specs)]
+    ws = [synth.conv_weights(oc, ic, 3, 3, 400 + i) for i, (n, ic, oc, ih, iw) in enumerate(specs)]
+    host_out = [np.zeros_like(w_) for w_ in wants]
+    stack.forward_host(xs, host_out)
+    for x_, w_, got in zip(xs, ws, host_out):
+        assert np.array_equal(got, oracle.wino_forward(x_, w_, 1))
     stack.close()
     for h in convs:
         lib.fc_conv_destroy(h)
