@@ -67,8 +67,8 @@ SIGNATURES = {
     "fc_conv_output_size": (C.c_int, [_dp, _ip, _ip]),
     "fc_select_algorithm": (C.c_int, [_dp, _ip]),
     "fc_wino_buffer_elems": (C.c_int, [_dp, C.c_int, _szp, _szp, _szp]),
-    "fc_wino_filter_transform": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int]),
-    "fc_wino_input_transform": (C.c_int, [_vp, _vp, _vp, _dp]),
+    "fc_wino_filter_transform": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
+    "fc_wino_input_transform": (C.c_int, [_vp, _vp, _vp, _dp, C.c_int]),
     "fc_wino_tensor_gemm": (C.c_int, [_vp, _vp, _vp, _vp, _dp, C.c_int]),
     "fc_wino_output_transform": (C.c_int, [_vp, _vp, _vp, _dp]),
     "fc_wino_forward": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _dp, C.c_int, _fp]),

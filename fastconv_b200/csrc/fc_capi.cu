@@ -63,6 +63,9 @@ int wino_geom(const fc_conv_desc *d, WinoGeom *g) {
     g->tiles = (int)tiles;
     g->icp = round_up(g->ic, 8);
     g->tp = round_up(g->tiles, 8);
+    g->n_ocb = (g->oc + U_BOX_ROWS - 1) / U_BOX_ROWS;
+    g->n_kb = (g->ic + U_BOX_COLS - 1) / U_BOX_COLS;
+    g->ocp = round_up(g->oc, 4);
     return FC_OK;
 }
 
@@ -366,11 +369,15 @@ int fc_select_algorithm(const fc_conv_desc *d, int *algo) {
     return FC_OK;
 }
 
+static size_t u_elems_for(const WinoGeom &g, int mode) {
+    return rowmajor_layout(mode) ? (size_t)64 * g.icp * g.ocp : (size_t)64 * g.n_ocb * g.n_kb * U_BOX_ELEMS;
+}
+
 int fc_wino_buffer_elems(const fc_conv_desc *d, int mode, size_t *u, size_t *v, size_t *m) {
-    (void)mode;
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32, FC_ERR_INVALID_ARG, "unknown math mode %d", mode);
     WinoGeom g;
     FC_PROPAGATE(wino_geom(d, &g));
-    if (u) *u = (size_t)64 * g.oc * g.icp;
+    if (u) *u = u_elems_for(g, mode);
     if (v) *v = (size_t)64 * g.tp * g.icp;
     if (m) *m = (size_t)64 * g.oc * g.tp;
     return FC_OK;
@@ -378,19 +385,27 @@ int fc_wino_buffer_elems(const fc_conv_desc *d, int mode, size_t *u, size_t *v, 
 
 // ---- Winograd stages -----------------------------------------------------------------------
 
-int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic) {
+int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int mode) {
     FC_REQUIRE(ctx && d_kernel && d_U, FC_ERR_INVALID_ARG, "NULL argument");
     FC_REQUIRE(oc > 0 && ic > 0, FC_ERR_INVALID_ARG, "non-positive channel count");
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32, FC_ERR_INVALID_ARG, "unknown math mode %d", mode);
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
-    return launch_filter_transform(ctx, d_kernel, d_U, oc, ic, round_up(ic, 8));
+    return rowmajor_layout(mode) ? launch_filter_transform_rowmajor(ctx, d_kernel, d_U, oc, ic)
+                                 : launch_filter_transform(ctx, d_kernel, d_U, oc, ic);
 }
 
-int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc) {
+static int input_transform_dispatch(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g, int mode) {
+    return rowmajor_layout(mode) ? launch_input_transform_rowmajor(ctx, d_in, d_V, g)
+                                 : launch_input_transform(ctx, d_in, d_V, g);
+}
+
+int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc, int mode) {
     FC_REQUIRE(ctx && d_in && d_V, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32, FC_ERR_INVALID_ARG, "unknown math mode %d", mode);
     WinoGeom g;
     FC_PROPAGATE(wino_geom(desc, &g));
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
-    return launch_input_transform(ctx, d_in, d_V, g);
+    return input_transform_dispatch(ctx, d_in, d_V, g, mode);
 }
 
 static int wino_gemm_dispatch(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
@@ -427,7 +442,7 @@ int fc_wino_forward(fc_context *ctx, const float *d_in, const float *d_U, float 
     FC_PROPAGATE(wino_geom(desc, &g));
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
-    FC_PROPAGATE(launch_input_transform(ctx, d_in, d_V, g));
+    FC_PROPAGATE(input_transform_dispatch(ctx, d_in, d_V, g, mode));
     if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
     FC_PROPAGATE(wino_gemm_dispatch(ctx, d_U, d_V, d_M, g, mode));
     if (stage_ms) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
@@ -517,12 +532,13 @@ static int conv_prepare(fc_conv *c, int algo) {
     if (algo == FC_ALGO_WINOGRAD) {
         const WinoGeom &g = c->geom;
         const bool fresh = c->d_U == nullptr;
-        st = grab(ctx, &c->d_U, (size_t)64 * g.oc * g.icp);
+        st = grab(ctx, &c->d_U, u_elems_for(g, c->mode));
         if (st == FC_OK) st = grab(ctx, &c->d_V, (size_t)64 * g.tp * g.icp);
         if (st == FC_OK) st = grab(ctx, &c->d_M, (size_t)64 * g.oc * g.tp);
         if (st == FC_OK && fresh) {
             cudaEventRecord(ctx->ev[0], ctx->stream);
-            st = launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic, g.icp);
+            st = rowmajor_layout(c->mode) ? launch_filter_transform_rowmajor(ctx, c->d_kernel, c->d_U, g.oc, g.ic)
+                                          : launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic);
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
         }
@@ -615,7 +631,7 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     fc_context *ctx = c->ctx;
     if (c->algo == FC_ALGO_WINOGRAD) {
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
-        FC_PROPAGATE(launch_input_transform(ctx, d_in, c->d_V, c->geom));
+        FC_PROPAGATE(input_transform_dispatch(ctx, d_in, c->d_V, c->geom, c->mode));
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
         FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, c->geom, c->mode, &c->cfg));
         if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));

@@ -33,7 +33,13 @@ struct TcParams {
     int *status;
     int oc, tp, bn, num_kb, stages, acc_cols;
     int n_tile_blk, n_oc_blk, n_items;
+    int n_kb_u;  // boxes per (position, oc block) of the packed filter
 };
+
+// row coordinate of U box (p, ocb, kb) in the packed filter viewed as a [boxes*128][32] matrix
+__device__ __forceinline__ int u_box_row(const TcParams &P, int p, int oc0, int kb) {
+    return ((p * P.n_oc_blk + (oc0 >> 7)) * P.n_kb_u + kb) * U_BOX_ROWS;
+}
 
 __device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p, int &oc0, int &t0) {
     // tile block fastest, then oc block, then position: CTAs next to each other share the same U box
@@ -107,7 +113,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                     const int pre = P.num_kb < S ? P.num_kb : S;
                     for (; kb < pre; ++kb) {
                         mbar_expect_tx(bar_full(kb), part_bytes);
-                        tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), kb * BK, oc0, p);
+                        tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), 0, u_box_row(P, p, oc0, kb), 0);
                     }
                     pdl_wait();
                     for (int j = 0; j < pre; ++j)
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                     if (!ok) break;
                     const uint32_t a_dst = ring + s * stage_bytes;
                     mbar_expect_tx(bar_full(s), part_bytes);
-                    tma_load_3d(a_dst, &tmU, bar_full(s), kb * BK, oc0, p);
+                    tma_load_3d(a_dst, &tmU, bar_full(s), 0, u_box_row(P, p, oc0, kb), 0);
                     tma_load_3d(a_dst + A_BYTES, &tmV, bar_full(s), kb * BK, t0, p);
                 }
             }
@@ -266,7 +272,8 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.num_kb = (g.icp + BK - 1) / BK;
     P.acc_cols = pow2_at_least(bn, 32);  // two accumulators: 2 * acc_cols TMEM columns (<= 512)
     P.n_tile_blk = n_blk;
-    P.n_oc_blk = (int)ceil_div(g.oc, BM);
+    P.n_oc_blk = g.n_ocb;
+    P.n_kb_u = g.n_kb;
     P.n_items = P.n_tile_blk * P.n_oc_blk * 64;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
     // More work items than SMs: size the ring so that two CTAs share an SM (one CTA's loads then overlap the
@@ -284,7 +291,7 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     if (ctas > P.n_items) ctas = P.n_items;
 
     CUtensorMap tmU, tmV;
-    FC_PROPAGATE(make_map_3d(&tmU, d_U, g.icp, g.oc, 64, BM));
+    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, U_BOX_ROWS));
     FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, bn));
 
     dim3 grid((unsigned)ctas), block(TC_THREADS);

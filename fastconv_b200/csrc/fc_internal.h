@@ -46,7 +46,28 @@ inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 // output size as the reference driver derives it (winoF63ZC/winoF63ZC.cpp:334-338).
 struct WinoGeom {
     int n, ic, oc, ih, iw, pad, oh, ow, th, tw, tiles, icp, tp;
+    int n_ocb, n_kb;  // boxes of the packed filter: ceil(oc/128) x ceil(ic/32)
+    int ocp;          // oc rounded up to 4: row length of the FP32-mode filter layout U[p][ic][ocp]
 };
+
+// Two operand layouts, chosen by the arithmetic mode of the TensorGEMM:
+//   tensor-core modes  U packed 128x32 boxes (upack_index), V[p][tp][icp]   -- K-major, what UMMA/TMA want
+//   fp32 mirrored mode U[p][icp][ocp],                      V[p][icp][tp]   -- row index contiguous, so GEMM
+//                      tiles reach shared memory as [k][row] with async 16-byte copies and no transposition
+// M[p][oc][tp] is the same in both.
+inline bool rowmajor_layout(int mode) { return mode == FC_MATH_FP32_MIRRORED; }
+
+// The transformed filter U is stored as contiguous boxes of 128 output channels x 32 input channels
+// (16 KB each, zero padded): box (p, ocb, kb) starts at ((p*n_ocb + ocb)*n_kb + kb)*4096 floats and holds
+// element (oc, ic) at (oc%128)*32 + ic%32.  One box is exactly one TMA load / one shared-memory stage of
+// the GEMM kernels, so the dominant weight stream reads HBM in 16 KB contiguous pieces.
+constexpr int U_BOX_ROWS = 128, U_BOX_COLS = 32, U_BOX_ELEMS = U_BOX_ROWS * U_BOX_COLS;
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline size_t upack_index(int p, int oc, int ic, int n_ocb, int n_kb) {
+    return ((((size_t)p * n_ocb + (oc >> 7)) * n_kb + (ic >> 5)) * U_BOX_ROWS + (oc & 127)) * U_BOX_COLS + (ic & 31);
+}
 
 int wino_geom(const fc_conv_desc *d, WinoGeom *g);  // validates and fills
 
@@ -110,7 +131,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // kernel launchers (device pointers, context stream) ------------------------------------------
 namespace fc {
 
-int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int icp);
+int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
+int launch_filter_transform_rowmajor(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
+int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g);
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,

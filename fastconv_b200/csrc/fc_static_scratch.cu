@@ -54,7 +54,7 @@ extern "C" int fc_wino_forward_static_scratch(const float *d_in, const float *d_
     FC_REQUIRE(device >= 0 && device < kMaxDevices, FC_ERR_UNSUPPORTED, "device index %d not supported", device);
     float *scratch = nullptr;
     FC_PROPAGATE(scratch_for_current_device(device, &scratch));
-    float *d_V = scratch;            // [64][tp][icp]; v_elems is a multiple of 64, so M stays 256-byte aligned
+    float *d_V = scratch;            // [64][icp][tp]; v_elems is a multiple of 64, so M stays 256-byte aligned
     float *d_M = scratch + v_elems;  // [64][oc][tp]
 
     // The stage launchers only read the stream and the device index from a context.
@@ -67,7 +67,7 @@ extern "C" int fc_wino_forward_static_scratch(const float *d_in, const float *d_
     // Nothing in the scratch has to start at zero: the input transform writes every element of V it
     // owns, zero padding of the tile and channel axes included, and the GEMM writes every element of M
     // before the output transform reads it.  Whatever an earlier call left behind is overwritten.
-    FC_PROPAGATE(fc::launch_input_transform(&view, d_in, d_V, g));
+    FC_PROPAGATE(fc::launch_input_transform_rowmajor(&view, d_in, d_V, g));
     FC_PROPAGATE(fc::launch_wino_gemm_ffma(&view, d_U, d_V, d_M, g));
     FC_PROPAGATE(fc::launch_output_transform(&view, d_M, d_out, g));
     return FC_OK;

@@ -1,15 +1,16 @@
 // TensorGEMM, fp32 "mirrored" mode: 64 independent GEMMs
-//     M_p[oc][tile] = sum_ic U_p[oc][ic] * V_p[tile][ic]
+//     M_p[oc][tile] = sum_ic U_p[ic][oc] * V_p[ic][tile]
 // on the FP32 pipes, with the reference's accumulation chain kept exactly: every output element
 // owns ONE accumulator that starts at 0 and takes one fused multiply-add per input channel, in
 // ascending channel order (TensorGEMMInnerKernel4x4x5_v1, winoF63ZC/TensorGEMMZC.cpp:585-697;
 // ic blocks of the reference continue the same chain through gemmBuf).  No split-K, no pairwise
 // sums, no reordering -- that is what makes the layer bit-identical to the reference.
 //
-// Both operands are K-major in global memory (ic contiguous).  A CTA stages a BM x BK slab of U
-// and a BN x BK slab of V into shared memory transposed ([k][row], padded) so that the inner
-// product reads 128-bit rows without bank conflicts; global loads of the next slab are issued
-// before the math of the current one (register-staged double buffering).
+// Operands arrive in the row-major layouts U[p][icp][ocp] / V[p][icp][tp] (row index contiguous), so a
+// BK x BM slab of U and a BK x BN slab of V are sets of contiguous runs: they go to shared memory as
+// [k][row] with 16-byte asynchronous copies (cp.async, zero-filled past the edges) through a 4-stage
+// ring, and the inner product reads 128-bit rows without bank conflicts.  No register staging, no
+// transposition, two CTAs per SM.
 #include "fc_tc_common.cuh"
 
 namespace fc {
@@ -18,127 +19,106 @@ namespace {
 
 constexpr int BK = 16;
 constexpr int THREADS = 256;
+constexpr int STAGES = 4;
 
-template <int BM, int BN>
-struct FfmaCfg {
-    static constexpr int TM = BM / 16;  // rows (oc) per thread
-    static constexpr int TN = BN / 16;  // columns (tiles) per thread
-    static constexpr int LDA = BM + 4;
-    static constexpr int LDB = BN + 4;
-    static constexpr int A_F4 = BM * BK / 4 / THREADS;  // float4 loads per thread per slab
-    static constexpr int B_F4 = BN * BK / 4 / THREADS;
-    static_assert(TM % 4 == 0 && TN % 4 == 0, "thread tile must be float4-granular");
-    static_assert(A_F4 >= 1 && B_F4 >= 1, "slab too small for the thread count");
-};
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 template <int BM, int BN>
 __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float *__restrict__ U,
-                                                                 const float *__restrict__ V, float *__restrict__ M,
-                                                                 int oc, int tp, int icp) {
-    using C = FfmaCfg<BM, BN>;
-    __shared__ __align__(16) float As[2][BK][C::LDA];
-    __shared__ __align__(16) float Bs[2][BK][C::LDB];
+                                                                    const float *__restrict__ V, float *__restrict__ M,
+                                                                    int oc, int ocp, int tp, int icp) {
+    constexpr int TM = BM / 16, TN = BN / 16;  // outputs per thread: TM output channels x TN tiles
+    constexpr int A_CHUNKS = BK * BM / 4 / THREADS, B_CHUNKS = BK * BN / 4 / THREADS;
+    static_assert(A_CHUNKS >= 1 && B_CHUNKS >= 1 && TM % 4 == 0 && TN % 4 == 0, "block shape");
+    extern __shared__ __align__(16) float smem[];
+    float(*As)[BK][BM] = reinterpret_cast<float(*)[BK][BM]>(smem);
+    float(*Bs)[BK][BN] = reinterpret_cast<float(*)[BK][BN]>(smem + STAGES * BK * BM);
 
-    const int p = blockIdx.z;
-    const int oc0 = blockIdx.y * BM;
-    const int t0 = blockIdx.x * BN;
-    const float *Up = U + (size_t)p * oc * icp;
-    const float *Vp = V + (size_t)p * tp * icp;
-    float *Mp = M + (size_t)p * oc * tp;
+    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * BN;
+    const float *Up = U + (size_t)p * icp * ocp;
+    const float *Vp = V + (size_t)p * icp * tp;
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
 
-    const int tid = threadIdx.x;
-    const int tx = tid % 16, ty = tid / 16;
-
-    float4 a_stage[C::A_F4], b_stage[C::B_F4];
-
-    auto load_slab = [&](int k0) {
+    auto load_stage = [&](int stage, int k0) {
 #pragma unroll
-        for (int i = 0; i < C::A_F4; ++i) {
+        for (int i = 0; i < A_CHUNKS; ++i) {
             const int idx = tid + i * THREADS;
-            const int row = idx / (BK / 4), kq = idx % (BK / 4);
-            const int r = oc0 + row, k = k0 + kq * 4;
-            a_stage[i] = (r < oc && k < icp) ? __ldg(reinterpret_cast<const float4 *>(Up + (size_t)r * icp + k))
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            const int kr = idx / (BM / 4), c4 = (idx % (BM / 4)) * 4;
+            const int k = k0 + kr, col = oc0 + c4;
+            const bool ok = k < icp && col < ocp;
+            cp_async_16(&As[stage][kr][c4], Up + (ok ? (size_t)k * ocp + col : 0), ok);
         }
 #pragma unroll
-        for (int i = 0; i < C::B_F4; ++i) {
+        for (int i = 0; i < B_CHUNKS; ++i) {
             const int idx = tid + i * THREADS;
-            const int row = idx / (BK / 4), kq = idx % (BK / 4);
-            const int r = t0 + row, k = k0 + kq * 4;
-            b_stage[i] = (r < tp && k < icp) ? __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)r * icp + k))
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    };
-    auto store_slab = [&](int buf) {
-#pragma unroll
-        for (int i = 0; i < C::A_F4; ++i) {
-            const int idx = tid + i * THREADS;
-            const int row = idx / (BK / 4), kq = idx % (BK / 4);
-            As[buf][kq * 4 + 0][row] = a_stage[i].x;
-            As[buf][kq * 4 + 1][row] = a_stage[i].y;
-            As[buf][kq * 4 + 2][row] = a_stage[i].z;
-            As[buf][kq * 4 + 3][row] = a_stage[i].w;
-        }
-#pragma unroll
-        for (int i = 0; i < C::B_F4; ++i) {
-            const int idx = tid + i * THREADS;
-            const int row = idx / (BK / 4), kq = idx % (BK / 4);
-            Bs[buf][kq * 4 + 0][row] = b_stage[i].x;
-            Bs[buf][kq * 4 + 1][row] = b_stage[i].y;
-            Bs[buf][kq * 4 + 2][row] = b_stage[i].z;
-            Bs[buf][kq * 4 + 3][row] = b_stage[i].w;
+            const int kr = idx / (BN / 4), c4 = (idx % (BN / 4)) * 4;
+            const int k = k0 + kr, col = t0 + c4;
+            const bool ok = k < icp && col < tp;
+            cp_async_16(&Bs[stage][kr][c4], Vp + (ok ? (size_t)k * tp + col : 0), ok);
         }
     };
 
-    float acc[C::TM][C::TN];
+    float acc[TM][TN];
 #pragma unroll
-    for (int i = 0; i < C::TM; ++i)
+    for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < C::TN; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
     pdl_trigger();
-    pdl_wait();
-
-    load_slab(0);
-    store_slab(0);
-    __syncthreads();
+    pdl_wait();  // V comes from the input transform launched just before
 
     const int n_slabs = (icp + BK - 1) / BK;
-    for (int s = 0; s < n_slabs; ++s) {
-        const int buf = s & 1;
-        if (s + 1 < n_slabs) load_slab((s + 1) * BK);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_slabs) load_stage(s, s * BK);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < n_slabs; ++kt) {
+        cp_async_wait<STAGES - 2>();  // slab kt has landed (for this thread's copies) ...
+        __syncthreads();              // ... and for everyone's; everyone is also done with slab kt-1
+        const int next = kt + STAGES - 1;
+        if (next < n_slabs) load_stage(next % STAGES, next * BK);  // overwrites the stage slab kt-1 used
+        cp_async_commit();
+        const int buf = kt % STAGES;
 #pragma unroll
         for (int k = 0; k < BK; ++k) {
-            float a[C::TM], b[C::TN];
-            // rows are split in float4 groups strided by 64 (16 threads x 4) so a warp's 128-bit
-            // reads of one k-row touch consecutive banks
+            float a[TM], b[TN];
+            // rows are taken in float4 groups strided by 64 (16 threads x 4), so a warp's 128-bit reads
+            // of one k-row touch consecutive banks
 #pragma unroll
-            for (int g = 0; g < C::TM / 4; ++g) {
+            for (int g = 0; g < TM / 4; ++g) {
                 const float4 v = *reinterpret_cast<const float4 *>(&As[buf][k][g * 64 + ty * 4]);
                 a[g * 4 + 0] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
             }
 #pragma unroll
-            for (int g = 0; g < C::TN / 4; ++g) {
+            for (int g = 0; g < TN / 4; ++g) {
                 const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][k][g * 64 + tx * 4]);
                 b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
             }
 #pragma unroll
-            for (int i = 0; i < C::TM; ++i)
+            for (int i = 0; i < TM; ++i)
 #pragma unroll
-                for (int j = 0; j < C::TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
-        }
-        if (s + 1 < n_slabs) {
-            store_slab(buf ^ 1);
-            __syncthreads();
+                for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
         }
     }
+    cp_async_wait<0>();
 
+    float *Mp = M + (size_t)p * oc * tp;
 #pragma unroll
-    for (int i = 0; i < C::TM; ++i) {
+    for (int i = 0; i < TM; ++i) {
         const int r = oc0 + (i / 4) * 64 + ty * 4 + (i % 4);
         if (r >= oc) continue;
 #pragma unroll
-        for (int g = 0; g < C::TN / 4; ++g) {
+        for (int g = 0; g < TN / 4; ++g) {
             const int c = t0 + g * 64 + tx * 4;
             if (c < tp)  // tp is a multiple of 8, so a float4 never straddles the end
                 *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) =
@@ -150,81 +130,12 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
 // ---------------------------------------------------------------------------------------------
 // Few tiles (small feature maps at batch 1: 28x28 -> 25 tiles, 14x14 -> 9, 7x7 -> 4).  The GEMM is a
 // stream over U with a short N, so the blocked kernel above would multiply mostly padding.  Here a
-// thread owns ONE output channel and ALL TN tiles of a position: its row of U goes straight from
-// global memory to registers (each element is used by exactly this thread), V_p is staged transposed
-// in shared memory a K-chunk at a time and read as broadcasts, and the TN accumulators take one FMA
-// per input channel in ascending order -- the same chain as the blocked kernel and the reference.
-// ---------------------------------------------------------------------------------------------
-constexpr int SK_THREADS = 128;
-constexpr int SK_KC = 256;  // input channels staged per chunk
-
-template <int TN>
-__global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const float *__restrict__ U,
-                                                                           const float *__restrict__ V,
-                                                                           float *__restrict__ M, int oc, int tp,
-                                                                           int icp) {
-    constexpr int TNP = (TN + 3) / 4 * 4;
-    __shared__ __align__(16) float Vs[SK_KC * TNP];
-    const int tid = threadIdx.x;
-    const int p = blockIdx.y;
-    const int row = blockIdx.x * SK_THREADS + tid;
-    const int row_ld = row < oc ? row : oc - 1;
-    const float *up = U + ((size_t)p * oc + row_ld) * icp;
-    const float *Vp = V + (size_t)p * tp * icp;
-
-    float acc[TN];
-#pragma unroll
-    for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
-
-    pdl_trigger();
-    pdl_wait();
-
-    for (int k0 = 0; k0 < icp; k0 += SK_KC) {
-        const int kc = min(SK_KC, icp - k0);  // multiple of 8
-        __syncthreads();
-        // stage V_p[t][k0..k0+kc) as Vs[k][t]; consecutive threads take consecutive tiles
-        for (int idx = tid; idx < TNP * (kc / 4); idx += SK_THREADS) {
-            const int t = idx % TNP, k4 = idx / TNP;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < tp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)t * icp + k0 + k4 * 4));
-            Vs[(k4 * 4 + 0) * TNP + t] = v.x;
-            Vs[(k4 * 4 + 1) * TNP + t] = v.y;
-            Vs[(k4 * 4 + 2) * TNP + t] = v.z;
-            Vs[(k4 * 4 + 3) * TNP + t] = v.w;
-        }
-        __syncthreads();
-        float4 u_next = __ldg(reinterpret_cast<const float4 *>(up + k0));
-        for (int k = 0; k < kc; k += 4) {
-            const float4 u = u_next;
-            if (k + 4 < kc) u_next = __ldg(reinterpret_cast<const float4 *>(up + k0 + k + 4));
-            const float uu[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const float4 *b4 = reinterpret_cast<const float4 *>(&Vs[(k + kk) * TNP]);
-#pragma unroll
-                for (int g = 0; g < TNP / 4; ++g) {
-                    const float4 b = b4[g];
-                    if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(uu[kk], b.x, acc[g * 4 + 0]);
-                    if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(uu[kk], b.y, acc[g * 4 + 1]);
-                    if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(uu[kk], b.z, acc[g * 4 + 2]);
-                    if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(uu[kk], b.w, acc[g * 4 + 3]);
-                }
-            }
-        }
-    }
-    if (row < oc) {
-        float *dst = M + ((size_t)p * oc + row) * tp;
-#pragma unroll
-        for (int j = 0; j < TN; ++j)
-            if (j < tp) dst[j] = acc[j];
-    }
-}
-
-// Same computation with U streamed by TMA: a producer warp keeps a ring of 128(oc) x 32(ic) boxes of U in
-// flight (128-byte swizzle), so HBM latency is hidden by the ring instead of by each thread's own
-// loads; the 128 consumer threads read their row of the landed box (conflict-free through the swizzle),
-// V_p is staged transposed a 256-channel chunk at a time.  The chain per output element is unchanged:
+// thread owns ONE output channel and ALL TN tiles of a position.  A producer warp keeps a ring of
+// 32(ic) x 128(oc) boxes of U in flight with TMA, so HBM latency is hidden by the ring; consumer thread
+// t reads column t of the landed box (consecutive lanes, consecutive words).  V_p is staged a
+// 256-channel chunk at a time and read as broadcasts.  The chain per output element is unchanged:
 // one accumulator, one FMA per input channel, ascending.
+// ---------------------------------------------------------------------------------------------
 constexpr int ST_STAGES = 5;
 constexpr int ST_KC = 256;
 constexpr int ST_THREADS = 160;  // 4 consumer warps + 1 producer warp
@@ -240,8 +151,8 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
     extern __shared__ uint8_t smem_raw[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[ST_STAGES], empty[ST_STAGES]
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * ST_STAGES);
-    const uint32_t ring = (smem_u32(smem_raw) + 128 + 1023) & ~1023u;
-    const uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    const uint32_t ring = (smem_u32(smem_raw) + 128 + 127) & ~127u;
+    const float *ring_ptr = reinterpret_cast<const float *>(smem_raw + (ring - smem_u32(smem_raw)));
     float *Vs = reinterpret_cast<float *>(smem_raw + (ring - smem_u32(smem_raw)) + ST_STAGES * ST_BOX);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -268,13 +179,13 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
                 const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
                 if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status)) break;
                 mbar_expect_tx(bar_full(s), ST_BOX);
-                tma_load_3d(ring + s * ST_BOX, &tmU, bar_full(s), kb * 32, oc0, p);
+                tma_load_3d(ring + s * ST_BOX, &tmU, bar_full(s), oc0, kb * 32, p);  // box: 128 oc x 32 ic
             }
         }
     } else {
         pdl_wait();  // V comes from the input transform launched just before
         const int row = oc0 + tid;
-        const float *Vp = V + (size_t)p * tp * icp;
+        const float *Vp = V + (size_t)p * icp * tp;
         float acc[TN];
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
@@ -285,14 +196,11 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
             if (kb % (ST_KC / 32) == 0) {
                 const int k0 = kb * 32;
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // consumers only: everyone is done with the old chunk
-                for (int idx = tid; idx < TNP * (ST_KC / 4); idx += 128) {
-                    const int t = idx % TNP, k4 = idx / TNP;
+                for (int idx = tid; idx < ST_KC * (TNP / 4); idx += 128) {
+                    const int k = idx / (TNP / 4), t4 = (idx % (TNP / 4)) * 4;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (t < tp && k0 + k4 * 4 < icp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)t * icp + k0 + k4 * 4));
-                    Vs[(k4 * 4 + 0) * TNP + t] = v.x;
-                    Vs[(k4 * 4 + 1) * TNP + t] = v.y;
-                    Vs[(k4 * 4 + 2) * TNP + t] = v.z;
-                    Vs[(k4 * 4 + 3) * TNP + t] = v.w;
+                    if (k0 + k < icp && t4 < tp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)(k0 + k) * tp + t4));
+                    *reinterpret_cast<float4 *>(&Vs[k * TNP + t4]) = v;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
@@ -300,23 +208,19 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
             const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), ph, abort_flag, status));
             if (!ok) continue;
-            const uint8_t *a = ring_ptr + s * ST_BOX + tid * 128;  // this thread's oc row: 32 floats, swizzled
+            const float *a = ring_ptr + (size_t)s * (ST_BOX / 4) + tid;  // this thread's oc column of the box
             const float *vk = Vs + (size_t)(kb % (ST_KC / 32)) * 32 * TNP;
+#pragma unroll 8
+            for (int kk = 0; kk < 32; ++kk) {
+                const float u = a[kk * 128];
+                const float4 *b4 = reinterpret_cast<const float4 *>(vk + kk * TNP);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float4 u = *reinterpret_cast<const float4 *>(a + ((c ^ (tid & 7)) << 4));
-                const float uu[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const float4 *b4 = reinterpret_cast<const float4 *>(vk + (c * 4 + kk) * TNP);
-#pragma unroll
-                    for (int g = 0; g < TNP / 4; ++g) {
-                        const float4 b = b4[g];
-                        if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(uu[kk], b.x, acc[g * 4 + 0]);
-                        if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(uu[kk], b.y, acc[g * 4 + 1]);
-                        if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(uu[kk], b.z, acc[g * 4 + 2]);
-                        if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(uu[kk], b.w, acc[g * 4 + 3]);
-                    }
+                for (int g = 0; g < TNP / 4; ++g) {
+                    const float4 b = b4[g];
+                    if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(u, b.x, acc[g * 4 + 0]);
+                    if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(u, b.y, acc[g * 4 + 1]);
+                    if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(u, b.z, acc[g * 4 + 2]);
+                    if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(u, b.w, acc[g * 4 + 3]);
                 }
             }
             __syncwarp();
@@ -325,7 +229,8 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
         if (ok && row < oc) {
             float *dst = M + ((size_t)p * oc + row) * tp;
 #pragma unroll
-            for (int j = 0; j < TN; ++j) dst[j] = acc[j];
+            for (int j = 0; j < TN; ++j)
+                if (j < tp) dst[j] = acc[j];
         }
     }
     if (*abort_flag) {
@@ -333,21 +238,100 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
     }
 }
 
-bool skinny_uses_tma() {
-    static int state = -1;
-    if (state < 0) {
-        const char *e = getenv("FASTCONV_SKINNY");
-        state = (e && e[0] == 'l') ? 0 : 1;  // FASTCONV_SKINNY=ldg keeps the per-thread global loads
+// The same computation with plain loads (no mbarriers, no status word), for callers that have no
+// context: consecutive threads read consecutive output channels of U[p][k][.], one coalesced line per k.
+constexpr int SK_THREADS = 128;
+constexpr int SK_KC = 256;
+
+template <int TN>
+__global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const float *__restrict__ U,
+                                                                           const float *__restrict__ V,
+                                                                           float *__restrict__ M, int oc, int ocp,
+                                                                           int tp, int icp) {
+    constexpr int TNP = (TN + 3) / 4 * 4;
+    __shared__ __align__(16) float Vs[SK_KC * TNP];
+    const int tid = threadIdx.x;
+    const int p = blockIdx.y;
+    const int row = blockIdx.x * SK_THREADS + tid;
+    const int row_ld = row < ocp ? row : ocp - 1;
+    const float *up = U + (size_t)p * icp * ocp + row_ld;
+    const float *Vp = V + (size_t)p * icp * tp;
+
+    float acc[TN];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
+    pdl_trigger();
+    pdl_wait();
+
+    for (int k0 = 0; k0 < icp; k0 += SK_KC) {
+        const int kc = min(SK_KC, icp - k0);
+        __syncthreads();
+        for (int idx = tid; idx < kc * (TNP / 4); idx += SK_THREADS) {
+            const int k = idx / (TNP / 4), t4 = (idx % (TNP / 4)) * 4;
+            *reinterpret_cast<float4 *>(&Vs[k * TNP + t4]) =
+                t4 < tp ? __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)(k0 + k) * tp + t4))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncthreads();
+        float u_next[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) u_next[q] = q < kc ? __ldg(up + (size_t)(k0 + q) * ocp) : 0.0f;
+        for (int k = 0; k < kc; k += 4) {
+            float uu[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) uu[q] = u_next[q];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) u_next[q] = k + 4 + q < kc ? __ldg(up + (size_t)(k0 + k + 4 + q) * ocp) : 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                if (k + kk >= kc) break;
+                const float4 *b4 = reinterpret_cast<const float4 *>(&Vs[(k + kk) * TNP]);
+#pragma unroll
+                for (int g = 0; g < TNP / 4; ++g) {
+                    const float4 b = b4[g];
+                    if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(uu[kk], b.x, acc[g * 4 + 0]);
+                    if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(uu[kk], b.y, acc[g * 4 + 1]);
+                    if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(uu[kk], b.z, acc[g * 4 + 2]);
+                    if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(uu[kk], b.w, acc[g * 4 + 3]);
+                }
+            }
+        }
     }
-    return state == 1;
+    if (row < oc) {
+        float *dst = M + ((size_t)p * oc + row) * tp;
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+            if (j < tp) dst[j] = acc[j];
+    }
+}
+
+// U[p][icp][ocp] as a 3-D tensor (oc, ic, p), box = 128 oc x 32 ic, no swizzle, zero fill outside
+int make_map_u_rowmajor(CUtensorMap *map, const float *base, int ocp, int icp) {
+    tc::EncodeTiledFn enc;
+    FC_PROPAGATE(tc::get_encoder(&enc));
+    cuuint64_t dims[3] = {(cuuint64_t)ocp, (cuuint64_t)icp, 64};
+    cuuint64_t strides[2] = {(cuuint64_t)ocp * 4, (cuuint64_t)ocp * icp * 4};
+    cuuint32_t box[3] = {128, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (ocp %d icp %d)", (int)r, ocp, icp);
+    return FC_OK;
 }
 
 template <int TN>
-int launch_skinny_tma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    if (ctx->d_status == nullptr) {  // no context behind the call: the plain-load kernel
+        dim3 grid((unsigned)ceil_div(g.oc, SK_THREADS), 64), block(SK_THREADS);
+        FC_CHECK_CUDA(launch_pdl(wino_gemm_ffma_skinny_kernel<TN>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.ocp,
+                                 g.tp, g.icp));
+        return FC_OK;
+    }
     constexpr int TNP = (TN + 3) / 4 * 4;
     CUtensorMap tmU;
-    FC_PROPAGATE(tc::make_map_3d(&tmU, d_U, g.icp, g.oc, 64, 128));
-    const size_t smem = 128 + 1024 + (size_t)ST_STAGES * ST_BOX + (size_t)ST_KC * TNP * sizeof(float);
+    FC_PROPAGATE(make_map_u_rowmajor(&tmU, d_U, g.ocp, g.icp));
+    const size_t smem = 128 + 128 + (size_t)ST_STAGES * ST_BOX + (size_t)ST_KC * TNP * sizeof(float);
     FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_skinny_tma_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid((unsigned)ceil_div(g.oc, 128), 64), block(ST_THREADS);
@@ -356,11 +340,13 @@ int launch_skinny_tma(fc_context *ctx, const float *d_U, const float *d_V, float
     return FC_OK;
 }
 
-template <int TN>
-int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
-    if (skinny_uses_tma() && ctx->d_status != nullptr) return launch_skinny_tma<TN>(ctx, d_U, d_V, d_M, g);
-    dim3 grid((unsigned)ceil_div(g.oc, SK_THREADS), 64), block(SK_THREADS);
-    FC_CHECK_CUDA(launch_pdl(wino_gemm_ffma_skinny_kernel<TN>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp));
+template <int BM, int BN>
+int launch_blocked(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    const size_t smem = (size_t)STAGES * BK * (BM + BN) * sizeof(float);
+    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)ceil_div(g.tp, BN), (unsigned)ceil_div(g.oc, BM), 64), block(THREADS);
+    FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<BM, BN>, grid, block, smem, ctx->stream, d_U, d_V, d_M, g.oc, g.ocp,
+                              g.tp, g.icp)));
     return FC_OK;
 }
 
@@ -381,22 +367,36 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
         if (t <= 28) return launch_skinny<28>(ctx, d_U, d_V, d_M, g);
         return launch_skinny<32>(ctx, d_U, d_V, d_M, g);
     }
-    // 64 is the float4-group stride of the thread mapping, so BM and BN are 64 or 128.
-    const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : g.tp > 64;
-    const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : g.oc > 64;
-    const unsigned gx_n = (unsigned)ceil_div(g.tp, wide_n ? 128 : 64);
-    const unsigned gy_m = (unsigned)ceil_div(g.oc, wide_m ? 128 : 64);
-    dim3 grid(gx_n, gy_m, 64), block(THREADS);
-    if (wide_m && wide_n)
-        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<128, 128>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
-    else if (wide_m)
-        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<128, 64>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
-    else if (wide_n)
-        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<64, 128>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
-    else
-        FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<64, 64>, grid, block, 0, ctx->stream, d_U, d_V, d_M, g.oc, g.tp, g.icp)));
-    FC_CHECK_CUDA(cudaGetLastError());
-    return FC_OK;
+    // 64 is the float4-group stride of the thread mapping, so BM and BN are 64 or 128.  Without a tuned
+    // configuration: the largest block that still gives every SM about one and a half CTAs (at batch 1 the
+    // GEMMs are small and a 128x128 grid would leave the machine half empty), else the one with most CTAs.
+    bool wide_m = g.oc > 64, wide_n = g.tp > 64;
+    if (cfg && (cfg->bm || cfg->bn)) {
+        if (cfg->bm) wide_m = cfg->bm == 128;
+        if (cfg->bn) wide_n = cfg->bn == 128;
+    } else {
+        const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+        const int shapes[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
+        size_t best_ctas = 0;
+        for (const auto &sh : shapes) {
+            if ((sh[0] == 128 && g.oc <= 64) || (sh[1] == 128 && g.tp <= 64)) continue;
+            const size_t ctas = ceil_div(g.oc, sh[0]) * ceil_div(g.tp, sh[1]) * 64;
+            if (2 * ctas >= 3 * (size_t)sms) {
+                wide_m = sh[0] == 128;
+                wide_n = sh[1] == 128;
+                break;
+            }
+            if (ctas > best_ctas) {
+                best_ctas = ctas;
+                wide_m = sh[0] == 128;
+                wide_n = sh[1] == 128;
+            }
+        }
+    }
+    if (wide_m && wide_n) return launch_blocked<128, 128>(ctx, d_U, d_V, d_M, g);
+    if (wide_m) return launch_blocked<128, 64>(ctx, d_U, d_V, d_M, g);
+    if (wide_n) return launch_blocked<64, 128>(ctx, d_U, d_V, d_M, g);
+    return launch_blocked<64, 64>(ctx, d_U, d_V, d_M, g);
 }
 
 }  // namespace fc

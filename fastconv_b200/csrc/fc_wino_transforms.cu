@@ -7,7 +7,7 @@
 // and __fmaf_rn appears exactly where the reference issues vfmaq_f32.
 //
 // Layouts (ic contiguous, padded with zeros to icp = roundup(ic, 8)):
-//   U[p][oc][icp]   V[p][tp][icp]   M[p][oc][tp]     p = col*8 + row
+//   U: packed 128 x 32 boxes (upack_index)   V[p][tp][icp]   M[p][oc][tp]     p = col*8 + row
 #include "fc_internal.h"
 
 namespace fc {
@@ -87,17 +87,19 @@ __device__ __forceinline__ void output_transform_1d(float m0, float m1, float m2
 
 // ---------------------------------------------------------------------------------------------
 // Filter transform: U = G g G^T, G over the filter rows first, then over the columns
-// (offline_kernel_transform_v1, winoF63ZC/winoF63ZC.cpp:286-297).  One thread per (oc, ic);
-// threads of a warp walk ic so the 64 stores per thread are coalesced.
+// (offline_kernel_transform_v1, winoF63ZC/winoF63ZC.cpp:286-297).  One thread per (oc, ic) of the padded
+// box grid; threads of a warp walk ic, so each of the 64 stores per thread is one 128-byte row of a
+// packed 128 x 32 box (see upack_index).  Padding rows and columns are written as zeros.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) filter_transform_kernel(const float *__restrict__ kernel,
-                                                               float *__restrict__ U, int oc, int ic, int icp) {
+                                                               float *__restrict__ U, int oc, int ic, int n_ocb,
+                                                               int n_kb) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int k = blockIdx.y;
-    if (c >= icp) return;
-    const size_t plane = (size_t)oc * icp;
-    float *dst = U + (size_t)k * icp + c;
-    if (c >= ic) {  // zero padding of the reduction axis
+    if (c >= n_kb * U_BOX_COLS) return;
+    const size_t plane = (size_t)n_ocb * n_kb * U_BOX_ELEMS;  // floats per position
+    float *dst = U + upack_index(0, k, c, n_ocb, n_kb);
+    if (c >= ic || k >= oc) {  // zero padding of the box grid
 #pragma unroll
         for (int p = 0; p < 64; ++p) dst[p * plane] = 0.0f;
         return;
@@ -123,9 +125,55 @@ __global__ void __launch_bounds__(128) filter_transform_kernel(const float *__re
     }
 }
 
-int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int icp) {
-    dim3 block(128), grid((unsigned)ceil_div(icp, 128), (unsigned)oc);
-    filter_transform_kernel<<<grid, block, 0, ctx->stream>>>(d_kernel, d_U, oc, ic, icp);
+int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic) {
+    const int n_ocb = (oc + U_BOX_ROWS - 1) / U_BOX_ROWS, n_kb = (ic + U_BOX_COLS - 1) / U_BOX_COLS;
+    dim3 block(128), grid((unsigned)ceil_div(n_kb * U_BOX_COLS, 128), (unsigned)(n_ocb * U_BOX_ROWS));
+    filter_transform_kernel<<<grid, block, 0, ctx->stream>>>(d_kernel, d_U, oc, ic, n_ocb, n_kb);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+// Same transform written in the layout of the FP32 (FFMA) TensorGEMM: U[p][ic][ocp] with the OUTPUT channel
+// contiguous (ocp = oc rounded up to 4), so that a k-row of a GEMM tile is one contiguous run and goes to
+// shared memory with plain 16-byte async copies, no transposition.  Threads of a warp walk oc.
+__global__ void __launch_bounds__(128) filter_transform_rowmajor_kernel(const float *__restrict__ kernel,
+                                                                        float *__restrict__ U, int oc, int ic, int icp,
+                                                                        int ocp) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = blockIdx.y;
+    if (k >= ocp) return;
+    const size_t plane = (size_t)icp * ocp;
+    float *dst = U + (size_t)c * ocp + k;
+    if (c >= ic || k >= oc) {
+#pragma unroll
+        for (int p = 0; p < 64; ++p) dst[p * plane] = 0.0f;
+        return;
+    }
+    const float *g = kernel + ((size_t)k * ic + c) * 9;
+    float gv[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) gv[i] = g[i];
+    float gg[8][3];
+#pragma unroll
+    for (int v = 0; v < 3; ++v) {
+        float w[8];
+        filter_transform_1d(gv[v], gv[3 + v], gv[6 + v], w);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) gg[r][v] = w[r];
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        float w[8];
+        filter_transform_1d(gg[r][0], gg[r][1], gg[r][2], w);
+#pragma unroll
+        for (int col = 0; col < 8; ++col) dst[(size_t)(col * 8 + r) * plane] = w[col];
+    }
+}
+
+int launch_filter_transform_rowmajor(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic) {
+    const int icp = round_up(ic, 8), ocp = round_up(oc, 4);
+    dim3 block(128), grid((unsigned)ceil_div(ocp, 128), (unsigned)icp);
+    filter_transform_rowmajor_kernel<<<grid, block, 0, ctx->stream>>>(d_kernel, d_U, oc, ic, icp, ocp);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -199,6 +247,73 @@ int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const
     dim3 block(256), grid((unsigned)g.tp, (unsigned)ceil_div(g.icp, IT_CH));
     FC_CHECK_CUDA(launch_pdl(input_transform_kernel, grid, block, 0, ctx->stream, d_in, d_V, g.tiles, g.ic, g.icp, g.tp,
                              g.ih, g.iw, g.pad, g.th, g.tw));
+    return FC_OK;
+}
+
+// The same transform written in the layout of the FP32 (FFMA) TensorGEMM: V[p][ic][tp] with the TILE axis
+// contiguous.  Lanes run along consecutive tiles (TPW = 32, 16 or 8 of them, the rest of the warp taking
+// further channels), so the window loads sweep contiguous image rows and every store is one run of
+// V[p][c][tile..].  Same three phases as above, eight threads per (tile, channel) item.
+template <int TPW>
+__global__ void __launch_bounds__(256) input_transform_rowmajor_kernel(const float *__restrict__ in,
+                                                                       float *__restrict__ V, int n_tiles, int ic,
+                                                                       int icp, int tp, int ih, int iw, int pad,
+                                                                       int th, int tw) {
+    constexpr int CPB = 32 / TPW;  // channels per block
+    __shared__ float win[64 * IT_LD];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int tl = lane % TPW, cl = lane / TPW;
+    const int tile = blockIdx.x * TPW + tl, c = blockIdx.y * CPB + cl;
+    pdl_trigger();
+    pdl_wait();
+    {   // phase 1: thread (lane, w) fetches row w of its item's window
+        const int per_img = th * tw;
+        const int img = tile / per_img, tt = tile - img * per_img;
+        const int yy = (tt / tw) * 6 - pad + w, col0 = (tt % tw) * 6 - pad;
+        const bool ok = c < ic && tile < n_tiles && yy >= 0 && yy < ih;
+        const float *src = in + (((size_t)img * ic + c) * ih + yy) * iw + col0;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+            const int xx = col0 + x;
+            win[(w * 8 + x) * IT_LD + lane] = (ok && xx >= 0 && xx < iw) ? __ldg(src + x) : 0.0f;
+        }
+    }
+    __syncthreads();
+    {
+        float *q = win + w * IT_LD + lane;  // column w
+        float r0 = q[0 * 8 * IT_LD], r1 = q[1 * 8 * IT_LD], r2 = q[2 * 8 * IT_LD], r3 = q[3 * 8 * IT_LD];
+        float r4 = q[4 * 8 * IT_LD], r5 = q[5 * 8 * IT_LD], r6 = q[6 * 8 * IT_LD], r7 = q[7 * 8 * IT_LD];
+        input_transform_1d(r0, r1, r2, r3, r4, r5, r6, r7);
+        q[0 * 8 * IT_LD] = r0; q[1 * 8 * IT_LD] = r1; q[2 * 8 * IT_LD] = r2; q[3 * 8 * IT_LD] = r3;
+        q[4 * 8 * IT_LD] = r4; q[5 * 8 * IT_LD] = r5; q[6 * 8 * IT_LD] = r6; q[7 * 8 * IT_LD] = r7;
+    }
+    __syncthreads();
+    if (c >= icp || tile >= tp) return;
+    const float *q = win + w * 8 * IT_LD + lane;  // row w
+    float r0 = q[0 * IT_LD], r1 = q[1 * IT_LD], r2 = q[2 * IT_LD], r3 = q[3 * IT_LD];
+    float r4 = q[4 * IT_LD], r5 = q[5 * IT_LD], r6 = q[6 * IT_LD], r7 = q[7 * IT_LD];
+    input_transform_1d(r0, r1, r2, r3, r4, r5, r6, r7);
+    const size_t plane = (size_t)icp * tp;
+    float *dst = V + (size_t)w * plane + (size_t)c * tp + tile;  // p = x*8 + w
+    dst[0 * 8 * plane] = r0; dst[1 * 8 * plane] = r1; dst[2 * 8 * plane] = r2; dst[3 * 8 * plane] = r3;
+    dst[4 * 8 * plane] = r4; dst[5 * 8 * plane] = r5; dst[6 * 8 * plane] = r6; dst[7 * 8 * plane] = r7;
+}
+
+int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
+    dim3 block(256);
+    if (g.tiles > 16) {
+        dim3 grid((unsigned)ceil_div(g.tp, 32), (unsigned)g.icp);
+        FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_kernel<32>, grid, block, 0, ctx->stream, d_in, d_V, g.tiles,
+                                 g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+    } else if (g.tiles > 8) {
+        dim3 grid((unsigned)ceil_div(g.tp, 16), (unsigned)ceil_div(g.icp, 2));
+        FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_kernel<16>, grid, block, 0, ctx->stream, d_in, d_V, g.tiles,
+                                 g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+    } else {
+        dim3 grid((unsigned)ceil_div(g.tp, 8), (unsigned)ceil_div(g.icp, 4));
+        FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_kernel<8>, grid, block, 0, ctx->stream, d_in, d_V, g.tiles,
+                                 g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+    }
     return FC_OK;
 }
 

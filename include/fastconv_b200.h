@@ -121,13 +121,22 @@ int fc_wino_buffer_elems(const fc_conv_desc *desc, int mode, size_t *u_elems, si
 
 /* ---- Winograd F(6x6,3x3) stages -------------------------------------------
  * Device-pointer entry points, one per stage of winoF63_v1_single / _multi
- * (winoF63ZC/winoF63ZC.h:5-9).  Layouts: U[64][oc][icp], V[64][tp][icp],
- * M[64][oc][tp] with icp = ic rounded up to 8 and tp = tiles rounded up to 8
- * (padding is zero); position p = col*8 + row of the 8x8 transformed tile. */
+ * (winoF63ZC/winoF63ZC.h:5-9).  icp = ic rounded up to 8, tp = tiles rounded up to 8, ocp = oc
+ * rounded up to 4; padding is zero; position p = col*8 + row of the 8x8 transformed tile.
+ * M is [64][oc][tp] in every mode.  The operand layouts follow the arithmetic mode that will
+ * multiply them, so `mode` must be the same for the transforms and the GEMM of one layer:
+ *   FC_MATH_FP32_MIRRORED  U[64][icp][ocp], V[64][icp][tp]  (row index contiguous: GEMM tiles reach
+ *                          shared memory with plain 16-byte async copies, no transposition)
+ *   FC_MATH_3XTF32 / TF32  V[64][tp][icp] (K-major, what UMMA and TMA boxes want) and U in contiguous
+ *                          boxes of 128 output channels x 32 input channels: with n_ocb = ceil(oc/128),
+ *                          n_kb = ceil(ic/32), box (p, ocb, kb) starts at ((p*n_ocb + ocb)*n_kb + kb)*4096
+ *                          floats and element (oc, ic) sits at (oc%128)*32 + ic%32 inside it -- one
+ *                          box is one TMA load of the GEMM.
+ * fc_wino_buffer_elems gives the float counts. */
 /* offline_kernel_transform_v1, winoF63ZC/winoF63ZC.h:14 (winoF63ZC.cpp:242-322) */
-int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
+int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int mode);
 /* input transform stage, winoF63ZC/winoF63ZC.cpp:512-813 */
-int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc);
+int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc, int mode);
 /* TensorGEMM stage, winoF63ZC/winoF63ZC.cpp:818-860 + winoF63ZC/TensorGEMMZC.cpp */
 int fc_wino_tensor_gemm(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const fc_conv_desc *desc,
                         int mode);
@@ -156,7 +165,7 @@ int fc_wino_forward(fc_context *ctx, const float *d_in, const float *d_U, float 
  *     or different host threads) race -- serialise them. */
 #define FC_STATIC_SCRATCH_FLOATS (4u << 20)
 int fc_wino_forward_static_scratch(const float *d_in, const float *d_U, float *d_out, const fc_conv_desc *desc,
-                                   void *stream);
+                                   void *stream); /* d_U: fc_wino_filter_transform(..., FC_MATH_FP32_MIRRORED) */
 
 /* ---- im2col / implicit GEMM ------------------------------------------------ */
 /* ConvIm2colLayer::im2col(), convLayer/im2colConv.cpp:285-309: materialises the gathered matrix

@@ -141,6 +141,17 @@ class Reference:
         return B
 
 
+def unpack_filter(packed, oc, ic):
+    """The library keeps the transformed filter in contiguous boxes of 128 output channels x 32 input
+    channels: box (p, ocb, kb) at ((p*n_ocb + ocb)*n_kb + kb)*4096 floats, element (oc%128)*32 + ic%32.
+    Returns the plain [64][oc][ic] view the oracle uses."""
+    n_ocb, n_kb = (oc + 127) // 128, (ic + 31) // 32
+    boxes = np.asarray(packed, np.float32).reshape(64, n_ocb, n_kb, 128, 32)
+    plain = boxes.transpose(0, 1, 3, 2, 4).reshape(64, n_ocb * 128, n_kb * 32)
+    assert not plain[:, oc:, :].any() and not plain[:, :, ic:].any(), "padding of the packed filter must be zero"
+    return np.ascontiguousarray(plain[:, :oc, :ic])
+
+
 def load_golden():
     z = np.load(ROOT / "tests" / "golden" / "fastconv_golden.npz")
     meta = json.loads(bytes(z["meta"]).decode())

@@ -84,11 +84,15 @@ def test_winograd_buffer_sizes_and_rejections():
     lib = fc.load()
     u, v, m = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
     d = fc.make_desc(1, 256, 56, 56, 256)
-    assert lib.fc_wino_buffer_elems(ctypes.byref(d), 0, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == 0
-    assert (u.value, v.value, m.value) == (64 * 256 * 256, 64 * 104 * 256, 64 * 256 * 104)  # 100 tiles -> 104
+    for mode in (0, 1, 2):
+        assert lib.fc_wino_buffer_elems(ctypes.byref(d), mode, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == 0
+        assert (u.value, v.value, m.value) == (64 * 256 * 256, 64 * 104 * 256, 64 * 256 * 104)  # 100 tiles -> 104
     d = fc.make_desc(2, 3, 224, 224, 64)
     assert lib.fc_wino_buffer_elems(ctypes.byref(d), 0, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == 0
-    assert (u.value, v.value, m.value) == (64 * 64 * 8, 64 * 2888 * 8, 64 * 64 * 2888)
+    assert (u.value, v.value, m.value) == (64 * 8 * 64, 64 * 2888 * 8, 64 * 64 * 2888)  # fp32 mode: U[64][icp][ocp]
+    assert lib.fc_wino_buffer_elems(ctypes.byref(d), 2, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == 0
+    assert u.value == 64 * 128 * 32  # tensor-core modes: U is padded to 128x32 boxes
+    assert lib.fc_wino_buffer_elems(ctypes.byref(d), 7, None, None, None) == -1
     for bad in (fc.make_desc(1, 8, 8, 8, 8, 3, 3, 2, 2), fc.make_desc(1, 8, 8, 8, 8, 5, 5), fc.make_desc(1, 8, 8, 8, 8, 3, 3, 1, 1, 1, 0, 1, 1)):
         assert lib.fc_wino_buffer_elems(ctypes.byref(bad), 0, None, None, None) == -2  # FC_ERR_UNSUPPORTED
 

@@ -74,39 +74,52 @@ def _dev(ctx, a):
     return C.c_void_p(ctx.upload(a))
 
 
-def test_each_stage_bit_exact(ctx, oracle):
+@pytest.mark.parametrize("mode", [0, 1])
+def test_each_stage_bit_exact(ctx, oracle, mode):
+    """Filter transform, input transform, TensorGEMM and output transform one by one, in the operand layouts
+    of the fp32 mirrored mode (0) and of the tensor-core modes (1 = 3xTF32)."""
+    from _oracle import unpack_filter
     lib = fc.load()
     n, ic, oc, ih, iw, pad = 2, 13, 21, 17, 11, 1
     x = synth.conv_input(n, ic, ih, iw, 51)
     w = synth.conv_weights(oc, ic, 3, 3, 52)
     d = fc.make_desc(n, ic, ih, iw, oc, 3, 3, 1, 1, pad, pad, pad, pad)
     u, v, m = C.c_size_t(), C.c_size_t(), C.c_size_t()
-    fc._lib.check(lib.fc_wino_buffer_elems(C.byref(d), 0, C.byref(u), C.byref(v), C.byref(m)), "elems")
-    icp, tiles = 16, 2 * 3 * 2
-    tp = 16
-    assert (u.value, v.value, m.value) == (64 * oc * icp, 64 * tp * icp, 64 * oc * tp)
+    fc._lib.check(lib.fc_wino_buffer_elems(C.byref(d), mode, C.byref(u), C.byref(v), C.byref(m)), "elems")
+    icp, ocp, tiles, tp = 16, 24, 2 * 3 * 2, 16
+    assert (u.value, v.value, m.value) == (64 * icp * ocp if mode == 0 else 64 * 128 * 32, 64 * tp * icp, 64 * oc * tp)
     dU, dV, dM = (C.c_void_p(ctx.alloc(4 * e.value)) for e in (u, v, m))
     d_out = C.c_void_p(ctx.alloc(4 * n * oc * ih * iw))
     dk, dx = _dev(ctx, w), _dev(ctx, x)
     h = ctx.handle
-    fc._lib.check(lib.fc_wino_filter_transform(h, dk, dU, oc, ic), "filter")
-    fc._lib.check(lib.fc_wino_input_transform(h, dx, dV, C.byref(d)), "input")
-    fc._lib.check(lib.fc_wino_tensor_gemm(h, dU, dV, dM, C.byref(d), 0), "gemm")
+    fc._lib.check(lib.fc_wino_filter_transform(h, dk, dU, oc, ic, mode), "filter")
+    fc._lib.check(lib.fc_wino_input_transform(h, dx, dV, C.byref(d), mode), "input")
+    fc._lib.check(lib.fc_wino_tensor_gemm(h, dU, dV, dM, C.byref(d), mode), "gemm")
     fc._lib.check(lib.fc_wino_output_transform(h, dM, d_out, C.byref(d)), "output")
-    U = ctx.download(dU.value, (64, oc, icp))
-    V = ctx.download(dV.value, (64, tp, icp))
+    Uo = oracle.filter_transform(w, icp=icp)          # [64][oc][icp]
+    Vo = oracle.input_transform(x, pad, tp=tp, icp=icp)  # [64][tp][icp]
+    if mode == 0:  # row-major: U[64][icp][ocp], V[64][icp][tp]
+        U = ctx.download(dU.value, (64, icp, ocp))
+        assert not U[:, :, oc:].any() and np.array_equal(U[:, :, :oc].transpose(0, 2, 1), Uo), "filter transform"
+        V = ctx.download(dV.value, (64, icp, tp)).transpose(0, 2, 1)
+    else:          # packed boxes / K-major
+        U = unpack_filter(ctx.download(dU.value, (u.value,)), oc, ic)
+        assert np.array_equal(U, Uo[:, :, :ic]), "filter transform"
+        V = ctx.download(dV.value, (64, tp, icp))
+    assert np.array_equal(V, Vo), "input transform (padding rows/channels must be zero)"
     M = ctx.download(dM.value, (64, oc, tp))
     out = ctx.download(d_out.value, (n, oc, ih, iw))
-    Uo = oracle.filter_transform(w, icp=icp)
-    Vo = oracle.input_transform(x, pad, tp=tp, icp=icp)
-    assert np.array_equal(U, Uo), "filter transform"
-    assert np.array_equal(V, Vo), "input transform (padding rows/channels must be zero)"
     Mo = oracle.wino_gemm(Uo, Vo, oc, icp, tp)
-    assert np.array_equal(M[:, :, :tiles], Mo[:, :, :tiles]), "TensorGEMM"
-    assert np.array_equal(out, oracle.output_transform(Mo, n, oc, ih, iw)), "output transform"
+    if mode == 0:
+        assert np.array_equal(M[:, :, :tiles], Mo[:, :, :tiles]), "TensorGEMM"
+        assert np.array_equal(out, oracle.output_transform(Mo, n, oc, ih, iw)), "output transform"
+    else:
+        assert rel_l2(M[:, :, :tiles], Mo[:, :, :tiles]) < 2e-6, "TensorGEMM (3xTF32)"
+        # the output transform itself is exact arithmetic in every mode: feed it the device's own M
+        assert np.array_equal(out, oracle.output_transform(M, n, oc, ih, iw)), "output transform"
     # the fused entry point gives the same bits and reports stage times
     ms = (C.c_float * 4)()
-    fc._lib.check(lib.fc_wino_forward(h, dx, dU, dV, dM, d_out, C.byref(d), 0, ms), "forward")
+    fc._lib.check(lib.fc_wino_forward(h, dx, dU, dV, dM, d_out, C.byref(d), mode, ms), "forward")
     assert np.array_equal(ctx.download(d_out.value, (n, oc, ih, iw)), out)
     assert ms[0] > 0 and ms[2] > 0 and ms[3] > 0 and ms[1] == 0
     for p in (dU, dV, dM, d_out, dk, dx):

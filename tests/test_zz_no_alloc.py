@@ -52,8 +52,10 @@ def test_static_scratch_matches_regular_entry_point_twice():
             oh, ow = ih + 2 * pad - 2, iw + 2 * pad - 2
             w = synth.conv_weights(oc, ic, 3, 3, 7)
             dk = ctx.upload(w)
-            dU = ctx.alloc(4 * 64 * oc * ((ic + 7) // 8 * 8))
-            _lib.check(lib.fc_wino_filter_transform(ctx.handle, C.c_void_p(dk), C.c_void_p(dU), oc, ic), "filter")
+            u_elems = C.c_size_t()
+            _lib.check(lib.fc_wino_buffer_elems(C.byref(desc), 0, C.byref(u_elems), None, None), "elems")
+            dU = ctx.alloc(4 * u_elems.value)
+            _lib.check(lib.fc_wino_filter_transform(ctx.handle, C.c_void_p(dk), C.c_void_p(dU), oc, ic, 0), "filter")
             ctx.synchronize()
             for seed in (11, 12):  # two calls in a row share the built-in array
                 x = synth.conv_input(n, ic, ih, iw, seed)
