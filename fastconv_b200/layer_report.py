@@ -1,0 +1,109 @@
+"""Per-layer report over the benchmark configurations: VGG-16, ResNet-50 v1.5 and the wide single-image sweep.
+
+    python -m fastconv_b200.layer_report --set resnet50 --mode fp32 [--batch N] [--tune] [--iters 50]
+
+Every layer is planned with `-a auto` (select_algorithm of ConvTest.cpp:318-331, 1x1 stride 1 routed to the
+implicit GEMM), run `iters` times back to back on device-resident data and timed with CUDA events; one
+JSON line per layer carries the algorithm, milliseconds, direct-equivalent GFLOP/s and the fraction of
+the layer's roofline  max(flops / peak, bytes / HBM bandwidth)  with
+    Winograd:  flops = 2*64*T*C*K,  bytes = 4*(N*C*H*W + 64*C*K + N*K*OH*OW)
+    im2col:    flops = 2*N*K*C*R*S*OH*OW,  bytes = 4*(N*C*H*W + K*C*R*S + N*K*OH*OW)
+Peaks: HBM from MEASURED_PEAKS.json (copy bandwidth), FP32 FFMA = SMs*128*2*max clock for the fp32 mode,
+half the measured bf16 GEMM rate for TF32 and a third of that for 3xTF32 (placeholders until a TF32 GEMM peak
+is measured on the pool).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+from pathlib import Path
+
+import numpy as np
+
+from . import _lib, synth
+from .layers import Context, make_desc
+
+ROOT = Path(__file__).resolve().parents[1]
+
+# ic, oc, hw, k, stride, pad
+VGG16 = [(3, 64, 224, 3, 1, 1), (64, 64, 224, 3, 1, 1), (64, 128, 112, 3, 1, 1), (128, 128, 112, 3, 1, 1),
+         (128, 256, 56, 3, 1, 1), (256, 256, 56, 3, 1, 1), (256, 256, 56, 3, 1, 1), (256, 512, 28, 3, 1, 1),
+         (512, 512, 28, 3, 1, 1), (512, 512, 28, 3, 1, 1), (512, 512, 14, 3, 1, 1), (512, 512, 14, 3, 1, 1),
+         (512, 512, 14, 3, 1, 1)]
+RESNET50 = [(3, 64, 224, 7, 2, 3),
+            (64, 64, 56, 1, 1, 0), (64, 64, 56, 3, 1, 1), (64, 256, 56, 1, 1, 0), (256, 64, 56, 1, 1, 0),
+            (256, 128, 56, 1, 1, 0), (128, 128, 56, 3, 2, 1), (256, 512, 56, 1, 2, 0),
+            (128, 128, 28, 3, 1, 1), (128, 512, 28, 1, 1, 0), (512, 128, 28, 1, 1, 0),
+            (512, 256, 28, 1, 1, 0), (256, 256, 28, 3, 2, 1), (512, 1024, 28, 1, 2, 0),
+            (256, 256, 14, 3, 1, 1), (256, 1024, 14, 1, 1, 0), (1024, 256, 14, 1, 1, 0),
+            (1024, 512, 14, 1, 1, 0), (512, 512, 14, 3, 2, 1), (1024, 2048, 14, 1, 2, 0),
+            (512, 512, 7, 3, 1, 1), (512, 2048, 7, 1, 1, 0), (2048, 512, 7, 1, 1, 0)]
+WIDE = [(c, c, h, 3, 1, 1) for c in (512, 1024, 2048) for h in (14, 28, 56)]
+SETS = {"vgg16": VGG16, "resnet50": RESNET50, "wide": WIDE}
+
+
+def peaks(mode: str):
+    hbm, bf16 = 6650.0, 1590.0
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        hbm, bf16 = float(d["hbm_gbs"]), float(d.get("bf16_tflops", bf16))
+    flops = {"fp32": 148 * 128 * 2 * 1.965e9 / 1e12, "tf32": bf16 / 2, "3xtf32": bf16 / 6}[mode]
+    return hbm, flops
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--set", default="resnet50", choices=sorted(SETS))
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--tune", action="store_true", help="run Tuning() (timed configuration search) before measuring")
+    ap.add_argument("--device", type=int, default=0)
+    args = ap.parse_args()
+
+    lib = _lib.load()
+    hbm, peak_tf = peaks(args.mode)
+    n = args.batch
+    total_ms = total_flops = 0.0
+    with Context(args.device, arena_bytes=12 << 30) as ctx:
+        for idx, (ic, oc, hw, k, s, p) in enumerate(SETS[args.set]):
+            desc = make_desc(n, ic, hw, hw, oc, k, k, s, s, p, p, p, p)
+            w = synth.conv_weights(oc, ic, k, k, 2000 + idx)
+            x = synth.conv_input(n, ic, hw, hw, 1000 + idx)
+            h = C.c_void_p()
+            _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_AUTO, _lib.MODE_NAMES[args.mode],
+                                          C.c_void_p(w.ctypes.data), C.byref(h)), "fc_conv_create")
+            if args.tune:
+                _lib.check(lib.fc_conv_tune(h, 10, 0), "fc_conv_tune")
+            d_in, d_out = C.c_void_p(), C.c_void_p()
+            _lib.check(lib.fc_conv_device_buffers(h, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
+            ctx.upload(x, d_in.value)
+            ms = C.c_float()
+            _lib.check(lib.fc_conv_time_device(h, d_in, d_out, 5, args.iters, C.byref(ms)), "fc_conv_time_device")
+            algo = C.c_int()
+            lib.fc_conv_algorithm(h, C.byref(algo))
+            oh = (hw + 2 * p - k) // s + 1
+            direct = 2.0 * n * oc * ic * k * k * oh * oh
+            if algo.value == _lib.ALGO_WINOGRAD:
+                tiles = n * ((oh + 5) // 6) ** 2
+                flops, nbytes = 2.0 * 64 * tiles * ic * oc, 4.0 * (n * ic * hw * hw + 64 * ic * oc + n * oc * oh * oh)
+            else:
+                flops, nbytes = direct, 4.0 * (n * ic * hw * hw + oc * ic * k * k + n * oc * oh * oh)
+            roof_ms = max(flops / (peak_tf * 1e12), nbytes / (hbm * 1e9)) * 1e3
+            print(json.dumps({
+                "layer": f"{ic}->{oc}@{hw} {k}x{k}s{s}", "batch": n, "mode": args.mode,
+                "algo": "winograd" if algo.value == _lib.ALGO_WINOGRAD else "im2col", "ms": round(ms.value, 5),
+                "gflops_direct_equiv": round(direct / ms.value / 1e6, 1), "roofline_ms": round(roof_ms, 5),
+                "frac_of_roofline": round(roof_ms / ms.value, 4),
+                "bound": "hbm" if nbytes / (hbm * 1e9) >= flops / (peak_tf * 1e12) else "math"}), flush=True)
+            total_ms += ms.value
+            total_flops += direct
+            lib.fc_conv_destroy(h)
+    print(json.dumps({"set": args.set, "mode": args.mode, "batch": n, "total_ms": round(total_ms, 4),
+                      "gflops_direct_equiv": round(total_flops / total_ms / 1e6, 1)}))
+
+
+if __name__ == "__main__":
+    main()
