@@ -760,6 +760,7 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
     if (c->mode == FC_MATH_FP32_MIRRORED) {
         if (algo == FC_ALGO_WINOGRAD && c->geom.tiles <= 32) push(0, 0, 1, 0);
+        if (algo == FC_ALGO_IM2COL) push(0, 0, 1, 0);  // thread-per-pixel kernel
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
     } else {
         const int widths[5] = {32, 64, 96, 128, 256};

@@ -161,6 +161,96 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Small problems (batch-1 ResNet layers: 49..3136 pixels, a few hundred channels).  The blocked kernel
+// above would launch a handful of CTAs, each walking the whole reduction alone.  Here a thread owns one
+// output pixel and TM output channels: consecutive threads read consecutive pixels of the input
+// (coalesced, stride sw), the k -> (c,u,v) decode is uniform per step and kept in counters, the
+// weights of the TM channels are staged in shared memory a chunk at a time and read as broadcasts.
+// The chain per output element is the same: one accumulator, one FMA per k, ascending.
+// ---------------------------------------------------------------------------------------------
+constexpr int DR_THREADS = 128;
+constexpr int DR_KC = 256;
+constexpr int DR_BATCH = 8;  // input values fetched ahead of the FMAs that consume them
+
+template <int TM, int PXB>
+__global__ void __launch_bounds__(DR_THREADS) igemm_ffma_direct_kernel(const float *__restrict__ in,
+                                                                       const float *__restrict__ A,
+                                                                       float *__restrict__ out, IgemmParams P) {
+    constexpr int GROUPS = DR_THREADS / PXB;  // channel groups per block
+    constexpr int OCB = TM * GROUPS;          // output channels per block
+    __shared__ __align__(16) float As[DR_KC][OCB];
+    const int tid = threadIdx.x;
+    const int px_l = tid % PXB, grp = tid / PXB;
+    const int pix = blockIdx.x * PXB + px_l;
+    const int ocb0 = blockIdx.y * OCB, oc0 = ocb0 + grp * TM;
+    const int ohw = P.oh * P.ow;
+    const bool pix_ok = pix < P.npix;
+    int img = 0, oi = 0, oj = 0;
+    if (pix_ok) {
+        img = pix / ohw;
+        const int rem = pix - img * ohw;
+        oi = rem / P.ow;
+        oj = rem - oi * P.ow;
+    }
+    const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
+    const float *pix_ptr = in + (size_t)img * P.ic * P.ih * P.iw + (ptrdiff_t)base_row * P.iw + base_col;
+
+    float acc[TM];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) acc[i] = 0.0f;
+
+    int c = 0, u = 0, v = 0;  // decode of the running k, the same in every thread
+    for (int k0 = 0; k0 < P.K; k0 += DR_KC) {
+        const int kc = min(DR_KC, P.K - k0);
+        __syncthreads();
+        for (int idx = tid; idx < DR_KC * OCB; idx += DR_THREADS) {
+            const int j = idx / DR_KC, kk = idx - j * DR_KC;  // consecutive threads walk k: coalesced rows of A
+            As[kk][j] = (ocb0 + j < P.oc && kk < kc) ? __ldg(A + (size_t)(ocb0 + j) * P.K + k0 + kk) : 0.0f;
+        }
+        __syncthreads();
+        for (int kk = 0; kk < kc; kk += DR_BATCH) {
+            float val[DR_BATCH];
+#pragma unroll
+            for (int j = 0; j < DR_BATCH; ++j) {  // all loads of the batch first, so they overlap
+                val[j] = 0.0f;
+                if (kk + j < kc) {
+                    const int row = base_row + u, col = base_col + v;
+                    if (pix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw)
+                        val[j] = __ldg(pix_ptr + (c * P.ih + u) * P.iw + v);
+                    if (++v == P.kw) {
+                        v = 0;
+                        if (++u == P.kh) {
+                            u = 0;
+                            ++c;
+                        }
+                    }
+                }
+            }
+            // rows of As past kc are zero, so a short last batch adds exact zeros
+#pragma unroll
+            for (int j = 0; j < DR_BATCH; ++j)
+#pragma unroll
+                for (int i = 0; i < TM; ++i) acc[i] = __fmaf_rn(As[kk + j][grp * TM + i], val[j], acc[i]);
+        }
+    }
+    if (pix_ok) {
+        float *dst = out + ((size_t)img * P.oc + oc0) * ohw + (pix - img * ohw);
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+            if (oc0 + i < P.oc) dst[(size_t)i * ohw] = acc[i];
+    }
+}
+
+template <int TM, int PXB>
+int launch_direct(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const IgemmParams &P) {
+    constexpr int OCB = TM * (DR_THREADS / PXB);
+    dim3 grid((unsigned)ceil_div(P.npix, PXB), (unsigned)ceil_div(P.oc, OCB)), block(DR_THREADS);
+    igemm_ffma_direct_kernel<TM, PXB><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
 }  // namespace
 
 int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
@@ -183,6 +273,20 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
     P.npix = d.batch * oh * ow;
     const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
     const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;
+    // skinny = 1 forces the thread-per-pixel kernel, 2 the blocked one; otherwise the blocked kernel only when
+    // its grid gives the machine about one and a half CTAs per SM
+    const size_t blocked_ctas = ceil_div(P.npix, wide_n ? 128 : 64) * ceil_div(d.oc, wide_m ? 128 : 64);
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int pick = cfg ? cfg->skinny : 0;
+    if (pick == 1 || (pick == 0 && 2 * blocked_ctas < 3 * (size_t)sms)) {
+        // few output elements: fewer channels per thread, so more threads share the (latency-bound) chains
+        const bool thin = (size_t)P.npix * d.oc < (size_t)sms * 2048;
+        if (P.npix >= 96) return thin ? launch_direct<4, 128>(ctx, d_in, d_kernel, d_out, P)
+                                      : launch_direct<8, 128>(ctx, d_in, d_kernel, d_out, P);
+        if (P.npix >= 48) return thin ? launch_direct<4, 64>(ctx, d_in, d_kernel, d_out, P)
+                                      : launch_direct<8, 64>(ctx, d_in, d_kernel, d_out, P);
+        return thin ? launch_direct<4, 32>(ctx, d_in, d_kernel, d_out, P) : launch_direct<8, 32>(ctx, d_in, d_kernel, d_out, P);
+    }
     dim3 grid((unsigned)ceil_div(P.npix, wide_n ? 128 : 64), (unsigned)ceil_div(d.oc, wide_m ? 128 : 64)), block(THREADS);
     if (wide_m && wide_n)
         igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);

@@ -26,6 +26,7 @@ struct IgemmTcParams {
     int *status;
     int ic, ih, iw, oc, kh, kw, sh, sw, pad_l, pad_t, oh, ow;
     int K, num_kb, bn, stages, tmem_cols;
+    int splits, kb_per_split;  // split-K over blockIdx.z: split s reduces k-blocks [s*kb_per_split, ...)
 };
 
 __global__ void pack_weights_kernel(const float *__restrict__ kernel, float *__restrict__ packed, int oc, int K,
@@ -56,8 +57,12 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
     const uint32_t stage_bytes = part_bytes * (kSplit ? 2 : 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int img = blockIdx.z, oc0 = blockIdx.y * BM, pix0 = blockIdx.x * P.bn;
+    const int img = blockIdx.z / P.splits, split = blockIdx.z % P.splits;
+    const int oc0 = blockIdx.y * BM, pix0 = blockIdx.x * P.bn;
     const int ohw = P.oh * P.ow;
+    const int kb0 = split * P.kb_per_split;
+    const int kb1 = min(P.num_kb, kb0 + P.kb_per_split);  // this CTA reduces k-blocks [kb0, kb1)
+    if (kb0 >= kb1) return;  // rounding can leave the last split empty (uniform for the whole CTA)
 
     auto bar_full_a = [&](int s) { return smem_u32(bars + s); };
     auto bar_full_b = [&](int s) { return smem_u32(bars + 8 + s); };
@@ -89,9 +94,9 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
     if (warp == 0) {
         // ---------------- TMA producer for the weights ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < P.num_kb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                const int s = (kb - kb0) % S;
+                const uint32_t ph = (uint32_t)((kb - kb0) / S) & 1u;
                 if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status)) break;
                 const uint32_t a_dst = ring + s * stage_bytes;
                 mbar_expect_tx(bar_full_a(s), kSplit ? 2 * A_BYTES : A_BYTES);
@@ -103,9 +108,9 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_tf32(BM, P.bn);
-            for (int kb = 0; kb < P.num_kb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                const int s = (kb - kb0) % S;
+                const uint32_t ph = (uint32_t)((kb - kb0) / S) & 1u;
                 if (!mbar_wait(bar_full_a(s), ph, abort_flag, P.status)) break;
                 if (!mbar_wait(bar_full_b(s), ph, abort_flag, P.status)) break;
                 tc_fence_after();
@@ -114,7 +119,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
 #pragma unroll
                 for (int ks = 0; ks < BK / 8; ++ks) {
                     const uint32_t koff = ks * 32;
-                    const uint32_t first = (kb == 0 && ks == 0) ? 0u : 1u;
+                    const uint32_t first = (kb == kb0 && ks == 0) ? 0u : 1u;
                     if (kSplit) {
                         tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_lo + koff), umma_desc_k_sw128(b_hi + koff), idesc, first);
                         tc_mma_tf32(tmem_base, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_lo + koff), idesc, 1u);
@@ -133,9 +138,9 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
         const int khw = P.kh * P.kw;
         const float *img_ptr = P.in + (size_t)img * P.ic * P.ih * P.iw;
         bool ok = true;
-        for (int kb = 0; kb < P.num_kb && ok; ++kb) {
-            const int s = kb % S;
-            const uint32_t ph = (uint32_t)(kb / S) & 1u;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            const int s = (kb - kb0) % S;
+            const uint32_t ph = (uint32_t)((kb - kb0) / S) & 1u;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status));  // warp-uniform
             if (!ok) break;
             // lane l of every warp decodes k = kb*32 + l once; the values travel by shuffle below
@@ -197,7 +202,10 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
                 if (row < P.oc) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (pix0 + c0 + j < ohw) dst[c0 + j] = v[j];
+                        if (pix0 + c0 + j < ohw) {
+                            if (P.splits > 1) atomicAdd(dst + c0 + j, v[j]);  // partial sum of this K range
+                            else dst[c0 + j] = v[j];
+                        }
                 }
             }
         }
@@ -233,21 +241,30 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     const bool split = mode == FC_MATH_3XTF32;
     const int K = d.ic * d.kh * d.kw, Kp = round_up(K, BK);
     const int ohw = oh * ow;
-    const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int num_kb = Kp / BK;
+    int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
+    if (!(cfg && cfg->bn))  // small problems: narrower pixel blocks first, then split-K, to fill the machine
+        while (max_bn > 32 && ceil_div(ohw, max_bn) * ceil_div(d.oc, BM) * d.batch < (size_t)sms) max_bn /= 2;
     const int n_blk = (ohw + max_bn - 1) / max_bn;
     const int bn = round_up((ohw + n_blk - 1) / n_blk, 16);
+    const size_t base_ctas = (size_t)n_blk * ceil_div(d.oc, BM) * d.batch;
+    int splits = 1;
+    while (base_ctas * splits * 2 <= (size_t)sms && num_kb / (splits * 2) >= 4 && (size_t)d.batch * splits * 2 <= 65535) splits *= 2;
     IgemmTcParams P;
     P.in = d_in; P.out = d_out; P.status = ctx->d_status;
     P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw; P.sh = d.sh; P.sw = d.sw;
     P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
-    P.K = K; P.num_kb = Kp / BK; P.bn = bn; P.tmem_cols = pow2_at_least(bn, 32);
+    P.K = K; P.num_kb = num_kb; P.bn = bn; P.tmem_cols = pow2_at_least(bn, 32);
+    P.splits = splits;
+    P.kb_per_split = (num_kb + splits - 1) / splits;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
-    const size_t n_ctas = (size_t)n_blk * ceil_div(d.oc, BM) * d.batch;
+    const size_t n_ctas = base_ctas * splits;
     const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024
                                               : (n_ctas > (size_t)ctx->sm_count ? 104 * 1024 : 200 * 1024);
     int stages = (int)(budget / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages > P.num_kb) stages = P.num_kb;
+    if (stages > P.kb_per_split) stages = P.kb_per_split;
     if (stages < 2) stages = 2;
     P.stages = stages;
     const size_t smem = 512 + 1024 + stages * stage_bytes;
@@ -255,7 +272,9 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
 
     CUtensorMap tmA;  // [2 planes][oc][Kp]
     FC_PROPAGATE(make_map_3d(&tmA, d_packed, Kp, d.oc, 2, BM));
-    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(d.oc, BM), (unsigned)d.batch), block(TC_THREADS);
+    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(d.oc, BM), (unsigned)(d.batch * splits)), block(TC_THREADS);
+    if (splits > 1)  // the K ranges add their partial sums into a zeroed output
+        FC_CHECK_CUDA(cudaMemsetAsync(d_out, 0, (size_t)d.batch * d.oc * ohw * sizeof(float), ctx->stream));
     if (split) {
         FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         igemm_tc_kernel<true><<<grid, block, smem, ctx->stream>>>(tmA, P);
