@@ -28,6 +28,17 @@ bool pdl_enabled() {
     return state == 1;
 }
 
+// FASTCONV_GRAPH=0 makes a layer list replay its layers as ordinary launches instead of one CUDA graph, so that a
+// profiler sees plain kernel launches.
+static bool graph_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_GRAPH");
+        state = (e && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
 static int check_desc(const fc_conv_desc *d) {
     FC_REQUIRE(d != nullptr, FC_ERR_INVALID_ARG, "descriptor is NULL");
     FC_REQUIRE(d->batch > 0 && d->ic > 0 && d->oc > 0 && d->ih > 0 && d->iw > 0 && d->kh > 0 && d->kw > 0,
@@ -79,6 +90,11 @@ struct fc_conv {
     int algo, mode;
     int oh, ow;
     WinoGeom geom;
+    // A large batch runs as several passes over blocks of images so that the Winograd-domain buffers V and M of
+    // one pass stay in L2 between the kernel that writes them and the one that reads them (plan_passes).
+    int pass_imgs;        // images per pass; == desc.batch when the layer runs in one pass
+    WinoGeom pass_geom;   // geometry of a full pass
+    WinoGeom tail_geom;   // geometry of the last, shorter pass (n == 0 when the batch divides evenly)
     float *d_kernel;  // raw [oc][ic*kh*kw]
     float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
     float *d_U, *d_V, *d_M;
@@ -524,13 +540,55 @@ static void drop(fc_context *ctx, float **p) {
 
 // Workspaces and one-time weight re-layout of one algorithm (idempotent): Winograd gets U/V/M and the
 // filter transform, the tensor-core implicit GEMM gets the packed hi/lo weight planes.
+// Optional L2 blocking over the batch.  Unblocked, V and M go out to HBM and come back: 2*(V+M) bytes of traffic that
+// the layer's own bytes (input, weights, output) do not contain.  With P passes over blocks of images V and M of a pass
+// can stay in L2, at the price of reading the transformed filter P times and of P times as many, smaller launches.
+// FASTCONV_L2_BUDGET_MB is the part of L2 that V and M of one pass may occupy.  It is OFF (0) by default: measured on
+// the batch-64 VGG-16 stack, a 48 MB budget was 1.2x (TF32) to 1.4x (fp32) SLOWER than one pass, because a pass of one
+// or two images runs the three kernels in their latency-bound regime.
+static size_t l2_budget_bytes() {  // read at every layer creation, so a caller can change it between layers
+    const char *e = getenv("FASTCONV_L2_BUDGET_MB");
+    long long mb = e ? atoll(e) : 0;
+    if (mb < 0) mb = 0;
+    return (size_t)mb << 20;
+}
+
+static int plan_passes(fc_conv *c) {
+    const WinoGeom &g = c->geom;
+    c->pass_imgs = g.n;
+    c->pass_geom = g;
+    memset(&c->tail_geom, 0, sizeof c->tail_geom);
+    const size_t budget = l2_budget_bytes();
+    const size_t per_img = (size_t)256 * g.th * g.tw * (g.icp + g.oc);  // V + M bytes of one image
+    const size_t vm = per_img * g.n, u = (size_t)256 * g.icp * g.oc;
+    if (budget == 0 || g.n == 1 || vm <= budget) return FC_OK;
+    int imgs = (int)(budget / per_img);
+    if (imgs < 1) imgs = 1;
+    const int passes = (g.n + imgs - 1) / imgs;
+    if ((size_t)(passes - 1) * u >= 2 * vm) return FC_OK;  // re-reading the filter would cost more than it saves
+    imgs = (g.n + passes - 1) / passes;  // even out the passes
+    fc_conv_desc d = c->desc;
+    d.batch = imgs;
+    FC_PROPAGATE(wino_geom(&d, &c->pass_geom));
+    c->pass_imgs = imgs;
+    if (g.n % imgs) {
+        d.batch = g.n % imgs;
+        FC_PROPAGATE(wino_geom(&d, &c->tail_geom));
+    }
+    return FC_OK;
+}
+
+static int conv_passes(const fc_conv *c) { return (c->desc.batch + c->pass_imgs - 1) / c->pass_imgs; }
+
 static int conv_prepare(fc_conv *c, int algo) {
     fc_context *ctx = c->ctx;
     const fc_conv_desc &d = c->desc;
     int st = FC_OK;
     bool timed = false;
     if (algo == FC_ALGO_WINOGRAD) {
-        const WinoGeom &g = c->geom;
+        st = plan_passes(c);
+        if (st != FC_OK) return st;
+        const WinoGeom &g = c->pass_geom;  // V and M hold one pass
         const bool fresh = c->d_U == nullptr;
         st = grab(ctx, &c->d_U, u_elems_for(g, c->mode));
         if (st == FC_OK) st = grab(ctx, &c->d_V, (size_t)64 * g.tp * g.icp);
@@ -627,16 +685,31 @@ int fc_conv_algorithm(const fc_conv *c, int *algo) {
     return FC_OK;
 }
 
+// One pass of a Winograd layer: images [pass*pass_imgs, ...) of the batch through the three kernels.
+static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_out, bool timed) {
+    fc_context *ctx = c->ctx;
+    const int img0 = pass * c->pass_imgs;
+    const bool tail = img0 + c->pass_imgs > c->desc.batch;
+    const WinoGeom &g = tail ? c->tail_geom : c->pass_geom;
+    const float *in = d_in + (size_t)img0 * g.ic * g.ih * g.iw;
+    float *out = d_out + (size_t)img0 * g.oc * g.oh * g.ow;
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
+    FC_PROPAGATE(input_transform_dispatch(ctx, in, c->d_V, g, c->mode));
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
+    FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, g, c->mode, &c->cfg));
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+    FC_PROPAGATE(launch_output_transform(ctx, c->d_M, out, g));
+    if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+    return FC_OK;
+}
+
+// `timed` records the stage events of an im2col layer or of a one-pass Winograd layer (fc_conv_profile walks the
+// passes of a split layer itself).
 static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed) {
     fc_context *ctx = c->ctx;
     if (c->algo == FC_ALGO_WINOGRAD) {
-        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
-        FC_PROPAGATE(input_transform_dispatch(ctx, d_in, c->d_V, c->geom, c->mode));
-        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
-        FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, c->geom, c->mode, &c->cfg));
-        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
-        FC_PROPAGATE(launch_output_transform(ctx, c->d_M, d_out, c->geom));
-        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+        const int passes = conv_passes(c);
+        for (int p = 0; p < passes; ++p) FC_PROPAGATE(wino_enqueue_pass(c, p, d_in, d_out, timed && passes == 1));
         return FC_OK;
     }
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
@@ -705,15 +778,21 @@ int fc_conv_profile(fc_conv *c, const float *d_in, float *d_out, int iters, floa
     fc_context *ctx = c->ctx;
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     double acc[5] = {0, 0, 0, 0, 0};
+    const int passes = c->algo == FC_ALGO_WINOGRAD ? conv_passes(c) : 1;
     for (int i = 0; i < iters; ++i) {
-        FC_PROPAGATE(conv_enqueue(c, d_in, d_out, true));
-        FC_CHECK_CUDA(cudaEventSynchronize(ctx->ev[3]));
-        float a = 0, b = 0, d = 0, t = 0;
-        FC_CHECK_CUDA(cudaEventElapsedTime(&a, ctx->ev[0], ctx->ev[1]));
-        FC_CHECK_CUDA(cudaEventElapsedTime(&b, ctx->ev[1], ctx->ev[2]));
-        FC_CHECK_CUDA(cudaEventElapsedTime(&d, ctx->ev[2], ctx->ev[3]));
-        FC_CHECK_CUDA(cudaEventElapsedTime(&t, ctx->ev[0], ctx->ev[3]));
-        acc[0] += a; acc[2] += b; acc[3] += d; acc[4] += t;
+        for (int p = 0; p < passes; ++p) {
+            if (passes == 1)
+                FC_PROPAGATE(conv_enqueue(c, d_in, d_out, true));
+            else
+                FC_PROPAGATE(wino_enqueue_pass(c, p, d_in, d_out, true));
+            FC_CHECK_CUDA(cudaEventSynchronize(ctx->ev[3]));
+            float a = 0, b = 0, d = 0, t = 0;
+            FC_CHECK_CUDA(cudaEventElapsedTime(&a, ctx->ev[0], ctx->ev[1]));
+            FC_CHECK_CUDA(cudaEventElapsedTime(&b, ctx->ev[1], ctx->ev[2]));
+            FC_CHECK_CUDA(cudaEventElapsedTime(&d, ctx->ev[2], ctx->ev[3]));
+            FC_CHECK_CUDA(cudaEventElapsedTime(&t, ctx->ev[0], ctx->ev[3]));
+            acc[0] += a; acc[2] += b; acc[3] += d; acc[4] += t;
+        }
     }
     stage_ms[0] = (float)(acc[0] / iters);
     stage_ms[1] = c->kernel_tran_ms;
@@ -759,7 +838,7 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
     };
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
     if (c->mode == FC_MATH_FP32_MIRRORED) {
-        if (algo == FC_ALGO_WINOGRAD && c->geom.tiles <= 32) push(0, 0, 1, 0);
+        if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
         if (algo == FC_ALGO_IM2COL) push(0, 0, 1, 0);  // thread-per-pixel kernel
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
     } else {
@@ -888,7 +967,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 : 1;
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : 1;
     return FC_OK;
 }
 
@@ -900,6 +979,8 @@ struct fc_layer_list {
     cudaGraphExec_t exec;
     int launches;
     std::vector<fc_conv *> convs;
+    std::vector<const float *> d_ins;
+    std::vector<float *> d_outs;
     std::vector<cudaEvent_t> uploaded, computed;  // per layer, for the pipelined host forward
 };
 
@@ -912,7 +993,7 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     for (int i = 0; i < count; ++i) {
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
-        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 : 1;
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i]) : 1;
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     // one eager pass first: kernel attributes are set and any error shows up outside the capture
@@ -926,6 +1007,12 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     l->exec = nullptr;
     l->launches = launches;
     l->convs.assign(convs, convs + count);
+    l->d_ins.assign(d_ins, d_ins + count);
+    l->d_outs.assign(d_outs, d_outs + count);
+    if (!graph_enabled()) {
+        *out = l;
+        return FC_OK;
+    }
     cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
     int st = FC_OK;
     if (e == cudaSuccess) {
@@ -946,6 +1033,10 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
 
 int fc_layer_list_forward(fc_layer_list *l) {
     FC_REQUIRE(l != nullptr, FC_ERR_INVALID_ARG, "list is NULL");
+    if (l->exec == nullptr) {  // FASTCONV_GRAPH=0
+        for (size_t i = 0; i < l->convs.size(); ++i) FC_PROPAGATE(conv_enqueue(l->convs[i], l->d_ins[i], l->d_outs[i], false));
+        return FC_OK;
+    }
     FC_CHECK_CUDA(cudaGraphLaunch(l->exec, l->ctx->stream));
     return FC_OK;
 }

@@ -394,8 +394,68 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const float *__re
     }
 }
 
+// Many tiles (large feature maps or batches): throughput matters more than latency.  One thread per
+// (oc, tile) item keeps all 64 loads of M in flight at once and does both passes in registers; a warp
+// covers 32 consecutive tiles of one output channel and stages its 6 x 192 results so that the stores
+// run along the output rows.  No block-wide synchronisation.
+constexpr int OTW_WARPS = 4;
+
+__global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(const float *__restrict__ M,
+                                                                              float *__restrict__ out, int n_tiles,
+                                                                              int oc, int tp, int oh, int ow, int th,
+                                                                              int tw) {
+    constexpr int ROW = 32 * 6 + 2;
+    __shared__ float stage[OTW_WARPS][6][ROW];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t_base = blockIdx.x * 32;
+    const int t = t_base + lane, k = blockIdx.y * OTW_WARPS + warp;
+    const size_t plane = (size_t)oc * tp;
+    pdl_trigger();
+    pdl_wait();  // M comes from the GEMM launched just before
+    if (k >= oc) return;  // whole warp
+    if (t < n_tiles) {
+        const float *src = M + (size_t)k * tp + t;
+        float h[8][6];
+#pragma unroll
+        for (int row = 0; row < 8; ++row) {
+            float m[8];
+#pragma unroll
+            for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
+            output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
+        }
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            float s[6];
+            output_transform_1d(h[0][j], h[1][j], h[2][j], h[3][j], h[4][j], h[5][j], h[6][j], h[7][j], s);
+#pragma unroll
+            for (int i = 0; i < 6; ++i) stage[warp][i][lane * 6 + j] = s[i];
+        }
+    }
+    __syncwarp();
+    const int per_img = th * tw;
+    // lane writes elements e = lane, lane+32, ... of every staged row: e -> (tile e/6, column e%6)
+    for (int e = lane; e < 32 * 6; e += 32) {
+        const int te = e / 6, j = e - te * 6;
+        const int tile = t_base + te;
+        if (tile >= n_tiles) continue;
+        const int img = tile / per_img, tt = tile - img * per_img;
+        const int y0 = (tt / tw) * 6, x = (tt % tw) * 6 + j;
+        if (x >= ow) continue;
+        float *dst = out + ((size_t)img * oc + k) * oh * ow + (size_t)y0 * ow + x;
+#pragma unroll
+        for (int i = 0; i < 6; ++i)
+            if (y0 + i < oh) dst[(size_t)i * ow] = stage[warp][i][e];
+    }
+}
+
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g) {
     dim3 block(256);
+    if (g.tiles >= 256) {
+        dim3 wblock(32 * OTW_WARPS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
+        FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
+                                 g.oh, g.ow, g.th, g.tw));
+        return FC_OK;
+    }
     if (g.tiles > 16) {
         dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
         FC_CHECK_CUDA(launch_pdl(output_transform_kernel<32>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,

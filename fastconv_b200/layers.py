@@ -280,6 +280,14 @@ class ConvLayer:
         for label, idx in labels:
             print("%s %fms" % (label, self.stage_ms[idx]))
 
+    @property
+    def kernel_launches(self) -> int:
+        """Kernel launches of one Forward (3 per pass of a Winograd layer, 1 for an implicit GEMM)."""
+        self._create()
+        k = C.c_int()
+        check(self._lib.fc_conv_launches_per_forward(self._conv, C.byref(k)), "fc_conv_launches_per_forward")
+        return k.value
+
     def release(self) -> None:
         if self._conv is not None:
             self._lib.fc_conv_destroy(self._conv)

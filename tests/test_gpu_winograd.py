@@ -32,7 +32,7 @@ def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
-def run_layer(ctx, x, w, pad, mode="fp32"):
+def run_layer(ctx, x, w, pad, mode="fp32", launches=None):
     n, ic, ih, iw = x.shape
     oc = w.shape[0]
     layer = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, ih, iw, oc, 3, 3, 1, 1, pad, pad, pad, pad, 1, False, 1, 1,
@@ -40,6 +40,8 @@ def run_layer(ctx, x, w, pad, mode="fp32"):
     assert layer.Init() == -1  # the reference's Init returns -1 (winoF63ConvZC.cpp:212)
     assert layer.Forward() == 1
     out = layer.output_data.copy()
+    if launches is not None:
+        assert layer.kernel_launches == launches
     layer.release()
     return out
 
@@ -68,6 +70,22 @@ def test_golden_vectors_full_size(ctx, golden):
         w = synth.conv_weights(rec["oc"], rec["ic"], 3, 3, rec["seed_w"])
         got = run_layer(ctx, x, w, rec["pad"])[0]
         assert sha(got) == rec["sha_wino"], f"{rec['ic']}->{rec['oc']}@{rec['ih']} differs from the reference output"
+
+
+@pytest.mark.parametrize("mode,budget_mb,passes", [("fp32", 8, 3), ("fp32", 3, 5), ("3xtf32", 8, 3)])
+def test_batch_split_into_l2_sized_passes(ctx, oracle, monkeypatch, mode, budget_mb, passes):
+    """A batch whose Winograd-domain buffers exceed the L2 budget runs as several passes over blocks of images
+    (here 3 passes of 2+2+1 and 5 passes of 1): same bits as the one-pass run and as the oracle."""
+    n, ic, oc, h = 5, 64, 64, 56
+    x = synth.conv_input(n, ic, h, h, 51)
+    w = synth.conv_weights(oc, ic, 3, 3, 52)
+    monkeypatch.setenv("FASTCONV_L2_BUDGET_MB", "0")
+    whole = run_layer(ctx, x, w, 1, mode, launches=3)
+    monkeypatch.setenv("FASTCONV_L2_BUDGET_MB", str(budget_mb))
+    split = run_layer(ctx, x, w, 1, mode, launches=3 * passes)
+    assert np.array_equal(split, whole)
+    if mode == "fp32":
+        assert np.array_equal(split, oracle.wino_forward(x, w, 1))
 
 
 def _dev(ctx, a):
