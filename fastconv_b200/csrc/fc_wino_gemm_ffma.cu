@@ -129,35 +129,40 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
 
 // ---------------------------------------------------------------------------------------------
 // Few tiles (small feature maps at batch 1: 28x28 -> 25 tiles, 14x14 -> 9, 7x7 -> 4).  The GEMM is a
-// stream over U with a short N, so the blocked kernel above would multiply mostly padding.  Here a
-// thread owns ONE output channel and ALL TN tiles of a position.  A producer warp keeps a ring of
-// 32(ic) x 128(oc) boxes of U in flight with TMA, so HBM latency is hidden by the ring; consumer thread
-// t reads column t of the landed box (consecutive lanes, consecutive words).  V_p is staged a
-// 256-channel chunk at a time and read as broadcasts.  The chain per output element is unchanged:
-// one accumulator, one FMA per input channel, ascending.
+// stream over U with a short N, so the blocked kernel above would multiply mostly padding.  Here a CTA
+// owns 128 output channels and all tiles of one position.  A producer warp keeps a ring of stages in
+// flight with TMA, each stage a 32(ic) x 128(oc) box of U and the matching 32(ic) x tp box of V, so
+// neither HBM nor L2 latency is waited for by the math warps.  There are four consumer warps, one per
+// scheduler of the SM, each covering 32 channels x 4*TT tiles as 8 x 4 lanes: a lane owns 4 channels (one
+// 128-bit read of the landed U row, shared by the 4 lanes of its column) and TT consecutive tiles (read
+// from the V row, shared by the 8 lanes of its row).  Both operands are thus reused across lanes inside
+// one shared-memory read, which is what keeps the kernel off the shared-memory bandwidth limit: a lane
+// per channel with broadcast V reads measured 0.34 issue slots used and 61 us for 512->512 at 25 tiles.
+// Operands of k-step kk+1 are read while the FMAs of kk issue.  The chain per output element is
+// unchanged: one accumulator, one FMA per input channel, ascending.
 // ---------------------------------------------------------------------------------------------
 constexpr int ST_STAGES = 5;
-constexpr int ST_KC = 256;
-constexpr int ST_THREADS = 160;  // 4 consumer warps + 1 producer warp
-constexpr int ST_BOX = 128 * 32 * 4;
+constexpr int ST_BOX = 128 * 32 * 4;         // bytes of a U box
+constexpr int ST_VBOX = 32 * 32 * 4;         // room for a V box (32 k-rows of tp <= 32 floats)
+constexpr int ST_STAGE = ST_BOX + ST_VBOX;
+constexpr int ST_THREADS = 160;              // 4 consumer warps + 1 producer warp
 
-template <int TN>
-__global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmU,
-                                                                               const float *__restrict__ V,
-                                                                               float *__restrict__ M, int *status,
-                                                                               int oc, int tp, int icp) {
+template <int TT>
+__global__ void __launch_bounds__(ST_THREADS, 2)
+    wino_gemm_ffma_skinny_tma_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
+                                     float *__restrict__ M, int *status, int oc, int tp, int icp) {
     using namespace tc;
-    constexpr int TNP = (TN + 3) / 4 * 4;
+    static_assert(TT == 1 || TT == 2 || TT == 4 || TT == 8, "tiles per lane");
     extern __shared__ uint8_t smem_raw[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[ST_STAGES], empty[ST_STAGES]
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * ST_STAGES);
     const uint32_t ring = (smem_u32(smem_raw) + 128 + 127) & ~127u;
-    const float *ring_ptr = reinterpret_cast<const float *>(smem_raw + (ring - smem_u32(smem_raw)));
-    float *Vs = reinterpret_cast<float *>(smem_raw + (ring - smem_u32(smem_raw)) + ST_STAGES * ST_BOX);
+    const uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int p = blockIdx.y, oc0 = blockIdx.x * 128;
     const int num_kb = (icp + 31) / 32;
+    const uint32_t stage_bytes = ST_BOX + 32u * (uint32_t)tp * 4u;
     auto bar_full = [&](int s) { return smem_u32(bars + s); };
     auto bar_empty = [&](int s) { return smem_u32(bars + ST_STAGES + s); };
 
@@ -173,64 +178,88 @@ __global__ void __launch_bounds__(ST_THREADS) wino_gemm_ffma_skinny_tma_kernel(c
     pdl_trigger();
 
     if (warp == 4) {
-        if (lane == 0) {  // U is constant: no need to wait for the input transform
-            for (int kb = 0; kb < num_kb; ++kb) {
+        if (lane == 0) {
+            // U is constant, so the first ring of U boxes is requested before the input transform that writes V
+            // is known to be complete; V boxes follow after the wait
+            const int head = num_kb < ST_STAGES ? num_kb : ST_STAGES;
+            for (int kb = 0; kb < head; ++kb) {
+                mbar_expect_tx(bar_full(kb), stage_bytes);
+                tma_load_3d(ring + kb * ST_STAGE, &tmU, bar_full(kb), oc0, kb * 32, p);  // box: 128 oc x 32 ic
+            }
+            pdl_wait();
+            for (int kb = 0; kb < head; ++kb)
+                tma_load_3d(ring + kb * ST_STAGE + ST_BOX, &tmV, bar_full(kb), 0, kb * 32, p);  // box: tp tiles x 32 ic
+            for (int kb = head; kb < num_kb; ++kb) {
                 const int s = kb % ST_STAGES;
                 const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
                 if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, status)) break;
-                mbar_expect_tx(bar_full(s), ST_BOX);
-                tma_load_3d(ring + s * ST_BOX, &tmU, bar_full(s), oc0, kb * 32, p);  // box: 128 oc x 32 ic
+                mbar_expect_tx(bar_full(s), stage_bytes);
+                tma_load_3d(ring + s * ST_STAGE, &tmU, bar_full(s), oc0, kb * 32, p);
+                tma_load_3d(ring + s * ST_STAGE + ST_BOX, &tmV, bar_full(s), 0, kb * 32, p);
             }
         }
     } else {
-        pdl_wait();  // V comes from the input transform launched just before
-        const int row = oc0 + tid;
-        const float *Vp = V + (size_t)p * icp * tp;
-        float acc[TN];
+        const int ocl = warp * 32 + (lane & 7) * 4;  // first of this lane's 4 channels within the box
+        const int j0 = (lane >> 3) * TT;             // first of this lane's TT tiles
+        float acc[4][TT];
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[j] = 0.0f;
-        // `ok` turns false when a bounded wait gives up; the warp then skips the math but still walks the
-        // loop so that all four consumer warps meet at every chunk barrier
-        bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
-            if (kb % (ST_KC / 32) == 0) {
-                const int k0 = kb * 32;
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // consumers only: everyone is done with the old chunk
-                for (int idx = tid; idx < ST_KC * (TNP / 4); idx += 128) {
-                    const int k = idx / (TNP / 4), t4 = (idx % (TNP / 4)) * 4;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (k0 + k < icp && t4 < tp) v = __ldg(reinterpret_cast<const float4 *>(Vp + (size_t)(k0 + k) * tp + t4));
-                    *reinterpret_cast<float4 *>(&Vs[k * TNP + t4]) = v;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < TT; ++j) acc[i][j] = 0.0f;
+        // TT floats of a V row; lanes past the last real tile read whatever follows inside the stage and never store
+        auto load_v = [&](const float *src, float (&b)[TT]) {
+            if constexpr (TT == 8) {
+                const float4 lo = *reinterpret_cast<const float4 *>(src), hi = *reinterpret_cast<const float4 *>(src + 4);
+                b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w; b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+            } else if constexpr (TT == 4) {
+                const float4 t = *reinterpret_cast<const float4 *>(src);
+                b[0] = t.x; b[1] = t.y; b[2] = t.z; b[3] = t.w;
+            } else if constexpr (TT == 2) {
+                const float2 t = *reinterpret_cast<const float2 *>(src);
+                b[0] = t.x; b[1] = t.y;
+            } else {
+                b[0] = *src;
             }
+        };
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
             const int s = kb % ST_STAGES;
             const uint32_t ph = (uint32_t)(kb / ST_STAGES) & 1u;
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), ph, abort_flag, status));
-            if (!ok) continue;
-            const float *a = ring_ptr + (size_t)s * (ST_BOX / 4) + tid;  // this thread's oc column of the box
-            const float *vk = Vs + (size_t)(kb % (ST_KC / 32)) * 32 * TNP;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), ph, abort_flag, status));
+            if (!ok) break;
+            const float *a = reinterpret_cast<const float *>(ring_ptr + (size_t)s * ST_STAGE) + ocl;
+            const float *vk = reinterpret_cast<const float *>(ring_ptr + (size_t)s * ST_STAGE + ST_BOX) + j0;
+            float4 u = *reinterpret_cast<const float4 *>(a);
+            float b[TT];
+            load_v(vk, b);
 #pragma unroll 8
             for (int kk = 0; kk < 32; ++kk) {
-                const float u = a[kk * 128];
-                const float4 *b4 = reinterpret_cast<const float4 *>(vk + kk * TNP);
+                // the row after the last one of the box is still inside the stage or the slack: read, never used
+                const float4 un = *reinterpret_cast<const float4 *>(a + (kk + 1) * 128);
+                float bn[TT];
+                load_v(vk + (kk + 1) * tp, bn);
+                const float uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-                for (int g = 0; g < TNP / 4; ++g) {
-                    const float4 b = b4[g];
-                    if (g * 4 + 0 < TN) acc[g * 4 + 0] = __fmaf_rn(u, b.x, acc[g * 4 + 0]);
-                    if (g * 4 + 1 < TN) acc[g * 4 + 1] = __fmaf_rn(u, b.y, acc[g * 4 + 1]);
-                    if (g * 4 + 2 < TN) acc[g * 4 + 2] = __fmaf_rn(u, b.z, acc[g * 4 + 2]);
-                    if (g * 4 + 3 < TN) acc[g * 4 + 3] = __fmaf_rn(u, b.w, acc[g * 4 + 3]);
-                }
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < TT; ++j) acc[i][j] = __fmaf_rn(uu[i], b[j], acc[i][j]);
+                u = un;
+#pragma unroll
+                for (int j = 0; j < TT; ++j) b[j] = bn[j];
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(s));  // this warp no longer reads the stage
         }
-        if (ok && row < oc) {
-            float *dst = M + ((size_t)p * oc + row) * tp;
+        if (ok) {
 #pragma unroll
-            for (int j = 0; j < TN; ++j)
-                if (j < tp) dst[j] = acc[j];
+            for (int i = 0; i < 4; ++i) {
+                const int row = oc0 + ocl + i;
+                if (row >= oc) continue;
+                float *dst = M + ((size_t)p * oc + row) * tp + j0;
+#pragma unroll
+                for (int j = 0; j < TT; ++j)
+                    if (j0 + j < tp) dst[j] = acc[i][j];
+            }
         }
     }
     if (*abort_flag) {
@@ -320,6 +349,21 @@ int make_map_u_rowmajor(CUtensorMap *map, const float *base, int ocp, int icp) {
     return FC_OK;
 }
 
+// V[p][icp][tp] as a 3-D tensor (tile, ic, p), box = tp tiles x 32 ic, no swizzle, zero fill outside
+int make_map_v_rowmajor(CUtensorMap *map, const float *base, int tp, int icp) {
+    tc::EncodeTiledFn enc;
+    FC_PROPAGATE(tc::get_encoder(&enc));
+    cuuint64_t dims[3] = {(cuuint64_t)tp, (cuuint64_t)icp, 64};
+    cuuint64_t strides[2] = {(cuuint64_t)tp * 4, (cuuint64_t)tp * icp * 4};
+    cuuint32_t box[3] = {(cuuint32_t)tp, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (tp %d icp %d)", (int)r, tp, icp);
+    return FC_OK;
+}
+
 template <int TN>
 int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
     if (ctx->d_status == nullptr) {  // no context behind the call: the plain-load kernel
@@ -328,15 +372,19 @@ int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_
                                  g.tp, g.icp));
         return FC_OK;
     }
-    constexpr int TNP = (TN + 3) / 4 * 4;
-    CUtensorMap tmU;
+    FC_REQUIRE(g.tp <= 32, FC_ERR_INVALID_ARG, "skinny TensorGEMM needs at most 32 tiles, got %d", g.tp);
+    constexpr int TT = TN <= 4 ? 1 : TN <= 8 ? 2 : TN <= 16 ? 4 : 8;  // tiles per lane: a warp covers 4*TT tiles
+    CUtensorMap tmU, tmV;
     FC_PROPAGATE(make_map_u_rowmajor(&tmU, d_U, g.ocp, g.icp));
-    const size_t smem = 128 + 128 + (size_t)ST_STAGES * ST_BOX + (size_t)ST_KC * TNP * sizeof(float);
-    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_skinny_tma_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FC_PROPAGATE(make_map_v_rowmajor(&tmV, d_V, g.tp, g.icp));
+    // 256 B of barriers and flag, alignment slack, the ring, and 4.5 KB that the look-ahead reads of the last k-step
+    // of the last stage run into (one V row past the box, one U row past that)
+    const size_t smem = 128 + 128 + (size_t)ST_STAGES * ST_STAGE + 4608;
+    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_skinny_tma_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid((unsigned)ceil_div(g.oc, 128), 64), block(ST_THREADS);
-    FC_CHECK_CUDA(launch_pdl(wino_gemm_ffma_skinny_tma_kernel<TN>, grid, block, smem, ctx->stream, tmU, d_V, d_M,
-                             ctx->d_status, g.oc, g.tp, g.icp));
+    FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_skinny_tma_kernel<TT>, grid, block, smem, ctx->stream, tmU, tmV, d_M,
+                              ctx->d_status, g.oc, g.tp, g.icp)));
     return FC_OK;
 }
 
