@@ -34,6 +34,18 @@ VGG16 = [(3, 64, 224), (64, 64, 224), (64, 128, 112), (128, 128, 112), (128, 256
 
 HBM_FALLBACK_GBS = 6650.0
 
+# Arithmetic peaks the per-layer roofline divides by, in TFLOP/s.  TF32 and FP32 are not in MEASURED_PEAKS.json;
+# they were measured on this pool's B200 the same way as its bf16 figure (torch.matmul 8192^3, best of 10, CUDA
+# events): TF32 759.9, FP32 (FFMA) 63.7.  3xTF32 issues three TF32 MMAs per product, so its peak is a third.
+TF32_TFLOPS = 759.9
+FP32_TFLOPS = 63.7
+MODE_PEAK_TFLOPS = {"tf32": TF32_TFLOPS, "3xtf32": TF32_TFLOPS / 3.0, "fp32": FP32_TFLOPS}
+
+# DRAM bytes (read + write) per TensorGEMM launch, averaged over the 13 launches of one step of the default
+# workload (VGG-16, batch 1), from one ncu capture of `dram__bytes_read.sum + dram__bytes_write.sum`
+# (profiles/tensorgemm_dram_traffic_vgg16_batch1.md).  None for any other workload.
+NCU_GEMM_TRAFFIC_BYTES = {"fp32": 43.26e6, "tf32": 44.78e6, "3xtf32": 44.78e6}
+
 
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
@@ -363,6 +375,7 @@ def main():
 
     # ---- per-layer and per-kernel device times (CUDA events around each stage, same inputs) ----------
     per_layer, stage_tot = [], [0.0] * 5
+    roof_sum_ms = 0.0
     launches_per_step = 0
     gemm_bytes = gemm_ms = gemm_flops = 0.0
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
@@ -375,14 +388,23 @@ def main():
         lib.fc_conv_launches_per_forward(hdl, C.byref(nl))
         launches_per_step += nl.value
         t, tp, icp = wino_geometry(n, c, k, h)
+        # roofline of a layer: the slower of its Winograd-domain flops at the mode's arithmetic peak and its HBM
+        # bytes (input, transformed filter, output) at the measured copy bandwidth
         bytes_wino = 4.0 * (n * c * h * h + 64 * c * k + n * k * h * h)
+        bytes_min = 4.0 * (n * c * h * h + 9 * c * k + n * k * h * h)
         wino_flops = 2.0 * 64 * t * c * k
+        t_hbm_ms = bytes_wino / hbm_peak / 1e6
+        t_flop_ms = wino_flops / (MODE_PEAK_TFLOPS[args.mode] * 1e12) * 1e3
+        roof_ms = max(t_hbm_ms, t_flop_ms)
+        roof_sum_ms += roof_ms
         per_layer.append({
             "layer": f"{c}->{k}@{h}", "ms": round(one.value, 5),
             "gflops_direct_equiv": round(layer_flops(n, c, k, h) / one.value / 1e6, 1),
             "stage_ms": [round(float(v), 5) for v in ms],
-            "hbm_roofline_ms": round(bytes_wino / hbm_peak / 1e6, 5),
-            "frac_of_hbm_roofline": round(bytes_wino / hbm_peak / 1e6 / one.value, 4),
+            "t_hbm_ms": round(t_hbm_ms, 5), "t_flop_ms": round(t_flop_ms, 5),
+            "bound": "hbm" if t_hbm_ms >= t_flop_ms else "math",
+            "frac_of_roofline": round(roof_ms / one.value, 4),
+            "frac_of_min_bytes_roofline": round(max(bytes_min / hbm_peak / 1e6, t_flop_ms) / one.value, 4),
         })
         for i in range(5):
             stage_tot[i] += ms[i]
@@ -396,8 +418,10 @@ def main():
         "kernel": "TensorGEMM (64 batched U*V products, one launch per layer)",
         "bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
         "frac": round(achieved_gbs / hbm_peak, 4), "peak_source": f"of {peak_kind}",
-        "traffic": None,
+        "traffic": NCU_GEMM_TRAFFIC_BYTES[args.mode] if (args.layers == "vgg16" and n == 1) else None,
         "algorithmic_bytes_per_launch": gemm_bytes / nl, "avg_launch_ms": gemm_ms / nl,
+        "stack_roofline_ms": round(roof_sum_ms, 5), "stack_frac_of_roofline": round(roof_sum_ms / ms_step, 4),
+        "arithmetic_peak_tflops": round(MODE_PEAK_TFLOPS[args.mode], 1),
         "winograd_domain_tflops": round(gemm_flops / (gemm_ms / 1e3) / 1e12, 2),
         "share_of_step": {"InputTran": round(stage_tot[0] / stage_tot[4], 3), "TensorGEMM": round(stage_tot[2] / stage_tot[4], 3),
                           "OutputTran": round(stage_tot[3] / stage_tot[4], 3)},

@@ -24,6 +24,7 @@ SOURCES = [
     "fc_gemm_tc.cu",
     "fc_igemm_tc.cu",
     "fc_static_scratch.cu",
+    "fc_peer.cu",
 ]
 
 NVCC_FLAGS = [

@@ -733,6 +733,31 @@ int fc_conv_forward_device(fc_conv *c, const float *d_in, float *d_out) {
     return conv_enqueue(c, d_in, d_out, false);
 }
 
+int fc_conv_forward_scatter(fc_conv *c, const float *d_in, float *const *outs, int *const *flags, int world, int rank,
+                            int k0, int oc_total, int step) {
+    FC_REQUIRE(c && d_in && outs && flags, FC_ERR_INVALID_ARG, "NULL argument");
+    FC_REQUIRE(world >= 1 && world <= FC_MAX_PEERS && rank >= 0 && rank < world, FC_ERR_INVALID_ARG,
+               "rank %d of %d outside the supported 1..%d ranks", rank, world, FC_MAX_PEERS);
+    FC_REQUIRE(c->algo == FC_ALGO_WINOGRAD, FC_ERR_UNSUPPORTED, "the channel-split forward is built for Winograd layers");
+    FC_REQUIRE(c->desc.batch == 1, FC_ERR_UNSUPPORTED, "the channel-split forward takes one image (batch %d)", c->desc.batch);
+    FC_REQUIRE(k0 >= 0 && k0 + c->desc.oc <= oc_total, FC_ERR_INVALID_ARG, "slab [%d, %d) outside %d channels", k0,
+               k0 + c->desc.oc, oc_total);
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    const WinoGeom &g = c->geom;
+    PeerOuts dst;
+    memset(&dst, 0, sizeof dst);
+    dst.count = world;
+    for (int r = 0; r < world; ++r) {
+        FC_REQUIRE(outs[r] && flags[r], FC_ERR_INVALID_ARG, "rank %d has a NULL buffer", r);
+        dst.base[r] = outs[r] + (size_t)k0 * g.oh * g.ow;
+    }
+    FC_PROPAGATE(input_transform_dispatch(ctx, d_in, c->d_V, g, c->mode));
+    FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, g, c->mode, &c->cfg));
+    FC_PROPAGATE(launch_output_transform_scatter(ctx, c->d_M, dst, g));
+    return launch_peer_publish(ctx, flags, world, rank, step);
+}
+
 int fc_conv_forward_host(fc_conv *c, const float *h_in, float *h_out) {
     FC_REQUIRE(c && h_in && h_out, FC_ERR_INVALID_ARG, "NULL argument");
     fc_context *ctx = c->ctx;

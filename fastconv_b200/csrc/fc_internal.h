@@ -79,6 +79,12 @@ struct KernelCfg {
     int smem_kb;    // tcgen05 kernels: shared-memory budget of the operand ring (sets the stage count / CTAs per SM)
 };
 
+// Output buffers of the ranks of a channel-split layer, as seen from this GPU (own memory or peer-mapped).
+struct PeerOuts {
+    float *base[FC_MAX_PEERS];
+    int count;
+};
+
 struct CommonSlot {
     size_t bytes;
     void *ptr;
@@ -136,6 +142,9 @@ int launch_filter_transform_rowmajor(fc_context *ctx, const float *d_kernel, flo
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g);
+int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g);
+int launch_peer_publish(fc_context *ctx, int *const *flags, int world, int rank, int step);
+int launch_peer_wait(fc_context *ctx, const int *flags, int world, int step);
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
                           const KernelCfg *cfg = nullptr);
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,

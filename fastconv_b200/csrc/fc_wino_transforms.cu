@@ -330,10 +330,9 @@ int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d
 //            that are neighbours in x are neighbours in memory.
 // TPW is 32, 16 or 8 so that small feature maps (9 or 4 tiles) do not idle most lanes.
 // ---------------------------------------------------------------------------------------------
-template <int TPW>
-__global__ void __launch_bounds__(256) output_transform_kernel(const float *__restrict__ M, float *__restrict__ out,
-                                                               int n_tiles, int oc, int tp, int oh, int ow, int th,
-                                                               int tw) {
+template <int TPW, typename Store>
+__device__ __forceinline__ void output_transform_block(const float *__restrict__ M, int n_tiles, int oc, int tp, int oh,
+                                                       int ow, int th, int tw, Store store) {
     constexpr int OCB = 32 / TPW;
     constexpr int ROW = TPW * 6 + 1;
     __shared__ float hbuf[8][6][33];          // [row][j][lane]
@@ -390,8 +389,30 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const float *__re
         if (org < 0 || kk >= oc) continue;
         const int y = (org >> 16) + i, x = (org & 0xffff) + j;
         const int img = (t_base + te) / per_img;
-        if (y < oh && x < ow) out[((size_t)img * oc + kk) * out_page + (size_t)y * ow + x] = stage[o][i][e];
+        if (y < oh && x < ow) store(((size_t)img * oc + kk) * out_page + (size_t)y * ow + x, stage[o][i][e]);
     }
+}
+
+template <int TPW>
+__global__ void __launch_bounds__(256) output_transform_kernel(const float *__restrict__ M, float *__restrict__ out,
+                                                               int n_tiles, int oc, int tp, int oh, int ow, int th,
+                                                               int tw) {
+    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [out](size_t at, float v) { out[at] = v; });
+}
+
+// The same transform for a layer whose output channels are split over several GPUs: every result is stored
+// into the output buffer of each GPU (its own and, through peer-mapped pointers over NVLink, the others'), so
+// the all-gather of the channel slabs happens in the stores of the transform itself.  dst.base[r] already
+// points at this rank's first channel inside rank r's buffer.
+template <int TPW>
+__global__ void __launch_bounds__(256) output_transform_scatter_kernel(const float *__restrict__ M, PeerOuts dst,
+                                                                       int n_tiles, int oc, int tp, int oh, int ow,
+                                                                       int th, int tw) {
+    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [&dst](size_t at, float v) {
+#pragma unroll
+        for (int r = 0; r < FC_MAX_PEERS; ++r)
+            if (r < dst.count) dst.base[r][at] = v;
+    });
 }
 
 // Many tiles (large feature maps or batches): throughput matters more than latency.  One thread per
@@ -470,6 +491,24 @@ int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, con
                                  g.oh, g.ow, g.th, g.tw));
     }
     FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g) {
+    dim3 block(256);
+    if (g.tiles > 16) {
+        dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<32>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
+                                 g.tp, g.oh, g.ow, g.th, g.tw));
+    } else if (g.tiles > 8) {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 2));
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<16>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
+                                 g.tp, g.oh, g.ow, g.th, g.tw));
+    } else {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<8>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
+                                 g.tp, g.oh, g.ow, g.th, g.tw));
+    }
     return FC_OK;
 }
 

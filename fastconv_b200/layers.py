@@ -45,16 +45,25 @@ class Context:
         self.device = device
         self._pinned = []
         self._children = weakref.WeakSet()  # layers / layer lists planned on this context
+        self._peer_arenas = {}  # IPC handle bytes -> base address of a peer's arena mapped into this process
 
     def adopt(self, child) -> None:
         """Registers an object with a release()/close() method that must run before the context goes."""
         self._children.add(child)
 
     # -- lifetime ---------------------------------------------------------------------------
+    def close_peer_mappings(self) -> None:
+        """Unmaps the arenas of other ranks.  Call it on every rank, then synchronise the ranks, BEFORE any of
+        them destroys its context: an exporter must not free memory a peer still has mapped."""
+        for base in self._peer_arenas.values():
+            self._lib.fc_peer_close(self._h, C.c_void_p(base))
+        self._peer_arenas = {}
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             for child in list(self._children):  # their device buffers live in this context's arena
                 (getattr(child, "release", None) or child.close)()
+            self.close_peer_mappings()
             for p in self._pinned:
                 self._lib.fc_host_free_pinned(p)
             self._pinned = []

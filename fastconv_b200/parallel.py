@@ -144,3 +144,99 @@ class KShardedConv:
 
         obj.forward = forward_on_library_stream
         return obj
+
+
+class PeerKShardedConv:
+    """K-sharded Winograd layer whose all-gather is fused into the output transform: the kernel of each rank
+    stores its channel slab into the output buffer of every rank through peer-mapped pointers over NVLink
+    (`fc_conv_forward_scatter`), publishes a step flag, and a bounded wait kernel on every rank makes the
+    stream wait for all slabs.  No NCCL call in the data path; torch.distributed only carries the CUDA IPC
+    handles at construction.  Two output buffers alternate by step, so a rank that runs one step ahead never
+    overwrites what a peer is still reading; `forward` returns the device address of the buffer just filled.
+    """
+
+    def __init__(self, ctx, weights: np.ndarray, ih: int, iw: int, pad: int = 1, mode: str = "fp32", group=None):
+        import torch.distributed as dist
+
+        from . import _lib
+        from .layers import make_desc
+
+        self._lib, self._check = _lib.load(), _lib.check
+        lib, check = self._lib, self._check
+        self.ctx, self.group = ctx, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.oc = int(weights.shape[0])
+        ic = int(weights.shape[1])
+        self.k0, self.k1 = shard_channels(self.oc, self.world, self.rank)
+        if self.k1 <= self.k0:
+            raise ValueError("a rank would own no output channel")
+        w_slice = np.ascontiguousarray(weights[self.k0:self.k1], dtype=np.float32)
+        self.oh, self.ow = ih + 2 * pad - 2, iw + 2 * pad - 2
+        desc = make_desc(1, ic, ih, iw, self.k1 - self.k0, 3, 3, 1, 1, pad, pad, pad, pad)
+        h = C.c_void_p()
+        check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, _lib.MODE_NAMES[mode],
+                                 C.c_void_p(w_slice.ctypes.data), C.byref(h)), "fc_conv_create")
+        self._conv = h
+        d_in = C.c_void_p()
+        check(lib.fc_conv_device_buffers(h, C.byref(d_in), None), "fc_conv_device_buffers")
+        self._d_in = d_in
+        self.out_bytes = 4 * self.oc * self.oh * self.ow
+        self._outs = [ctx.alloc(self.out_bytes), ctx.alloc(self.out_bytes)]  # alternate by step
+        self._flags = ctx.zeros(4 * 8)
+        ctx.synchronize()  # the flags are zero before any peer can learn their address
+        self.step = 0
+
+        # exchange the IPC handle of this rank's arena and the offsets of its three buffers
+        handle = (C.c_ubyte * 64)()
+        offs = []
+        for p in (*self._outs, self._flags):
+            off = C.c_size_t()
+            check(lib.fc_peer_export(ctx.handle, C.c_void_p(p), handle, C.byref(off)), "fc_peer_export")
+            offs.append(off.value)
+        mine = (bytes(handle), offs)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._peer_outs = [[0] * self.world, [0] * self.world]
+        self._peer_flags = [0] * self.world
+        opened = ctx._peer_arenas
+        for r, (hbytes, roffs) in enumerate(everyone):
+            if r == self.rank:
+                base = None
+            else:
+                if hbytes not in opened:  # one mapping per peer arena and process
+                    b = C.c_void_p()
+                    buf = (C.c_ubyte * 64).from_buffer_copy(hbytes)
+                    check(lib.fc_peer_open(ctx.handle, buf, C.byref(b)), "fc_peer_open")
+                    opened[hbytes] = b.value
+                base = opened[hbytes]
+            for i in range(2):
+                self._peer_outs[i][r] = self._outs[i] if base is None else base + roffs[i]
+            self._peer_flags[r] = self._flags if base is None else base + roffs[2]
+        dist.barrier(group=group)
+        ctx.adopt(self)
+
+    def upload(self, x: np.ndarray) -> None:
+        self.ctx.upload(np.ascontiguousarray(x, dtype=np.float32), self._d_in.value)
+
+    def forward(self) -> int:
+        """Enqueues one forward on the context stream; returns the device address of the full output."""
+        self.step += 1
+        which = self.step & 1
+        vp = C.c_void_p * self.world
+        outs, flags = vp(*self._peer_outs[which]), vp(*self._peer_flags)
+        self._check(self._lib.fc_conv_forward_scatter(self._conv, self._d_in, outs, flags, self.world, self.rank,
+                                                      self.k0, self.oc, self.step), "fc_conv_forward_scatter")
+        self._check(self._lib.fc_peer_wait(self.ctx.handle, C.c_void_p(self._flags), self.world, self.step),
+                    "fc_peer_wait")
+        return self._outs[which]
+
+    def result(self, dptr: int) -> np.ndarray:
+        self.ctx.synchronize()
+        return self.ctx.download(dptr, (1, self.oc, self.oh, self.ow))
+
+    def release(self) -> None:
+        if self._conv is not None:
+            self._lib.fc_conv_destroy(self._conv)
+            self._conv = None

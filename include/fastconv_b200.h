@@ -227,6 +227,32 @@ int fc_layer_list_forward_host(fc_layer_list *list, const float *const *h_ins, f
 int fc_layer_list_launches(const fc_layer_list *list, int *kernel_launches);
 int fc_layer_list_destroy(fc_layer_list *list);
 
+/* ---- channel-split layer over several GPUs ----------------------------------
+ * No counterpart in the reference, which is a single-process CPU program; its closest relative is
+ * the OpenMP split of the output-channel loop (winoF63ZC/winoF63ZC.cpp:1486-1544).  One process per
+ * GPU; rank r owns output channels [k0, k1) of a single-image layer (a fc_conv created from that
+ * slice of the weights).  The ranks export their full-size output buffers and a small flag array
+ * with fc_peer_export, exchange the handles by any means (the Python host uses torch.distributed)
+ * and map each other's with fc_peer_open.  fc_conv_forward_scatter then runs the layer with an
+ * output transform that stores the slab into EVERY rank's buffer (plain stores over NVLink) and
+ * publishes `step` in flag[rank] of every rank; fc_peer_wait enqueues a bounded wait until all
+ * ranks have published `step`, after which this rank's buffer holds the whole [oc_total][oh][ow]
+ * output.  `step` must grow by one per forward; a caller that lets ranks run ahead of each other
+ * alternates between two output buffers.  A wait that gives up reports FC_ERR_TIMEOUT at the next
+ * fc_context_synchronize. */
+#define FC_MAX_PEERS 8
+#define FC_PEER_HANDLE_BYTES 64
+/* handle of the context's arena allocation and the offset of `dptr` inside it */
+int fc_peer_export(fc_context *ctx, const void *dptr, unsigned char handle[FC_PEER_HANDLE_BYTES], size_t *offset);
+/* maps a peer's arena into this process; *base + offset is the peer's `dptr` as this GPU sees it */
+int fc_peer_open(fc_context *ctx, const unsigned char handle[FC_PEER_HANDLE_BYTES], void **base);
+int fc_peer_close(fc_context *ctx, void *base);
+/* outs[r]: rank r's [oc_total][oh][ow] buffer, flags[r]: rank r's int[world] array, both as seen
+ * from this GPU (index `rank` is local memory).  k0 = first output channel of this rank's slab. */
+int fc_conv_forward_scatter(fc_conv *conv, const float *d_in, float *const *outs, int *const *flags, int world,
+                            int rank, int k0, int oc_total, int step);
+int fc_peer_wait(fc_context *ctx, const int *d_flags, int world, int step);
+
 /* ---- error metrics on the host ---------------------------------------------- */
 /* diff(), utility/helper.cpp:74-89: mean |a-b| over the elements with |a-b| > 1e-5 */
 float fc_diff(const float *a, const float *b, int len);

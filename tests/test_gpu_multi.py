@@ -49,6 +49,21 @@ def _worker(rank, world, port, ret):
             full = fc.ConvWinoF63ZCLayer(xb, w, None, None, ic, hw, hw, oc, batch=4, iter=1, ctx=ctx)
             full.Init(); full.Forward()
             ok = ok and np.array_equal(mine.output_data, full.output_data[b0:b1])
+            # K sharding with the all-gather fused into the output transform (peer stores over NVLink, flags,
+            # bounded wait): every rank ends with the whole output, bit-equal to the one-GPU layer, on both of
+            # the alternating output buffers and in both operand layouts
+            for mode, ref in (("fp32", whole.output_data), ("3xtf32", None)):
+                peer = parallel.PeerKShardedConv(ctx, w, hw, hw, 1, mode)
+                peer.upload(x)
+                if ref is None:
+                    one = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, hw, hw, oc, iter=1, mode=mode, ctx=ctx)
+                    one.Init(); one.Forward()
+                    ref = one.output_data
+                for _ in range(3):
+                    ok = ok and np.array_equal(peer.result(peer.forward()), ref)
+                dist.barrier()
+            ctx.close_peer_mappings()
+            dist.barrier()
         flag = torch.tensor([1 if ok else 0], device=f"cuda:{rank}")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
