@@ -200,15 +200,23 @@ def run_k_sharded(args, rank, world, local_rank, dist):
     for idx, (c, k, h) in enumerate(layers):
         w = synth.conv_weights(k, c, 3, 3, 2000 + idx)
         x = synth.conv_input(1, c, h, h, 1000 + idx)
-        conv = parallel.KShardedConv.gpu(ctx, w, h, h, 1, args.mode)
-        conv.forward(x)  # plans the slice, uploads the input once
+        if args.gather == "peer":
+            conv = parallel.PeerKShardedConv(ctx, w, h, h, 1, args.mode)
+            conv.upload(x)
+            conv.forward()
+        else:
+            conv = parallel.KShardedConv.gpu(ctx, w, h, h, 1, args.mode)
+            conv.forward(x)  # plans the slice, uploads the input once
         convs.append(conv)
         flops += layer_flops(1, c, k, h)
         del w
 
     def step():
         for conv in convs:
-            conv.forward(None)
+            if args.gather == "peer":
+                conv.forward()
+            else:
+                conv.forward(None)
 
     for _ in range(args.warmup):
         step()
@@ -233,9 +241,14 @@ def run_k_sharded(args, rank, world, local_rank, dist):
             "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": args.mode, "data": "synthetic",
             "config": {"workload": "3x3 s1 p1, batch 1, " + ";".join(f"{c}->{k}@{h}" for c, k, h in layers),
-                       "parallelism": f"output channels split over {world} GPU(s), one NCCL all-gather per layer",
+                       "parallelism": f"output channels split over {world} GPU(s), " + (
+                           "slabs stored into every rank's output by the output transform (peer stores over NVLink)"
+                           if args.gather == "peer" else "one NCCL all-gather per layer"),
                        "math_mode": args.mode},
-            "gpu_launches": 3 * len(layers) * args.steps, "clocks": clocks}))
+            "gpu_launches": (5 if args.gather == "peer" else 3) * len(layers) * args.steps, "clocks": clocks}))
+    ctx.synchronize()
+    ctx.close_peer_mappings()
+    dist.barrier()
     ctx.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -254,6 +267,9 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "k"],
                     help="'batch': every rank runs the stack on its own images (no collective, the default); "
                          "'k': single-image wide layers with output channels split over the ranks + NCCL all-gather")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="with --shard k: 'peer' = slabs stored into every rank's output by the output transform itself "
+                         "(peer pointers over NVLink, flags); 'nccl' = separate all-gather after the layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "fastconv":
