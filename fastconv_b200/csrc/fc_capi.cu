@@ -97,6 +97,7 @@ struct fc_conv {
     WinoGeom tail_geom;   // geometry of the last, shorter pass (n == 0 when the batch divides evenly)
     float *d_kernel;  // raw [oc][ic*kh*kw]
     float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
+    float *d_ktab;    // fp32 implicit GEMM: int pairs (offset, u:v) per k, in a float-typed arena slot
     float *d_U, *d_V, *d_M;
     float *d_in, *d_out;  // staging for forward_host
     float kernel_tran_ms;
@@ -519,7 +520,7 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
 
 static void conv_release(fc_conv *c) {
     fc_context *ctx = c->ctx;
-    float *bufs[] = {c->d_kernel, c->d_packed, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
     for (float *b : bufs)
         if (b) ctx->arena.release((uintptr_t)b);
     delete c;
@@ -538,8 +539,6 @@ static void drop(fc_context *ctx, float **p) {
     *p = nullptr;
 }
 
-// Workspaces and one-time weight re-layout of one algorithm (idempotent): Winograd gets U/V/M and the
-// filter transform, the tensor-core implicit GEMM gets the packed hi/lo weight planes.
 // Optional L2 blocking over the batch.  Unblocked, V and M go out to HBM and come back: 2*(V+M) bytes of traffic that
 // the layer's own bytes (input, weights, output) do not contain.  With P passes over blocks of images V and M of a pass
 // can stay in L2, at the price of reading the transformed filter P times and of P times as many, smaller launches.
@@ -580,11 +579,15 @@ static int plan_passes(fc_conv *c) {
 
 static int conv_passes(const fc_conv *c) { return (c->desc.batch + c->pass_imgs - 1) / c->pass_imgs; }
 
+// Workspaces and one-time weight re-layout of one algorithm (idempotent): Winograd gets U/V/M and the
+// filter transform, the tensor-core implicit GEMM gets the packed hi/lo weight planes, the fp32 implicit
+// GEMM its k -> (offset, u:v) decode table.
 static int conv_prepare(fc_conv *c, int algo) {
     fc_context *ctx = c->ctx;
     const fc_conv_desc &d = c->desc;
     int st = FC_OK;
     bool timed = false;
+    std::vector<int> ktab;  // host copy of the decode table; must outlive the asynchronous upload below
     if (algo == FC_ALGO_WINOGRAD) {
         st = plan_passes(c);
         if (st != FC_OK) return st;
@@ -609,6 +612,22 @@ static int conv_prepare(fc_conv *c, int algo) {
             st = launch_igemm_pack_weights(ctx, c->d_kernel, c->d_packed, d.oc, K);
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
+        }
+    }
+    else if (c->d_ktab == nullptr) {
+        FC_REQUIRE((long long)d.ic * d.ih * d.iw < (1ll << 31) && d.kh < 0x4000 && d.kw < 0x4000, FC_ERR_UNSUPPORTED,
+                   "image or kernel too large for the 32-bit decode table");
+        const size_t entries = igemm_ktab_entries(d);
+        ktab.resize(2 * entries);
+        igemm_fill_ktab(d, ktab.data());
+        st = grab(ctx, &c->d_ktab, 2 * entries);
+        if (st == FC_OK) {
+            cudaError_t ce = cudaMemcpyAsync(c->d_ktab, ktab.data(), 2 * entries * sizeof(int), cudaMemcpyHostToDevice,
+                                             ctx->stream);
+            if (ce != cudaSuccess) {
+                set_error("decode table upload failed: %s", cudaGetErrorString(ce));
+                st = FC_ERR_CUDA;
+            }
         }
     }
     if (st != FC_OK) return st;
@@ -716,7 +735,8 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
     int st;
     if (c->mode == FC_MATH_FP32_MIRRORED)
-        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg);
+        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg,
+                               reinterpret_cast<const int *>(c->d_ktab));
     else
         st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg);
     FC_PROPAGATE(st);
@@ -864,7 +884,10 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
     if (c->mode == FC_MATH_FP32_MIRRORED) {
         if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
-        if (algo == FC_ALGO_IM2COL) push(0, 0, 1, 0);  // thread-per-pixel kernel
+        if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its five block shapes
+            const int small_tiles[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};
+            for (auto &t : small_tiles) push(t[0], t[1], 1, 0);
+        }
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
     } else {
         const int widths[5] = {32, 64, 96, 128, 256};
@@ -981,6 +1004,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
         drop(ctx, &c->d_U); drop(ctx, &c->d_V); drop(ctx, &c->d_M);
     } else {
         drop(ctx, &c->d_packed);
+        drop(ctx, &c->d_ktab);
     }
     if (verbose)
         printf("Best Config: (%d %d %d) algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", c->desc.ic, c->desc.oc,

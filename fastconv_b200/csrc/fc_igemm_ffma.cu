@@ -162,91 +162,154 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
 }
 
 // ---------------------------------------------------------------------------------------------
-// Small problems (batch-1 ResNet layers: 49..3136 pixels, a few hundred channels).  The blocked kernel
-// above would launch a handful of CTAs, each walking the whole reduction alone.  Here a thread owns one
-// output pixel and TM output channels: consecutive threads read consecutive pixels of the input
-// (coalesced, stride sw), the k -> (c,u,v) decode is uniform per step and kept in counters, the
-// weights of the TM channels are staged in shared memory a chunk at a time and read as broadcasts.
-// The chain per output element is the same: one accumulator, one FMA per k, ascending.
+// Small and medium problems (batch-1 ResNet layers: 49..3136 pixels, up to 4608-long reductions).  The
+// 16 x 16-thread kernel above launches a handful of CTAs for them and decodes k -> (c,u,v) with two integer
+// divisions per gathered element.  This kernel takes the decode from a per-layer table (one int2 per k:
+// element offset inside the image and (u,v)), brings both operands to shared memory with asynchronous
+// copies through a 3-stage ring (weights as 16-byte pieces along k, gathered input as 4-byte pieces with
+// zero fill for the padding), and comes in block shapes from 64x64 down to 8x32 so that even a 49-pixel
+// layer spreads over the machine.  Lanes run along output channels, so a thread reads four k-steps of
+// its weight rows in one conflict-free 128-bit read and its pixels as a broadcast.  The chain per output
+// element is unchanged: one accumulator, one FMA per k, ascending.
 // ---------------------------------------------------------------------------------------------
-constexpr int DR_THREADS = 128;
-constexpr int DR_KC = 256;
-constexpr int DR_BATCH = 8;  // input values fetched ahead of the FMAs that consume them
+constexpr int TK_KC = 32, TK_KCP = 36, TK_STAGES = 3;
 
-template <int TM, int PXB>
-__global__ void __launch_bounds__(DR_THREADS) igemm_ffma_direct_kernel(const float *__restrict__ in,
-                                                                       const float *__restrict__ A,
-                                                                       float *__restrict__ out, IgemmParams P) {
-    constexpr int GROUPS = DR_THREADS / PXB;  // channel groups per block
-    constexpr int OCB = TM * GROUPS;          // output channels per block
-    __shared__ __align__(16) float As[DR_KC][OCB];
+__device__ __forceinline__ void cp_async_zfill_16(void *smem_dst, const void *gmem_src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_zfill_4(void *smem_dst, const void *gmem_src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+template <int BM, int BN, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+    igemm_ffma_tile_kernel(const float *__restrict__ in, const float *__restrict__ A, float *__restrict__ out,
+                           const int2 *__restrict__ ktab, IgemmParams P, int a_vec) {
+    constexpr int OCL = BM / TM, NT = OCL * (BN / TN), BNP = BN + 4;
+    constexpr int B_STEP = NT / BN, B_ITERS = TK_KC / B_STEP;
+    static_assert(NT % BN == 0 && TK_KC % B_STEP == 0 && (TN == 1 || TN == 2 || TN == 4), "block shape");
+    extern __shared__ __align__(16) float tk_smem[];
+    float(*As)[BM][TK_KCP] = reinterpret_cast<float(*)[BM][TK_KCP]>(tk_smem);
+    float(*Bs)[TK_KC][BNP] = reinterpret_cast<float(*)[TK_KC][BNP]>(tk_smem + TK_STAGES * BM * TK_KCP);
+
     const int tid = threadIdx.x;
-    const int px_l = tid % PXB, grp = tid / PXB;
-    const int pix = blockIdx.x * PXB + px_l;
-    const int ocb0 = blockIdx.y * OCB, oc0 = ocb0 + grp * TM;
+    const int oc0 = blockIdx.y * BM, pix0 = blockIdx.x * BN;
     const int ohw = P.oh * P.ow;
-    const bool pix_ok = pix < P.npix;
-    int img = 0, oi = 0, oj = 0;
-    if (pix_ok) {
-        img = pix / ohw;
-        const int rem = pix - img * ohw;
-        oi = rem / P.ow;
-        oj = rem - oi * P.ow;
+
+    // the pixel this thread gathers for is fixed for the whole reduction
+    const int lp = tid % BN, lk0 = tid / BN;
+    const int gpix = pix0 + lp;
+    const bool gpix_ok = gpix < P.npix;
+    int base_row = 0, base_col = 0;
+    const float *pix_ptr = in;
+    if (gpix_ok) {
+        const int img = gpix / ohw, rem = gpix - img * ohw;
+        const int oi = rem / P.ow, oj = rem - oi * P.ow;
+        base_row = oi * P.sh - P.pad_t;
+        base_col = oj * P.sw - P.pad_l;
+        pix_ptr = in + (size_t)img * P.ic * P.ih * P.iw + (ptrdiff_t)base_row * P.iw + base_col;
     }
-    const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
-    const float *pix_ptr = in + (size_t)img * P.ic * P.ih * P.iw + (ptrdiff_t)base_row * P.iw + base_col;
 
-    float acc[TM];
-#pragma unroll
-    for (int i = 0; i < TM; ++i) acc[i] = 0.0f;
-
-    int c = 0, u = 0, v = 0;  // decode of the running k, the same in every thread
-    for (int k0 = 0; k0 < P.K; k0 += DR_KC) {
-        const int kc = min(DR_KC, P.K - k0);
-        __syncthreads();
-        for (int idx = tid; idx < DR_KC * OCB; idx += DR_THREADS) {
-            const int j = idx / DR_KC, kk = idx - j * DR_KC;  // consecutive threads walk k: coalesced rows of A
-            As[kk][j] = (ocb0 + j < P.oc && kk < kc) ? __ldg(A + (size_t)(ocb0 + j) * P.K + k0 + kk) : 0.0f;
+    auto load_stage = [&](int st, int k0) {
+        if (a_vec) {  // rows of A are 16-byte aligned: K is a multiple of 4
+            for (int idx = tid; idx < BM * (TK_KC / 4); idx += NT) {
+                const int row = idx / (TK_KC / 4), c4 = (idx % (TK_KC / 4)) * 4;
+                const bool ok = oc0 + row < P.oc && k0 + c4 < P.K;
+                cp_async_zfill_16(&As[st][row][c4], A + (ok ? (size_t)(oc0 + row) * P.K + k0 + c4 : 0), ok);
+            }
+        } else {
+            for (int idx = tid; idx < BM * TK_KC; idx += NT) {
+                const int row = idx / TK_KC, kk = idx % TK_KC;
+                const bool ok = oc0 + row < P.oc && k0 + kk < P.K;
+                cp_async_zfill_4(&As[st][row][kk], A + (ok ? (size_t)(oc0 + row) * P.K + k0 + kk : 0), ok);
+            }
         }
-        __syncthreads();
-        for (int kk = 0; kk < kc; kk += DR_BATCH) {
-            float val[DR_BATCH];
 #pragma unroll
-            for (int j = 0; j < DR_BATCH; ++j) {  // all loads of the batch first, so they overlap
-                val[j] = 0.0f;
-                if (kk + j < kc) {
-                    const int row = base_row + u, col = base_col + v;
-                    if (pix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw)
-                        val[j] = __ldg(pix_ptr + (c * P.ih + u) * P.iw + v);
-                    if (++v == P.kw) {
-                        v = 0;
-                        if (++u == P.kh) {
-                            u = 0;
-                            ++c;
-                        }
-                    }
+        for (int r = 0; r < B_ITERS; ++r) {
+            const int kk = lk0 + r * B_STEP;
+            const int2 e = __ldg(ktab + k0 + kk);  // the table is padded to a multiple of 32 with out-of-image entries
+            const int row = base_row + (e.y >> 16), col = base_col + (e.y & 0xffff);
+            const bool ok = gpix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw;
+            cp_async_zfill_4(&Bs[st][kk][lp], ok ? pix_ptr + e.x : in, ok);
+        }
+    };
+
+    const int ox = tid % OCL, pxl = tid / OCL;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+    const int n_slabs = (P.K + TK_KC - 1) / TK_KC;
+#pragma unroll
+    for (int s = 0; s < TK_STAGES - 1; ++s) {
+        if (s < n_slabs) load_stage(s, s * TK_KC);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int s = 0; s < n_slabs; ++s) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(TK_STAGES - 2) : "memory");
+        __syncthreads();  // slab s has landed for everyone, and everyone is done with the stage refilled next
+        const int nxt = s + TK_STAGES - 1;
+        if (nxt < n_slabs) load_stage(nxt % TK_STAGES, nxt * TK_KC);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = s % TK_STAGES;
+#pragma unroll
+        for (int k4 = 0; k4 < TK_KC / 4; ++k4) {
+            float4 a[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = *reinterpret_cast<const float4 *>(&As[st][ox + OCL * i][k4 * 4]);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                float b[TN];
+                const float *bp = &Bs[st][k4 * 4 + kk][pxl * TN];
+                if constexpr (TN == 4) {
+                    const float4 t = *reinterpret_cast<const float4 *>(bp);
+                    b[0] = t.x; b[1] = t.y; b[2] = t.z; b[3] = t.w;
+                } else if constexpr (TN == 2) {
+                    const float2 t = *reinterpret_cast<const float2 *>(bp);
+                    b[0] = t.x; b[1] = t.y;
+                } else {
+                    b[0] = *bp;
+                }
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(av, b[j], acc[i][j]);
                 }
             }
-            // rows of As past kc are zero, so a short last batch adds exact zeros
-#pragma unroll
-            for (int j = 0; j < DR_BATCH; ++j)
-#pragma unroll
-                for (int i = 0; i < TM; ++i) acc[i] = __fmaf_rn(As[kk + j][grp * TM + i], val[j], acc[i]);
         }
     }
-    if (pix_ok) {
-        float *dst = out + ((size_t)img * P.oc + oc0) * ohw + (pix - img * ohw);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
 #pragma unroll
-        for (int i = 0; i < TM; ++i)
-            if (oc0 + i < P.oc) dst[(size_t)i * ohw] = acc[i];
+    for (int j = 0; j < TN; ++j) {
+        const int pix = pix0 + pxl * TN + j;
+        if (pix >= P.npix) continue;
+        const int img = pix / ohw, rem = pix - img * ohw;
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int r = oc0 + ox + OCL * i;
+            if (r < P.oc) out[((size_t)img * P.oc + r) * ohw + rem] = acc[i][j];
+        }
     }
 }
 
-template <int TM, int PXB>
-int launch_direct(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const IgemmParams &P) {
-    constexpr int OCB = TM * (DR_THREADS / PXB);
-    dim3 grid((unsigned)ceil_div(P.npix, PXB), (unsigned)ceil_div(P.oc, OCB)), block(DR_THREADS);
-    igemm_ffma_direct_kernel<TM, PXB><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+template <int BM, int BN, int TM, int TN>
+int launch_tile(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const int2 *d_ktab,
+                const IgemmParams &P) {
+    constexpr int NT = (BM / TM) * (BN / TN);
+    const size_t smem = (size_t)TK_STAGES * (BM * TK_KCP + TK_KC * (BN + 4)) * sizeof(float);
+    FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_ffma_tile_kernel<BM, BN, TM, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    dim3 grid((unsigned)ceil_div(P.npix, BN), (unsigned)ceil_div(P.oc, BM)), block(NT);
+    igemm_ffma_tile_kernel<BM, BN, TM, TN><<<grid, block, smem, ctx->stream>>>(d_in, d_kernel, d_out, d_ktab, P,
+                                                                              P.K % 4 == 0 ? 1 : 0);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -264,29 +327,59 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
     return FC_OK;
 }
 
+size_t igemm_ktab_entries(const fc_conv_desc &d) { return (size_t)round_up(d.ic * d.kh * d.kw, TK_KC); }
+
+void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs) {
+    const int K = d.ic * d.kh * d.kw, Kp = round_up(K, TK_KC);
+    for (int k = 0; k < Kp; ++k) {
+        if (k < K) {
+            const int c = k / (d.kh * d.kw), r = k - c * d.kh * d.kw, u = r / d.kw, v = r - u * d.kw;
+            host_pairs[2 * k] = (c * d.ih + u) * d.iw + v;
+            host_pairs[2 * k + 1] = (u << 16) | v;
+        } else {  // past the reduction: a row far below the image, so the copy zero-fills
+            host_pairs[2 * k] = 0;
+            host_pairs[2 * k + 1] = 0x4000 << 16;
+        }
+    }
+}
+
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow, const KernelCfg *cfg) {
+                      int oh, int ow, const KernelCfg *cfg, const int *d_ktab) {
     IgemmParams P;
     P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
     P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
     P.K = d.ic * d.kh * d.kw;
     P.npix = d.batch * oh * ow;
-    const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
-    const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;
-    // skinny = 1 forces the thread-per-pixel kernel, 2 the blocked one; otherwise the blocked kernel only when
-    // its grid gives the machine about one and a half CTAs per SM
-    const size_t blocked_ctas = ceil_div(P.npix, wide_n ? 128 : 64) * ceil_div(d.oc, wide_m ? 128 : 64);
     const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const int pick = cfg ? cfg->skinny : 0;
-    if (pick == 1 || (pick == 0 && 2 * blocked_ctas < 3 * (size_t)sms)) {
-        // few output elements: fewer channels per thread, so more threads share the (latency-bound) chains
-        const bool thin = (size_t)P.npix * d.oc < (size_t)sms * 2048;
-        if (P.npix >= 96) return thin ? launch_direct<4, 128>(ctx, d_in, d_kernel, d_out, P)
-                                      : launch_direct<8, 128>(ctx, d_in, d_kernel, d_out, P);
-        if (P.npix >= 48) return thin ? launch_direct<4, 64>(ctx, d_in, d_kernel, d_out, P)
-                                      : launch_direct<8, 64>(ctx, d_in, d_kernel, d_out, P);
-        return thin ? launch_direct<4, 32>(ctx, d_in, d_kernel, d_out, P) : launch_direct<8, 32>(ctx, d_in, d_kernel, d_out, P);
+    const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
+    const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;
+    const size_t blocked_ctas = ceil_div(P.npix, wide_n ? 128 : 64) * ceil_div(d.oc, wide_m ? 128 : 64);
+    // skinny = 1: the table-driven kernel in the block shape bm x bn (or the heuristic's), 2: the 16x16-thread kernel;
+    // otherwise the latter only when its grid gives the machine three CTAs per SM
+    if (d_ktab && (pick == 1 || (pick == 0 && blocked_ctas < 3 * (size_t)sms))) {
+        const int2 *tab = reinterpret_cast<const int2 *>(d_ktab);
+        const int shapes[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};
+        int bm = 0, bn = 0;
+        if (pick == 1 && cfg->bm && cfg->bn) {
+            bm = cfg->bm; bn = cfg->bn;
+        } else {  // the largest block that still gives one and a half CTAs per SM, else the one with most CTAs
+            size_t best = 0;
+            for (const auto &sh : shapes) {
+                const size_t ctas = ceil_div(P.npix, sh[1]) * ceil_div(d.oc, sh[0]);
+                if (2 * ctas >= 3 * (size_t)sms) { bm = sh[0]; bn = sh[1]; break; }
+                if (ctas > best) { best = ctas; bm = sh[0]; bn = sh[1]; }
+            }
+        }
+        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P);
+        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4>(ctx, d_in, d_kernel, d_out, tab, P);
+        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2>(ctx, d_in, d_kernel, d_out, tab, P);
+        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2>(ctx, d_in, d_kernel, d_out, tab, P);
+        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1>(ctx, d_in, d_kernel, d_out, tab, P);
+        set_error("no table-driven implicit GEMM with a %d x %d block", bm, bn);
+        return FC_ERR_INVALID_ARG;
     }
+    // no table (the stage entry point outside a planned layer): the 16x16-thread kernel for every size
     dim3 grid((unsigned)ceil_div(P.npix, wide_n ? 128 : 64), (unsigned)ceil_div(d.oc, wide_m ? 128 : 64)), block(THREADS);
     if (wide_m && wide_n)
         igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);

@@ -151,8 +151,11 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
                         int mode, const KernelCfg *cfg = nullptr);
 int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
                          int image);
+// d_ktab: per-layer k -> (offset, u:v) table (igemm_fill_ktab), or NULL outside a planned layer
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow, const KernelCfg *cfg = nullptr);
+                      int oh, int ow, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr);
+size_t igemm_ktab_entries(const fc_conv_desc &d);
+void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs);  // 2 ints per entry
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
                     int oh, int ow, int mode, const KernelCfg *cfg = nullptr);
 size_t igemm_packed_elems(int oc, int K);
