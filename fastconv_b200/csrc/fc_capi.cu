@@ -614,7 +614,7 @@ static int conv_prepare(fc_conv *c, int algo) {
             timed = true;
         }
     }
-    else if (c->d_ktab == nullptr) {
+    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_ktab == nullptr) {  // every implicit GEMM reads the table
         FC_REQUIRE((long long)d.ic * d.ih * d.iw < (1ll << 31) && d.kh < 0x4000 && d.kw < 0x4000, FC_ERR_UNSUPPORTED,
                    "image or kernel too large for the 32-bit decode table");
         const size_t entries = igemm_ktab_entries(d);
@@ -738,7 +738,8 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
         st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg,
                                reinterpret_cast<const int *>(c->d_ktab));
     else
-        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg);
+        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg,
+                             reinterpret_cast<const int *>(c->d_ktab));
     FC_PROPAGATE(st);
     if (timed) {
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));

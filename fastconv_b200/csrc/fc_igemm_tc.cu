@@ -27,6 +27,7 @@ struct IgemmTcParams {
     int ic, ih, iw, oc, kh, kw, sh, sw, pad_l, pad_t, oh, ow;
     int K, num_kb, bn, stages, tmem_cols;
     int splits, kb_per_split;  // split-K over blockIdx.z: split s reduces k-blocks [s*kb_per_split, ...)
+    const int2 *ktab;          // per-layer k -> (offset, u:v) table padded to 32 entries, or NULL
 };
 
 __global__ void pack_weights_kernel(const float *__restrict__ kernel, float *__restrict__ packed, int oc, int K,
@@ -134,63 +135,92 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
         }
     } else {
         // ---------------- gather producers, then epilogue ----------------
+        // The gather is asynchronous: a thread issues 4-byte cp.async copies (zero fill outside the image) for its
+        // pixel rows of k-block `it` straight to their swizzled place, commits them as one group, and only then
+        // finishes k-block it-LAG (waits for that group, splits hi/lo in place for 3xTF32, hands the slab to the MMA
+        // warp).  So LAG k-blocks of loads are in flight per thread and global latency is not on the critical path.
         const int gt = threadIdx.x - 64;  // 0..127
         const int khw = P.kh * P.kw;
         const float *img_ptr = P.in + (size_t)img * P.ic * P.ih * P.iw;
+        const int lag = S > 2 ? 2 : S - 1;
         bool ok = true;
-        for (int kb = kb0; kb < kb1 && ok; ++kb) {
-            const int s = (kb - kb0) % S;
-            const uint32_t ph = (uint32_t)((kb - kb0) / S) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status));  // warp-uniform
-            if (!ok) break;
-            // lane l of every warp decodes k = kb*32 + l once; the values travel by shuffle below
-            const int k_mine = kb * BK + lane;
-            int off_mine = -1, uv_mine = 0;
-            if (k_mine < P.K) {
-                const int c = k_mine / khw, r2 = k_mine - c * khw;
-                const int u = r2 / P.kw, v = r2 - u * P.kw;
-                off_mine = (c * P.ih + u) * P.iw + v;
-                uv_mine = (u << 16) | v;
-            }
-            uint8_t *b_hi = ring_ptr + s * stage_bytes + A_BYTES;
-            uint8_t *b_lo = b_hi + part_bytes;
-            // a thread owns pixel rows n = gt, gt+128, ... of the slab (bn <= 256)
-            // (every lane runs the loop and its shuffles; lanes past the slab only skip the accesses)
-            for (int nb = 0; nb < P.bn; nb += 128) {
-                const int n = nb + gt;
-                const bool n_ok = n < P.bn;
-                const int pix = pix0 + n;
-                const bool pix_ok = n_ok && pix < ohw;
-                const int oi = pix_ok ? pix / P.ow : 0, oj = pix_ok ? pix - oi * P.ow : 0;
-                const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
-                const float *pix_ptr = img_ptr + (ptrdiff_t)base_row * P.iw + base_col;
-                const uint32_t row_off = (uint32_t)(n >> 3) * 1024u + (uint32_t)(n & 7) * 128u;
-                const uint32_t sw = (uint32_t)(n & 7);
+        for (int it = kb0; it < kb1 + lag && ok; ++it) {
+            if (it < kb1) {
+                const int s = (it - kb0) % S;
+                const uint32_t ph = (uint32_t)((it - kb0) / S) & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status));  // warp-uniform
+                if (!ok) break;
+                // lane l of every warp decodes k = it*32 + l once (from the layer's table when there is one);
+                // the values travel by shuffle below
+                const int k_mine = it * BK + lane;
+                int off_mine = 0, uv_mine = 0x4000 << 16;  // a row far below the image: zero fill
+                if (P.ktab != nullptr) {
+                    const int2 e = __ldg(P.ktab + k_mine);  // padded to a multiple of 32 entries
+                    off_mine = e.x;
+                    uv_mine = e.y;
+                } else if (k_mine < P.K) {
+                    const int c = k_mine / khw, r2 = k_mine - c * khw;
+                    const int u = r2 / P.kw, v = r2 - u * P.kw;
+                    off_mine = (c * P.ih + u) * P.iw + v;
+                    uv_mine = (u << 16) | v;
+                }
+                const uint32_t b_hi = ring + s * stage_bytes + A_BYTES;
+                // a thread owns pixel rows n = gt, gt+128, ... of the slab (bn <= 256); every lane runs the loop
+                // and its shuffles, lanes past the slab only skip the copies
+                for (int nb = 0; nb < P.bn; nb += 128) {
+                    const int n = nb + gt;
+                    const bool n_ok = n < P.bn;
+                    const int pix = pix0 + n;
+                    const bool pix_ok = n_ok && pix < ohw;
+                    const int oi = pix_ok ? pix / P.ow : 0, oj = pix_ok ? pix - oi * P.ow : 0;
+                    const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
+                    const float *pix_ptr = img_ptr + (ptrdiff_t)base_row * P.iw + base_col;
+                    const uint32_t row_off = (uint32_t)(n >> 3) * 1024u + (uint32_t)(n & 7) * 128u;
+                    const uint32_t sw = (uint32_t)(n & 7);
 #pragma unroll 8
-                for (int kk = 0; kk < BK; ++kk) {
-                    const int off = __shfl_sync(0xffffffffu, off_mine, kk);
-                    const int uv = __shfl_sync(0xffffffffu, uv_mine, kk);
-                    float val = 0.0f;
-                    if (pix_ok && off >= 0) {
+                    for (int kk = 0; kk < BK; ++kk) {
+                        const int off = __shfl_sync(0xffffffffu, off_mine, kk);
+                        const int uv = __shfl_sync(0xffffffffu, uv_mine, kk);
                         const int row = base_row + (uv >> 16), col = base_col + (uv & 0xffff);
-                        if ((unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw) val = __ldg(pix_ptr + off);
-                    }
-                    // K-major, 128-byte swizzle: 16-byte chunk index XOR row-in-group
-                    const uint32_t o = row_off + ((((uint32_t)kk >> 2) ^ sw) << 4) + ((uint32_t)kk & 3u) * 4u;
-                    if (n_ok) {
-                        if (kSplit) {
-                            const float hi = to_tf32(val);
-                            *reinterpret_cast<float *>(b_hi + o) = hi;
-                            *reinterpret_cast<float *>(b_lo + o) = val - hi;
-                        } else {
-                            *reinterpret_cast<float *>(b_hi + o) = val;
+                        const bool in_img = pix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw;
+                        // K-major, 128-byte swizzle: 16-byte chunk index XOR row-in-group
+                        const uint32_t o = row_off + ((((uint32_t)kk >> 2) ^ sw) << 4) + ((uint32_t)kk & 3u) * 4u;
+                        if (n_ok) {
+                            const float *src = in_img ? pix_ptr + off : P.in;
+                            const int bytes = in_img ? 4 : 0;  // 0 source bytes: the destination is zero-filled
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(b_hi + o), "l"(src), "r"(bytes)
+                                         : "memory");
                         }
                     }
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar_full_b(s));
+            asm volatile("cp.async.commit_group;" ::: "memory");  // one group per iteration, empty ones in the tail
+            const int done = it - lag;
+            if (done >= kb0) {
+                if (lag == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+                else if (lag == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                else asm volatile("cp.async.wait_group 0;" ::: "memory");
+                const int sd = (done - kb0) % S;
+                if (kSplit) {  // this thread's rows only: hi = tf32(x) stays in place, lo = x - hi goes to the lo slab
+                    uint8_t *b_hi = ring_ptr + sd * stage_bytes + A_BYTES;
+                    uint8_t *b_lo = b_hi + part_bytes;
+                    for (int n = gt; n < P.bn; n += 128) {
+                        const uint32_t row_off = (uint32_t)(n >> 3) * 1024u + (uint32_t)(n & 7) * 128u;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            float4 x = *reinterpret_cast<const float4 *>(b_hi + row_off + c * 16);
+                            float4 h = make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w));
+                            *reinterpret_cast<float4 *>(b_hi + row_off + c * 16) = h;
+                            *reinterpret_cast<float4 *>(b_lo + row_off + c * 16) =
+                                make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(bar_full_b(sd));
+            }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // nothing of this thread is in flight past this point
         if (mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
             tc_fence_after();
             const int q = warp & 3;
@@ -236,7 +266,7 @@ int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_p
 }
 
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode, const KernelCfg *cfg) {
+                    int oh, int ow, int mode, const KernelCfg *cfg, const int *d_ktab) {
     using namespace tc;
     const bool split = mode == FC_MATH_3XTF32;
     const int K = d.ic * d.kh * d.kw, Kp = round_up(K, BK);
@@ -257,6 +287,7 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
     P.K = K; P.num_kb = num_kb; P.bn = bn; P.tmem_cols = pow2_at_least(bn, 32);
     P.splits = splits;
+    P.ktab = reinterpret_cast<const int2 *>(d_ktab);
     P.kb_per_split = (num_kb + splits - 1) / splits;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
     const size_t n_ctas = base_ctas * splits;

@@ -157,7 +157,7 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
 size_t igemm_ktab_entries(const fc_conv_desc &d);
 void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs);  // 2 ints per entry
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode, const KernelCfg *cfg = nullptr);
+                    int oh, int ow, int mode, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr);
 size_t igemm_packed_elems(int oc, int K);
 int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 
