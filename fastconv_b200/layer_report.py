@@ -1,6 +1,6 @@
 """Per-layer report over the benchmark configurations: VGG-16, ResNet-50 v1.5 and the wide single-image sweep.
 
-    python -m fastconv_b200.layer_report --set resnet50 --mode fp32 [--batch N] [--tune] [--iters 50]
+    python -m fastconv_b200.layer_report --set resnet50 --mode fp32 [--batch N] [--tune] [--iters 50] [--only I]
 
 Every layer is planned with `-a auto` (select_algorithm of ConvTest.cpp:318-331, 1x1 stride 1 routed to the
 implicit GEMM), run `iters` times back to back on device-resident data and timed with CUDA events; one
@@ -62,6 +62,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--tune", action="store_true", help="run Tuning() (timed configuration search) before measuring")
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--only", type=int, default=None, help="index of the one layer of the set to run")
     args = ap.parse_args()
 
     lib = _lib.load()
@@ -70,6 +71,8 @@ def main() -> None:
     total_ms = total_flops = 0.0
     with Context(args.device, arena_bytes=12 << 30) as ctx:
         for idx, (ic, oc, hw, k, s, p) in enumerate(SETS[args.set]):
+            if args.only is not None and idx != args.only:
+                continue
             desc = make_desc(n, ic, hw, hw, oc, k, k, s, s, p, p, p, p)
             w = synth.conv_weights(oc, ic, k, k, 2000 + idx)
             x = synth.conv_input(n, ic, hw, hw, 1000 + idx)
