@@ -11,6 +11,8 @@ from pathlib import Path
 from . import build as _build
 
 FC_OK = 0
+(FC_ERR_INVALID_ARG, FC_ERR_UNSUPPORTED, FC_ERR_OUT_OF_MEMORY, FC_ERR_CUDA, FC_ERR_NO_DEVICE, FC_ERR_TIMEOUT,
+ FC_ERR_COMM) = -1, -2, -3, -4, -5, -6, -7
 ALGO_AUTO, ALGO_DIRECT, ALGO_IM2COL, ALGO_WINOGRAD = 0, 1, 2, 3
 MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32 = 0, 1, 2
 MODE_NAMES = {"fp32": MATH_FP32_MIRRORED, "ffma": MATH_FP32_MIRRORED, "3xtf32": MATH_3XTF32, "tf32": MATH_TF32}
