@@ -1,6 +1,6 @@
 """Generates tests/golden/fastconv_golden.npz from the FastConv reference itself.
 
-Run in a container that has the reference tree (default /root/reference):
+Run where the reference tree is present (its location is the REF variable of oracle/Makefile):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
