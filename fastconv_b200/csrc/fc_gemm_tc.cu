@@ -16,6 +16,11 @@
 //               hi = tf32(x) and lo = x - hi, so each k-step becomes lo*hi + hi*lo + hi*hi with fp32
 //               accumulation: fp32-class accuracy without touching HBM twice.
 //
+// Layers with at most 64 output channels run with the operand roles exchanged (kSwap): the 128 accumulator rows
+// are 128 TILES and the N columns are the output channels, M_p^T[tile][oc] = sum_ic V_p[tile][ic] * U_p[oc][ic].
+// Both operands are K-major either way, so only the descriptors trade places; no accumulator row is padding, and
+// the epilogue's stores (lane = tile) are full 128-byte lines of M[p][oc][tile..].
+//
 // U is constant, so the producer fills the ring's U halves before griddepcontrol.wait (the kernel may
 // have been launched while the input transform is still running) and adds V afterwards.
 // Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
@@ -41,16 +46,17 @@ __device__ __forceinline__ int u_box_row(const TcParams &P, int p, int oc0, int 
     return ((p * P.n_oc_blk + (oc0 >> 7)) * P.n_kb_u + kb) * U_BOX_ROWS;
 }
 
+template <bool kSwap>
 __device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p, int &oc0, int &t0) {
     // tile block fastest, then oc block, then position: CTAs next to each other share the same U box
     const int tb = item % P.n_tile_blk;
     const int rest = item / P.n_tile_blk;
-    t0 = tb * P.bn;
+    t0 = tb * (kSwap ? BM : P.bn);  // exchanged roles: a block is 128 tiles (rows) x all output channels (columns)
     oc0 = (rest % P.n_oc_blk) * BM;
     p = rest / P.n_oc_blk;
 }
 
-template <bool kSplit>
+template <bool kSplit, bool kSwap>
 __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const TcParams P) {
@@ -102,22 +108,28 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            // the first slot of a stage (A operand, 128 rows) and the second (B operand, bn rows): U, V or V, U
+            auto load_u = [&](uint32_t stage, uint32_t bar, int p, int oc0, int kb) {
+                tma_load_3d(stage + (kSwap ? A_BYTES : 0), &tmU, bar, 0, u_box_row(P, p, oc0, kb), 0);
+            };
+            auto load_v = [&](uint32_t stage, uint32_t bar, int p, int t0, int kb) {
+                tma_load_3d(stage + (kSwap ? 0 : A_BYTES), &tmV, bar, kb * BK, t0, p);
+            };
             int g = 0;  // k-blocks issued so far by this CTA, over all its items
             bool first = true, ok = true;
             for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
                 int p, oc0, t0;
-                item_coords(P, item, p, oc0, t0);
+                item_coords<kSwap>(P, item, p, oc0, t0);
                 int kb = 0;
                 if (first) {
                     // the ring is empty: fill it with U boxes before waiting for the producer of V
                     const int pre = P.num_kb < S ? P.num_kb : S;
                     for (; kb < pre; ++kb) {
                         mbar_expect_tx(bar_full(kb), part_bytes);
-                        tma_load_3d(ring + kb * stage_bytes, &tmU, bar_full(kb), 0, u_box_row(P, p, oc0, kb), 0);
+                        load_u(ring + kb * stage_bytes, bar_full(kb), p, oc0, kb);
                     }
                     pdl_wait();
-                    for (int j = 0; j < pre; ++j)
-                        tma_load_3d(ring + j * stage_bytes + A_BYTES, &tmV, bar_full(j), j * BK, t0, p);
+                    for (int j = 0; j < pre; ++j) load_v(ring + j * stage_bytes, bar_full(j), p, t0, j);
                     g = pre;
                     first = false;
                 }
@@ -128,8 +140,8 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                     if (!ok) break;
                     const uint32_t a_dst = ring + s * stage_bytes;
                     mbar_expect_tx(bar_full(s), part_bytes);
-                    tma_load_3d(a_dst, &tmU, bar_full(s), 0, u_box_row(P, p, oc0, kb), 0);
-                    tma_load_3d(a_dst + A_BYTES, &tmV, bar_full(s), kb * BK, t0, p);
+                    load_u(a_dst, bar_full(s), p, oc0, kb);
+                    load_v(a_dst, bar_full(s), p, t0, kb);
                 }
             }
         }
@@ -179,7 +191,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
         bool ok = true, waited = false;
         for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
             int p, oc0, t0;
-            item_coords(P, item, p, oc0, t0);
+            item_coords<kSwap>(P, item, p, oc0, t0);
             if (kSplit) {
                 const int all_chunks = (int)(part_bytes / 16);
                 for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
@@ -212,29 +224,48 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
             ok = mbar_wait(bar_acc_full(acc), acc_ph, abort_flag, P.status);
             if (!ok) break;
             tc_fence_after();
-            const int row = oc0 + q * 32 + lane;
-            float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
             const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * P.acc_cols);
-            for (int c0 = 0; c0 < P.bn; c0 += 32) {
-                float va[16], vb[16];
-                tc_ld16(t_addr + (uint32_t)c0, va);
-                const bool second = c0 + 16 < P.bn;
-                if (second) tc_ld16(t_addr + (uint32_t)(c0 + 16), vb);
-                if (c0 + 32 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
-                    tc_fence_before();
-                    mbar_arrive(bar_acc_empty(acc));
-                }
-                if (row < P.oc) {
+            if constexpr (kSwap) {
+                // accumulator row = tile, column = output channel: for every channel a warp stores 32 consecutive tiles
+                const int tile = t0 + q * 32 + lane;
+                float *dst = P.M + (size_t)p * P.oc * P.tp + tile;
+                for (int c0 = 0; c0 < P.bn; c0 += 16) {
+                    float va[16];
+                    tc_ld16(t_addr + (uint32_t)c0, va);
+                    if (c0 + 16 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
+                        tc_fence_before();
+                        mbar_arrive(bar_acc_empty(acc));
+                    }
+                    if (tile < P.tp) {
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        if (t0 + c0 + j < P.tp)  // tp is a multiple of 8: a float4 never straddles the end
-                            *reinterpret_cast<float4 *>(dst + c0 + j) = make_float4(va[j], va[j + 1], va[j + 2], va[j + 3]);
-                    if (second) {
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < P.oc) dst[(size_t)(c0 + j) * P.tp] = va[j];
+                    }
+                }
+            } else {
+                const int row = oc0 + q * 32 + lane;
+                float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
+                for (int c0 = 0; c0 < P.bn; c0 += 32) {
+                    float va[16], vb[16];
+                    tc_ld16(t_addr + (uint32_t)c0, va);
+                    const bool second = c0 + 16 < P.bn;
+                    if (second) tc_ld16(t_addr + (uint32_t)(c0 + 16), vb);
+                    if (c0 + 32 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
+                        tc_fence_before();
+                        mbar_arrive(bar_acc_empty(acc));
+                    }
+                    if (row < P.oc) {
 #pragma unroll
                         for (int j = 0; j < 16; j += 4)
-                            if (t0 + c0 + 16 + j < P.tp)
-                                *reinterpret_cast<float4 *>(dst + c0 + 16 + j) =
-                                    make_float4(vb[j], vb[j + 1], vb[j + 2], vb[j + 3]);
+                            if (t0 + c0 + j < P.tp)  // tp is a multiple of 8: a float4 never straddles the end
+                                *reinterpret_cast<float4 *>(dst + c0 + j) = make_float4(va[j], va[j + 1], va[j + 2], va[j + 3]);
+                        if (second) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                if (t0 + c0 + 16 + j < P.tp)
+                                    *reinterpret_cast<float4 *>(dst + c0 + 16 + j) =
+                                        make_float4(vb[j], vb[j + 1], vb[j + 2], vb[j + 3]);
+                        }
                     }
                 }
             }
@@ -259,10 +290,12 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode,
                         const KernelCfg *cfg) {
     const bool split = mode == FC_MATH_3XTF32;
-    // tile blocks of at most 128 tiles (or the tuned width), balanced, multiple of 16 (UMMA N granularity at M=128)
+    // At most 64 output channels: exchanged roles, rows = 128 tiles, columns = the channels (multiple of 16).
+    // Otherwise tile blocks of at most 128 tiles (or the tuned width), balanced, multiple of 16 (UMMA N at M=128).
+    const bool swap = g.oc <= 64;
     const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
-    const int n_blk = (g.tp + max_bn - 1) / max_bn;
-    const int bn = round_up((g.tp + n_blk - 1) / n_blk, 16);
+    const int n_blk = swap ? (g.tp + BM - 1) / BM : (g.tp + max_bn - 1) / max_bn;
+    const int bn = swap ? round_up(g.oc, 16) : round_up((g.tp + n_blk - 1) / n_blk, 16);
     TcParams P;
     P.M = d_M;
     P.status = ctx->d_status;
@@ -290,18 +323,18 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     int ctas = ctx->sm_count * per_sm;
     if (ctas > P.n_items) ctas = P.n_items;
 
-    CUtensorMap tmU, tmV;
-    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, U_BOX_ROWS));
-    FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, bn));
+    CUtensorMap tmU, tmV;  // box rows: the 128-row operand and the bn-row operand
+    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap ? bn : U_BOX_ROWS));
+    FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, swap ? BM : bn));
 
     dim3 grid((unsigned)ctas), block(TC_THREADS);
-    if (split) {
-        FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FC_CHECK_CUDA(launch_pdl(wino_gemm_tc_kernel<true>, grid, block, smem, ctx->stream, tmU, tmV, P));
-    } else {
-        FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FC_CHECK_CUDA(launch_pdl(wino_gemm_tc_kernel<false>, grid, block, smem, ctx->stream, tmU, tmV, P));
-    }
+    auto launch = [&](auto kernel) -> int {
+        FC_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FC_CHECK_CUDA(launch_pdl(kernel, grid, block, smem, ctx->stream, tmU, tmV, P));
+        return FC_OK;
+    };
+    if (split) FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<true, true>) : launch(wino_gemm_tc_kernel<true, false>));
+    else FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<false, true>) : launch(wino_gemm_tc_kernel<false, false>));
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }

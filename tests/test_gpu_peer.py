@@ -48,7 +48,13 @@ def test_scatter_forward_of_two_slabs_equals_the_whole_layer(ctx, mode, hw):
         ctx.synchronize()
         assert ctx.download(d_flags, (8,)).view(np.int32)[0] == step
         lib.fc_conv_destroy(slab)
-    assert np.array_equal(ctx.download(d_out, (1, oc, hw, hw)), ref)
+    got = ctx.download(d_out, (1, oc, hw, hw))
+    if mode == "fp32":
+        assert np.array_equal(got, ref)
+    else:
+        # slabs of at most 64 channels run the tensor-core GEMM with exchanged operand roles (another MMA shape), so
+        # the tensor-core modes agree with the unsplit layer to rounding of the accumulation, not bit for bit
+        assert np.linalg.norm(got - ref) <= 1e-6 * np.linalg.norm(ref)
     lib.fc_conv_destroy(whole)
 
 
