@@ -39,6 +39,9 @@ struct TcParams {
     int oc, tp, bn, num_kb, stages, acc_cols;
     int n_tile_blk, n_oc_blk, n_items;
     int n_kb_u;  // boxes per (position, oc block) of the packed filter
+    int n_oc_items;  // work items along the output channels: n_oc_blk blocks of 128, or blocks of `bn` with exchanged roles
+    int b_bytes;     // bytes of the second operand slot of a stage
+    int u_loads;     // exchanged roles: 128-row boxes of U per stage (1 or 2)
 };
 
 // row coordinate of U box (p, ocb, kb) in the packed filter viewed as a [boxes*128][32] matrix
@@ -51,9 +54,9 @@ __device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p,
     // tile block fastest, then oc block, then position: CTAs next to each other share the same U box
     const int tb = item % P.n_tile_blk;
     const int rest = item / P.n_tile_blk;
-    t0 = tb * (kSwap ? BM : P.bn);  // exchanged roles: a block is 128 tiles (rows) x all output channels (columns)
-    oc0 = (rest % P.n_oc_blk) * BM;
-    p = rest / P.n_oc_blk;
+    t0 = tb * (kSwap ? BM : P.bn);  // exchanged roles: a block is 128 tiles (rows) x bn output channels (columns)
+    oc0 = (rest % P.n_oc_items) * (kSwap ? P.bn : BM);
+    p = rest / P.n_oc_items;
 }
 
 template <bool kSplit, bool kSwap>
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t ring = (smem_u32(smem_raw) + 512 + 1023) & ~1023u;
-    const uint32_t b_bytes = (uint32_t)P.bn * BK * 4;
+    const uint32_t b_bytes = (uint32_t)P.b_bytes;
     const uint32_t part_bytes = A_BYTES + b_bytes;  // one (A,B) pair
     const uint32_t stage_bytes = part_bytes * (kSplit ? 2 : 1);
 
@@ -111,6 +114,8 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
             // the first slot of a stage (A operand, 128 rows) and the second (B operand, bn rows): U, V or V, U
             auto load_u = [&](uint32_t stage, uint32_t bar, int p, int oc0, int kb) {
                 tma_load_3d(stage + (kSwap ? A_BYTES : 0), &tmU, bar, 0, u_box_row(P, p, oc0, kb), 0);
+                if (kSwap && P.u_loads == 2)  // channels oc0+128.. of a 256-wide block: the next packed box
+                    tma_load_3d(stage + 2 * A_BYTES, &tmU, bar, 0, u_box_row(P, p, oc0 + BM, kb), 0);
             };
             auto load_v = [&](uint32_t stage, uint32_t bar, int p, int t0, int kb) {
                 tma_load_3d(stage + (kSwap ? 0 : A_BYTES), &tmV, bar, kb * BK, t0, p);
@@ -228,7 +233,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
             if constexpr (kSwap) {
                 // accumulator row = tile, column = output channel: for every channel a warp stores 32 consecutive tiles
                 const int tile = t0 + q * 32 + lane;
-                float *dst = P.M + (size_t)p * P.oc * P.tp + tile;
+                float *dst = P.M + ((size_t)p * P.oc + oc0) * P.tp + tile;
                 for (int c0 = 0; c0 < P.bn; c0 += 16) {
                     float va[16];
                     tc_ld16(t_addr + (uint32_t)c0, va);
@@ -239,7 +244,7 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                     if (tile < P.tp) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c0 + j < P.oc) dst[(size_t)(c0 + j) * P.tp] = va[j];
+                            if (oc0 + c0 + j < P.oc) dst[(size_t)(c0 + j) * P.tp] = va[j];
                     }
                 }
             } else {
@@ -290,12 +295,30 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode,
                         const KernelCfg *cfg) {
     const bool split = mode == FC_MATH_3XTF32;
-    // At most 64 output channels: exchanged roles, rows = 128 tiles, columns = the channels (multiple of 16).
-    // Otherwise tile blocks of at most 128 tiles (or the tuned width), balanced, multiple of 16 (UMMA N at M=128).
-    const bool swap = g.oc <= 64;
+    // Exchanged roles (rows = 128 tiles, columns = a block of at most 128 output channels, a multiple of 16) when no
+    // accumulator row is left empty by it: at most 64 channels, or -- in the single-pass mode -- at least 128 tiles.
+    // Measured on the batch-8 VGG-16 stack in TF32: 1.233 ms with rows = channels everywhere, 1.143 ms with this rule;
+    // 256-wide channel blocks (one CTA per SM, all of TMEM) were slower (1.197 ms), and in 3xTF32 the four
+    // splitter/epilogue warps are the bottleneck, so the exchanged epilogue (4x the store instructions) loses there.
+    // Otherwise rows = 128 channels and tile blocks of at most 128 tiles (or the tuned width), balanced, a multiple
+    // of 16 (UMMA N granularity at M=128).
+    constexpr int swap_block = 128;
+    const bool swap = g.oc <= 64 || (!split && g.tp >= 128);
     const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
-    const int n_blk = swap ? (g.tp + BM - 1) / BM : (g.tp + max_bn - 1) / max_bn;
-    const int bn = swap ? round_up(g.oc, 16) : round_up((g.tp + n_blk - 1) / n_blk, 16);
+    int n_blk, bn, n_oc_items, b_bytes, u_loads = 1;
+    if (swap) {
+        n_blk = (g.tp + BM - 1) / BM;
+        n_oc_items = (g.oc + swap_block - 1) / swap_block;
+        bn = round_up((g.oc + n_oc_items - 1) / n_oc_items, 16);       // balanced blocks of channels
+        if (bn > BM) bn = round_up(bn, BM);                             // wider than one packed box: whole boxes
+        u_loads = bn > BM ? 2 : 1;
+        b_bytes = bn * BK * 4;
+    } else {
+        n_blk = (g.tp + max_bn - 1) / max_bn;
+        bn = round_up((g.tp + n_blk - 1) / n_blk, 16);
+        n_oc_items = g.n_ocb;
+        b_bytes = bn * BK * 4;
+    }
     TcParams P;
     P.M = d_M;
     P.status = ctx->d_status;
@@ -307,8 +330,11 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.n_tile_blk = n_blk;
     P.n_oc_blk = g.n_ocb;
     P.n_kb_u = g.n_kb;
-    P.n_items = P.n_tile_blk * P.n_oc_blk * 64;
-    const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
+    P.n_oc_items = n_oc_items;
+    P.b_bytes = b_bytes;
+    P.u_loads = u_loads;
+    P.n_items = P.n_tile_blk * P.n_oc_items * 64;
+    const size_t stage_bytes = (size_t)(A_BYTES + b_bytes) * (split ? 2 : 1);
     // More work items than SMs: size the ring so that two CTAs share an SM (one CTA's loads then overlap the
     // other's epilogue); otherwise one CTA takes the whole SM.  512 TMEM columns cannot be shared.
     const bool two_per_sm = P.n_items > ctx->sm_count && 2 * P.acc_cols <= 256;
@@ -324,7 +350,7 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     if (ctas > P.n_items) ctas = P.n_items;
 
     CUtensorMap tmU, tmV;  // box rows: the 128-row operand and the bn-row operand
-    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap ? bn : U_BOX_ROWS));
+    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap && bn < U_BOX_ROWS ? bn : U_BOX_ROWS));
     FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, swap ? BM : bn));
 
     dim3 grid((unsigned)ctas), block(TC_THREADS);
