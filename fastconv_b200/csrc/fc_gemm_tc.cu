@@ -59,8 +59,10 @@ __device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p,
     p = rest / P.n_oc_items;
 }
 
+constexpr int TC_SPLIT_THREADS = TC_THREADS + 128;  // 3xTF32: four more warps that do nothing but split stages
+
 template <bool kSplit, bool kSwap>
-__global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
+__global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const TcParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -188,16 +190,15 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                 if (ok) tc_commit(bar_acc_full(acc));
             }
         }
-    } else {
-        // ---------------- splitters (3xTF32) + epilogue ----------------
-        const int et = threadIdx.x - 64;  // 0..127
-        const int q = warp & 3;           // TMEM lane quarter this warp may read
-        int g = 0, it = 0;
-        bool ok = true, waited = false;
-        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
-            int p, oc0, t0;
-            item_coords<kSwap>(P, item, p, oc0, t0);
-            if (kSplit) {
+    } else if (warp >= 6) {
+        // ---------------- splitters (3xTF32 only): warps 6..9 ----------------
+        // hi = tf32(x) stays in place, lo = x - hi goes to the second half of the stage; the MMA warp waits for
+        // bar_split instead of bar_full.  Warps of their own, so that splitting never queues behind an epilogue.
+        const int et = threadIdx.x - TC_THREADS;  // 0..127
+        int g = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+            {
                 const int all_chunks = (int)(part_bytes / 16);
                 for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
                     const int s = g % S;
@@ -218,8 +219,16 @@ __global__ void __launch_bounds__(TC_THREADS) wino_gemm_tc_kernel(const __grid_c
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
                     mbar_arrive(bar_split(s));
                 }
-                if (!ok) break;
             }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int it = 0;
+        bool ok = true, waited = false;
+        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+            int p, oc0, t0;
+            item_coords<kSwap>(P, item, p, oc0, t0);
             if (!waited) {  // M may still be read by the output transform of the forward before this one
                 pdl_wait();
                 waited = true;
@@ -296,14 +305,13 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
                         const KernelCfg *cfg) {
     const bool split = mode == FC_MATH_3XTF32;
     // Exchanged roles (rows = 128 tiles, columns = a block of at most 128 output channels, a multiple of 16) when no
-    // accumulator row is left empty by it: at most 64 channels, or -- in the single-pass mode -- at least 128 tiles.
-    // Measured on the batch-8 VGG-16 stack in TF32: 1.233 ms with rows = channels everywhere, 1.143 ms with this rule;
-    // 256-wide channel blocks (one CTA per SM, all of TMEM) were slower (1.197 ms), and in 3xTF32 the four
-    // splitter/epilogue warps are the bottleneck, so the exchanged epilogue (4x the store instructions) loses there.
+    // accumulator row is left empty by it: at most 64 channels, or at least 128 tiles.  Measured on the batch-8
+    // VGG-16 stack: TF32 1.233 ms with rows = channels everywhere, 1.143 ms with this rule (3xTF32: 1.624 -> 1.577 ms);
+    // 256-wide channel blocks (one CTA per SM, all of TMEM) were slower (1.197 ms).
     // Otherwise rows = 128 channels and tile blocks of at most 128 tiles (or the tuned width), balanced, a multiple
     // of 16 (UMMA N granularity at M=128).
     constexpr int swap_block = 128;
-    const bool swap = g.oc <= 64 || (!split && g.tp >= 128);
+    const bool swap = g.oc <= 64 || g.tp >= 128;
     const int max_bn = cfg && cfg->bn >= 16 && cfg->bn <= 256 ? cfg->bn : 128;
     int n_blk, bn, n_oc_items, b_bytes, u_loads = 1;
     if (swap) {
@@ -340,6 +348,9 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     const bool two_per_sm = P.n_items > ctx->sm_count && 2 * P.acc_cols <= 256;
     const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024 : (two_per_sm ? 104 * 1024 : 200 * 1024);
     int stages = (int)(budget / stage_bytes);
+    if (stages < 2) stages = 2;
+    // a ring that no longer lets two CTAs share an SM (3xTF32 stages are twice as large) takes the whole SM instead
+    if (!(cfg && cfg->smem_kb) && 512 + 1024 + stages * stage_bytes > 113 * 1024) stages = (int)((200 * 1024) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
     P.stages = stages;
@@ -353,7 +364,7 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap && bn < U_BOX_ROWS ? bn : U_BOX_ROWS));
     FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, swap ? BM : bn));
 
-    dim3 grid((unsigned)ctas), block(TC_THREADS);
+    dim3 grid((unsigned)ctas), block(split ? TC_SPLIT_THREADS : TC_THREADS);
     auto launch = [&](auto kernel) -> int {
         FC_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FC_CHECK_CUDA(launch_pdl(kernel, grid, block, smem, ctx->stream, tmU, tmV, P));
