@@ -44,7 +44,7 @@ MODE_PEAK_TFLOPS = {"tf32": TF32_TFLOPS, "3xtf32": TF32_TFLOPS / 3.0, "fp32": FP
 # DRAM bytes (read + write) per TensorGEMM launch, averaged over the 13 launches of one step of the default
 # workload (VGG-16, batch 1), from one ncu capture of `dram__bytes_read.sum + dram__bytes_write.sum`
 # (profiles/tensorgemm_dram_traffic_vgg16_batch1.md).  None for any other workload.
-NCU_GEMM_TRAFFIC_BYTES = {"fp32": 43.20e6, "tf32": 44.84e6, "3xtf32": 44.84e6}
+NCU_GEMM_TRAFFIC_BYTES = {"fp32": 43.20e6, "tf32": 44.01e6, "3xtf32": 44.01e6}
 
 
 def measured_peaks():
