@@ -452,17 +452,28 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
             for (int i = 0; i < 6; ++i) stage[warp][i][lane * 6 + j] = s[i];
         }
     }
+    // every lane decodes the origin of ITS tile once; the store loop below fetches the origin of the tile an element
+    // belongs to by shuffle instead of dividing again
+    int my_org = -1;  // y0 << 16 | x0 of the tile's first output, -1 past the end
+    size_t my_base = 0;
+    if (t < n_tiles) {
+        const int per_img = th * tw;
+        const int img = t / per_img, tt = t - img * per_img;
+        my_org = ((tt / tw) * 6) << 16 | ((tt % tw) * 6);
+        my_base = ((size_t)img * oc + k) * oh * ow;
+    }
     __syncwarp();
-    const int per_img = th * tw;
     // lane writes elements e = lane, lane+32, ... of every staged row: e -> (tile e/6, column e%6)
-    for (int e = lane; e < 32 * 6; e += 32) {
+#pragma unroll
+    for (int it = 0; it < 6; ++it) {
+        const int e = lane + it * 32;
         const int te = e / 6, j = e - te * 6;
-        const int tile = t_base + te;
-        if (tile >= n_tiles) continue;
-        const int img = tile / per_img, tt = tile - img * per_img;
-        const int y0 = (tt / tw) * 6, x = (tt % tw) * 6 + j;
+        const int org = __shfl_sync(0xffffffffu, my_org, te);
+        const size_t base = __shfl_sync(0xffffffffu, my_base, te);
+        if (org < 0) continue;
+        const int y0 = org >> 16, x = (org & 0xffff) + j;
         if (x >= ow) continue;
-        float *dst = out + ((size_t)img * oc + k) * oh * ow + (size_t)y0 * ow + x;
+        float *dst = out + base + (size_t)y0 * ow + x;
 #pragma unroll
         for (int i = 0; i < 6; ++i)
             if (y0 + i < oh) dst[(size_t)i * ow] = stage[warp][i][e];
