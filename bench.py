@@ -270,6 +270,9 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="with --shard k: 'peer' = slabs stored into every rank's output by the output transform itself "
                          "(peer pointers over NVLink, flags); 'nccl' = separate all-gather after the layer")
+    ap.add_argument("--chain", action="store_true",
+                    help="not the reference's per-layer benchmark: layers of one VGG block feed each other on the device "
+                         "(bias + ReLU in the epilogue), only block inputs and outputs cross PCIe in the end-to-end number")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "fastconv":
@@ -339,8 +342,21 @@ def main():
         t, tp, icp = wino_geometry(n, c, k, h)
         footprint += 4 * (64 * k * icp + 64 * tp * icp + 64 * k * tp + n * c * h * h + n * k * h * h)
 
+    d_ins, d_outs = [c[1].value for c in convs], [c[2].value for c in convs]
+    if args.chain:
+        # layer i+1 of a block (same H, its C == the K before it) reads layer i's output where it lies on the device
+        for i in range(1, len(layers)):
+            if layers[i][0] == layers[i - 1][1] and layers[i][2] == layers[i - 1][2]:
+                d_ins[i] = d_outs[i - 1]
+                h2d -= host_in[i].nbytes
+                d2h -= host_out[i - 1].nbytes
+                host_in[i] = None
+                host_out[i - 1] = None
+        for i, (hdl, _, _, _) in enumerate(convs):
+            bias = (synth.conv_input(1, 1, 1, layers[i][1], 3000 + i).reshape(-1) * np.float32(0.1)).astype(np.float32)
+            _lib.check(lib.fc_conv_set_epilogue(hdl, C.c_void_p(bias.ctypes.data), 1), "fc_conv_set_epilogue")
     # the whole stack as one CUDA graph: a step is one graph launch
-    stack = fc.LayerList(ctx, [c[0] for c in convs], [c[1].value for c in convs], [c[2].value for c in convs])
+    stack = fc.LayerList(ctx, [c[0] for c in convs], d_ins, d_outs)
 
     def step_device():
         stack.forward()
@@ -455,6 +471,7 @@ def main():
             "config": {"workload": f"{workload_name}, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
                        "algorithm": "winograd F(6x6,3x3)", "math_mode": args.mode,
                        "launch": "all layers of a step replayed as one CUDA graph",
+                       "chain": bool(args.chain),
                        "parallelism": f"images sharded over {world} GPU(s), no collective",
                        "l2": f"inputs larger than L2: the stack touches {footprint / 1e6:.0f} MB per step"},
             "e2e": {"value": round(e2e_value, 1), "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -94,6 +94,7 @@ SIGNATURES = {
     "fc_layer_list_forward_host": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "fc_layer_list_launches": (C.c_int, [_vp, _ip]),
     "fc_layer_list_destroy": (C.c_int, [_vp]),
+    "fc_conv_set_epilogue": (C.c_int, [_vp, _vp, C.c_int]),
     "fc_peer_export": (C.c_int, [_vp, _vp, _vp, _vp]),
     "fc_peer_open": (C.c_int, [_vp, _vp, _vp]),
     "fc_peer_close": (C.c_int, [_vp, _vp]),

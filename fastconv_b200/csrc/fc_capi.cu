@@ -98,6 +98,8 @@ struct fc_conv {
     float *d_kernel;  // raw [oc][ic*kh*kw]
     float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
     float *d_ktab;    // fp32 implicit GEMM: int pairs (offset, u:v) per k, in a float-typed arena slot
+    float *d_bias;    // per-channel bias of the epilogue, or NULL
+    int relu;         // epilogue: clamp at zero after the bias
     float *d_U, *d_V, *d_M;
     float *d_in, *d_out;  // staging for forward_host
     float kernel_tran_ms;
@@ -520,7 +522,7 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
 
 static void conv_release(fc_conv *c) {
     fc_context *ctx = c->ctx;
-    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_bias, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
     for (float *b : bufs)
         if (b) ctx->arena.release((uintptr_t)b);
     delete c;
@@ -717,7 +719,7 @@ static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_o
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
     FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, g, c->mode, &c->cfg));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
-    FC_PROPAGATE(launch_output_transform(ctx, c->d_M, out, g));
+    FC_PROPAGATE(launch_output_transform(ctx, c->d_M, out, g, Epilogue{c->d_bias, c->relu}));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
     return FC_OK;
 }
@@ -736,15 +738,32 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     int st;
     if (c->mode == FC_MATH_FP32_MIRRORED)
         st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg,
-                               reinterpret_cast<const int *>(c->d_ktab));
+                               reinterpret_cast<const int *>(c->d_ktab), Epilogue{c->d_bias, c->relu});
     else
         st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg,
-                             reinterpret_cast<const int *>(c->d_ktab));
+                             reinterpret_cast<const int *>(c->d_ktab), Epilogue{c->d_bias, c->relu});
     FC_PROPAGATE(st);
     if (timed) {
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
     }
+    return FC_OK;
+}
+
+int fc_conv_set_epilogue(fc_conv *c, const float *h_bias, int relu) {
+    FC_REQUIRE(c != nullptr, FC_ERR_INVALID_ARG, "layer is NULL");
+    fc_context *ctx = c->ctx;
+    FC_CHECK_CUDA(cudaSetDevice(ctx->device));
+    FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));  // no forward of this layer is in flight while its epilogue changes
+    if (h_bias != nullptr) {
+        FC_PROPAGATE(grab(ctx, &c->d_bias, (size_t)c->desc.oc));
+        FC_CHECK_CUDA(cudaMemcpyAsync(c->d_bias, h_bias, (size_t)c->desc.oc * sizeof(float), cudaMemcpyHostToDevice,
+                                      ctx->stream));
+        FC_CHECK_CUDA(cudaStreamSynchronize(ctx->stream));
+    } else {
+        drop(ctx, &c->d_bias);
+    }
+    c->relu = relu ? 1 : 0;
     return FC_OK;
 }
 
@@ -775,7 +794,7 @@ int fc_conv_forward_scatter(fc_conv *c, const float *d_in, float *const *outs, i
     }
     FC_PROPAGATE(input_transform_dispatch(ctx, d_in, c->d_V, g, c->mode));
     FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, g, c->mode, &c->cfg));
-    FC_PROPAGATE(launch_output_transform_scatter(ctx, c->d_M, dst, g));
+    FC_PROPAGATE(launch_output_transform_scatter(ctx, c->d_M, dst, g, Epilogue{c->d_bias, c->relu}));
     return launch_peer_publish(ctx, flags, world, rank, step);
 }
 
@@ -1107,16 +1126,23 @@ int fc_layer_list_forward_host(fc_layer_list *l, const float *const *h_ins, floa
     }
     for (size_t i = 0; i < n; ++i) {
         fc_conv *c = l->convs[i];
-        FC_REQUIRE(h_ins[i] && h_outs[i], FC_ERR_INVALID_ARG, "layer %zu has a NULL host buffer", i);
+        // a NULL host pointer means "chained": the layer reads what an earlier layer of the list wrote on the device
+        // (or leaves its output there for a later one), so nothing is copied on that side
+        float *din = const_cast<float *>(l->d_ins[i]);
+        float *dout = l->d_outs[i];
         const size_t in_bytes = (size_t)c->desc.batch * c->desc.ic * c->desc.ih * c->desc.iw * sizeof(float);
         const size_t out_bytes = (size_t)c->desc.batch * c->desc.oc * c->oh * c->ow * sizeof(float);
-        FC_CHECK_CUDA(cudaMemcpyAsync(c->d_in, h_ins[i], in_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
-        FC_CHECK_CUDA(cudaEventRecord(l->uploaded[i], ctx->copy_in));
-        FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, l->uploaded[i], 0));
-        FC_PROPAGATE(conv_enqueue(c, c->d_in, c->d_out, false));
-        FC_CHECK_CUDA(cudaEventRecord(l->computed[i], ctx->stream));
-        FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->copy_out, l->computed[i], 0));
-        FC_CHECK_CUDA(cudaMemcpyAsync(h_outs[i], c->d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+        if (h_ins[i] != nullptr) {
+            FC_CHECK_CUDA(cudaMemcpyAsync(din, h_ins[i], in_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+            FC_CHECK_CUDA(cudaEventRecord(l->uploaded[i], ctx->copy_in));
+            FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, l->uploaded[i], 0));
+        }
+        FC_PROPAGATE(conv_enqueue(c, din, dout, false));
+        if (h_outs[i] != nullptr) {
+            FC_CHECK_CUDA(cudaEventRecord(l->computed[i], ctx->stream));
+            FC_CHECK_CUDA(cudaStreamWaitEvent(ctx->copy_out, l->computed[i], 0));
+            FC_CHECK_CUDA(cudaMemcpyAsync(h_outs[i], dout, out_bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+        }
     }
     FC_CHECK_CUDA(cudaStreamSynchronize(ctx->copy_out));
     return sync_and_check_status(ctx);

@@ -43,7 +43,7 @@ struct IgemmParams {
 template <int BM, int BN>
 __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__restrict__ in,
                                                              const float *__restrict__ A, float *__restrict__ out,
-                                                             IgemmParams P) {
+                                                             IgemmParams P, Epilogue ep) {
     constexpr int TM = BM / 16, TN = BN / 16;
     constexpr int LDA = BM + 4, LDB = BN + 4;
     constexpr int A_PER = BM * BK / THREADS;  // scalar A loads per thread per slab
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
             const int px = pix0 + (j / 4) * 64 + tx * 4 + (j % 4);
             if (px >= P.npix) continue;
             const int im = px / ohw;
-            out[((size_t)im * P.oc + r) * ohw + (px - im * ohw)] = acc[i][j];
+            out[((size_t)im * P.oc + r) * ohw + (px - im * ohw)] = ep(acc[i][j], r);
         }
     }
 }
@@ -188,7 +188,7 @@ __device__ __forceinline__ void cp_async_zfill_4(void *smem_dst, const void *gme
 template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
     igemm_ffma_tile_kernel(const float *__restrict__ in, const float *__restrict__ A, float *__restrict__ out,
-                           const int2 *__restrict__ ktab, IgemmParams P, int a_vec) {
+                           const int2 *__restrict__ ktab, IgemmParams P, int a_vec, Epilogue ep) {
     constexpr int OCL = BM / TM, NT = OCL * (BN / TN), BNP = BN + 4;
     constexpr int B_STEP = NT / BN, B_ITERS = TK_KC / B_STEP;
     static_assert(NT % BN == 0 && TK_KC % B_STEP == 0 && (TN == 1 || TN == 2 || TN == 4), "block shape");
@@ -295,21 +295,21 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = oc0 + ox + OCL * i;
-            if (r < P.oc) out[((size_t)img * P.oc + r) * ohw + rem] = acc[i][j];
+            if (r < P.oc) out[((size_t)img * P.oc + r) * ohw + rem] = ep(acc[i][j], r);
         }
     }
 }
 
 template <int BM, int BN, int TM, int TN>
 int launch_tile(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const int2 *d_ktab,
-                const IgemmParams &P) {
+                const IgemmParams &P, const Epilogue &ep) {
     constexpr int NT = (BM / TM) * (BN / TN);
     const size_t smem = (size_t)TK_STAGES * (BM * TK_KCP + TK_KC * (BN + 4)) * sizeof(float);
     FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_ffma_tile_kernel<BM, BN, TM, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid((unsigned)ceil_div(P.npix, BN), (unsigned)ceil_div(P.oc, BM)), block(NT);
     igemm_ffma_tile_kernel<BM, BN, TM, TN><<<grid, block, smem, ctx->stream>>>(d_in, d_kernel, d_out, d_ktab, P,
-                                                                              P.K % 4 == 0 ? 1 : 0);
+                                                                              P.K % 4 == 0 ? 1 : 0, ep);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -344,7 +344,7 @@ void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs) {
 }
 
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow, const KernelCfg *cfg, const int *d_ktab) {
+                      int oh, int ow, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep) {
     IgemmParams P;
     P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
     P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
@@ -371,24 +371,24 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
                 if (ctas > best) { best = ctas; bm = sh[0]; bn = sh[1]; }
             }
         }
-        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P);
-        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4>(ctx, d_in, d_kernel, d_out, tab, P);
-        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2>(ctx, d_in, d_kernel, d_out, tab, P);
-        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2>(ctx, d_in, d_kernel, d_out, tab, P);
-        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1>(ctx, d_in, d_kernel, d_out, tab, P);
+        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1>(ctx, d_in, d_kernel, d_out, tab, P, ep);
         set_error("no table-driven implicit GEMM with a %d x %d block", bm, bn);
         return FC_ERR_INVALID_ARG;
     }
     // no table (the stage entry point outside a planned layer): the 16x16-thread kernel for every size
     dim3 grid((unsigned)ceil_div(P.npix, wide_n ? 128 : 64), (unsigned)ceil_div(d.oc, wide_m ? 128 : 64)), block(THREADS);
     if (wide_m && wide_n)
-        igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+        igemm_ffma_kernel<128, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P, ep);
     else if (wide_m)
-        igemm_ffma_kernel<128, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+        igemm_ffma_kernel<128, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P, ep);
     else if (wide_n)
-        igemm_ffma_kernel<64, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+        igemm_ffma_kernel<64, 128><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P, ep);
     else
-        igemm_ffma_kernel<64, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P);
+        igemm_ffma_kernel<64, 64><<<grid, block, 0, ctx->stream>>>(d_in, d_kernel, d_out, P, ep);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }

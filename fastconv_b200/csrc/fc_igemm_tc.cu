@@ -28,6 +28,7 @@ struct IgemmTcParams {
     int K, num_kb, bn, stages, tmem_cols;
     int splits, kb_per_split;  // split-K over blockIdx.z: split s reduces k-blocks [s*kb_per_split, ...)
     const int2 *ktab;          // per-layer k -> (offset, u:v) table padded to 32 entries, or NULL
+    Epilogue ep;               // applied by the epilogue warps; never together with split-K
 };
 
 __global__ void pack_weights_kernel(const float *__restrict__ kernel, float *__restrict__ packed, int oc, int K,
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
                     for (int j = 0; j < 16; ++j)
                         if (pix0 + c0 + j < ohw) {
                             if (P.splits > 1) atomicAdd(dst + c0 + j, v[j]);  // partial sum of this K range
-                            else dst[c0 + j] = v[j];
+                            else dst[c0 + j] = P.ep(v[j], row);
                         }
                 }
             }
@@ -266,7 +267,7 @@ int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_p
 }
 
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode, const KernelCfg *cfg, const int *d_ktab) {
+                    int oh, int ow, int mode, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep) {
     using namespace tc;
     const bool split = mode == FC_MATH_3XTF32;
     const int K = d.ic * d.kh * d.kw, Kp = round_up(K, BK);
@@ -280,7 +281,8 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     const int bn = round_up((ohw + n_blk - 1) / n_blk, 16);
     const size_t base_ctas = (size_t)n_blk * ceil_div(d.oc, BM) * d.batch;
     int splits = 1;
-    while (base_ctas * splits * 2 <= (size_t)sms && num_kb / (splits * 2) >= 4 && (size_t)d.batch * splits * 2 <= 65535) splits *= 2;
+    const bool may_split = ep.bias == nullptr && !ep.relu;  // bias and ReLU act on the complete sum only
+    while (may_split && base_ctas * splits * 2 <= (size_t)sms && num_kb / (splits * 2) >= 4 && (size_t)d.batch * splits * 2 <= 65535) splits *= 2;
     IgemmTcParams P;
     P.in = d_in; P.out = d_out; P.status = ctx->d_status;
     P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw; P.sh = d.sh; P.sw = d.sw;
@@ -288,6 +290,7 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     P.K = K; P.num_kb = num_kb; P.bn = bn; P.tmem_cols = pow2_at_least(bn, 32);
     P.splits = splits;
     P.ktab = reinterpret_cast<const int2 *>(d_ktab);
+    P.ep = ep;
     P.kb_per_split = (num_kb + splits - 1) / splits;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
     const size_t n_ctas = base_ctas * splits;

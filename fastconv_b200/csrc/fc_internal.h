@@ -79,6 +79,20 @@ struct KernelCfg {
     int smem_kb;    // tcgen05 kernels: shared-memory budget of the operand ring (sets the stage count / CTAs per SM)
 };
 
+// What a layer applies to every output element before storing it: y = relu(y + bias[oc]); both parts optional.
+// The bias add is one rounded fp32 addition, so a chain of layers stays reproducible bit for bit.
+struct Epilogue {
+    const float *bias;  // per output channel, device memory, or NULL
+    int relu;
+#ifdef __CUDACC__
+    __device__ __forceinline__ float operator()(float v, int ch) const {
+        if (bias != nullptr) v = __fadd_rn(v, __ldg(bias + ch));
+        return relu ? fmaxf(v, 0.0f) : v;
+    }
+#endif
+};
+constexpr Epilogue kNoEpilogue = {nullptr, 0};
+
 // Output buffers of the ranks of a channel-split layer, as seen from this GPU (own memory or peer-mapped).
 struct PeerOuts {
     float *base[FC_MAX_PEERS];
@@ -141,8 +155,10 @@ int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, 
 int launch_filter_transform_rowmajor(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
-int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g);
-int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g);
+int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g,
+                            const Epilogue &ep = kNoEpilogue);
+int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g,
+                                    const Epilogue &ep = kNoEpilogue);
 int launch_peer_publish(fc_context *ctx, int *const *flags, int world, int rank, int step);
 int launch_peer_wait(fc_context *ctx, const int *flags, int world, int step);
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
@@ -153,11 +169,13 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
                          int image);
 // d_ktab: per-layer k -> (offset, u:v) table (igemm_fill_ktab), or NULL outside a planned layer
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr);
+                      int oh, int ow, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
+                      const Epilogue &ep = kNoEpilogue);
 size_t igemm_ktab_entries(const fc_conv_desc &d);
 void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs);  // 2 ints per entry
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr);
+                    int oh, int ow, int mode, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
+                    const Epilogue &ep = kNoEpilogue);
 size_t igemm_packed_elems(int oc, int K);
 int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 

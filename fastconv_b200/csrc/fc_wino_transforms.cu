@@ -389,15 +389,16 @@ __device__ __forceinline__ void output_transform_block(const float *__restrict__
         if (org < 0 || kk >= oc) continue;
         const int y = (org >> 16) + i, x = (org & 0xffff) + j;
         const int img = (t_base + te) / per_img;
-        if (y < oh && x < ow) store(((size_t)img * oc + kk) * out_page + (size_t)y * ow + x, stage[o][i][e]);
+        if (y < oh && x < ow) store(((size_t)img * oc + kk) * out_page + (size_t)y * ow + x, kk, stage[o][i][e]);
     }
 }
 
 template <int TPW>
 __global__ void __launch_bounds__(256) output_transform_kernel(const float *__restrict__ M, float *__restrict__ out,
                                                                int n_tiles, int oc, int tp, int oh, int ow, int th,
-                                                               int tw) {
-    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [out](size_t at, float v) { out[at] = v; });
+                                                               int tw, Epilogue ep) {
+    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw,
+                                [out, ep](size_t at, int ch, float v) { out[at] = ep(v, ch); });
 }
 
 // The same transform for a layer whose output channels are split over several GPUs: every result is stored
@@ -407,8 +408,9 @@ __global__ void __launch_bounds__(256) output_transform_kernel(const float *__re
 template <int TPW>
 __global__ void __launch_bounds__(256) output_transform_scatter_kernel(const float *__restrict__ M, PeerOuts dst,
                                                                        int n_tiles, int oc, int tp, int oh, int ow,
-                                                                       int th, int tw) {
-    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [&dst](size_t at, float v) {
+                                                                       int th, int tw, Epilogue ep) {
+    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [&dst, ep](size_t at, int ch, float v) {
+        v = ep(v, ch);
 #pragma unroll
         for (int r = 0; r < FC_MAX_PEERS; ++r)
             if (r < dst.count) dst.base[r][at] = v;
@@ -424,7 +426,7 @@ constexpr int OTW_WARPS = 4;
 __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(const float *__restrict__ M,
                                                                               float *__restrict__ out, int n_tiles,
                                                                               int oc, int tp, int oh, int ow, int th,
-                                                                              int tw) {
+                                                                              int tw, Epilogue ep) {
     constexpr int ROW = 32 * 6 + 2;
     __shared__ float stage[OTW_WARPS][6][ROW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -476,49 +478,50 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
         float *dst = out + base + (size_t)y0 * ow + x;
 #pragma unroll
         for (int i = 0; i < 6; ++i)
-            if (y0 + i < oh) dst[(size_t)i * ow] = stage[warp][i][e];
+            if (y0 + i < oh) dst[(size_t)i * ow] = ep(stage[warp][i][e], k);
     }
 }
 
-int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g) {
+int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g, const Epilogue &ep) {
     dim3 block(256);
     if (g.tiles >= 256) {
         dim3 wblock(32 * OTW_WARPS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
         FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
-                                 g.oh, g.ow, g.th, g.tw));
+                                 g.oh, g.ow, g.th, g.tw, ep));
         return FC_OK;
     }
     if (g.tiles > 16) {
         dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
         FC_CHECK_CUDA(launch_pdl(output_transform_kernel<32>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
-                                 g.oh, g.ow, g.th, g.tw));
+                                 g.oh, g.ow, g.th, g.tw, ep));
     } else if (g.tiles > 8) {
         dim3 grid(1, (unsigned)ceil_div(g.oc, 2));
         FC_CHECK_CUDA(launch_pdl(output_transform_kernel<16>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
-                                 g.oh, g.ow, g.th, g.tw));
+                                 g.oh, g.ow, g.th, g.tw, ep));
     } else {
         dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
         FC_CHECK_CUDA(launch_pdl(output_transform_kernel<8>, grid, block, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
-                                 g.oh, g.ow, g.th, g.tw));
+                                 g.oh, g.ow, g.th, g.tw, ep));
     }
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
 
-int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g) {
+int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g,
+                                    const Epilogue &ep) {
     dim3 block(256);
     if (g.tiles > 16) {
         dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
         FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<32>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
-                                 g.tp, g.oh, g.ow, g.th, g.tw));
+                                 g.tp, g.oh, g.ow, g.th, g.tw, ep));
     } else if (g.tiles > 8) {
         dim3 grid(1, (unsigned)ceil_div(g.oc, 2));
         FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<16>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
-                                 g.tp, g.oh, g.ow, g.th, g.tw));
+                                 g.tp, g.oh, g.ow, g.th, g.tw, ep));
     } else {
         dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
         FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<8>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
-                                 g.tp, g.oh, g.ow, g.th, g.tw));
+                                 g.tp, g.oh, g.ow, g.th, g.tw, ep));
     }
     return FC_OK;
 }

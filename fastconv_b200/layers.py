@@ -289,6 +289,17 @@ class ConvLayer:
         for label, idx in labels:
             print("%s %fms" % (label, self.stage_ms[idx]))
 
+    def set_epilogue(self, bias: Optional[np.ndarray] = None, relu: bool = False) -> None:
+        """Per-channel bias (oc floats) and/or ReLU applied to every output element inside the layer's last kernel."""
+        self._create()
+        b = None
+        if bias is not None:
+            b = _as_f32(bias, "bias")
+            if b.size != self.desc.oc:
+                raise ValueError(f"bias has {b.size} values, the layer {self.desc.oc} output channels")
+        check(self._lib.fc_conv_set_epilogue(self._conv, None if b is None else _ptr(b), 1 if relu else 0),
+              "fc_conv_set_epilogue")
+
     @property
     def kernel_launches(self) -> int:
         """Kernel launches of one Forward (3 per pass of a Winograd layer, 1 for an implicit GEMM)."""
@@ -408,11 +419,13 @@ class LayerList:
         check(self._lib.fc_layer_list_forward(self._h), "fc_layer_list_forward")
 
     def forward_host(self, host_ins, host_outs) -> None:
-        """All layers from/to host arrays; uploads, kernels and downloads of neighbouring layers overlap."""
+        """All layers from/to host arrays; uploads, kernels and downloads of neighbouring layers overlap.
+        A None entry skips that copy: the layer is chained to its neighbour on the device."""
         n = len(host_ins)
         arr = C.c_void_p * n
-        check(self._lib.fc_layer_list_forward_host(self._h, arr(*[a.ctypes.data for a in host_ins]),
-                                                   arr(*[a.ctypes.data for a in host_outs])),
+        ptr = lambda a: None if a is None else a.ctypes.data  # noqa: E731
+        check(self._lib.fc_layer_list_forward_host(self._h, arr(*[ptr(a) for a in host_ins]),
+                                                   arr(*[ptr(a) for a in host_outs])),
               "fc_layer_list_forward_host")
 
     def close(self) -> None:

@@ -191,6 +191,16 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
                    fc_conv **out);
 int fc_conv_destroy(fc_conv *conv);
 int fc_conv_algorithm(const fc_conv *conv, int *algo);
+/* Epilogue of the layer: every output element becomes relu(y + bias[oc]) before it is stored (both
+ * parts optional: h_bias NULL = no bias, relu 0 = no clamp).  The reference carries a bias operand
+ * (bias_term / bias_data, conv_layer.h:46-48,72-77) that only its general naive layer adds
+ * (convLayer/naiveConv_wudu.h:78, one value per output ELEMENT); its Winograd and im2col layers ignore
+ * it and have no activation.  Here the bias is one value per output CHANNEL (`oc` floats, copied),
+ * added with one rounded fp32 addition, which is what lets consecutive layers of a network run
+ * device to device (fc_layer_list with layer i's output as layer i+1's input) with nothing between
+ * them.  Not to be called while a forward of the layer is in flight; a layer list that captured the
+ * layer must be rebuilt afterwards. */
+int fc_conv_set_epilogue(fc_conv *conv, const float *h_bias, int relu);
 /* Forward() on device-resident tensors, asynchronous on the context stream */
 int fc_conv_forward_device(fc_conv *conv, const float *d_in, float *d_out);
 /* Forward() from / to host memory: H2D copy, kernels, D2H copy, synchronous */
@@ -222,7 +232,9 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
 int fc_layer_list_forward(fc_layer_list *list);
 /* The same list from / to HOST memory (pinned buffers recommended): layer i's input upload, its
  * kernels and its output download run on three streams chained by events, so the PCIe traffic of
- * neighbouring layers overlaps in both directions with the kernels.  Synchronous on return. */
+ * neighbouring layers overlaps in both directions with the kernels.  h_ins[i] == NULL skips the upload
+ * (the layer reads what is already at its device input, e.g. the output of layer i-1 in a chained
+ * list), h_outs[i] == NULL skips the download.  Synchronous on return. */
 int fc_layer_list_forward_host(fc_layer_list *list, const float *const *h_ins, float *const *h_outs);
 int fc_layer_list_launches(const fc_layer_list *list, int *kernel_launches);
 int fc_layer_list_destroy(fc_layer_list *list);
