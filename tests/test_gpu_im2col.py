@@ -104,3 +104,26 @@ def test_tensor_core_modes_within_tolerance(ctx, oracle, mode, tol_l2, tol_max, 
     assert rel_l2(layer.output_data, want) <= tol_l2, f"{mode} rel-L2 {rel_l2(layer.output_data, want):.3e}"
     assert max_abs_rel(layer.output_data, want) <= tol_max
     layer.release()
+
+
+@pytest.mark.parametrize("mode", ["fp32", "3xtf32"])
+@pytest.mark.parametrize("pads", [(0, 2, 1, 0), (3, 0, 0, 2), (1, 2, 2, 1)])  # left, right, top, bottom
+def test_four_separate_paddings_and_a_non_square_kernel(ctx, oracle, mode, pads):
+    """The operator interface carries one padding per side and kh != kw (conv_layer.h:51-58); the reference's own
+    paths only ever use one value for all four.  The implicit GEMM computes the general case."""
+    pl, pr, pt, pb = pads
+    n, ic, oc, ih, iw, kh, kw, sh, sw = 2, 12, 20, 13, 17, 3, 5, 2, 1
+    x = synth.conv_input(n, ic, ih, iw, 15)
+    w = synth.conv_weights(oc, ic, kh, kw, 16)
+    layer = fc.ConvIm2colLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, sh, sw, pl, pr, pt, pb, 1, False, 1, 1,
+                               batch=n, mode=mode, ctx=ctx)
+    layer.Init(); layer.Forward()
+    want = oracle.im2col_gemm_forward(x, w, sh, sw, pl, pr, pt, pb)
+    assert layer.output_data.shape == want.shape
+    if mode == "fp32":
+        assert np.array_equal(layer.output_data, want)
+    else:
+        assert rel_l2(layer.output_data, want) <= 1e-5
+    for img in range(n):
+        assert np.array_equal(layer.im2col(img), oracle.im2col(x[img], kh, kw, sh, sw, pl, pr, pt, pb))
+    layer.release()
