@@ -706,6 +706,20 @@ int fc_conv_algorithm(const fc_conv *c, int *algo) {
     return FC_OK;
 }
 
+// Which implicit GEMM a layer runs.  The fp32 mode always takes the FFMA kernels.  A tensor-core mode states the
+// precision the caller tolerates, not a unit: for short reductions the tcgen05 kernel's fixed cost (TMEM allocation,
+// barriers, the gather's look-ahead) exceeds the whole FFMA kernel, whose exact fp32 result is inside any tensor-core
+// tolerance.  Measured at batch 1 (ResNet-50 1x1 layers): K = 64..256 -> FFMA 6-18 us against 10-25 us; from K = 512 on
+// the tensor cores win in TF32, from K = 1024 on in 3xTF32 (three MMAs and a split pass per k-step).  Tuning() decides by measurement (cfg.skinny 1 = FFMA, 2 = tcgen05).
+static bool igemm_on_fp32_pipe(const fc_conv *c) {
+    if (c->mode == FC_MATH_FP32_MIRRORED) return true;
+    if (c->cfg.skinny == 1) return true;
+    if (c->cfg.skinny == 2 || c->cfg.bn || c->cfg.smem_kb) return false;
+    const long long K = (long long)c->desc.ic * c->desc.kh * c->desc.kw;
+    const long long flops = 2ll * c->desc.batch * c->desc.oc * K * c->oh * c->ow;
+    return K <= (c->mode == FC_MATH_3XTF32 ? 512 : 256) && flops <= 500000000ll;  // short reduction AND a small problem
+}
+
 // One pass of a Winograd layer: images [pass*pass_imgs, ...) of the batch through the three kernels.
 static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_out, bool timed) {
     fc_context *ctx = c->ctx;
@@ -736,7 +750,7 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
     int st;
-    if (c->mode == FC_MATH_FP32_MIRRORED)
+    if (igemm_on_fp32_pipe(c))
         st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg,
                                reinterpret_cast<const int *>(c->d_ktab), Epilogue{c->d_bias, c->relu});
     else
@@ -913,7 +927,11 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
         const int widths[5] = {32, 64, 96, 128, 256};
         const int budgets[3] = {72, 104, 200};
         for (int w : widths)
-            for (int b : budgets) push(0, w, 0, b);
+            for (int b : budgets) push(0, w, algo == FC_ALGO_IM2COL ? 2 : 0, b);
+        if (algo == FC_ALGO_IM2COL) {  // and the FFMA kernel, which wins on short reductions
+            const int small_tiles[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};
+            for (auto &t : small_tiles) push(t[0], t[1], 1, 0);
+        }
     }
 }
 

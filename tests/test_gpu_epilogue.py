@@ -77,13 +77,15 @@ def test_tensor_core_modes_apply_the_epilogue(ctx, oracle, mode):
     layer.Init(); layer.Forward()
     assert rel_l2(layer.output_data, _expect(oracle.wino_forward(x, w3, 1), b, True)) <= tol
     layer.release()
-    # a small 1x1 layer, which would otherwise split K and add partial sums: the epilogue must see complete sums
-    w1 = synth.conv_weights(96, 64, 1, 1, 80)
-    layer = fc.ConvIm2colLayer(x, w1, None, None, 64, 28, 28, 96, 1, 1, 1, 1, 0, 0, 0, 0, 1, False, 1, 1, mode=mode, ctx=ctx)
+    # a small strided 3x3 layer (K = 576: long enough for the tcgen05 implicit GEMM), which would otherwise split K
+    # and add partial sums: the epilogue must see complete sums
+    w2 = synth.conv_weights(96, 64, 3, 3, 80)
+    layer = fc.ConvIm2colLayer(x, w2, None, None, 64, 28, 28, 96, 3, 3, 2, 2, 1, 1, 1, 1, 1, False, 1, 1, mode=mode, ctx=ctx)
     layer.set_epilogue(b, True)
     layer.Init(); layer.Forward()
-    want = _expect(oracle.im2col_gemm_forward(x, w1, 1, 1, 0, 0, 0, 0), b, True)
+    want = _expect(oracle.im2col_gemm_forward(x, w2, 2, 2, 1, 1, 1, 1), b, True)
     assert rel_l2(layer.output_data, want) <= (1e-5 if mode == "3xtf32" else 3e-3)
+    assert not np.array_equal(layer.output_data, want)  # i.e. it really ran on the tensor cores
     layer.release()
 
 
