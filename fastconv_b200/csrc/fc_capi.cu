@@ -46,8 +46,8 @@ static int check_desc(const fc_conv_desc *d) {
     FC_REQUIRE(d->sh > 0 && d->sw > 0, FC_ERR_INVALID_ARG, "stride must be positive (conv_layer.h:62-63)");
     FC_REQUIRE(d->pad_left >= 0 && d->pad_right >= 0 && d->pad_top >= 0 && d->pad_bottom >= 0, FC_ERR_INVALID_ARG,
                "negative padding");
-    FC_REQUIRE(d->group == 1, FC_ERR_UNSUPPORTED, "group=%d: only group 1 is computed (as in the reference)",
-               d->group);
+    FC_REQUIRE(d->group >= 1 && d->ic % d->group == 0 && d->oc % d->group == 0, FC_ERR_INVALID_ARG,
+               "group=%d must divide the %d input and %d output channels", d->group, d->ic, d->oc);
     FC_REQUIRE(d->iw + d->pad_left + d->pad_right >= d->kw && d->ih + d->pad_top + d->pad_bottom >= d->kh,
                FC_ERR_INVALID_ARG, "kernel larger than the padded input");
     return FC_OK;
@@ -57,6 +57,7 @@ int wino_geom(const fc_conv_desc *d, WinoGeom *g) {
     FC_PROPAGATE(check_desc(d));
     // The reference driver ignores kh/kw/stride and assumes 3x3 s1 with one symmetric pad
     // (winoF63ZC/winoF63ZC.cpp:334-338); anything else is refused here instead of computed wrongly.
+    FC_REQUIRE(d->group == 1, FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) is built for group 1, got %d", d->group);
     FC_REQUIRE(d->kh == 3 && d->kw == 3, FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) needs a 3x3 kernel, got %dx%d",
                d->kh, d->kw);
     FC_REQUIRE(d->sh == 1 && d->sw == 1, FC_ERR_UNSUPPORTED, "winograd F(6x6,3x3) needs stride 1, got %dx%d", d->sh,
@@ -376,7 +377,7 @@ int fc_select_algorithm(const fc_conv_desc *d, int *algo) {
     FC_PROPAGATE(check_desc(d));
     FC_REQUIRE(algo != nullptr, FC_ERR_INVALID_ARG, "algo is NULL");
     int a = FC_ALGO_IM2COL;  // fall-back, ConvTest.cpp:329-330
-    if ((d->sh > d->sw ? d->sh : d->sw) == 1) {
+    if (d->group == 1 && (d->sh > d->sw ? d->sh : d->sw) == 1) {  // grouped layers: implicit GEMM per group
         if ((d->kh > d->kw ? d->kh : d->kw) == 1) {
             a = FC_ALGO_IM2COL;  // "direct" in the reference, whose case body is empty
         } else if (d->kh == 3 && d->kw == 3 && d->pad_left == d->pad_right && d->pad_left == d->pad_top &&
@@ -507,6 +508,7 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
     FC_REQUIRE(ctx && d_in && d_kernel && d_out, FC_ERR_INVALID_ARG, "NULL argument");
     int oh, ow;
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
+    FC_REQUIRE(desc->group == 1, FC_ERR_UNSUPPORTED, "the stage entry point computes group 1 (a planned layer takes groups)");
     FC_REQUIRE((long long)desc->batch * oh * ow < (1ll << 31) && (long long)desc->ic * desc->kh * desc->kw < (1ll << 31),
                FC_ERR_UNSUPPORTED, "GEMM extent exceeds 32-bit indexing");
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
@@ -539,6 +541,15 @@ static int grab(fc_context *ctx, float **p, size_t elems) {
 static void drop(fc_context *ctx, float **p) {
     if (*p) ctx->arena.release((uintptr_t)*p);
     *p = nullptr;
+}
+
+// One group of a (possibly grouped) layer as a convolution of its own: ic/group input and oc/group output channels.
+static fc_conv_desc group_desc(const fc_conv *c) {
+    fc_conv_desc d = c->desc;
+    d.ic /= d.group;
+    d.oc /= d.group;
+    d.group = 1;
+    return d;
 }
 
 // Optional L2 blocking over the batch.  Unblocked, V and M go out to HBM and come back: 2*(V+M) bytes of traffic that
@@ -605,23 +616,30 @@ static int conv_prepare(fc_conv *c, int algo) {
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
         }
+    } else if (d.group > 1 && d.group == d.ic) {
+        // depthwise: one plain fp32 kernel over the raw weights in every mode, nothing to prepare
     } else if (c->mode != FC_MATH_FP32_MIRRORED) {
         const bool fresh = c->d_packed == nullptr;
-        const int K = d.ic * d.kh * d.kw;
-        st = grab(ctx, &c->d_packed, igemm_packed_elems(d.oc, K));
+        const fc_conv_desc gd = group_desc(c);
+        const int K = gd.ic * gd.kh * gd.kw;
+        const size_t per_group = igemm_packed_elems(gd.oc, K);
+        st = grab(ctx, &c->d_packed, per_group * d.group);
         if (st == FC_OK && fresh) {
             cudaEventRecord(ctx->ev[0], ctx->stream);
-            st = launch_igemm_pack_weights(ctx, c->d_kernel, c->d_packed, d.oc, K);
+            for (int g = 0; g < d.group && st == FC_OK; ++g)
+                st = launch_igemm_pack_weights(ctx, c->d_kernel + (size_t)g * gd.oc * K, c->d_packed + g * per_group, gd.oc, K);
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
         }
     }
-    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_ktab == nullptr) {  // every implicit GEMM reads the table
+    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_ktab == nullptr && !(d.group > 1 && d.group == d.ic)) {
+        // every implicit GEMM reads the k decode table
         FC_REQUIRE((long long)d.ic * d.ih * d.iw < (1ll << 31) && d.kh < 0x4000 && d.kw < 0x4000, FC_ERR_UNSUPPORTED,
                    "image or kernel too large for the 32-bit decode table");
-        const size_t entries = igemm_ktab_entries(d);
+        const fc_conv_desc gd = group_desc(c);  // offsets are relative to the group's first channel
+        const size_t entries = igemm_ktab_entries(gd);
         ktab.resize(2 * entries);
-        igemm_fill_ktab(d, ktab.data());
+        igemm_fill_ktab(gd, ktab.data());
         st = grab(ctx, &c->d_ktab, 2 * entries);
         if (st == FC_OK) {
             cudaError_t ce = cudaMemcpyAsync(c->d_ktab, ktab.data(), 2 * entries * sizeof(int), cudaMemcpyHostToDevice,
@@ -669,7 +687,7 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     c->auto_requested = auto_requested;
     c->wino_eligible = wino_eligible;
 
-    const size_t k_elems = (size_t)desc->oc * desc->ic * desc->kh * desc->kw;
+    const size_t k_elems = (size_t)desc->oc * (desc->ic / desc->group) * desc->kh * desc->kw;  // [oc][ic/group][kh][kw]
     const size_t in_elems = (size_t)desc->batch * desc->ic * desc->ih * desc->iw;
     const size_t out_elems = (size_t)desc->batch * desc->oc * oh * ow;
     int st = grab(ctx, &c->d_kernel, k_elems);
@@ -715,8 +733,9 @@ static bool igemm_on_fp32_pipe(const fc_conv *c) {
     if (c->mode == FC_MATH_FP32_MIRRORED) return true;
     if (c->cfg.skinny == 1) return true;
     if (c->cfg.skinny == 2 || c->cfg.bn || c->cfg.smem_kb) return false;
-    const long long K = (long long)c->desc.ic * c->desc.kh * c->desc.kw;
-    const long long flops = 2ll * c->desc.batch * c->desc.oc * K * c->oh * c->ow;
+    const fc_conv_desc gd = group_desc(c);
+    const long long K = (long long)gd.ic * gd.kh * gd.kw;
+    const long long flops = 2ll * gd.batch * gd.oc * K * c->oh * c->ow;
     return K <= (c->mode == FC_MATH_3XTF32 ? 512 : 256) && flops <= 500000000ll;  // short reduction AND a small problem
 }
 
@@ -749,13 +768,29 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     }
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
-    int st;
-    if (igemm_on_fp32_pipe(c))
-        st = launch_igemm_ffma(ctx, d_in, c->d_kernel, d_out, c->desc, c->oh, c->ow, &c->cfg,
-                               reinterpret_cast<const int *>(c->d_ktab), Epilogue{c->d_bias, c->relu});
-    else
-        st = launch_igemm_tc(ctx, d_in, c->d_packed, d_out, c->desc, c->oh, c->ow, c->mode, &c->cfg,
-                             reinterpret_cast<const int *>(c->d_ktab), Epilogue{c->d_bias, c->relu});
+    int st = FC_OK;
+    const fc_conv_desc &full = c->desc;
+    if (full.group > 1 && full.group == full.ic) {  // depthwise: every output channel reads one input channel
+        st = launch_depthwise(ctx, d_in, c->d_kernel, d_out, full, c->oh, c->ow, Epilogue{c->d_bias, c->relu});
+    } else {
+        // a grouped layer is `group` independent convolutions over channel slices of the same tensors
+        const fc_conv_desc gd = group_desc(c);
+        const size_t Kg = (size_t)gd.ic * gd.kh * gd.kw;
+        const size_t in_stride = (size_t)full.ic * full.ih * full.iw, out_stride = (size_t)full.oc * c->oh * c->ow;
+        const bool fp32_pipe = igemm_on_fp32_pipe(c);
+        for (int g = 0; g < full.group && st == FC_OK; ++g) {
+            const float *in_g = d_in + (size_t)g * gd.ic * gd.ih * gd.iw;
+            float *out_g = d_out + (size_t)g * gd.oc * c->oh * c->ow;
+            const Epilogue ep{c->d_bias ? c->d_bias + (size_t)g * gd.oc : nullptr, c->relu};
+            if (fp32_pipe)
+                st = launch_igemm_ffma(ctx, in_g, c->d_kernel + (size_t)g * gd.oc * Kg, out_g, gd, c->oh, c->ow, &c->cfg,
+                                       reinterpret_cast<const int *>(c->d_ktab), ep, in_stride, out_stride);
+            else
+                st = launch_igemm_tc(ctx, in_g, c->d_packed + (size_t)g * igemm_packed_elems(gd.oc, (int)Kg), out_g, gd,
+                                     c->oh, c->ow, c->mode, &c->cfg, reinterpret_cast<const int *>(c->d_ktab), ep,
+                                     in_stride, out_stride);
+        }
+    }
     FC_PROPAGATE(st);
     if (timed) {
         FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
@@ -1054,7 +1089,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : 1;
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : (c->desc.group == c->desc.ic ? 1 : c->desc.group);
     return FC_OK;
 }
 
@@ -1080,7 +1115,8 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     for (int i = 0; i < count; ++i) {
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
-        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i]) : 1;
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i])
+                                                        : (convs[i]->desc.group == convs[i]->desc.ic ? 1 : convs[i]->desc.group);
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     // one eager pass first: kernel attributes are set and any error shows up outside the capture

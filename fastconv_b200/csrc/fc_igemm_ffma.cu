@@ -38,6 +38,9 @@ struct IgemmParams {
     int n, ic, ih, iw, oc, kh, kw, sh, sw, pad_l, pad_t, oh, ow;
     int K;        // ic*kh*kw
     int npix;     // n*oh*ow
+    // elements from one image to the next in the input and in the output: ic*ih*iw and oc*oh*ow, or those of the
+    // whole tensors when the launch computes one group of a grouped convolution
+    long long in_img_stride, out_img_stride;
 };
 
 template <int BM, int BN>
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
         oj = rem - oi * P.ow;
     }
     const int base_row = oi * P.sh - P.pad_t, base_col = oj * P.sw - P.pad_l;
-    const float *img_ptr = in + (size_t)img * P.ic * P.ih * P.iw;
+    const float *img_ptr = in + (size_t)img * P.in_img_stride;
     const int khw = P.kh * P.kw;
 
     float a_stage[A_PER], b_stage[B_PER];
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
             const int px = pix0 + (j / 4) * 64 + tx * 4 + (j % 4);
             if (px >= P.npix) continue;
             const int im = px / ohw;
-            out[((size_t)im * P.oc + r) * ohw + (px - im * ohw)] = ep(acc[i][j], r);
+            out[(size_t)im * P.out_img_stride + (size_t)r * ohw + (px - im * ohw)] = ep(acc[i][j], r);
         }
     }
 }
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
         const int oi = rem / P.ow, oj = rem - oi * P.ow;
         base_row = oi * P.sh - P.pad_t;
         base_col = oj * P.sw - P.pad_l;
-        pix_ptr = in + (size_t)img * P.ic * P.ih * P.iw + (ptrdiff_t)base_row * P.iw + base_col;
+        pix_ptr = in + (size_t)img * P.in_img_stride + (ptrdiff_t)base_row * P.iw + base_col;
     }
 
     auto load_stage = [&](int st, int k0) {
@@ -295,7 +298,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = oc0 + ox + OCL * i;
-            if (r < P.oc) out[((size_t)img * P.oc + r) * ohw + rem] = ep(acc[i][j], r);
+            if (r < P.oc) out[(size_t)img * P.out_img_stride + (size_t)r * ohw + rem] = ep(acc[i][j], r);
         }
     }
 }
@@ -314,7 +317,55 @@ int launch_tile(fc_context *ctx, const float *d_in, const float *d_kernel, float
     return FC_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Depthwise convolution (group == input channels): every output channel reads ONE input channel, so the
+// reduction is kh*kw long and the layer is pure streaming.  One thread per output element, the same chain as
+// everywhere else: one accumulator, one FMA per (u,v), ascending.  `mult` output channels share an input channel.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) depthwise_kernel(const float *__restrict__ in, const float *__restrict__ w,
+                                                        float *__restrict__ out, IgemmParams P, int mult, Epilogue ep) {
+    const int ohw = P.oh * P.ow;
+    const size_t total = (size_t)P.n * P.oc * ohw;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int rem = (int)(idx % ohw);
+        const size_t r = idx / ohw;
+        const int k = (int)(r % P.oc), img = (int)(r / P.oc);
+        const int oi = rem / P.ow, oj = rem - oi * P.ow;
+        const int row0 = oi * P.sh - P.pad_t, col0 = oj * P.sw - P.pad_l;
+        const float *src = in + ((size_t)img * P.ic + k / mult) * P.ih * P.iw;
+        const float *wk = w + (size_t)k * P.kh * P.kw;
+        float acc = 0.0f;
+        for (int u = 0; u < P.kh; ++u) {
+            const int row = row0 + u;
+            for (int v = 0; v < P.kw; ++v) {
+                const int col = col0 + v;
+                const float b = ((unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw)
+                                    ? __ldg(src + (size_t)row * P.iw + col) : 0.0f;
+                acc = __fmaf_rn(__ldg(wk + u * P.kw + v), b, acc);
+            }
+        }
+        out[idx] = ep(acc, k);
+    }
+}
+
 }  // namespace
+
+int launch_depthwise(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+                     int oh, int ow, const Epilogue &ep) {
+    IgemmParams P;
+    P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
+    P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
+    P.K = d.kh * d.kw;
+    P.npix = d.batch * oh * ow;
+    P.in_img_stride = (long long)d.ic * d.ih * d.iw;
+    P.out_img_stride = (long long)d.oc * oh * ow;
+    const size_t total = (size_t)d.batch * d.oc * oh * ow;
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const unsigned blocks = (unsigned)(ceil_div(total, 256) > (size_t)sms * 16 ? (size_t)sms * 16 : ceil_div(total, 256));
+    depthwise_kernel<<<blocks, 256, 0, ctx->stream>>>(d_in, d_kernel, d_out, P, d.oc / d.ic, ep);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
 
 int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
                          int image) {
@@ -344,12 +395,15 @@ void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs) {
 }
 
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
-                      int oh, int ow, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep) {
+                      int oh, int ow, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep, size_t in_img_stride,
+                      size_t out_img_stride) {
     IgemmParams P;
     P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
     P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
     P.K = d.ic * d.kh * d.kw;
     P.npix = d.batch * oh * ow;
+    P.in_img_stride = in_img_stride ? (long long)in_img_stride : (long long)d.ic * d.ih * d.iw;
+    P.out_img_stride = out_img_stride ? (long long)out_img_stride : (long long)d.oc * oh * ow;
     const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const int pick = cfg ? cfg->skinny : 0;
     const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;

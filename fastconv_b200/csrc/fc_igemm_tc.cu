@@ -29,6 +29,7 @@ struct IgemmTcParams {
     int splits, kb_per_split;  // split-K over blockIdx.z: split s reduces k-blocks [s*kb_per_split, ...)
     const int2 *ktab;          // per-layer k -> (offset, u:v) table padded to 32 entries, or NULL
     Epilogue ep;               // applied by the epilogue warps; never together with split-K
+    long long in_img_stride, out_img_stride;  // elements between images (whole tensors for one group of a grouped layer)
 };
 
 __global__ void pack_weights_kernel(const float *__restrict__ kernel, float *__restrict__ packed, int oc, int K,
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
         // warp).  So LAG k-blocks of loads are in flight per thread and global latency is not on the critical path.
         const int gt = threadIdx.x - 64;  // 0..127
         const int khw = P.kh * P.kw;
-        const float *img_ptr = P.in + (size_t)img * P.ic * P.ih * P.iw;
+        const float *img_ptr = P.in + (size_t)img * P.in_img_stride;
         const int lag = S > 2 ? 2 : S - 1;
         bool ok = true;
         for (int it = kb0; it < kb1 + lag && ok; ++it) {
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
             tc_fence_after();
             const int q = warp & 3;
             const int row = oc0 + q * 32 + lane;
-            float *dst = P.out + ((size_t)img * P.oc + row) * ohw + pix0;
+            float *dst = P.out + (size_t)img * P.out_img_stride + (size_t)row * ohw + pix0;
             for (int c0 = 0; c0 < P.bn; c0 += 16) {
                 float v[16];
                 tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
@@ -267,7 +268,8 @@ int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_p
 }
 
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
-                    int oh, int ow, int mode, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep) {
+                    int oh, int ow, int mode, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep,
+                    size_t in_img_stride, size_t out_img_stride) {
     using namespace tc;
     const bool split = mode == FC_MATH_3XTF32;
     const int K = d.ic * d.kh * d.kw, Kp = round_up(K, BK);
@@ -305,6 +307,8 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     P.splits = splits;
     P.ktab = reinterpret_cast<const int2 *>(d_ktab);
     P.ep = ep;
+    P.in_img_stride = in_img_stride ? (long long)in_img_stride : (long long)d.ic * d.ih * d.iw;
+    P.out_img_stride = out_img_stride ? (long long)out_img_stride : (long long)d.oc * ohw;
     P.kb_per_split = (num_kb + splits - 1) / splits;
     const size_t stage_bytes = (size_t)(A_BYTES + bn * BK * 4) * (split ? 2 : 1);
     const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024
@@ -320,8 +324,14 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
     CUtensorMap tmA;  // [2 planes][oc][Kp]
     FC_PROPAGATE(make_map_3d(&tmA, d_packed, Kp, d.oc, 2, BM));
     dim3 grid((unsigned)n_blk, (unsigned)ceil_div(d.oc, BM), (unsigned)(d.batch * splits)), block(TC_THREADS);
-    if (splits > 1)  // the K ranges add their partial sums into a zeroed output
-        FC_CHECK_CUDA(cudaMemsetAsync(d_out, 0, (size_t)d.batch * d.oc * ohw * sizeof(float), ctx->stream));
+    if (splits > 1) {  // the K ranges add their partial sums into a zeroed output (this launch's channels only)
+        if (P.out_img_stride == (long long)d.oc * ohw) {
+            FC_CHECK_CUDA(cudaMemsetAsync(d_out, 0, (size_t)d.batch * d.oc * ohw * sizeof(float), ctx->stream));
+        } else {
+            FC_CHECK_CUDA(cudaMemset2DAsync(d_out, (size_t)P.out_img_stride * sizeof(float), 0,
+                                            (size_t)d.oc * ohw * sizeof(float), (size_t)d.batch, ctx->stream));
+        }
+    }
     if (split) {
         FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         igemm_tc_kernel<true><<<grid, block, smem, ctx->stream>>>(tmA, P);

@@ -170,12 +170,15 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
 // d_ktab: per-layer k -> (offset, u:v) table (igemm_fill_ktab), or NULL outside a planned layer
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                       int oh, int ow, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
-                      const Epilogue &ep = kNoEpilogue);
+                      const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0);
+// group == ic: one thread per output element, reduction over the kh*kw taps only
+int launch_depthwise(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
+                     int oh, int ow, const Epilogue &ep = kNoEpilogue);
 size_t igemm_ktab_entries(const fc_conv_desc &d);
 void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs);  // 2 ints per entry
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
                     int oh, int ow, int mode, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
-                    const Epilogue &ep = kNoEpilogue);
+                    const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0);
 size_t igemm_packed_elems(int oc, int K);
 int launch_igemm_pack_weights(fc_context *ctx, const float *d_kernel, float *d_packed, int oc, int K);
 

@@ -237,7 +237,7 @@ class ConvLayer:
         self.output_width = (self.input_width + pad_left + pad_right - kw) // sw + 1
         self.output_height = (self.input_height + pad_top + pad_bottom - kh) // sh + 1
         self.input_data = _as_f32(input, "input").reshape(self.batch, ic, ih, iw).copy()
-        self.kernel_data = _as_f32(kernel, "kernel").reshape(oc, ic, kh, kw).copy()
+        self.kernel_data = _as_f32(kernel, "kernel").reshape(oc, ic // int(g), kh, kw).copy()
         self.bias_data = None if biasw is None else _as_f32(biasw, "bias").copy()
         self.output_data = np.zeros((self.batch, oc, self.output_height, self.output_width), dtype=np.float32)
         self._ctx = ctx

@@ -62,7 +62,9 @@ typedef struct fc_conv_desc {
     int32_t oc, kh, kw;
     int32_t sh, sw;
     int32_t pad_left, pad_right, pad_top, pad_bottom;
-    int32_t group; /* must be 1: parsed but unused by every reference fast path */
+    int32_t group; /* parsed but unused by every reference path (conv_layer.h:27).  Here: must divide ic and oc;
+                    * group > 1 runs the implicit GEMM once per group (weights [oc][ic/group][kh][kw]), group == ic a
+                    * depthwise kernel; the Winograd stages and the stage-level implicit GEMM take group 1 only */
 } fc_conv_desc;
 
 typedef struct fc_context fc_context; /* one GPU + stream + device arena */

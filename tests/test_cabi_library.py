@@ -64,10 +64,11 @@ def test_select_algorithm_follows_reference():
     assert fc.select_algorithm(fc.make_desc(1, 64, 56, 56, 256, 1, 1, 1, 1, 0, 0, 0, 0)) == I  # "direct" -> implicit GEMM
     assert fc.select_algorithm(fc.make_desc(1, 3, 224, 224, 64, 7, 7, 2, 2, 3, 3, 3, 3)) == I
     assert fc.select_algorithm(fc.make_desc(1, 8, 20, 20, 8, 5, 5, 1, 1, 2, 2, 2, 2)) == I
+    assert fc.select_algorithm(fc.make_desc(1, 64, 56, 56, 64, group=4)) == I  # grouped 3x3 s1: implicit GEMM per group
 
 
 @pytest.mark.parametrize("bad, status", [
-    (dict(ic=0), -1), (dict(oc=-3), -1), (dict(sh=0), -1), (dict(pad_left=-1), -1), (dict(group=2), -2),
+    (dict(ic=0), -1), (dict(oc=-3), -1), (dict(sh=0), -1), (dict(pad_left=-1), -1), (dict(group=3), -1), (dict(group=0), -1),
     (dict(kh=9, ih=3, pad_top=0, pad_bottom=0), -1), (dict(batch=0), -1),
 ])
 def test_descriptor_validation(bad, status):
@@ -93,6 +94,8 @@ def test_winograd_buffer_sizes_and_rejections():
     assert lib.fc_wino_buffer_elems(ctypes.byref(d), 2, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == 0
     assert u.value == 64 * 128 * 32  # tensor-core modes: U is padded to 128x32 boxes
     assert lib.fc_wino_buffer_elems(ctypes.byref(d), 7, None, None, None) == -1
+    d = fc.make_desc(1, 64, 56, 56, 64, group=2)  # the Winograd stages are built for group 1
+    assert lib.fc_wino_buffer_elems(ctypes.byref(d), 0, ctypes.byref(u), ctypes.byref(v), ctypes.byref(m)) == -2
     for bad in (fc.make_desc(1, 8, 8, 8, 8, 3, 3, 2, 2), fc.make_desc(1, 8, 8, 8, 8, 5, 5), fc.make_desc(1, 8, 8, 8, 8, 3, 3, 1, 1, 1, 0, 1, 1)):
         assert lib.fc_wino_buffer_elems(ctypes.byref(bad), 0, None, None, None) == -2  # FC_ERR_UNSUPPORTED
 
