@@ -31,6 +31,22 @@ __global__ void im2col_gather_kernel(const float *__restrict__ in, float *__rest
     }
 }
 
+// Packed fp32 arithmetic of sm_100: one instruction, two independent IEEE fused multiply-adds (the halves of 64-bit
+// register pairs), each rounded exactly like a scalar fma.rn: same chains, half the issue slots.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 constexpr int BK = 16;
 constexpr int THREADS = 256;
 
@@ -111,11 +127,11 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
         for (int i = 0; i < B_PER; ++i) Bs[buf][bk0 + i * B_KSTEP][bn] = b_stage[i];
     };
 
-    float acc[TM][TN];
+    uint64_t acc2[TM][TN / 2];  // pairs of neighbouring pixels, one packed FMA per pair
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN / 2; ++j) acc2[i][j] = 0ull;
 
     load_slab(0);
     store_slab(0);
@@ -138,10 +154,15 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
                 const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][k][g * 64 + tx * 4]);
                 b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
             }
+            uint64_t bp[TN / 2];
 #pragma unroll
-            for (int i = 0; i < TM; ++i)
+            for (int j = 0; j < TN / 2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+            for (int i = 0; i < TM; ++i) {
+                const uint64_t ap = pack2(a[i], a[i]);
+#pragma unroll
+                for (int j = 0; j < TN / 2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+            }
         }
         if (s + 1 < n_slabs) {
             store_slab(buf ^ 1);
@@ -159,7 +180,9 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
             const int px = pix0 + (j / 4) * 64 + tx * 4 + (j % 4);
             if (px >= P.npix) continue;
             const int im = px / ohw;
-            out[(size_t)im * P.out_img_stride + (size_t)r * ohw + (px - im * ohw)] = ep(acc[i][j], r);
+            float lo, hi;
+            unpack2(acc2[i][j / 2], lo, hi);
+            out[(size_t)im * P.out_img_stride + (size_t)r * ohw + (px - im * ohw)] = ep(j % 2 ? hi : lo, r);
         }
     }
 }
@@ -242,11 +265,16 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
     };
 
     const int ox = tid % OCL, pxl = tid / OCL;
-    float acc[TM][TN];
+    // accumulators: pairs of neighbouring pixels in one 64-bit register when a thread owns at least two
+    constexpr int TP = TN >= 2 ? TN / 2 : 1;
+    uint64_t acc2[TM][TP];
+    float acc1[TM];
 #pragma unroll
-    for (int i = 0; i < TM; ++i)
+    for (int i = 0; i < TM; ++i) {
+        acc1[i] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TP; ++j) acc2[i][j] = 0ull;
+    }
 
     const int n_slabs = (P.K + TK_KC - 1) / TK_KC;
 #pragma unroll
@@ -279,11 +307,21 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
                 } else {
                     b[0] = *bp;
                 }
+                uint64_t bpair[TP];
+                if constexpr (TN >= 2) {
+#pragma unroll
+                    for (int j = 0; j < TP; ++j) bpair[j] = pack2(b[2 * j], b[2 * j + 1]);
+                }
 #pragma unroll
                 for (int i = 0; i < TM; ++i) {
                     const float av = kk == 0 ? a[i].x : kk == 1 ? a[i].y : kk == 2 ? a[i].z : a[i].w;
+                    if constexpr (TN >= 2) {
+                        const uint64_t ap = pack2(av, av);
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(av, b[j], acc[i][j]);
+                        for (int j = 0; j < TP; ++j) acc2[i][j] = fma2(ap, bpair[j], acc2[i][j]);
+                    } else {
+                        acc1[i] = __fmaf_rn(av, b[0], acc1[i]);
+                    }
                 }
             }
         }
@@ -298,7 +336,13 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = oc0 + ox + OCL * i;
-            if (r < P.oc) out[(size_t)img * P.out_img_stride + (size_t)r * ohw + rem] = ep(acc[i][j], r);
+            float v = acc1[i];
+            if constexpr (TN >= 2) {
+                float lo, hi;
+                unpack2(acc2[i][j / 2], lo, hi);
+                v = j % 2 ? hi : lo;
+            }
+            if (r < P.oc) out[(size_t)img * P.out_img_stride + (size_t)r * ohw + rem] = ep(v, r);
         }
     }
 }

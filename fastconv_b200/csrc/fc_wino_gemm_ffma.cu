@@ -27,6 +27,23 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Packed fp32 arithmetic of sm_100: one instruction, two independent IEEE fused multiply-adds (lo and hi halves of
+// 64-bit register pairs).  Each half rounds exactly like a scalar fma.rn, so the accumulation chains are unchanged;
+// what changes is that the same math needs half the issue slots.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -67,11 +84,12 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
         }
     };
 
-    float acc[TM][TN];
+    // accumulators as pairs of neighbouring tiles: one packed FMA per pair (same rounding per element as a scalar FMA)
+    uint64_t acc2[TM][TN / 2];
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN / 2; ++j) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
 
     pdl_trigger();
     pdl_wait();  // V comes from the input transform launched just before
@@ -104,10 +122,15 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
                 const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][k][g * 64 + tx * 4]);
                 b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
             }
+            uint64_t bp[TN / 2];
 #pragma unroll
-            for (int i = 0; i < TM; ++i)
+            for (int j = 0; j < TN / 2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+            for (int i = 0; i < TM; ++i) {
+                const uint64_t ap = pack2(a[i], a[i]);
+#pragma unroll
+                for (int j = 0; j < TN / 2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+            }
         }
     }
     cp_async_wait<0>();
@@ -120,9 +143,12 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
 #pragma unroll
         for (int g = 0; g < TN / 4; ++g) {
             const int c = t0 + g * 64 + tx * 4;
-            if (c < tp)  // tp is a multiple of 8, so a float4 never straddles the end
-                *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) =
-                    make_float4(acc[i][g * 4 + 0], acc[i][g * 4 + 1], acc[i][g * 4 + 2], acc[i][g * 4 + 3]);
+            if (c < tp) {  // tp is a multiple of 8, so a float4 never straddles the end
+                float4 v;
+                unpack2(acc2[i][g * 2 + 0], v.x, v.y);
+                unpack2(acc2[i][g * 2 + 1], v.z, v.w);
+                *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) = v;
+            }
         }
     }
 }
@@ -201,11 +227,17 @@ __global__ void __launch_bounds__(ST_THREADS, 2)
     } else {
         const int ocl = warp * 32 + (lane & 7) * 4;  // first of this lane's 4 channels within the box
         const int j0 = (lane >> 3) * TT;             // first of this lane's TT tiles
-        float acc[4][TT];
+        // accumulators: pairs of neighbouring tiles in one 64-bit register (one packed FMA updates both); a single
+        // tile per lane stays scalar
+        constexpr int TP = TT >= 2 ? TT / 2 : 1;
+        uint64_t acc2[4][TP];
+        float acc1[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 4; ++i) {
+            acc1[i] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < TT; ++j) acc[i][j] = 0.0f;
+            for (int j = 0; j < TP; ++j) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
+        }
         // TT floats of a V row; lanes past the last real tile read whatever follows inside the stage and never store
         auto load_v = [&](const float *src, float (&b)[TT]) {
             if constexpr (TT == 8) {
@@ -239,10 +271,20 @@ __global__ void __launch_bounds__(ST_THREADS, 2)
                 float bn[TT];
                 load_v(vk + (kk + 1) * tp, bn);
                 const float uu[4] = {u.x, u.y, u.z, u.w};
+                if constexpr (TT >= 2) {
+                    uint64_t bp[TP];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                    for (int j = 0; j < TP; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
 #pragma unroll
-                    for (int j = 0; j < TT; ++j) acc[i][j] = __fmaf_rn(uu[i], b[j], acc[i][j]);
+                    for (int i = 0; i < 4; ++i) {
+                        const uint64_t up = pack2(uu[i], uu[i]);
+#pragma unroll
+                        for (int j = 0; j < TP; ++j) acc2[i][j] = fma2(up, bp[j], acc2[i][j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc1[i] = __fmaf_rn(uu[i], b[0], acc1[i]);
+                }
                 u = un;
 #pragma unroll
                 for (int j = 0; j < TT; ++j) b[j] = bn[j];
@@ -256,9 +298,16 @@ __global__ void __launch_bounds__(ST_THREADS, 2)
                 const int row = oc0 + ocl + i;
                 if (row >= oc) continue;
                 float *dst = M + ((size_t)p * oc + row) * tp + j0;
+                float res[TT];
+                if constexpr (TT >= 2) {
+#pragma unroll
+                    for (int j = 0; j < TP; ++j) unpack2(acc2[i][j], res[2 * j], res[2 * j + 1]);
+                } else {
+                    res[0] = acc1[i];
+                }
 #pragma unroll
                 for (int j = 0; j < TT; ++j)
-                    if (j0 + j < tp) dst[j] = acc[i][j];
+                    if (j0 + j < tp) dst[j] = res[j];
             }
         }
     }
