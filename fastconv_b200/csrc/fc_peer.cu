@@ -10,7 +10,7 @@
 //   3. a one-warp kernel on every rank polls its own flag array until all ranks have published s.
 // No kernel of one GPU waits for a kernel of the SAME GPU, the wait of step 3 has an iteration limit and
 // reports FC_ERR_TIMEOUT through the context status word instead of spinning forever, and only plain stores
-// and loads cross NVLink (no multicast objects, nothing that needs a peer to stay alive).
+// and loads cross NVLink (no switch-side reduction or replication objects, nothing that needs a peer to stay alive).
 #include "fc_internal.h"
 
 #include <cstring>
