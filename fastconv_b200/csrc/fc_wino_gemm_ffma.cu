@@ -10,7 +10,8 @@
 // BK x BM slab of U and a BK x BN slab of V are sets of contiguous runs: they go to shared memory as
 // [k][row] with 16-byte asynchronous copies (cp.async, zero-filled past the edges) through a 4-stage
 // ring, and the inner product reads 128-bit rows without bank conflicts.  No register staging, no
-// transposition, two CTAs per SM.
+// transposition, two CTAs per SM.  The FMAs of two neighbouring tiles are issued as one packed instruction
+// (fma.rn.f32x2): each half rounds like a scalar FMA, so the chains are unchanged.
 #include "fc_tc_common.cuh"
 
 namespace fc {
