@@ -11,7 +11,8 @@
 // descriptor expects (and its lo part in 3xTF32 mode), then hand it to the MMA warp over an mbarrier.
 //
 //   warp 0      TMA producer for A        warp 1   TMEM owner + MMA issuer
-//   warps 2..5  B gather producers, then the epilogue (tcgen05.ld -> global)
+//   warps 2..9  B gather producers (a thread owns a pixel row and one half of the 32 k-steps of a stage);
+//   warps 2..5  then run the epilogue (tcgen05.ld -> global)
 #include "fc_tc_common.cuh"
 
 namespace fc {
@@ -45,8 +46,10 @@ __global__ void pack_weights_kernel(const float *__restrict__ kernel, float *__r
     }
 }
 
+constexpr int IG_THREADS = TC_THREADS + 128;  // 2 + 8 warps
+
 template <bool kSplit>
-__global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+__global__ void __launch_bounds__(IG_THREADS) igemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                                                               const IgemmTcParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full_a[8], full_b[8], empty[8], tmem_full
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(bar_full_a(s), 1);
-            mbar_init(bar_full_b(s), 128);
+            mbar_init(bar_full_b(s), 256);
             mbar_init(bar_empty(s), 1);
         }
         mbar_init(bar_tmem_full, 1);
@@ -141,7 +144,8 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
         // pixel rows of k-block `it` straight to their swizzled place, commits them as one group, and only then
         // finishes k-block it-LAG (waits for that group, splits hi/lo in place for 3xTF32, hands the slab to the MMA
         // warp).  So LAG k-blocks of loads are in flight per thread and global latency is not on the critical path.
-        const int gt = threadIdx.x - 64;  // 0..127
+        const int gt = (threadIdx.x - 64) & 127;   // pixel row of the slab (and gt + 128 when bn > 128)
+        const int kh0 = ((threadIdx.x - 64) >> 7) * (BK / 2);  // this thread gathers k-steps [kh0, kh0 + 16) of a stage
         const int khw = P.kh * P.kw;
         const float *img_ptr = P.in + (size_t)img * P.in_img_stride;
         const int lag = S > 2 ? 2 : S - 1;
@@ -180,7 +184,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
                     const uint32_t row_off = (uint32_t)(n >> 3) * 1024u + (uint32_t)(n & 7) * 128u;
                     const uint32_t sw = (uint32_t)(n & 7);
 #pragma unroll 8
-                    for (int kk = 0; kk < BK; ++kk) {
+                    for (int kk = kh0; kk < kh0 + BK / 2; ++kk) {
                         const int off = __shfl_sync(0xffffffffu, off_mine, kk);
                         const int uv = __shfl_sync(0xffffffffu, uv_mine, kk);
                         const int row = base_row + (uv >> 16), col = base_col + (uv & 0xffff);
@@ -209,12 +213,12 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
                     for (int n = gt; n < P.bn; n += 128) {
                         const uint32_t row_off = (uint32_t)(n >> 3) * 1024u + (uint32_t)(n & 7) * 128u;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            float4 x = *reinterpret_cast<const float4 *>(b_hi + row_off + c * 16);
+                        for (int c = kh0 / 4; c < kh0 / 4 + 4; ++c) {  // the four 16-byte chunks this thread copied
+                            const uint32_t at = row_off + (((uint32_t)c ^ (uint32_t)(n & 7)) << 4);
+                            float4 x = *reinterpret_cast<const float4 *>(b_hi + at);
                             float4 h = make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w));
-                            *reinterpret_cast<float4 *>(b_hi + row_off + c * 16) = h;
-                            *reinterpret_cast<float4 *>(b_lo + row_off + c * 16) =
-                                make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+                            *reinterpret_cast<float4 *>(b_hi + at) = h;
+                            *reinterpret_cast<float4 *>(b_lo + at) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
                         }
                     }
                 }
@@ -223,7 +227,7 @@ __global__ void __launch_bounds__(TC_THREADS) igemm_tc_kernel(const __grid_const
             }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");  // nothing of this thread is in flight past this point
-        if (mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
+        if (warp < 6 && mbar_wait(bar_tmem_full, 0u, abort_flag, P.status)) {
             tc_fence_after();
             const int q = warp & 3;
             const int row = oc0 + q * 32 + lane;
@@ -323,7 +327,7 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
 
     CUtensorMap tmA;  // [2 planes][oc][Kp]
     FC_PROPAGATE(make_map_3d(&tmA, d_packed, Kp, d.oc, 2, BM));
-    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(d.oc, BM), (unsigned)(d.batch * splits)), block(TC_THREADS);
+    dim3 grid((unsigned)n_blk, (unsigned)ceil_div(d.oc, BM), (unsigned)(d.batch * splits)), block(IG_THREADS);
     if (splits > 1) {  // the K ranges add their partial sums into a zeroed output (this launch's channels only)
         if (P.out_img_stride == (long long)d.oc * ohw) {
             FC_CHECK_CUDA(cudaMemsetAsync(d_out, 0, (size_t)d.batch * d.oc * ohw * sizeof(float), ctx->stream));
