@@ -192,13 +192,13 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
 // 16 x 16-thread kernel above launches a handful of CTAs for them and decodes k -> (c,u,v) with two integer
 // divisions per gathered element.  This kernel takes the decode from a per-layer table (one int2 per k:
 // element offset inside the image and (u,v)), brings both operands to shared memory with asynchronous
-// copies through a 3-stage ring (weights as 16-byte pieces along k, gathered input as 4-byte pieces with
+// copies through a ring of 3 to 8 stages (weights as 16-byte pieces along k, gathered input as 4-byte pieces with
 // zero fill for the padding), and comes in block shapes from 64x64 down to 8x32 so that even a 49-pixel
 // layer spreads over the machine.  Lanes run along output channels, so a thread reads four k-steps of
 // its weight rows in one conflict-free 128-bit read and its pixels as a broadcast.  The chain per output
 // element is unchanged: one accumulator, one FMA per k, ascending.
 // ---------------------------------------------------------------------------------------------
-constexpr int TK_KC = 32, TK_KCP = 36, TK_STAGES = 3;
+constexpr int TK_KC = 32, TK_KCP = 36;
 
 __device__ __forceinline__ void cp_async_zfill_16(void *smem_dst, const void *gmem_src, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -211,8 +211,13 @@ __device__ __forceinline__ void cp_async_zfill_4(void *smem_dst, const void *gme
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
 }
 
-template <int BM, int BN, int TM, int TN>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+// The second launch bound is there for the register allocator: without it ptxas squeezes the small shapes into 32
+// registers and every shared-memory read is consumed right after it is issued, its latency exposed on a chain that
+// is already sequential in k.
+// TK_STAGES: depth of the ring.  Small blocks do little math per stage, so they need a deeper ring to keep the
+// two dependent global accesses of the gather (decode table, then the element) off the critical path.
+template <int BM, int BN, int TM, int TN, int TK_STAGES>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     igemm_ffma_tile_kernel(const float *__restrict__ in, const float *__restrict__ A, float *__restrict__ out,
                            const int2 *__restrict__ ktab, IgemmParams P, int a_vec, Epilogue ep) {
     constexpr int OCL = BM / TM, NT = OCL * (BN / TN), BNP = BN + 4;
@@ -240,7 +245,20 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
         pix_ptr = in + (size_t)img * P.in_img_stride + (ptrdiff_t)base_row * P.iw + base_col;
     }
 
-    auto load_stage = [&](int st, int k0) {
+    // The decode entries of the NEXT slab are fetched while the copies of this one are issued, so the table read
+    // (a global load) is never waited for on the way to the copy that depends on it.
+    const int k_padded = ((P.K + TK_KC - 1) / TK_KC) * TK_KC;  // entries in the table
+    int2 dec[B_ITERS];
+    auto fetch_decode = [&](int k0) {
+#pragma unroll
+        for (int r = 0; r < B_ITERS; ++r) {
+            const int k = k0 + lk0 + r * B_STEP;
+            dec[r] = k < k_padded ? __ldg(ktab + k) : make_int2(0, 0x4000 << 16);
+        }
+    };
+    fetch_decode(0);
+
+    auto load_stage = [&](int st, int k0) {  // called with k0 = 0, 32, 64, ... in this order
         if (a_vec) {  // rows of A are 16-byte aligned: K is a multiple of 4
             for (int idx = tid; idx < BM * (TK_KC / 4); idx += NT) {
                 const int row = idx / (TK_KC / 4), c4 = (idx % (TK_KC / 4)) * 4;
@@ -257,11 +275,12 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 #pragma unroll
         for (int r = 0; r < B_ITERS; ++r) {
             const int kk = lk0 + r * B_STEP;
-            const int2 e = __ldg(ktab + k0 + kk);  // the table is padded to a multiple of 32 with out-of-image entries
+            const int2 e = dec[r];  // the table is padded to a multiple of 32 with out-of-image entries
             const int row = base_row + (e.y >> 16), col = base_col + (e.y & 0xffff);
             const bool ok = gpix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw;
             cp_async_zfill_4(&Bs[st][kk][lp], ok ? pix_ptr + e.x : in, ok);
         }
+        fetch_decode(k0 + TK_KC);
     };
 
     const int ox = tid % OCL, pxl = tid / OCL;
@@ -291,26 +310,31 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
         const int st = s % TK_STAGES;
 #pragma unroll
         for (int k4 = 0; k4 < TK_KC / 4; ++k4) {
+            // all operands of four k-steps first (TM 128-bit reads of the weights, four reads of the pixels), then
+            // their FMAs: the reads of the next group overlap the chain of this one
             float4 a[TM];
+            float b[4][TN];
 #pragma unroll
             for (int i = 0; i < TM; ++i) a[i] = *reinterpret_cast<const float4 *>(&As[st][ox + OCL * i][k4 * 4]);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-                float b[TN];
                 const float *bp = &Bs[st][k4 * 4 + kk][pxl * TN];
                 if constexpr (TN == 4) {
                     const float4 t = *reinterpret_cast<const float4 *>(bp);
-                    b[0] = t.x; b[1] = t.y; b[2] = t.z; b[3] = t.w;
+                    b[kk][0] = t.x; b[kk][1] = t.y; b[kk][2] = t.z; b[kk][3] = t.w;
                 } else if constexpr (TN == 2) {
                     const float2 t = *reinterpret_cast<const float2 *>(bp);
-                    b[0] = t.x; b[1] = t.y;
+                    b[kk][0] = t.x; b[kk][1] = t.y;
                 } else {
-                    b[0] = *bp;
+                    b[kk][0] = *bp;
                 }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
                 uint64_t bpair[TP];
                 if constexpr (TN >= 2) {
 #pragma unroll
-                    for (int j = 0; j < TP; ++j) bpair[j] = pack2(b[2 * j], b[2 * j + 1]);
+                    for (int j = 0; j < TP; ++j) bpair[j] = pack2(b[kk][2 * j], b[kk][2 * j + 1]);
                 }
 #pragma unroll
                 for (int i = 0; i < TM; ++i) {
@@ -320,7 +344,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 #pragma unroll
                         for (int j = 0; j < TP; ++j) acc2[i][j] = fma2(ap, bpair[j], acc2[i][j]);
                     } else {
-                        acc1[i] = __fmaf_rn(av, b[0], acc1[i]);
+                        acc1[i] = __fmaf_rn(av, b[kk][0], acc1[i]);
                     }
                 }
             }
@@ -347,15 +371,15 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
     }
 }
 
-template <int BM, int BN, int TM, int TN>
+template <int BM, int BN, int TM, int TN, int TK_STAGES>
 int launch_tile(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const int2 *d_ktab,
                 const IgemmParams &P, const Epilogue &ep) {
     constexpr int NT = (BM / TM) * (BN / TN);
     const size_t smem = (size_t)TK_STAGES * (BM * TK_KCP + TK_KC * (BN + 4)) * sizeof(float);
-    FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_ffma_tile_kernel<BM, BN, TM, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_ffma_tile_kernel<BM, BN, TM, TN, TK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid((unsigned)ceil_div(P.npix, BN), (unsigned)ceil_div(P.oc, BM)), block(NT);
-    igemm_ffma_tile_kernel<BM, BN, TM, TN><<<grid, block, smem, ctx->stream>>>(d_in, d_kernel, d_out, d_ktab, P,
+    igemm_ffma_tile_kernel<BM, BN, TM, TN, TK_STAGES><<<grid, block, smem, ctx->stream>>>(d_in, d_kernel, d_out, d_ktab, P,
                                                                               P.K % 4 == 0 ? 1 : 0, ep);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
@@ -472,11 +496,11 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
                 if (ctas > best) { best = ctas; bm = sh[0]; bn = sh[1]; }
             }
         }
-        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2, 6>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep);
         set_error("no table-driven implicit GEMM with a %d x %d block", bm, bn);
         return FC_ERR_INVALID_ARG;
     }
