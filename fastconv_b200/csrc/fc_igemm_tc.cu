@@ -149,6 +149,20 @@ __global__ void __launch_bounds__(IG_THREADS) igemm_tc_kernel(const __grid_const
         const int khw = P.kh * P.kw;
         const float *img_ptr = P.in + (size_t)img * P.in_img_stride;
         const int lag = S > 2 ? 2 : S - 1;
+        // k -> (element offset, u:v): from the layer's table when there is one (padded to a multiple of 32 entries),
+        // else by division; past the reduction a row far below the image, so the copy zero-fills
+        auto decode = [&](int k, bool wanted) -> int2 {
+            int2 e = make_int2(0, 0x4000 << 16);
+            if (!wanted) return e;
+            if (P.ktab != nullptr) return __ldg(P.ktab + k);
+            if (k < P.K) {
+                const int c = k / khw, r2 = k - c * khw;
+                const int u = r2 / P.kw, v = r2 - u * P.kw;
+                e = make_int2((c * P.ih + u) * P.iw + v, (u << 16) | v);
+            }
+            return e;
+        };
+        int2 next_dec = decode(kb0 * BK + lane, true);
         bool ok = true;
         for (int it = kb0; it < kb1 + lag && ok; ++it) {
             if (it < kb1) {
@@ -156,20 +170,10 @@ __global__ void __launch_bounds__(IG_THREADS) igemm_tc_kernel(const __grid_const
                 const uint32_t ph = (uint32_t)((it - kb0) / S) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status));  // warp-uniform
                 if (!ok) break;
-                // lane l of every warp decodes k = it*32 + l once (from the layer's table when there is one);
-                // the values travel by shuffle below
-                const int k_mine = it * BK + lane;
-                int off_mine = 0, uv_mine = 0x4000 << 16;  // a row far below the image: zero fill
-                if (P.ktab != nullptr) {
-                    const int2 e = __ldg(P.ktab + k_mine);  // padded to a multiple of 32 entries
-                    off_mine = e.x;
-                    uv_mine = e.y;
-                } else if (k_mine < P.K) {
-                    const int c = k_mine / khw, r2 = k_mine - c * khw;
-                    const int u = r2 / P.kw, v = r2 - u * P.kw;
-                    off_mine = (c * P.ih + u) * P.iw + v;
-                    uv_mine = (u << 16) | v;
-                }
+                // lane l of every warp holds the decode of k = it*32 + l (fetched during the previous iteration, so the
+                // table read is not waited for here); the values travel by shuffle below
+                const int off_mine = next_dec.x, uv_mine = next_dec.y;
+                next_dec = decode((it + 1) * BK + lane, it + 1 < kb1);
                 const uint32_t b_hi = ring + s * stage_bytes + A_BYTES;
                 // a thread owns pixel rows n = gt, gt+128, ... of the slab (bn <= 256); every lane runs the loop
                 // and its shuffles, lanes past the slab only skip the copies
