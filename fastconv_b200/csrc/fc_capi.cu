@@ -99,6 +99,7 @@ struct fc_conv {
     float *d_kernel;  // raw [oc][ic*kh*kw]
     float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
     float *d_ktab;    // fp32 implicit GEMM: int pairs (offset, u:v) per k, in a float-typed arena slot
+    float *d_bmat;    // fp32 implicit GEMM of a few-pixel, long-reduction layer: the materialised gathered matrix
     float *d_bias;    // per-channel bias of the epilogue, or NULL
     int relu;         // epilogue: clamp at zero after the bias
     float *d_U, *d_V, *d_M;
@@ -524,7 +525,7 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
 
 static void conv_release(fc_conv *c) {
     fc_context *ctx = c->ctx;
-    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_bias, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_bmat, c->d_bias, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
     for (float *b : bufs)
         if (b) ctx->arena.release((uintptr_t)b);
     delete c;
@@ -650,6 +651,8 @@ static int conv_prepare(fc_conv *c, int algo) {
             }
         }
     }
+    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_bmat == nullptr && igemm_wants_matrix(d, c->oh, c->ow))
+        st = grab(ctx, &c->d_bmat, (size_t)d.ic * d.kh * d.kw * igemm_matrix_ld(d, c->oh, c->ow));
     if (st != FC_OK) return st;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
@@ -739,6 +742,13 @@ static bool igemm_on_fp32_pipe(const fc_conv *c) {
     return K <= (c->mode == FC_MATH_3XTF32 ? 512 : 256) && flops <= 500000000ll;  // short reduction AND a small problem
 }
 
+// kernel launches of one forward of an implicit-GEMM layer
+static int igemm_launches(const fc_conv *c) {
+    if (c->desc.group > 1) return c->desc.group == c->desc.ic ? 1 : c->desc.group;
+    const bool tile_kernel = c->cfg.skinny != 2;  // the matrix is written only ahead of the table-driven kernel
+    return c->d_bmat != nullptr && igemm_on_fp32_pipe(c) && tile_kernel ? 2 : 1;
+}
+
 // One pass of a Winograd layer: images [pass*pass_imgs, ...) of the batch through the three kernels.
 static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_out, bool timed) {
     fc_context *ctx = c->ctx;
@@ -784,7 +794,7 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
             const Epilogue ep{c->d_bias ? c->d_bias + (size_t)g * gd.oc : nullptr, c->relu};
             if (fp32_pipe)
                 st = launch_igemm_ffma(ctx, in_g, c->d_kernel + (size_t)g * gd.oc * Kg, out_g, gd, c->oh, c->ow, &c->cfg,
-                                       reinterpret_cast<const int *>(c->d_ktab), ep, in_stride, out_stride);
+                                       reinterpret_cast<const int *>(c->d_ktab), ep, in_stride, out_stride, c->d_bmat);
             else
                 st = launch_igemm_tc(ctx, in_g, c->d_packed + (size_t)g * igemm_packed_elems(gd.oc, (int)Kg), out_g, gd,
                                      c->oh, c->ow, c->mode, &c->cfg, reinterpret_cast<const int *>(c->d_ktab), ep,
@@ -1089,7 +1099,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : (c->desc.group == c->desc.ic ? 1 : c->desc.group);
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : igemm_launches(c);
     return FC_OK;
 }
 
@@ -1115,8 +1125,7 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     for (int i = 0; i < count; ++i) {
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
-        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i])
-                                                        : (convs[i]->desc.group == convs[i]->desc.ic ? 1 : convs[i]->desc.group);
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i]) : igemm_launches(convs[i]);
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     // one eager pass first: kernel attributes are set and any error shows up outside the capture

@@ -219,7 +219,8 @@ __device__ __forceinline__ void cp_async_zfill_4(void *smem_dst, const void *gme
 template <int BM, int BN, int TM, int TN, int TK_STAGES>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     igemm_ffma_tile_kernel(const float *__restrict__ in, const float *__restrict__ A, float *__restrict__ out,
-                           const int2 *__restrict__ ktab, IgemmParams P, int a_vec, Epilogue ep) {
+                           const int2 *__restrict__ ktab, IgemmParams P, int a_vec, Epilogue ep,
+                           const float *__restrict__ bmat, int ld) {
     constexpr int OCL = BM / TM, NT = OCL * (BN / TN), BNP = BN + 4;
     constexpr int B_STEP = NT / BN, B_ITERS = TK_KC / B_STEP;
     static_assert(NT % BN == 0 && TK_KC % B_STEP == 0 && (TN == 1 || TN == 2 || TN == 4), "block shape");
@@ -250,6 +251,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     const int k_padded = ((P.K + TK_KC - 1) / TK_KC) * TK_KC;  // entries in the table
     int2 dec[B_ITERS];
     auto fetch_decode = [&](int k0) {
+        if (bmat != nullptr) return;  // the gathered matrix was materialised: no decode needed
 #pragma unroll
         for (int r = 0; r < B_ITERS; ++r) {
             const int k = k0 + lk0 + r * B_STEP;
@@ -271,6 +273,14 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
                 const bool ok = oc0 + row < P.oc && k0 + kk < P.K;
                 cp_async_zfill_4(&As[st][row][kk], A + (ok ? (size_t)(oc0 + row) * P.K + k0 + kk : 0), ok);
             }
+        }
+        if (bmat != nullptr) {  // rows of the materialised matrix: 16-byte pieces, no index arithmetic per element
+            for (int idx = tid; idx < TK_KC * (BN / 4); idx += NT) {
+                const int kk = idx / (BN / 4), c4 = (idx % (BN / 4)) * 4;
+                const bool ok = k0 + kk < P.K;
+                cp_async_zfill_16(&Bs[st][kk][c4], bmat + (ok ? (size_t)(k0 + kk) * ld + pix0 + c4 : 0), ok);
+            }
+            return;
         }
 #pragma unroll
         for (int r = 0; r < B_ITERS; ++r) {
@@ -371,16 +381,39 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     }
 }
 
+// Few output pixels and a long reduction (the 7x7 and 14x14 ResNet layers): every block row would gather the same
+// K x pixels matrix again, at some sixteen instructions per element against one FMA per element and channel.  Here
+// the matrix is written once -- B[k][pixel], rows padded with zeros to `ld` floats -- and the blocks stream it with
+// 16-byte copies.  It is at most a few MB and stays in L2.
+__global__ void __launch_bounds__(256) im2col_matrix_kernel(const float *__restrict__ in, const int2 *__restrict__ ktab,
+                                                            float *__restrict__ B, IgemmParams P, int ld) {
+    const int ohw = P.oh * P.ow;
+    const size_t total = (size_t)P.K * ld;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int pix = (int)(idx % ld), k = (int)(idx / ld);
+        float v = 0.0f;
+        if (pix < P.npix) {
+            const int img = pix / ohw, rem = pix - img * ohw;
+            const int oi = rem / P.ow, oj = rem - oi * P.ow;
+            const int2 e = __ldg(ktab + k);
+            const int row = oi * P.sh - P.pad_t + (e.y >> 16), col = oj * P.sw - P.pad_l + (e.y & 0xffff);
+            if ((unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw)
+                v = __ldg(in + (size_t)img * P.in_img_stride + (ptrdiff_t)(oi * P.sh - P.pad_t) * P.iw + (oj * P.sw - P.pad_l) + e.x);
+        }
+        B[idx] = v;
+    }
+}
+
 template <int BM, int BN, int TM, int TN, int TK_STAGES>
 int launch_tile(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const int2 *d_ktab,
-                const IgemmParams &P, const Epilogue &ep) {
+                const IgemmParams &P, const Epilogue &ep, const float *d_bmat = nullptr, int ld = 0) {
     constexpr int NT = (BM / TM) * (BN / TN);
     const size_t smem = (size_t)TK_STAGES * (BM * TK_KCP + TK_KC * (BN + 4)) * sizeof(float);
     FC_CHECK_CUDA(cudaFuncSetAttribute(igemm_ffma_tile_kernel<BM, BN, TM, TN, TK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid((unsigned)ceil_div(P.npix, BN), (unsigned)ceil_div(P.oc, BM)), block(NT);
     igemm_ffma_tile_kernel<BM, BN, TM, TN, TK_STAGES><<<grid, block, smem, ctx->stream>>>(d_in, d_kernel, d_out, d_ktab, P,
-                                                                              P.K % 4 == 0 ? 1 : 0, ep);
+                                                                              P.K % 4 == 0 ? 1 : 0, ep, d_bmat, ld);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -446,6 +479,13 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
     return FC_OK;
 }
 
+// A layer streams a materialised gathered matrix when it has few output pixels and a long reduction (see
+// im2col_matrix_kernel); its rows are padded to a multiple of 64 floats, the widest pixel block.
+bool igemm_wants_matrix(const fc_conv_desc &d, int oh, int ow) {
+    return d.group == 1 && (long long)d.batch * oh * ow <= 256 && (long long)d.ic * d.kh * d.kw >= 512;
+}
+size_t igemm_matrix_ld(const fc_conv_desc &d, int oh, int ow) { return (size_t)round_up(d.batch * oh * ow, 64); }
+
 size_t igemm_ktab_entries(const fc_conv_desc &d) { return (size_t)round_up(d.ic * d.kh * d.kw, TK_KC); }
 
 void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs) {
@@ -464,7 +504,7 @@ void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs) {
 
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                       int oh, int ow, const KernelCfg *cfg, const int *d_ktab, const Epilogue &ep, size_t in_img_stride,
-                      size_t out_img_stride) {
+                      size_t out_img_stride, float *d_bmat) {
     IgemmParams P;
     P.n = d.batch; P.ic = d.ic; P.ih = d.ih; P.iw = d.iw; P.oc = d.oc; P.kh = d.kh; P.kw = d.kw;
     P.sh = d.sh; P.sw = d.sw; P.pad_l = d.pad_left; P.pad_t = d.pad_top; P.oh = oh; P.ow = ow;
@@ -496,11 +536,21 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
                 if (ctas > best) { best = ctas; bm = sh[0]; bn = sh[1]; }
             }
         }
-        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2, 6>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep);
-        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep);
+        const float *bmat = nullptr;
+        int ld = 0;
+        if (d_bmat != nullptr && igemm_wants_matrix(d, oh, ow)) {  // write the gathered matrix once, then stream it
+            ld = (int)igemm_matrix_ld(d, oh, ow);
+            const size_t total = (size_t)P.K * ld;
+            const unsigned blocks = (unsigned)(ceil_div(total, 256) > (size_t)sms * 8 ? (size_t)sms * 8 : ceil_div(total, 256));
+            im2col_matrix_kernel<<<blocks, 256, 0, ctx->stream>>>(d_in, tab, d_bmat, P, ld);
+            FC_CHECK_CUDA(cudaGetLastError());
+            bmat = d_bmat;
+        }
+        if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2, 6>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 16 && bn == 32) return launch_tile<16, 32, 1, 2, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 8 && bn == 32) return launch_tile<8, 32, 1, 1, 8>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
         set_error("no table-driven implicit GEMM with a %d x %d block", bm, bn);
         return FC_ERR_INVALID_ARG;
     }

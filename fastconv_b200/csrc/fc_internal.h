@@ -170,7 +170,11 @@ int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const f
 // d_ktab: per-layer k -> (offset, u:v) table (igemm_fill_ktab), or NULL outside a planned layer
 int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                       int oh, int ow, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
-                      const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0);
+                      const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0,
+                      float *d_bmat = nullptr);
+// scratch for the materialised gathered matrix of a few-pixel, long-reduction layer: K x igemm_matrix_ld floats
+bool igemm_wants_matrix(const fc_conv_desc &d, int oh, int ow);
+size_t igemm_matrix_ld(const fc_conv_desc &d, int oh, int ow);
 // group == ic: one thread per output element, reduction over the kh*kw taps only
 int launch_depthwise(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                      int oh, int ow, const Epilogue &ep = kNoEpilogue);
