@@ -72,6 +72,7 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.gpu, self.proc, self.lines, self.marks = gpu_index, None, [], []
+        self.topped_up = False
 
     def mark(self):
         """Remembers how many samples had arrived: the first two marks bracket the device-timed region."""
@@ -91,6 +92,27 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first(self, timeout: float = 4.0) -> None:
+        """Blocks until nvidia-smi has delivered its first sample (its start-up can take longer than the whole run)."""
+        t_end = time.time() + timeout
+        while self.proc is not None and not self.lines and time.time() < t_end:
+            time.sleep(0.01)
+
+    def samples_since_first_mark(self) -> int:
+        return len(self.lines) - (self.marks[0] if self.marks else 0)
+
+    def top_up(self, step, sync, seconds: float = 0.4, want: int = 4) -> None:
+        """The timed region is a few milliseconds, shorter than one sampling period.  When too few samples fell
+        under load, the same steps are repeated, untimed, right after it until a handful of samples exists."""
+        if self.proc is None or self.samples_since_first_mark() >= want:
+            return
+        self.topped_up = True
+        t_end = time.time() + seconds
+        while time.time() < t_end and self.samples_since_first_mark() < want:
+            for _ in range(20):
+                step()
+            sync()
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -105,6 +127,8 @@ class ClockSampler:
         lines = self.lines[self.marks[0]:self.marks[1]] if len(self.marks) >= 2 else []
         if len(lines) < 2:  # region shorter than the sampling period: use every sample taken under load
             lines, window = self.lines[self.marks[0] if self.marks else 0:], "timed + end-to-end regions"
+            if self.topped_up:
+                window += " + the same steps repeated untimed right after (the timed region is shorter than a sampling period)"
         for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
@@ -222,6 +246,7 @@ def run_k_sharded(args, rank, world, local_rank, dist):
         step()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.wait_first()
     ctx.synchronize(); torch.cuda.synchronize(); dist.barrier()
     sampler.mark()
     ctx.timer_record(0)
@@ -231,6 +256,12 @@ def run_k_sharded(args, rank, world, local_rank, dist):
     ms = ctx.timer_elapsed_ms(0, 1)
     torch.cuda.synchronize(); dist.barrier()
     sampler.mark()
+    # the timed region is shorter than a sampling period: the same steps once more, untimed, the same count on every
+    # rank (the ranks exchange step flags), so that the clock record has samples under this load
+    for _ in range(10 * args.steps):
+        step()
+    ctx.synchronize(); torch.cuda.synchronize(); dist.barrier()
+    sampler.topped_up = True
     clocks = sampler.stop()
     t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local_rank}")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -380,6 +411,7 @@ def main():
     # ---- device-resident throughput (`value`) -----------------------------------------------------
     sampler = ClockSampler(local_rank)
     sampler.start()
+    sampler.wait_first()
     for _ in range(args.warmup):
         step_device()
     barrier()
@@ -403,6 +435,7 @@ def main():
     ctx.synchronize()
     e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3) / args.steps
     barrier()
+    sampler.top_up(step_device, ctx.synchronize)
     clocks = sampler.stop()
 
     # ---- per-layer and per-kernel device times (CUDA events around each stage, same inputs) ----------
