@@ -269,3 +269,41 @@ def test_layer_list_graph_replays_every_layer(ctx, oracle):
         lib.fc_conv_destroy(h)
     for p in ins + outs:
         ctx.free(p)
+
+
+def _random_shapes(seed, count):
+    rng = np.random.default_rng(seed)
+    shapes = []
+    for _ in range(count):
+        n = int(rng.integers(1, 4))
+        ic, oc = int(rng.integers(1, 72)), int(rng.integers(1, 150))
+        ih, iw = int(rng.integers(1, 44)), int(rng.integers(1, 44))
+        pad = int(rng.integers(0, 3))
+        if ih + 2 * pad < 3 or iw + 2 * pad < 3:
+            pad = 1
+            ih, iw = max(ih, 1), max(iw, 1)
+        shapes.append((n, ic, oc, ih, iw, pad))
+    return shapes
+
+
+@pytest.mark.parametrize("shape", _random_shapes(2024, 28))
+def test_random_shapes_mirrored_mode_bit_exact(ctx, oracle, shape):
+    """Seeded random shapes: 1..150 channels, 1..43 pixels a side, batch 1..3, padding 0..2 -- every tile-count bucket
+    of the skinny kernel, ragged channel counts, tiles that overhang the image on both sides."""
+    n, ic, oc, ih, iw, pad = shape
+    x = synth.conv_input(n, ic, ih, iw, 91)
+    w = synth.conv_weights(oc, ic, 3, 3, 92)
+    assert np.array_equal(run_layer(ctx, x, w, pad), oracle.wino_forward(x, w, pad))
+
+
+@pytest.mark.parametrize("shape", _random_shapes(4048, 20))
+def test_random_shapes_3xtf32_within_tolerance(ctx, oracle, shape):
+    """The same family of shapes through the tcgen05 kernel (both operand-role variants occur: at most 64 output
+    channels or at least 128 tiles exchange the roles)."""
+    n, ic, oc, ih, iw, pad = shape
+    x = synth.conv_input(n, ic, ih, iw, 93)
+    w = synth.conv_weights(oc, ic, 3, 3, 94)
+    want = oracle.wino_forward(x, w, pad)
+    got = run_layer(ctx, x, w, pad, "3xtf32")
+    assert rel_l2(got, want) <= 1e-5
+    assert max_abs_rel(got, want) <= 1e-4
