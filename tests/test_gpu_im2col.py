@@ -127,3 +127,44 @@ def test_four_separate_paddings_and_a_non_square_kernel(ctx, oracle, mode, pads)
     for img in range(n):
         assert np.array_equal(layer.im2col(img), oracle.im2col(x[img], kh, kw, sh, sw, pl, pr, pt, pb))
     layer.release()
+
+
+def _random_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    cases = []
+    for _ in range(count):
+        kh, kw = int(rng.choice([1, 3, 5, 7])), int(rng.choice([1, 3, 5, 7]))
+        n, ic, oc = int(rng.integers(1, 3)), int(rng.integers(1, 97)), int(rng.integers(1, 97))
+        ih, iw = int(rng.integers(kh, 25)), int(rng.integers(kw, 25))
+        sh, sw = int(rng.integers(1, 3)), int(rng.integers(1, 3))
+        pad = int(rng.integers(0, min(kh, kw) // 2 + 1))
+        cases.append((n, ic, oc, ih, iw, kh, kw, sh, sw, pad))
+    # few pixels and a long reduction: the layers that write the gathered matrix once and stream it
+    cases += [(1, 128, 40, 14, 14, 3, 3, 2, 2, 1), (1, 600, 24, 7, 7, 1, 1, 1, 1, 0), (2, 64, 72, 9, 9, 3, 3, 1, 1, 1)]
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_cases(77, 24))
+def test_random_cases_mirrored_gemm_bit_exact(ctx, oracle, case):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 17)
+    w = synth.conv_weights(oc, ic, kh, kw, 18)
+    layer = fc.ConvIm2colLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, sh, sw, pad, pad, pad, pad, 1, False, 1, 1,
+                               batch=n, ctx=ctx)
+    layer.Init(); layer.Forward()
+    assert np.array_equal(layer.output_data, oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad))
+    layer.release()
+
+
+@pytest.mark.parametrize("mode,tol", [("3xtf32", 1e-5), ("tf32", 3e-3)])
+@pytest.mark.parametrize("case", _random_cases(78, 10))
+def test_random_cases_tensor_core_modes(ctx, oracle, case, mode, tol):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 19)
+    w = synth.conv_weights(oc, ic, kh, kw, 20)
+    layer = fc.ConvIm2colLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, sh, sw, pad, pad, pad, pad, 1, False, 1, 1,
+                               batch=n, mode=mode, ctx=ctx)
+    layer.Init(); layer.Forward()
+    want = oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad)
+    assert rel_l2(layer.output_data, want) <= max(tol, 8e-9 * ic * kh * kw)
+    layer.release()
