@@ -963,8 +963,10 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
     if (c->mode == FC_MATH_FP32_MIRRORED) {
         if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
-        if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its five block shapes
+        if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its eight block shapes
             const int small_tiles[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};
+            for (auto &t : ffma_tiles)
+                if (t[0] * t[1] > 64 * 64) push(t[0], t[1], 1, 0);
             for (auto &t : small_tiles) push(t[0], t[1], 1, 0);
         }
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) igemm_ffma_kernel(const float *__rest
 // divisions per gathered element.  This kernel takes the decode from a per-layer table (one int2 per k:
 // element offset inside the image and (u,v)), brings both operands to shared memory with asynchronous
 // copies through a ring of 3 to 8 stages (weights as 16-byte pieces along k, gathered input as 4-byte pieces with
-// zero fill for the padding), and comes in block shapes from 64x64 down to 8x32 so that even a 49-pixel
+// zero fill for the padding), and comes in block shapes from 128x128 down to 8x32 so that even a 49-pixel
 // layer spreads over the machine.  Lanes run along output channels, so a thread reads four k-steps of
 // its weight rows in one conflict-free 128-bit read and its pixels as a broadcast.  The chain per output
 // element is unchanged: one accumulator, one FMA per k, ascending.
@@ -217,13 +217,16 @@ __device__ __forceinline__ void cp_async_zfill_4(void *smem_dst, const void *gme
 // TK_STAGES: depth of the ring.  Small blocks do little math per stage, so they need a deeper ring to keep the
 // two dependent global accesses of the gather (decode table, then the element) off the critical path.
 template <int BM, int BN, int TM, int TN, int TK_STAGES>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), TK_STAGES * (BM * 36 + 32 * (BN + 4)) * 4 > 113 * 1024 ? 1 : 2)
     igemm_ffma_tile_kernel(const float *__restrict__ in, const float *__restrict__ A, float *__restrict__ out,
                            const int2 *__restrict__ ktab, IgemmParams P, int a_vec, Epilogue ep,
                            const float *__restrict__ bmat, int ld) {
     constexpr int OCL = BM / TM, NT = OCL * (BN / TN), BNP = BN + 4;
     constexpr int B_STEP = NT / BN, B_ITERS = TK_KC / B_STEP;
-    static_assert(NT % BN == 0 && TK_KC % B_STEP == 0 && (TN == 1 || TN == 2 || TN == 4), "block shape");
+    static_assert(NT % BN == 0 && TK_KC % B_STEP == 0 && (TN == 1 || TN == 2 || TN == 4 || TN == 8), "block shape");
+    // a thread of a large block gathers many elements per slab; holding their decode entries one slab ahead would
+    // cost two registers each, and such a block has the math to cover the table read instead
+    constexpr bool DEC_AHEAD = B_ITERS <= 8;
     extern __shared__ __align__(16) float tk_smem[];
     float(*As)[BM][TK_KCP] = reinterpret_cast<float(*)[BM][TK_KCP]>(tk_smem);
     float(*Bs)[TK_KC][BNP] = reinterpret_cast<float(*)[TK_KC][BNP]>(tk_smem + TK_STAGES * BM * TK_KCP);
@@ -249,9 +252,9 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     // The decode entries of the NEXT slab are fetched while the copies of this one are issued, so the table read
     // (a global load) is never waited for on the way to the copy that depends on it.
     const int k_padded = ((P.K + TK_KC - 1) / TK_KC) * TK_KC;  // entries in the table
-    int2 dec[B_ITERS];
+    int2 dec[DEC_AHEAD ? B_ITERS : 1];
     auto fetch_decode = [&](int k0) {
-        if (bmat != nullptr) return;  // the gathered matrix was materialised: no decode needed
+        if (!DEC_AHEAD || bmat != nullptr) return;  // (the gathered matrix was materialised: no decode needed)
 #pragma unroll
         for (int r = 0; r < B_ITERS; ++r) {
             const int k = k0 + lk0 + r * B_STEP;
@@ -285,7 +288,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
 #pragma unroll
         for (int r = 0; r < B_ITERS; ++r) {
             const int kk = lk0 + r * B_STEP;
-            const int2 e = dec[r];  // the table is padded to a multiple of 32 with out-of-image entries
+            // the table is padded to a multiple of 32 with out-of-image entries
+            const int2 e = DEC_AHEAD ? dec[DEC_AHEAD ? r : 0] : __ldg(ktab + k0 + kk);
             const int row = base_row + (e.y >> 16), col = base_col + (e.y & 0xffff);
             const bool ok = gpix_ok && (unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw;
             cp_async_zfill_4(&Bs[st][kk][lp], ok ? pix_ptr + e.x : in, ok);
@@ -329,7 +333,11 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
                 const float *bp = &Bs[st][k4 * 4 + kk][pxl * TN];
-                if constexpr (TN == 4) {
+                if constexpr (TN == 8) {
+                    const float4 t = *reinterpret_cast<const float4 *>(bp), w = *reinterpret_cast<const float4 *>(bp + 4);
+                    b[kk][0] = t.x; b[kk][1] = t.y; b[kk][2] = t.z; b[kk][3] = t.w;
+                    b[kk][4] = w.x; b[kk][5] = w.y; b[kk][6] = w.z; b[kk][7] = w.w;
+                } else if constexpr (TN == 4) {
                     const float4 t = *reinterpret_cast<const float4 *>(bp);
                     b[kk][0] = t.x; b[kk][1] = t.y; b[kk][2] = t.z; b[kk][3] = t.w;
                 } else if constexpr (TN == 2) {
@@ -362,6 +370,29 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), 2)
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
+    if constexpr (TN >= 4) {
+        // four consecutive pixels from a multiple of four lie in one image and on a 16-byte boundary when the
+        // plane size is a multiple of four: one 128-bit store per channel instead of four scattered words
+        if (ohw % 4 == 0 && P.out_img_stride % 4 == 0) {
+#pragma unroll
+            for (int q = 0; q < TN / 4; ++q) {
+                const int pix = pix0 + pxl * TN + q * 4;
+                if (pix >= P.npix) continue;  // npix is a multiple of four here, so a started group is complete
+                const int img = pix / ohw, rem = pix - img * ohw;
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const int r = oc0 + ox + OCL * i;
+                    if (r >= P.oc) continue;
+                    float4 v;
+                    unpack2(acc2[i][q * 2], v.x, v.y);
+                    unpack2(acc2[i][q * 2 + 1], v.z, v.w);
+                    v.x = ep(v.x, r); v.y = ep(v.y, r); v.z = ep(v.z, r); v.w = ep(v.w, r);
+                    *reinterpret_cast<float4 *>(out + (size_t)img * P.out_img_stride + (size_t)r * ohw + rem) = v;
+                }
+            }
+            return;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
         const int pix = pix0 + pxl * TN + j;
@@ -516,12 +547,14 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
     const int pick = cfg ? cfg->skinny : 0;
     const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
     const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;
-    const size_t blocked_ctas = ceil_div(P.npix, wide_n ? 128 : 64) * ceil_div(d.oc, wide_m ? 128 : 64);
-    // skinny = 1: the table-driven kernel in the block shape bm x bn (or the heuristic's), 2: the 16x16-thread kernel;
-    // otherwise the latter only when its grid gives the machine three CTAs per SM
-    if (d_ktab && (pick == 1 || (pick == 0 && blocked_ctas < 3 * (size_t)sms))) {
+    // skinny = 2 asks for the 16x16-thread kernel; otherwise the table-driven kernel, in the block shape bm x bn when
+    // skinny = 1 names one, else in the heuristic's
+    if (d_ktab && pick != 2) {
         const int2 *tab = reinterpret_cast<const int2 *>(d_ktab);
         const int shapes[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};
+        // 8x8 and 8x4 outputs per thread, two CTAs per SM: a third to a half fewer shared-memory reads per FMA
+        // than 64x64, once the grid fills every CTA slot of the machine and the channel blocks are not mostly padding
+        const int large[3][2] = {{128, 128}, {128, 64}, {64, 128}};
         int bm = 0, bn = 0;
         if (pick == 1 && cfg->bm && cfg->bn) {
             bm = cfg->bm; bn = cfg->bn;
@@ -530,7 +563,11 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
             // Tuning() consistently preferred ~100-130 CTAs of a larger block (fewer gather instructions per FMA,
             // fewer re-reads of the weights) over 200-400 CTAs of the smallest one
             size_t best = 0;
-            for (const auto &sh : shapes) {
+            for (const auto &sh : large) {
+                const size_t rows = ceil_div(d.oc, sh[0]), ctas = ceil_div(P.npix, sh[1]) * rows;
+                if (ctas >= 2 * (size_t)sms && 4 * (size_t)d.oc >= 3 * rows * sh[0]) { bm = sh[0]; bn = sh[1]; break; }
+            }
+            if (bm == 0) for (const auto &sh : shapes) {
                 const size_t ctas = ceil_div(P.npix, sh[1]) * ceil_div(d.oc, sh[0]);
                 if (20 * ctas >= 13 * (size_t)sms) { bm = sh[0]; bn = sh[1]; break; }
                 if (ctas > best) { best = ctas; bm = sh[0]; bn = sh[1]; }
@@ -546,6 +583,9 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
             FC_CHECK_CUDA(cudaGetLastError());
             bmat = d_bmat;
         }
+        if (bm == 128 && bn == 128) return launch_tile<128, 128, 8, 8, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 128 && bn == 64) return launch_tile<128, 64, 8, 4, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
+        if (bm == 64 && bn == 128) return launch_tile<64, 128, 4, 8, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
         if (bm == 64 && bn == 64) return launch_tile<64, 64, 4, 4, 3>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
         if (bm == 32 && bn == 64) return launch_tile<32, 64, 2, 4, 4>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);
         if (bm == 32 && bn == 32) return launch_tile<32, 32, 2, 2, 6>(ctx, d_in, d_kernel, d_out, tab, P, ep, bmat, ld);

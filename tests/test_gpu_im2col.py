@@ -156,6 +156,26 @@ def test_random_cases_mirrored_gemm_bit_exact(ctx, oracle, case):
     layer.release()
 
 
+# enough pixels x channels for the 128x128, 128x64 and 64x128 block shapes: whole blocks, a ragged channel block, a
+# ragged pixel block, an odd plane size (which takes the scalar stores instead of the 128-bit ones), 64 channels
+# (64x128) and a grid that only fills the machine in 128x64 blocks
+LARGE_CASES = [(16, 64, 128, 56, 56, 1, 1, 1, 1, 0), (8, 32, 200, 112, 112, 3, 3, 2, 2, 1),
+               (10, 24, 128, 63, 63, 1, 1, 1, 1, 0), (5, 16, 250, 100, 100, 3, 3, 1, 1, 1),
+               (4, 3, 64, 224, 224, 7, 7, 2, 2, 3), (4, 32, 256, 56, 56, 3, 3, 1, 1, 1)]
+
+
+@pytest.mark.parametrize("case", LARGE_CASES)
+def test_large_problems_mirrored_gemm_bit_exact(ctx, oracle, case):
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 19)
+    w = synth.conv_weights(oc, ic, kh, kw, 20)
+    layer = fc.ConvIm2colLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, sh, sw, pad, pad, pad, pad, 1, False, 1, 1,
+                               batch=n, ctx=ctx)
+    layer.Init(); layer.Forward()
+    assert np.array_equal(layer.output_data, oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad))
+    layer.release()
+
+
 @pytest.mark.parametrize("mode,tol", [("3xtf32", 1e-5), ("tf32", 3e-3)])
 @pytest.mark.parametrize("case", _random_cases(78, 10))
 def test_random_cases_tensor_core_modes(ctx, oracle, case, mode, tol):
