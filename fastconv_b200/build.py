@@ -23,6 +23,7 @@ SOURCES = [
     "fc_igemm_ffma.cu",
     "fc_gemm_tc.cu",
     "fc_igemm_tc.cu",
+    "fc_direct_tc.cu",
     "fc_static_scratch.cu",
     "fc_peer.cu",
 ]

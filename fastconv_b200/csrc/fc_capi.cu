@@ -100,6 +100,8 @@ struct fc_conv {
     float *d_packed;  // tensor-core implicit GEMM: padded hi/lo planes of the weights
     float *d_ktab;    // fp32 implicit GEMM: int pairs (offset, u:v) per k, in a float-typed arena slot
     float *d_bmat;    // fp32 implicit GEMM of a few-pixel, long-reduction layer: the materialised gathered matrix
+    float *d_nhwc;    // direct tensor-core path: the input of one forward as [n][h][w][channels padded to 32]
+    float *d_wp;      // direct tensor-core path: weights as [tap][oc][channels padded to 32]
     float *d_bias;    // per-channel bias of the epilogue, or NULL
     int relu;         // epilogue: clamp at zero after the bias
     float *d_U, *d_V, *d_M;
@@ -525,7 +527,8 @@ int fc_igemm_forward(fc_context *ctx, const float *d_in, const float *d_kernel, 
 
 static void conv_release(fc_conv *c) {
     fc_context *ctx = c->ctx;
-    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_bmat, c->d_bias, c->d_U, c->d_V, c->d_M, c->d_in, c->d_out};
+    float *bufs[] = {c->d_kernel, c->d_packed, c->d_ktab, c->d_bmat, c->d_nhwc, c->d_wp, c->d_bias, c->d_U, c->d_V, c->d_M,
+                     c->d_in, c->d_out};
     for (float *b : bufs)
         if (b) ctx->arena.release((uintptr_t)b);
     delete c;
@@ -617,6 +620,16 @@ static int conv_prepare(fc_conv *c, int algo) {
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
         }
+    } else if (algo == FC_ALGO_DIRECT) {
+        const bool fresh = c->d_wp == nullptr;
+        st = grab(ctx, &c->d_wp, direct_packed_elems(d));
+        if (st == FC_OK) st = grab(ctx, &c->d_nhwc, direct_nhwc_elems(d));
+        if (st == FC_OK && fresh) {
+            cudaEventRecord(ctx->ev[0], ctx->stream);
+            st = launch_direct_pack_weights(ctx, c->d_kernel, c->d_wp, d);
+            cudaEventRecord(ctx->ev[1], ctx->stream);
+            timed = true;
+        }
     } else if (d.group > 1 && d.group == d.ic) {
         // depthwise: one plain fp32 kernel over the raw weights in every mode, nothing to prepare
     } else if (c->mode != FC_MATH_FP32_MIRRORED) {
@@ -633,7 +646,8 @@ static int conv_prepare(fc_conv *c, int algo) {
             timed = true;
         }
     }
-    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_ktab == nullptr && !(d.group > 1 && d.group == d.ic)) {
+    const bool gathers = algo == FC_ALGO_IM2COL;  // the implicit GEMMs; Winograd and the direct path index nothing
+    if (st == FC_OK && gathers && c->d_ktab == nullptr && !(d.group > 1 && d.group == d.ic)) {
         // every implicit GEMM reads the k decode table
         FC_REQUIRE((long long)d.ic * d.ih * d.iw < (1ll << 31) && d.kh < 0x4000 && d.kw < 0x4000, FC_ERR_UNSUPPORTED,
                    "image or kernel too large for the 32-bit decode table");
@@ -651,7 +665,7 @@ static int conv_prepare(fc_conv *c, int algo) {
             }
         }
     }
-    if (st == FC_OK && algo != FC_ALGO_WINOGRAD && c->d_bmat == nullptr && igemm_wants_matrix(d, c->oh, c->ow))
+    if (st == FC_OK && gathers && c->d_bmat == nullptr && igemm_wants_matrix(d, c->oh, c->ow))
         st = grab(ctx, &c->d_bmat, (size_t)d.ic * d.kh * d.kw * igemm_matrix_ld(d, c->oh, c->ow));
     if (st != FC_OK) return st;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
@@ -674,7 +688,9 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
     const bool auto_requested = algo == FC_ALGO_AUTO;
     if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
-    if (algo == FC_ALGO_DIRECT) algo = FC_ALGO_IM2COL;
+    // the direct tensor-core kernel is a TF32 kernel for stride-1, ungrouped layers; anything else asked for as
+    // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
+    if (algo == FC_ALGO_DIRECT && !(mode == FC_MATH_TF32 && direct_tc_eligible(*desc))) algo = FC_ALGO_IM2COL;
     int auto_pick = FC_ALGO_IM2COL;
     fc_select_algorithm(desc, &auto_pick);
     const bool wino_eligible = auto_pick == FC_ALGO_WINOGRAD;
@@ -780,6 +796,15 @@ static int conv_enqueue(fc_conv *c, const float *d_in, float *d_out, bool timed)
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));  // the gather is fused: no separate stage
     int st = FC_OK;
     const fc_conv_desc &full = c->desc;
+    if (c->algo == FC_ALGO_DIRECT) {
+        FC_PROPAGATE(launch_direct_tc(ctx, d_in, c->d_nhwc, c->d_wp, d_out, full, c->oh, c->ow, &c->cfg,
+                                      Epilogue{c->d_bias, c->relu}));
+        if (timed) {
+            FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+            FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+        }
+        return FC_OK;
+    }
     if (full.group > 1 && full.group == full.ic) {  // depthwise: every output channel reads one input channel
         st = launch_depthwise(ctx, d_in, c->d_kernel, d_out, full, c->oh, c->ow, Epilogue{c->d_bias, c->relu});
     } else {
@@ -953,6 +978,10 @@ static int time_current(fc_conv *c, int iters, float *ms) {
     return FC_OK;
 }
 
+static const char *algo_label(int algo) {
+    return algo == FC_ALGO_WINOGRAD ? "winograd" : algo == FC_ALGO_DIRECT ? "direct" : "im2col";
+}
+
 static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCandidate> *out) {
     auto push = [&](int bm, int bn, int skinny, int smem_kb) {
         TuneCandidate t;
@@ -961,6 +990,12 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
         out->push_back(t);
     };
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
+    if (algo == FC_ALGO_DIRECT) {  // the ring's size decides between one and two CTAs per SM
+        push(0, 0, 0, 0);
+        push(0, 0, 0, 104);
+        push(0, 0, 0, 200);
+        return;
+    }
     if (c->mode == FC_MATH_FP32_MIRRORED) {
         if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
         if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its eight block shapes
@@ -1056,6 +1091,9 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
         const int other = c->algo == FC_ALGO_WINOGRAD ? FC_ALGO_IM2COL : FC_ALGO_WINOGRAD;
         if (conv_prepare(c, other) == FC_OK) enumerate_candidates(c, other, &cands);
     }
+    if (c->auto_requested && c->mode == FC_MATH_TF32 && direct_tc_eligible(c->desc) && c->algo != FC_ALGO_DIRECT &&
+        conv_prepare(c, FC_ALGO_DIRECT) == FC_OK)
+        enumerate_candidates(c, FC_ALGO_DIRECT, &cands);
     const int start_algo = c->algo;
     const KernelCfg start_cfg = c->cfg;
     TuneCandidate best;
@@ -1076,7 +1114,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
             return st;
         }
         if (verbose)
-            printf("algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", t.algo == FC_ALGO_WINOGRAD ? "winograd" : "im2col",
+            printf("algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", algo_label(t.algo),
                    t.cfg.bm, t.cfg.bn, t.cfg.skinny, t.cfg.smem_kb, ms);
         if (ms < best_ms) {
             best_ms = ms;
@@ -1085,15 +1123,13 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
     }
     c->algo = best.algo;
     c->cfg = best.cfg;
-    if (best.algo != FC_ALGO_WINOGRAD) {  // the loser's workspaces go back to the arena
-        drop(ctx, &c->d_U); drop(ctx, &c->d_V); drop(ctx, &c->d_M);
-    } else {
-        drop(ctx, &c->d_packed);
-        drop(ctx, &c->d_ktab);
-    }
+    // the losers' workspaces go back to the arena
+    if (best.algo != FC_ALGO_WINOGRAD) { drop(ctx, &c->d_U); drop(ctx, &c->d_V); drop(ctx, &c->d_M); }
+    if (best.algo != FC_ALGO_IM2COL) { drop(ctx, &c->d_packed); drop(ctx, &c->d_ktab); drop(ctx, &c->d_bmat); }
+    if (best.algo != FC_ALGO_DIRECT) { drop(ctx, &c->d_nhwc); drop(ctx, &c->d_wp); }
     if (verbose)
         printf("Best Config: (%d %d %d) algo=%s bm=%d bn=%d skinny=%d smem=%dKB time=%.3f\n", c->desc.ic, c->desc.oc,
-               c->desc.iw, best.algo == FC_ALGO_WINOGRAD ? "winograd" : "im2col", best.cfg.bm, best.cfg.bn,
+               c->desc.iw, algo_label(best.algo), best.cfg.bm, best.cfg.bn,
                best.cfg.skinny, best.cfg.smem_kb, best_ms);
     if (best_ms < 1e29f) tuning_log_append(c, best, best_ms * 1e3f);
     return FC_OK;
@@ -1101,7 +1137,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : igemm_launches(c);
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : c->algo == FC_ALGO_DIRECT ? 2 : igemm_launches(c);
     return FC_OK;
 }
 
@@ -1127,7 +1163,8 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     for (int i = 0; i < count; ++i) {
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
-        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i]) : igemm_launches(convs[i]);
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i])
+                    : convs[i]->algo == FC_ALGO_DIRECT ? 2 : igemm_launches(convs[i]);
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     // one eager pass first: kernel attributes are set and any error shows up outside the capture

@@ -1,0 +1,341 @@
+// Direct convolution on the 5th-generation tensor cores for stride-1 layers (`-a direct`; the reference parses
+// the name but its case is empty, ConvTest.cpp:369-371).
+//
+//   out[n][oc][y][x] = sum_{u,v} sum_c  W[oc][c][u][v] * in[n][c][y + u - pad_t][x + v - pad_l]
+//
+// is kh*kw GEMMs that accumulate into ONE accumulator: for every (u,v) the second operand is the input shifted
+// by (u,v).  With the input in NHWC (channels innermost, padded to a multiple of 32) a shifted patch of
+// bh x bw pixels x 32 channels is one 4-D TMA box whose innermost coordinate is the channel block -- always 16-byte
+// aligned, whatever the shift -- and whose rows (one pixel = 128 bytes) land in shared memory exactly as a K-major,
+// 128-byte-swizzled UMMA operand of 128 rows.  Pixels outside the image are the box's out-of-range elements and read as
+// zero: the padding costs nothing and no im2col index is ever computed.  The weights, re-laid out once as
+// Wp[u*kw+v][oc][c], are the other K-major operand.
+//
+//   nchw_to_nhwc_kernel     one pass over the input per forward (the layer keeps the reference's NCHW at its boundary)
+//   direct_tc_kernel        persistent; a work item = one patch of 128 output pixels x a block of <= 128 channels
+//     warp 0      TMA producer: per k-block (u,v, 32 channels) one 4-D box of the input and one 3-D box of Wp
+//     warp 1      tcgen05.mma kind::tf32, M = 128 pixels, N = channel block, two TMEM accumulators
+//     warps 2..5  epilogue: tcgen05.ld (lane = pixel), bias/ReLU, NCHW stores (a warp writes runs of bw pixels)
+//
+// There is no Winograd transform in the way, so single-pass TF32 keeps its plain accuracy (rel-L2 ~3e-4 against
+// 6.4e-3 through F(6x6,3x3)).  Every mbarrier wait is bounded as in the other tensor-core kernels.
+#include "fc_tc_common.cuh"
+
+namespace fc {
+
+namespace {
+
+using namespace tc;
+
+struct DirectParams {
+    float *out;
+    int *status;
+    Epilogue ep;
+    int oc, oh, ow;
+    int bh, bw, n_px, n_py;  // patch shape (bh * bw = 128) and patches per image along x and y
+    int bn, n_oc_items;      // channel block (multiple of 16, <= 128) and blocks per layer
+    int num_kb, taps, kw;    // 32-channel blocks per tap, kh*kw, kw
+    int pad_t, pad_l;
+    int stages, acc_cols, n_items;
+    int b_bytes;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// channel block fastest: CTAs next to each other read the same input patch
+__device__ __forceinline__ void item_coords(const DirectParams &P, int item, int &img, int &y0, int &x0, int &oc0) {
+    oc0 = (item % P.n_oc_items) * P.bn;
+    int patch = item / P.n_oc_items;
+    x0 = (patch % P.n_px) * P.bw;
+    patch /= P.n_px;
+    y0 = (patch % P.n_py) * P.bh;
+    img = patch / P.n_py;
+}
+
+__global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_constant__ CUtensorMap tmX,
+                                                              const __grid_constant__ CUtensorMap tmW,
+                                                              const DirectParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[8] empty[8] acc_full[2] acc_empty[2]
+    const int S = P.stages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t ring = (smem_u32(smem_raw) + 512 + 1023) & ~1023u;
+    const uint32_t stage_bytes = A_BYTES + (uint32_t)P.b_bytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    auto bar_full = [&](int s) { return smem_u32(bars + s); };
+    auto bar_empty = [&](int s) { return smem_u32(bars + 8 + s); };
+    auto bar_acc_full = [&](int a) { return smem_u32(bars + 16 + a); };
+    auto bar_acc_empty = [&](int a) { return smem_u32(bars + 18 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_acc_full(a), 1);
+            mbar_init(bar_acc_empty(a), 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)(2 * P.acc_cols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
+
+    const int kb_per_item = P.taps * P.num_kb;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            pdl_wait();  // the NHWC copy of the input is written by the kernel launched just before
+            int g = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+                int img, y0, x0, oc0;
+                item_coords(P, item, img, y0, x0, oc0);
+                for (int tap = 0; tap < P.taps && ok; ++tap) {
+                    const int u = tap / P.kw, v = tap - u * P.kw;
+                    for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
+                        const int s = g % S;
+                        const uint32_t ph = (uint32_t)(g / S) & 1u;
+                        ok = mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status);
+                        if (!ok) break;
+                        const uint32_t dst = ring + s * stage_bytes;
+                        mbar_expect_tx(bar_full(s), stage_bytes);
+                        // innermost coordinate = channel block (a multiple of 32 floats); x and y may be negative or
+                        // past the image: those pixels read as zero
+                        tma_load_4d(dst, &tmX, bar_full(s), kb * BK, x0 + v - P.pad_l, y0 + u - P.pad_t, img);
+                        tma_load_3d(dst + A_BYTES, &tmW, bar_full(s), kb * BK, oc0, tap);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_tf32(BM, P.bn);
+            int g = 0, it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                ok = mbar_wait(bar_acc_empty(acc), acc_ph ^ 1u, abort_flag, P.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.acc_cols);
+                for (int kb = 0; kb < kb_per_item; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(bar_full(s), ph, abort_flag, P.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a = ring + s * stage_bytes, b = a + A_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < BK / 8; ++ks) {
+                        const uint32_t koff = ks * 32;  // 8 tf32 = 32 bytes further along K inside the swizzle span
+                        tc_mma_tf32(d_tmem, umma_desc_k_sw128(a + koff), umma_desc_k_sw128(b + koff), idesc,
+                                    (kb == 0 && ks == 0) ? 0u : 1u);
+                    }
+                    tc_commit(bar_empty(s));
+                }
+                if (ok) tc_commit(bar_acc_full(acc));
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane, py = r / P.bw, px = r - py * P.bw;
+        int it = 0;
+        bool ok = true, waited = false;
+        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+            int img, y0, x0, oc0;
+            item_coords(P, item, img, y0, x0, oc0);
+            if (!waited) {  // the output may still be read by whatever consumed the forward before this one
+                pdl_wait();
+                waited = true;
+            }
+            const int acc = it & 1;
+            const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+            ok = mbar_wait(bar_acc_full(acc), acc_ph, abort_flag, P.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * P.acc_cols);
+            const int y = y0 + py, x = x0 + px;
+            const bool inside = y < P.oh && x < P.ow;
+            const size_t plane = (size_t)P.oh * P.ow;
+            float *dst = P.out + ((size_t)img * P.oc + oc0) * plane + (size_t)y * P.ow + x;
+            for (int c0 = 0; c0 < P.bn; c0 += 16) {
+                float va[16];
+                tc_ld16(t_addr + (uint32_t)c0, va);
+                if (c0 + 16 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
+                    tc_fence_before();
+                    mbar_arrive(bar_acc_empty(acc));
+                }
+                if (inside) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (oc0 + c0 + j < P.oc) dst[(size_t)(c0 + j) * plane] = P.ep(va[j], oc0 + c0 + j);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before the CTA's shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)(2 * P.acc_cols))
+                     : "memory");
+    }
+}
+
+// in[n][C][HW] -> out[n][HW][Cp], channels C..Cp-1 written as zeros.  32 x 32 tiles through shared memory: reads run
+// along HW, writes along the channels, both as whole 128-byte lines.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restrict__ in, float *__restrict__ out, int C,
+                                                          int Cp, int HW) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const size_t img = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();  // the input may be the previous layer's output; the NHWC buffer may still be read by an earlier forward
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, p = p0 + tx;
+        tile[ty + 8 * i][tx] = (c < C && p < HW) ? __ldg(in + (img * C + c) * HW + p) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = p0 + ty + 8 * i;
+        if (p < HW) out[(img * HW + p) * Cp + c0 + tx] = tile[tx][ty + 8 * i];
+    }
+}
+
+// W[oc][ic][kh][kw] -> Wp[tap = u*kw + v][oc][icp], channels ic..icp-1 zero
+__global__ void direct_pack_weights_kernel(const float *__restrict__ w, float *__restrict__ wp, int oc, int ic, int icp,
+                                           int taps) {
+    const size_t total = (size_t)taps * oc * icp;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % icp);
+        const size_t rest = idx / icp;
+        const int o = (int)(rest % oc), tap = (int)(rest / oc);
+        wp[idx] = c < ic ? __ldg(w + ((size_t)o * ic + c) * taps + tap) : 0.0f;
+    }
+}
+
+// NHWC input as a 4-D tensor (channel, x, y, image), box = 32 channels x bw x bh x 1, 128-byte swizzle, zero fill
+int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, int n, int bw, int bh) {
+    EncodeTiledFn enc;
+    FC_PROPAGATE(get_encoder(&enc));
+    cuuint64_t dims[4] = {(cuuint64_t)icp, (cuuint64_t)iw, (cuuint64_t)ih, (cuuint64_t)n};
+    cuuint64_t strides[3] = {(cuuint64_t)icp * 4, (cuuint64_t)icp * iw * 4, (cuuint64_t)icp * iw * ih * 4};
+    cuuint32_t box[4] = {BK, (cuuint32_t)bw, (cuuint32_t)bh, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (icp %d iw %d ih %d n %d box %dx%d)",
+               (int)r, icp, iw, ih, n, bw, bh);
+    return FC_OK;
+}
+
+}  // namespace
+
+bool direct_tc_eligible(const fc_conv_desc &d) {
+    return d.sh == 1 && d.sw == 1 && d.group == 1 && d.iw <= (1 << 20) && d.ih <= (1 << 20);
+}
+
+size_t direct_nhwc_elems(const fc_conv_desc &d) { return (size_t)d.batch * d.ih * d.iw * round_up(d.ic, BK); }
+
+size_t direct_packed_elems(const fc_conv_desc &d) { return (size_t)d.kh * d.kw * d.oc * round_up(d.ic, BK); }
+
+int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_wp, const fc_conv_desc &d) {
+    const int icp = round_up(d.ic, BK);
+    const size_t total = direct_packed_elems(d);
+    const unsigned blocks = (unsigned)(ceil_div(total, 256) > 4096 ? 4096 : ceil_div(total, 256));
+    direct_pack_weights_kernel<<<blocks, 256, 0, ctx->stream>>>(d_kernel, d_wp, d.oc, d.ic, icp, d.kh * d.kw);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const float *d_wp, float *d_out,
+                     const fc_conv_desc &d, int oh, int ow, const KernelCfg *cfg, const Epilogue &ep) {
+    FC_REQUIRE(direct_tc_eligible(d), FC_ERR_UNSUPPORTED, "the direct tensor-core path takes stride-1, ungrouped layers");
+    FC_REQUIRE(ctx->d_status != nullptr, FC_ERR_INVALID_ARG, "the tensor-core kernels need a context with a status word");
+    const int icp = round_up(d.ic, BK), hw = d.ih * d.iw;
+    {
+        dim3 grid((unsigned)ceil_div(hw, 32), (unsigned)(icp / 32), (unsigned)d.batch), block(256);
+        FC_CHECK_CUDA(launch_pdl(nchw_to_nhwc_kernel, grid, block, 0, ctx->stream, d_in, d_nhwc, d.ic, icp, hw));
+    }
+    // patch of 128 output pixels: the shape that wastes the fewest pixels, the widest one among equals (longer runs
+    // in the output rows)
+    const int shapes[6][2] = {{1, 128}, {2, 64}, {4, 32}, {8, 16}, {16, 8}, {32, 4}};
+    int bh = 8, bw = 16;
+    size_t best = ~(size_t)0;
+    for (const auto &s : shapes) {
+        const size_t covered = (size_t)round_up(oh, s[0]) * round_up(ow, s[1]);
+        if (covered < best) { best = covered; bh = s[0]; bw = s[1]; }
+    }
+    DirectParams P;
+    P.out = d_out;
+    P.status = ctx->d_status;
+    P.ep = ep;
+    P.oc = d.oc; P.oh = oh; P.ow = ow;
+    P.bh = bh; P.bw = bw;
+    P.n_px = ceil_div(ow, bw);
+    P.n_py = ceil_div(oh, bh);
+    P.n_oc_items = ceil_div(d.oc, 128);
+    P.bn = round_up(ceil_div(d.oc, P.n_oc_items), 16);  // balanced blocks of channels
+    P.num_kb = icp / BK;
+    P.taps = d.kh * d.kw;
+    P.kw = d.kw;
+    P.pad_t = d.pad_top; P.pad_l = d.pad_left;
+    P.acc_cols = pow2_at_least(P.bn, 32);
+    P.b_bytes = P.bn * BK * 4;
+    const long long items = (long long)P.n_px * P.n_py * d.batch * P.n_oc_items;
+    FC_REQUIRE(items < (1ll << 31), FC_ERR_UNSUPPORTED, "too many work items");
+    P.n_items = (int)items;
+    const size_t stage_bytes = (size_t)A_BYTES + P.b_bytes;
+    const bool two_per_sm = P.n_items > ctx->sm_count && 2 * P.acc_cols <= 256;
+    const size_t budget = cfg && cfg->smem_kb ? (size_t)cfg->smem_kb * 1024 : (two_per_sm ? 104 * 1024 : 200 * 1024);
+    int stages = (int)(budget / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) stages = 2;
+    P.stages = stages;
+    const size_t smem = 512 + 1024 + stages * stage_bytes;
+    const int per_sm = (2 * P.acc_cols > 256 || smem > 113 * 1024) ? 1 : 2;
+    int ctas = ctx->sm_count * per_sm;
+    if (ctas > P.n_items) ctas = P.n_items;
+
+    CUtensorMap tmX, tmW;
+    FC_PROPAGATE(make_map_nhwc(&tmX, d_nhwc, icp, d.iw, d.ih, d.batch, bw, bh));
+    FC_PROPAGATE(make_map_3d(&tmW, d_wp, icp, d.oc, P.taps, P.bn));
+    FC_CHECK_CUDA(cudaFuncSetAttribute(direct_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FC_CHECK_CUDA(launch_pdl(direct_tc_kernel, dim3((unsigned)ctas), dim3(TC_THREADS), smem, ctx->stream, tmX, tmW, P));
+    return FC_OK;
+}
+
+}  // namespace fc

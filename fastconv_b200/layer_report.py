@@ -1,16 +1,16 @@
 """Per-layer report over the benchmark configurations: VGG-16, ResNet-50 v1.5 and the wide single-image sweep.
 
     python -m fastconv_b200.layer_report --set resnet50 --mode fp32 [--batch N] [--tune] [--iters 50] [--only I]
+                                         [--algo auto|winograd|im2col|direct]
 
-Every layer is planned with `-a auto` (select_algorithm of ConvTest.cpp:318-331, 1x1 stride 1 routed to the
-implicit GEMM), run `iters` times back to back on device-resident data and timed with CUDA events; one
+Every layer is planned with `-a auto` unless --algo says otherwise (select_algorithm of ConvTest.cpp:318-331,
+1x1 stride 1 routed to the implicit GEMM), run `iters` times back to back on device-resident data and timed with CUDA events; one
 JSON line per layer carries the algorithm, milliseconds, direct-equivalent GFLOP/s and the fraction of
 the layer's roofline  max(flops / peak, bytes / HBM bandwidth)  with
     Winograd:  flops = 2*64*T*C*K,  bytes = 4*(N*C*H*W + 64*C*K + N*K*OH*OW)
     im2col:    flops = 2*N*K*C*R*S*OH*OW,  bytes = 4*(N*C*H*W + K*C*R*S + N*K*OH*OW)
-Peaks: HBM from MEASURED_PEAKS.json (copy bandwidth), FP32 FFMA = SMs*128*2*max clock for the fp32 mode,
-half the measured bf16 GEMM rate for TF32 and a third of that for 3xTF32 (placeholders until a TF32 GEMM peak
-is measured on the pool).
+Peaks: HBM from MEASURED_PEAKS.json (copy bandwidth); FP32 63.7 and TF32 759.9 TFLOP/s measured with an
+8192^3 library GEMM on a B200, 3xTF32 a third of the TF32 figure.
 """
 from __future__ import annotations
 
@@ -63,6 +63,8 @@ def main() -> None:
     ap.add_argument("--tune", action="store_true", help="run Tuning() (timed configuration search) before measuring")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--only", type=int, default=None, help="index of the one layer of the set to run")
+    ap.add_argument("--algo", default="auto", choices=["auto", "winograd", "im2col", "direct"],
+                    help="-a of ConvTest: force one path for every layer that it can run")
     args = ap.parse_args()
 
     lib = _lib.load()
@@ -77,7 +79,8 @@ def main() -> None:
             w = synth.conv_weights(oc, ic, k, k, 2000 + idx)
             x = synth.conv_input(n, ic, hw, hw, 1000 + idx)
             h = C.c_void_p()
-            _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_AUTO, _lib.MODE_NAMES[args.mode],
+            want = _lib.ALGO_NAMES[args.algo]
+            _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), want, _lib.MODE_NAMES[args.mode],
                                           C.c_void_p(w.ctypes.data), C.byref(h)), "fc_conv_create")
             if args.tune:
                 _lib.check(lib.fc_conv_tune(h, 10, 0), "fc_conv_tune")
@@ -98,7 +101,7 @@ def main() -> None:
             roof_ms = max(flops / (peak_tf * 1e12), nbytes / (hbm * 1e9)) * 1e3
             print(json.dumps({
                 "layer": f"{ic}->{oc}@{hw} {k}x{k}s{s}", "batch": n, "mode": args.mode,
-                "algo": "winograd" if algo.value == _lib.ALGO_WINOGRAD else "im2col", "ms": round(ms.value, 5),
+                "algo": {v: k for k, v in _lib.ALGO_NAMES.items()}[algo.value], "ms": round(ms.value, 5),
                 "gflops_direct_equiv": round(direct / ms.value / 1e6, 1), "roofline_ms": round(roof_ms, 5),
                 "frac_of_roofline": round(roof_ms / ms.value, 4),
                 "bound": "hbm" if nbytes / (hbm * 1e9) >= flops / (peak_tf * 1e12) else "math"}), flush=True)

@@ -397,6 +397,39 @@ class ConvIm2colLayer(ConvLayer):
             ctx.free(d_in)
 
 
+class ConvDirectLayer(ConvLayer):
+    """`-a direct`: the reference parses the name but its case is empty (ConvTest.cpp:369-371).  Here it is the direct
+    convolution on the tensor cores: stride-1, ungrouped layers in mode "tf32" (shifted TMA boxes of an NHWC copy of
+    the input, no Winograd transform, so single-pass TF32 keeps its plain accuracy); any other layer or mode runs as
+    the implicit GEMM.  Init() and Forward() return 1 like the im2col layer's."""
+
+    _algo = _lib.ALGO_DIRECT
+
+    def Tuning(self) -> int:
+        self._create()
+        check(self._lib.fc_conv_tune(self._conv, max(1, self.iterations), 1), "fc_conv_tune")
+        return 1
+
+    def Init(self) -> int:
+        print("Algorithm: direct")
+        self._create()
+        return 1
+
+    def Forward(self) -> int:
+        self._forward_iterations([("Gemm time:", 2), ("Total time:", 4)])
+        if self.output_ref is not None:
+            diff(np.asarray(self.output_ref), self.output_data)
+        return 1
+
+    @property
+    def algorithm(self) -> int:
+        """The algorithm the layer actually runs (ALGO_DIRECT or ALGO_IM2COL)."""
+        self._create()
+        a = C.c_int()
+        check(self._lib.fc_conv_algorithm(self._conv, C.byref(a)), "fc_conv_algorithm")
+        return a.value
+
+
 class LayerList:
     """Several initialised layers replayed as one CUDA graph (fc_layer_list): the in-process form of the
     reference's per-network shell loops (run_vgg16.sh:5-13, run_resnet50.sh:10-30)."""
@@ -442,4 +475,6 @@ def make_layer(algorithm: str, *args, **kw) -> ConvLayer:
         algo = select_algorithm(probe.desc)
     if algo == _lib.ALGO_WINOGRAD:
         return ConvWinoF63ZCLayer(*args, **kw)
+    if algo == _lib.ALGO_DIRECT:
+        return ConvDirectLayer(*args, **kw)
     return ConvIm2colLayer(*args, **kw)

@@ -43,7 +43,8 @@ typedef enum fc_status {
 /* Same numbering as nnp_convolution_algorithm, utility/helper.h:94-103. */
 typedef enum fc_algorithm {
     FC_ALGO_AUTO = 0,
-    FC_ALGO_DIRECT = 1, /* routed to the implicit-GEMM kernel (the reference's case is empty, ConvTest.cpp:369-371) */
+    FC_ALGO_DIRECT = 1, /* the reference's case is empty (ConvTest.cpp:369-371); here: direct convolution on the tensor
+                           cores for stride-1 ungrouped layers in FC_MATH_TF32, the implicit-GEMM kernel for anything else */
     FC_ALGO_IM2COL = 2,
     FC_ALGO_WINOGRAD = 3
 } fc_algorithm;

@@ -1,0 +1,105 @@
+"""`-a direct`: direct convolution on the tensor cores (stride 1, TF32) against the oracle's convolution.
+
+The reference has no code behind the name (ConvTest.cpp:369-371), so the expected values are those of its im2col
+layer restated by the oracle (im2colConv.cpp:285-309 + the sequential GEMM).  Tolerance: relative L2 <= 3e-3, the
+figure stated for the TF32 mode; the kernel has no Winograd transform to amplify the operand rounding, so the tests
+also pin the much smaller error it really has (<= 1e-3)."""
+import numpy as np
+import pytest
+
+import fastconv_b200 as fc
+from _oracle import rel_l2
+from fastconv_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+
+CASES = [  # n, ic, oc, ih, iw, kh, kw, pad_l, pad_r, pad_t, pad_b
+    (1, 3, 8, 30, 30, 3, 3, 1, 1, 1, 1),        # 3 channels padded to 32, one ragged patch row
+    (2, 64, 64, 56, 56, 3, 3, 1, 1, 1, 1),      # two images, two 32-channel blocks per tap
+    (1, 70, 130, 14, 14, 3, 3, 1, 1, 1, 1),     # ragged channel blocks on both sides, 14x14 in 8x16 patches
+    (1, 16, 12, 14, 14, 1, 1, 0, 0, 0, 0),      # 1x1: a plain GEMM
+    (1, 4, 4, 9, 11, 5, 3, 1, 1, 2, 2),         # non-square kernel
+    (3, 33, 17, 7, 7, 3, 3, 1, 1, 1, 1),        # 7x7 maps
+    (1, 8, 200, 28, 28, 3, 3, 0, 2, 1, 0),      # four different paddings, two channel blocks of 112
+    (1, 1, 1, 1, 1, 1, 1, 0, 0, 0, 0),          # one pixel
+    (1, 32, 16, 20, 20, 7, 7, 3, 3, 3, 3),      # 49 taps
+    (1, 24, 40, 5, 130, 3, 3, 1, 1, 1, 1),      # a wide, flat image: 1x128 patches
+    (1, 24, 40, 130, 5, 3, 3, 1, 1, 1, 1),      # a tall, narrow one: 32x4 patches
+    (1, 16, 16, 12, 12, 3, 3, 0, 0, 0, 0),      # no padding: the output is smaller than the input
+]
+
+
+def _layer(ctx, x, w, case, mode="tf32"):
+    n, ic, oc, ih, iw, kh, kw, pl, pr, pt, pb = case
+    return fc.ConvDirectLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, 1, 1, pl, pr, pt, pb, 1, False, 1, 1, batch=n,
+                              mode=mode, ctx=ctx)
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_direct_tf32_within_tolerance(ctx, oracle, case):
+    n, ic, oc, ih, iw, kh, kw, pl, pr, pt, pb = case
+    x = synth.conv_input(n, ic, ih, iw, 91)
+    w = synth.conv_weights(oc, ic, kh, kw, 92)
+    layer = _layer(ctx, x, w, case)
+    assert layer.Init() == 1 and layer.Forward() == 1
+    assert layer.algorithm == _lib.ALGO_DIRECT
+    want = oracle.im2col_gemm_forward(x, w, 1, 1, pl, pr, pt, pb)
+    assert layer.output_data.shape == want.shape
+    err = rel_l2(layer.output_data, want)
+    assert err <= 3e-3, err   # the tolerance stated for the TF32 mode
+    assert err <= 1e-3, err   # what single-pass TF32 gives without a Winograd transform in the way
+    assert np.abs(layer.output_data - want).max() <= 3e-2 * np.abs(want).max()
+    layer.Forward()  # a second forward reuses the NHWC buffer
+    assert rel_l2(layer.output_data, want) <= 1e-3
+    layer.release()
+
+
+def test_direct_epilogue_and_repeatability(ctx, oracle):
+    case = (2, 48, 72, 28, 28, 3, 3, 1, 1, 1, 1)
+    n, ic, oc, ih, iw, kh, kw, pl, pr, pt, pb = case
+    x = synth.conv_input(n, ic, ih, iw, 93)
+    w = synth.conv_weights(oc, ic, kh, kw, 94)
+    b = (synth.conv_input(1, 1, 1, oc, 95).reshape(oc) * np.float32(0.5)).astype(np.float32)
+    layer = _layer(ctx, x, w, case)
+    layer.set_epilogue(b, True)
+    layer.Init(); layer.Forward()
+    first = layer.output_data.copy()
+    want = np.maximum(oracle.im2col_gemm_forward(x, w, 1, 1, pl, pr, pt, pb) + b[None, :, None, None], 0).astype(np.float32)
+    assert rel_l2(first, want) <= 1e-3
+    assert (first >= 0).all()
+    layer.Forward()
+    assert np.array_equal(layer.output_data, first)  # one accumulator per output, fixed order: no run-to-run noise
+    layer.release()
+
+
+def test_direct_falls_back_to_the_implicit_gemm(ctx, oracle, capsys):
+    """Strided layers and the other math modes have no direct kernel: they run as the im2col layer, bit-exact in fp32."""
+    x = synth.conv_input(1, 8, 15, 15, 96)
+    w = synth.conv_weights(8, 8, 3, 3, 97)
+    strided = fc.ConvDirectLayer(x, w, None, None, 8, 15, 15, 8, 3, 3, 2, 2, 1, 1, 1, 1, 1, False, 1, 1, mode="tf32", ctx=ctx)
+    strided.Init(); strided.Forward()
+    assert strided.algorithm == _lib.ALGO_IM2COL
+    assert rel_l2(strided.output_data, oracle.im2col_gemm_forward(x, w, 2, 2, 1, 1, 1, 1)) <= 3e-3
+    strided.release()
+    exact = fc.make_layer("direct", x, w, None, None, 8, 15, 15, 8, 3, 3, 1, 1, 1, 1, 1, 1, ctx=ctx)  # mode fp32
+    assert isinstance(exact, fc.ConvDirectLayer)
+    exact.Init(); exact.Forward()
+    assert "Algorithm: direct" in capsys.readouterr().out
+    assert exact.algorithm == _lib.ALGO_IM2COL
+    assert np.array_equal(exact.output_data, oracle.im2col_gemm_forward(x, w, 1, 1, 1, 1, 1, 1))
+    exact.release()
+
+
+def test_direct_vgg_layer_and_tuner(ctx, oracle, tmp_path, monkeypatch):
+    """conv3_2 of VGG-16 (256 -> 256 at 56x56): the TF32 figure that the Winograd path misses (6.4e-3) is met here."""
+    monkeypatch.setenv("FASTCONV_TUNING_LOG", str(tmp_path / "tuning_log"))
+    x = synth.conv_input(1, 256, 56, 56, 98)
+    w = synth.conv_weights(256, 256, 3, 3, 99)
+    layer = fc.ConvDirectLayer(x, w, None, None, 256, 56, 56, 256, iter=3, mode="tf32", ctx=ctx)
+    layer.Tuning()
+    layer.Init(); layer.Forward()
+    assert layer.algorithm == _lib.ALGO_DIRECT
+    err = rel_l2(layer.output_data, oracle.im2col_gemm_forward(x, w, 1, 1, 1, 1, 1, 1))
+    assert err <= 1e-3, err
+    assert layer.kernel_launches == 2
+    layer.release()
