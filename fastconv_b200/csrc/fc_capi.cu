@@ -688,6 +688,11 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
     const bool auto_requested = algo == FC_ALGO_AUTO;
     if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
+    // the TF32 mode states a tolerance, not an algorithm: where the direct tensor-core kernel is the faster way to
+    // meet it, `auto` takes it (Tuning() still measures all of them)
+    if (auto_requested && mode == FC_MATH_TF32 &&
+        direct_tc_preferred(*desc, oh, ow, ctx->sm_count > 0 ? ctx->sm_count : 148, algo == FC_ALGO_WINOGRAD))
+        algo = FC_ALGO_DIRECT;
     // the direct tensor-core kernel is a TF32 kernel for stride-1, ungrouped layers; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
     if (algo == FC_ALGO_DIRECT && !(mode == FC_MATH_TF32 && direct_tc_eligible(*desc))) algo = FC_ALGO_IM2COL;

@@ -268,6 +268,38 @@ bool direct_tc_eligible(const fc_conv_desc &d) {
     return d.sh == 1 && d.sw == 1 && d.group == 1 && d.iw <= (1 << 20) && d.ih <= (1 << 20);
 }
 
+// patch of 128 output pixels: the shape that wastes the fewest pixels, the widest one among equals (longer runs in
+// the output rows)
+static void direct_patch_shape(int oh, int ow, int *bh, int *bw) {
+    const int shapes[6][2] = {{1, 128}, {2, 64}, {4, 32}, {8, 16}, {16, 8}, {32, 4}};
+    size_t best = ~(size_t)0;
+    for (const auto &s : shapes) {
+        const size_t covered = (size_t)round_up(oh, s[0]) * round_up(ow, s[1]);
+        if (covered < best) { best = covered; *bh = s[0]; *bw = s[1]; }
+    }
+}
+
+// Whether `-a auto` in the TF32 mode should take this kernel instead of the Winograd path (3x3) or the gathering
+// implicit GEMM (anything else of stride 1).  From per-layer timings of the VGG-16 and ResNet-50 layers at batch
+// 1, 2, 8 and 64 on a B200:
+//  * against Winograd the kernel does 2.25x the multiplications but moves no V and M, so it wins where the
+//    channels are few -- ic*oc/(ic+oc) up to about 100 (128 -> 256 yes, 256 -> 256 a tie) -- provided the layer
+//    has a work item for every SM, or so few channels (up to about 48) that the transforms dominate anyway;
+//  * against the gathering kernel it wins by 1.5x to 3.5x as soon as there are 16 work items and 0.15 GFLOP;
+//    below that the extra launch of the layout pass decides.
+bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bool over_winograd) {
+    if (!direct_tc_eligible(d)) return false;
+    int bh = 8, bw = 16;
+    direct_patch_shape(oh, ow, &bh, &bw);
+    const double items = (double)ceil_div(oh, bh) * ceil_div(ow, bw) * d.batch * ceil_div(d.oc, 128);
+    if (over_winograd) {
+        const double h = (double)d.ic * d.oc / (d.ic + d.oc);
+        return h <= 100.0 && (items >= sm_count || h <= 48.0);
+    }
+    const double flops = 2.0 * d.batch * d.oc * d.ic * d.kh * d.kw * oh * ow;
+    return items >= 16 && flops >= 1.5e8;
+}
+
 size_t direct_nhwc_elems(const fc_conv_desc &d) { return (size_t)d.batch * d.ih * d.iw * round_up(d.ic, BK); }
 
 size_t direct_packed_elems(const fc_conv_desc &d) { return (size_t)d.kh * d.kw * d.oc * round_up(d.ic, BK); }
@@ -290,15 +322,8 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
         dim3 grid((unsigned)ceil_div(hw, 32), (unsigned)(icp / 32), (unsigned)d.batch), block(256);
         FC_CHECK_CUDA(launch_pdl(nchw_to_nhwc_kernel, grid, block, 0, ctx->stream, d_in, d_nhwc, d.ic, icp, hw));
     }
-    // patch of 128 output pixels: the shape that wastes the fewest pixels, the widest one among equals (longer runs
-    // in the output rows)
-    const int shapes[6][2] = {{1, 128}, {2, 64}, {4, 32}, {8, 16}, {16, 8}, {32, 4}};
     int bh = 8, bw = 16;
-    size_t best = ~(size_t)0;
-    for (const auto &s : shapes) {
-        const size_t covered = (size_t)round_up(oh, s[0]) * round_up(ow, s[1]);
-        if (covered < best) { best = covered; bh = s[0]; bw = s[1]; }
-    }
+    direct_patch_shape(oh, ow, &bh, &bw);
     DirectParams P;
     P.out = d_out;
     P.status = ctx->d_status;
