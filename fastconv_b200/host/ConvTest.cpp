@@ -9,6 +9,8 @@
 // reference harness, all deliberate:
 //   * `-a auto` on a 1x1 stride-1 layer runs the implicit-GEMM layer (the reference's `direct` case is
 //     empty, ConvTest.cpp:369-371, so nothing ran);
+//   * `-a direct` runs ConvDirectLayer: the direct tensor-core kernel for stride-1 layers with `-m tf32`, the
+//     implicit GEMM otherwise;
 //   * the self-check honours kernel size, stride and padding (the reference always checks against a
 //     3x3 / pad 1 naive layer, ConvTest.cpp:360) and also covers the im2col path;
 //   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32, -seed N (the reference seeds from
@@ -21,6 +23,7 @@
 #include <algorithm>
 
 #include "conv_layer.h"
+#include "convLayer/directConv.h"
 #include "convLayer/im2colConv.h"
 #include "convLayer/naiveConv.h"
 #include "convLayer/winoF63ConvZC.h"
@@ -216,7 +219,6 @@ int main(int argc, char *argv[]) {
     fillTestKernel(test_kernel, k_elems);
 
     if (options.algorithm == nnp_convolution_algorithm_auto) options.algorithm = select_algorithm(d);
-    if (options.algorithm == nnp_convolution_algorithm_direct) options.algorithm = nnp_convolution_algorithm_im2col;
 
     if (fastconv_default_context() == NULL && options.gpu != 0) {
         fc_context *ctx = NULL;
@@ -241,6 +243,10 @@ int main(int argc, char *argv[]) {
         conv = new ConvWinoF63ZCLayer(test_input, test_kernel, NULL, ref, ic, in.height, in.width, oc, ks.height, ks.width,
                                       st.height, st.width, pad, pad, pad, pad, 1, false, options.threads,
                                       options.iterations);
+    else if (options.algorithm == nnp_convolution_algorithm_direct)
+        conv = new ConvDirectLayer(test_input, test_kernel, NULL, ref, ic, in.height, in.width, oc, ks.height, ks.width,
+                                   st.height, st.width, pad, pad, pad, pad, 1, false, options.threads,
+                                   options.iterations);
     else
         conv = new ConvIm2colLayer(test_input, test_kernel, NULL, ref, ic, in.height, in.width, oc, ks.height, ks.width,
                                    st.height, st.width, pad, pad, pad, pad, 1, false, options.threads,

@@ -80,3 +80,17 @@ def test_runs_and_prints_reference_lines(binary, args, algo, labels):
 def test_winograd_refuses_shapes_the_reference_computes_wrongly(binary):
     r = run(binary, "-ic", "8", "-oc", "8", "-is", "16", "16", "-ks", "3", "3", "-s", "2", "2", "-a", "winograd")
     assert r.returncode != 0 and "stride 1" in r.stderr
+
+
+@pytest.mark.gpu
+def test_direct_runs_the_tensor_core_kernel_in_tf32_and_the_implicit_gemm_otherwise(binary):
+    base = ["-ic", "16", "-oc", "16", "-is", "20", "20", "-ks", "3", "3", "-a", "direct", "-i", "2", "-seed", "7"]
+    exact = run(binary, *base)
+    assert exact.returncode == 0, exact.stderr
+    assert "Algorithm: direct" in exact.stdout and "Gemm time:" in exact.stdout
+    assert float(re.search(r"The difference is ([0-9.]+)", exact.stdout).group(1)) < 0.05  # fp32: the implicit GEMM
+    fast = run(binary, *base, "-m", "tf32")
+    assert fast.returncode == 0, fast.stderr
+    assert "Algorithm: direct" in fast.stdout
+    # outputs are ~1e4 (inputs in [0,256), 144 taps): a mean absolute difference of a few units is TF32 rounding (3e-4)
+    assert float(re.search(r"The difference is ([0-9.]+)", fast.stdout).group(1)) < 10.0
