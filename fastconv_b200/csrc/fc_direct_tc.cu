@@ -246,6 +246,35 @@ __global__ void direct_pack_weights_kernel(const float *__restrict__ w, float *_
     }
 }
 
+// A layer whose whole reduction fits one k-block (ic*kh*kw <= 32: the 3-channel first layer of a network) would
+// spend kh*kw k-blocks of 32 channels on 3 real ones.  For it the layout pass writes the taps next to each other
+// instead -- F[n][y][x][k], k = (c*kh + u)*kw + v as in a row of W, zero for pixels outside the image and for
+// k >= ic*kh*kw -- and the convolution becomes a 1x1 layer over 32 channels: one k-block per patch instead of kh*kw.
+__global__ void __launch_bounds__(256) fold_taps_kernel(const float *__restrict__ in, float *__restrict__ out, int ic,
+                                                       int ih, int iw, int kh, int kw, int pad_t, int pad_l, int oh,
+                                                       int ow) {
+    // one block per output row: the ic*kh input rows it needs (at most 32 of them), padded left and right with zeros,
+    // are staged in shared memory with coalesced reads; a warp then writes the 32 floats of one pixel per step
+    extern __shared__ float rows[];  // [ic*kh][ow + kw - 1]
+    const int y = blockIdx.x % oh, img = blockIdx.x / oh;
+    const int wrow = ow + kw - 1, nrows = ic * kh;
+    pdl_trigger();
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < nrows * wrow; idx += 256) {
+        const int r = idx / wrow, xs = idx - r * wrow;
+        const int c = r / kh, u = r - c * kh;
+        const int yy = y + u - pad_t, xx = xs - pad_l;
+        rows[idx] = (yy >= 0 && yy < ih && xx >= 0 && xx < iw) ? __ldg(in + (((size_t)img * ic + c) * ih + yy) * iw + xx) : 0.0f;
+    }
+    __syncthreads();
+    const int k = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int r = k / kw, v = k - r * kw;  // r = c*kh + u
+    const bool real = r < nrows;
+    const float *src = rows + (real ? r * wrow + v : 0);
+    float *dst = out + ((size_t)blockIdx.x * ow) * 32 + k;
+    for (int x = w; x < ow; x += 8) dst[(size_t)x * 32] = real ? src[x] : 0.0f;
+}
+
 // NHWC input as a 4-D tensor (channel, x, y, image), box = 32 channels x bw x bh x 1, 128-byte swizzle, zero fill
 int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, int n, int bw, int bh) {
     EncodeTiledFn enc;
@@ -263,6 +292,12 @@ int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, 
 }
 
 }  // namespace
+
+static bool folds_taps(const fc_conv_desc &d) {  // ... and the staged rows of one output row fit shared memory
+    const long long row_floats = (long long)d.ic * d.kh * (d.iw + d.pad_left + d.pad_right);
+    return d.kh * d.kw > 1 && d.ic * d.kh * d.kw <= BK && row_floats * 4 <= 160 * 1024 &&
+           (long long)d.batch * (d.ih + d.pad_top + d.pad_bottom) < (1ll << 31);
+}
 
 bool direct_tc_eligible(const fc_conv_desc &d) {
     return d.sh == 1 && d.sw == 1 && d.group == 1 && d.iw <= (1 << 20) && d.ih <= (1 << 20);
@@ -300,25 +335,46 @@ bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bo
     return items >= 16 && flops >= 1.5e8;
 }
 
-size_t direct_nhwc_elems(const fc_conv_desc &d) { return (size_t)d.batch * d.ih * d.iw * round_up(d.ic, BK); }
+size_t direct_nhwc_elems(const fc_conv_desc &d) {
+    if (folds_taps(d)) {  // one 32-float pixel per OUTPUT position
+        const int oh = d.ih + d.pad_top + d.pad_bottom - d.kh + 1, ow = d.iw + d.pad_left + d.pad_right - d.kw + 1;
+        return (size_t)d.batch * oh * ow * BK;
+    }
+    return (size_t)d.batch * d.ih * d.iw * round_up(d.ic, BK);
+}
 
-size_t direct_packed_elems(const fc_conv_desc &d) { return (size_t)d.kh * d.kw * d.oc * round_up(d.ic, BK); }
+size_t direct_packed_elems(const fc_conv_desc &d) {
+    return folds_taps(d) ? (size_t)d.oc * BK : (size_t)d.kh * d.kw * d.oc * round_up(d.ic, BK);
+}
 
 int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_wp, const fc_conv_desc &d) {
-    const int icp = round_up(d.ic, BK);
+    // folded taps: a row of W (ic*kh*kw floats) padded to 32 is the one tap of a 1x1 layer over 32 channels
+    const bool fold = folds_taps(d);
+    const int ic = fold ? d.ic * d.kh * d.kw : d.ic, taps = fold ? 1 : d.kh * d.kw;
+    const int icp = round_up(ic, BK);
     const size_t total = direct_packed_elems(d);
     const unsigned blocks = (unsigned)(ceil_div(total, 256) > 4096 ? 4096 : ceil_div(total, 256));
-    direct_pack_weights_kernel<<<blocks, 256, 0, ctx->stream>>>(d_kernel, d_wp, d.oc, d.ic, icp, d.kh * d.kw);
+    direct_pack_weights_kernel<<<blocks, 256, 0, ctx->stream>>>(d_kernel, d_wp, d.oc, ic, icp, taps);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
 
 int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const float *d_wp, float *d_out,
-                     const fc_conv_desc &d, int oh, int ow, const KernelCfg *cfg, const Epilogue &ep) {
-    FC_REQUIRE(direct_tc_eligible(d), FC_ERR_UNSUPPORTED, "the direct tensor-core path takes stride-1, ungrouped layers");
+                     const fc_conv_desc &full, int oh, int ow, const KernelCfg *cfg, const Epilogue &ep) {
+    FC_REQUIRE(direct_tc_eligible(full), FC_ERR_UNSUPPORTED, "the direct tensor-core path takes stride-1, ungrouped layers");
     FC_REQUIRE(ctx->d_status != nullptr, FC_ERR_INVALID_ARG, "the tensor-core kernels need a context with a status word");
+    fc_conv_desc d = full;
+    if (folds_taps(full)) {
+        const size_t smem = (size_t)full.ic * full.kh * (ow + full.kw - 1) * sizeof(float);
+        FC_CHECK_CUDA(cudaFuncSetAttribute(fold_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FC_CHECK_CUDA(launch_pdl(fold_taps_kernel, dim3((unsigned)(full.batch * oh)), dim3(256), smem, ctx->stream, d_in,
+                                 d_nhwc, full.ic, full.ih, full.iw, full.kh, full.kw, full.pad_top, full.pad_left, oh, ow));
+        // from here on: a 1x1, unpadded layer over the 32 folded channels of an oh x ow image
+        d.ic = BK; d.ih = oh; d.iw = ow; d.kh = d.kw = 1;
+        d.pad_left = d.pad_right = d.pad_top = d.pad_bottom = 0;
+    }
     const int icp = round_up(d.ic, BK), hw = d.ih * d.iw;
-    {
+    if (!folds_taps(full)) {
         dim3 grid((unsigned)ceil_div(hw, 32), (unsigned)(icp / 32), (unsigned)d.batch), block(256);
         FC_CHECK_CUDA(launch_pdl(nchw_to_nhwc_kernel, grid, block, 0, ctx->stream, d_in, d_nhwc, d.ic, icp, hw));
     }

@@ -26,6 +26,9 @@ CASES = [  # n, ic, oc, ih, iw, kh, kw, pad_l, pad_r, pad_t, pad_b
     (1, 24, 40, 5, 130, 3, 3, 1, 1, 1, 1),      # a wide, flat image: 1x128 patches
     (1, 24, 40, 130, 5, 3, 3, 1, 1, 1, 1),      # a tall, narrow one: 32x4 patches
     (1, 16, 16, 12, 12, 3, 3, 0, 0, 0, 0),      # no padding: the output is smaller than the input
+    (2, 2, 20, 17, 19, 3, 5, 1, 2, 0, 1),       # ic*kh*kw = 30 <= 32: taps folded into one k-block, four paddings
+    (1, 1, 16, 12, 12, 5, 5, 2, 2, 2, 2),       # one channel, 25 taps folded
+    (3, 3, 64, 64, 64, 3, 3, 1, 1, 1, 1),       # the first layer of VGG-16 in small: 27 folded taps, three images
 ]
 
 
