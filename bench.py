@@ -304,6 +304,10 @@ def main():
     ap.add_argument("--chain", action="store_true",
                     help="not the reference's per-layer benchmark: layers of one VGG block feed each other on the device "
                          "(bias + ReLU in the epilogue), only block inputs and outputs cross PCIe in the end-to-end number")
+    ap.add_argument("--algo", default="winograd", choices=["winograd", "auto", "direct"],
+                    help="winograd: every layer through F(6x6,3x3) (the reference's path, the default); auto: the "
+                         "library's choice per layer (in --mode tf32 the direct tensor-core kernel where it is faster); "
+                         "direct: the direct tensor-core kernel for every layer (--mode tf32; rel-L2 <= 1e-3)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "fastconv":
@@ -347,6 +351,9 @@ def main():
     for c, k, h in layers:
         t, tp, icp = wino_geometry(n, c, k, h)
         need += 4 * (64 * k * icp + 64 * tp * icp + 64 * k * tp + k * c * 9 + n * c * h * h + n * k * h * h) + 8 * 4096
+        if args.algo != "winograd":  # the direct kernel's NHWC copy of the input and its re-laid-out weights
+            c32 = (c + 31) // 32 * 32
+            need += 4 * (n * c32 * h * h + 9 * k * c32) + 2 * 4096
     ctx = fc.Context(local_rank, arena_bytes=int(need * 1.05) + (64 << 20))
 
     convs, flops, h2d, d2h, footprint = [], 0.0, 0, 0, 0
@@ -356,8 +363,8 @@ def main():
         w = synth.conv_weights(k, c, 3, 3, 2000 + idx)
         x = synth.conv_input(n, c, h, h, 1000 + idx + 100 * rank)
         hdl = C.c_void_p()
-        _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, mode, C.c_void_p(w.ctypes.data),
-                                      C.byref(hdl)), "fc_conv_create")
+        _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_NAMES[args.algo], mode,
+                                      C.c_void_p(w.ctypes.data), C.byref(hdl)), "fc_conv_create")
         d_in, d_out = C.c_void_p(), C.c_void_p()
         _lib.check(lib.fc_conv_device_buffers(hdl, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
         ctx.upload(x, d_in.value)
@@ -443,6 +450,8 @@ def main():
     roof_sum_ms = 0.0
     launches_per_step = 0
     gemm_bytes = gemm_ms = gemm_flops = 0.0
+    direct_ms = direct_flops = 0.0
+    n_wino = n_direct = 0
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
     for (hdl, d_in, d_out, desc), (c, k, h) in zip(convs, layers):
         ms = (C.c_float * 5)()
@@ -452,18 +461,23 @@ def main():
         nl = C.c_int()
         lib.fc_conv_launches_per_forward(hdl, C.byref(nl))
         launches_per_step += nl.value
+        algo = C.c_int()
+        lib.fc_conv_algorithm(hdl, C.byref(algo))
+        is_wino = algo.value == _lib.ALGO_WINOGRAD
         t, tp, icp = wino_geometry(n, c, k, h)
-        # roofline of a layer: the slower of its Winograd-domain flops at the mode's arithmetic peak and its HBM
-        # bytes (input, transformed filter, output) at the measured copy bandwidth
-        bytes_wino = 4.0 * (n * c * h * h + 64 * c * k + n * k * h * h)
+        # roofline of a layer: the slower of its flops (Winograd-domain for a Winograd layer, direct otherwise) at the
+        # mode's arithmetic peak and its HBM bytes (input, filter as the kernel reads it, output) at the measured
+        # copy bandwidth
         bytes_min = 4.0 * (n * c * h * h + 9 * c * k + n * k * h * h)
-        wino_flops = 2.0 * 64 * t * c * k
+        bytes_wino = 4.0 * (n * c * h * h + 64 * c * k + n * k * h * h) if is_wino else bytes_min
+        wino_flops = 2.0 * 64 * t * c * k if is_wino else layer_flops(n, c, k, h)
         t_hbm_ms = bytes_wino / hbm_peak / 1e6
         t_flop_ms = wino_flops / (MODE_PEAK_TFLOPS[args.mode] * 1e12) * 1e3
         roof_ms = max(t_hbm_ms, t_flop_ms)
         roof_sum_ms += roof_ms
         per_layer.append({
-            "layer": f"{c}->{k}@{h}", "ms": round(one.value, 5),
+            "layer": f"{c}->{k}@{h}", "algo": {v: kk for kk, v in _lib.ALGO_NAMES.items()}[algo.value],
+            "ms": round(one.value, 5),
             "gflops_direct_equiv": round(layer_flops(n, c, k, h) / one.value / 1e6, 1),
             "stage_ms": [round(float(v), 5) for v in ms],
             "t_hbm_ms": round(t_hbm_ms, 5), "t_flop_ms": round(t_flop_ms, 5),
@@ -473,12 +487,18 @@ def main():
         })
         for i in range(5):
             stage_tot[i] += ms[i]
-        gemm_bytes += 4.0 * (64 * k * icp + 64 * tp * icp + 64 * k * tp)
-        gemm_ms += ms[2]
-        gemm_flops += wino_flops
+        if is_wino:
+            gemm_bytes += 4.0 * (64 * k * icp + 64 * tp * icp + 64 * k * tp)
+            gemm_ms += ms[2]
+            gemm_flops += wino_flops
+            n_wino += 1
+        else:  # stage 2 of a direct layer = the layout pass + direct_tc_kernel
+            direct_ms += ms[2]
+            direct_flops += wino_flops
+            n_direct += 1
 
-    nl = len(layers)
-    achieved_gbs = gemm_bytes / (gemm_ms / 1e3) / 1e9
+    nl = max(n_wino, 1)
+    achieved_gbs = gemm_bytes / (gemm_ms / 1e3) / 1e9 if gemm_ms > 0 else 0.0
     roofline = {
         "kernel": "TensorGEMM (64 batched U*V products, one launch per layer)",
         "bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
@@ -487,10 +507,22 @@ def main():
         "algorithmic_bytes_per_launch": gemm_bytes / nl, "avg_launch_ms": gemm_ms / nl,
         "stack_roofline_ms": round(roof_sum_ms, 5), "stack_frac_of_roofline": round(roof_sum_ms / ms_step, 4),
         "arithmetic_peak_tflops": round(MODE_PEAK_TFLOPS[args.mode], 1),
-        "winograd_domain_tflops": round(gemm_flops / (gemm_ms / 1e3) / 1e12, 2),
+        "winograd_domain_tflops": round(gemm_flops / (gemm_ms / 1e3) / 1e12, 2) if gemm_ms > 0 else None,
         "share_of_step": {"InputTran": round(stage_tot[0] / stage_tot[4], 3), "TensorGEMM": round(stage_tot[2] / stage_tot[4], 3),
                           "OutputTran": round(stage_tot[3] / stage_tot[4], 3)},
     }
+    if direct_ms > gemm_ms:
+        # the direct tensor-core kernel dominates the step: bound by the tensor pipe
+        ach = direct_flops / (direct_ms / 1e3) / 1e12
+        roofline = {
+            "kernel": "direct_tc_kernel (+ its layout pass), one launch pair per layer",
+            "bound": "tensor", "achieved": round(ach, 1), "peak": MODE_PEAK_TFLOPS["tf32"], "unit": "TFLOP/s",
+            "frac": round(ach / MODE_PEAK_TFLOPS["tf32"], 4),
+            "peak_source": "TF32 library GEMM (8192^3) measured on a B200 of this pool",
+            "traffic": None, "algorithmic_flops_per_launch": direct_flops / n_direct, "avg_launch_ms": direct_ms / n_direct,
+            "stack_roofline_ms": round(roof_sum_ms, 5), "stack_frac_of_roofline": round(roof_sum_ms / ms_step, 4),
+            "layers_direct": n_direct, "layers_winograd": n_wino,
+        }
 
     line = None
     if rank == 0:
@@ -502,7 +534,9 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32"}[args.mode], "data": "synthetic",
             "config": {"workload": f"{workload_name}, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
-                       "algorithm": "winograd F(6x6,3x3)", "math_mode": args.mode,
+                       "algorithm": {"winograd": "winograd F(6x6,3x3)", "direct": "direct convolution on the tensor cores",
+                                     "auto": "per layer: winograd F(6x6,3x3) or direct convolution on the tensor cores"}[args.algo],
+                       "math_mode": args.mode,
                        "launch": "all layers of a step replayed as one CUDA graph",
                        "chain": bool(args.chain),
                        "parallelism": f"images sharded over {world} GPU(s), no collective",
