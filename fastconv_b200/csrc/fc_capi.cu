@@ -995,10 +995,12 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
         out->push_back(t);
     };
     const int ffma_tiles[4][2] = {{128, 128}, {128, 64}, {64, 128}, {64, 64}};
-    if (algo == FC_ALGO_DIRECT) {  // the ring's size decides between one and two CTAs per SM
+    if (algo == FC_ALGO_DIRECT) {  // the ring's size and the width of the channel blocks
         push(0, 0, 0, 0);
         push(0, 0, 0, 104);
         push(0, 0, 0, 200);
+        push(0, 128, 0, 0);  // channel blocks of 128 (two CTAs per SM) or 256 (one)
+        push(0, 256, 0, 0);
         return;
     }
     if (c->mode == FC_MATH_FP32_MIRRORED) {

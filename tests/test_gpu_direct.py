@@ -29,6 +29,7 @@ CASES = [  # n, ic, oc, ih, iw, kh, kw, pad_l, pad_r, pad_t, pad_b
     (2, 2, 20, 17, 19, 3, 5, 1, 2, 0, 1),       # ic*kh*kw = 30 <= 32: taps folded into one k-block, four paddings
     (1, 1, 16, 12, 12, 5, 5, 2, 2, 2, 2),       # one channel, 25 taps folded
     (3, 3, 64, 64, 64, 3, 3, 1, 1, 1, 1),       # the first layer of VGG-16 in small: 27 folded taps, three images
+    (12, 32, 300, 56, 56, 3, 3, 1, 1, 1, 1),    # enough work items for channel blocks wider than 128: two of 160
 ]
 
 
