@@ -693,7 +693,7 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     if (auto_requested && mode == FC_MATH_TF32 &&
         direct_tc_preferred(*desc, oh, ow, ctx->sm_count > 0 ? ctx->sm_count : 148, algo == FC_ALGO_WINOGRAD))
         algo = FC_ALGO_DIRECT;
-    // the direct tensor-core kernel is a TF32 kernel for stride-1, ungrouped layers; anything else asked for as
+    // the direct tensor-core kernel is a TF32 kernel for ungrouped layers of stride 1 or 2; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
     if (algo == FC_ALGO_DIRECT && !(mode == FC_MATH_TF32 && direct_tc_eligible(*desc))) algo = FC_ALGO_IM2COL;
     int auto_pick = FC_ALGO_IM2COL;

@@ -1,23 +1,24 @@
-// Direct convolution on the 5th-generation tensor cores for stride-1 layers (`-a direct`; the reference parses
+// Direct convolution on the 5th-generation tensor cores for layers of stride 1 or 2 (`-a direct`; the reference parses
 // the name but its case is empty, ConvTest.cpp:369-371).
 //
-//   out[n][oc][y][x] = sum_{u,v} sum_c  W[oc][c][u][v] * in[n][c][y + u - pad_t][x + v - pad_l]
+//   out[n][oc][y][x] = sum_{u,v} sum_c  W[oc][c][u][v] * in[n][c][sh*y + u - pad_t][sw*x + v - pad_l]
 //
 // is kh*kw GEMMs that accumulate into ONE accumulator: for every (u,v) the second operand is the input shifted
 // by (u,v).  With the input in NHWC (channels innermost, padded to a multiple of 32) a shifted patch of
 // bh x bw pixels x 32 channels is one 4-D TMA box whose innermost coordinate is the channel block -- always 16-byte
 // aligned, whatever the shift -- and whose rows (one pixel = 128 bytes) land in shared memory exactly as a K-major,
 // 128-byte-swizzled UMMA operand of 128 rows.  Pixels outside the image are the box's out-of-range elements and read as
-// zero: the padding costs nothing and no im2col index is ever computed.  The weights, re-laid out once as
-// Wp[u*kw+v][oc][c], are the other K-major operand.
+// zero: the padding costs nothing and no im2col index is ever computed.  A stride of 2 is the tensor map's element
+// stride along x and y (the box spans twice the pixels, the copy takes every second one).  The weights, re-laid
+// out once as Wp[u*kw+v][oc][c], are the other K-major operand.
 //
 //   nchw_to_nhwc_kernel     one pass over the input per forward (the layer keeps the reference's NCHW at its boundary)
-//   direct_tc_kernel        persistent; a work item = one patch of 128 output pixels x a block of <= 128 channels
+//   direct_tc_kernel        persistent; a work item = one patch of 128 output pixels x a block of <= 256 channels
 //     warp 0      TMA producer: per k-block (u,v, 32 channels) one 4-D box of the input and one 3-D box of Wp
 //     warp 1      tcgen05.mma kind::tf32, M = 128 pixels, N = channel block, two TMEM accumulators
 //     warps 2..5  epilogue: tcgen05.ld (lane = pixel), bias/ReLU, NCHW stores (a warp writes runs of bw pixels)
 //
-// There is no Winograd transform in the way, so single-pass TF32 keeps its plain accuracy (rel-L2 ~3e-4 against
+// There is no Winograd transform in the way, so single-pass TF32 keeps its plain accuracy (rel-L2 3e-4..8e-4 against
 // 6.4e-3 through F(6x6,3x3)).  Every mbarrier wait is bounded as in the other tensor-core kernels.
 #include "fc_tc_common.cuh"
 
@@ -35,7 +36,7 @@ struct DirectParams {
     int bh, bw, n_px, n_py;  // patch shape (bh * bw = 128) and patches per image along x and y
     int bn, n_oc_items;      // channel block (multiple of 16, <= 128) and blocks per layer
     int num_kb, taps, kw;    // 32-channel blocks per tap, kh*kw, kw
-    int pad_t, pad_l;
+    int pad_t, pad_l, sh, sw;
     int stages, acc_cols, n_items;
     int b_bytes;
 };
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
                         mbar_expect_tx(bar_full(s), stage_bytes);
                         // innermost coordinate = channel block (a multiple of 32 floats); x and y may be negative or
                         // past the image: those pixels read as zero
-                        tma_load_4d(dst, &tmX, bar_full(s), kb * BK, x0 + v - P.pad_l, y0 + u - P.pad_t, img);
+                        tma_load_4d(dst, &tmX, bar_full(s), kb * BK, x0 * P.sw + v - P.pad_l, y0 * P.sh + u - P.pad_t, img);
                         tma_load_3d(dst + A_BYTES, &tmW, bar_full(s), kb * BK, oc0, tap);
                     }
                 }
@@ -275,14 +276,16 @@ __global__ void __launch_bounds__(256) fold_taps_kernel(const float *__restrict_
     for (int x = w; x < ow; x += 8) dst[(size_t)x * 32] = real ? src[x] : 0.0f;
 }
 
-// NHWC input as a 4-D tensor (channel, x, y, image), box = 32 channels x bw x bh x 1, 128-byte swizzle, zero fill
-int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, int n, int bw, int bh) {
+// NHWC input as a 4-D tensor (channel, x, y, image), box = 32 channels x bw x bh x 1, 128-byte swizzle, zero fill.
+// A strided layer reads every sw-th column and sh-th row: the box spans bw*sw x bh*sh elements and the map's element
+// strides make the copy take one in sw (sh) of them, so the landed tile is the same 128 pixels x 32 channels.
+int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, int n, int bw, int bh, int sw, int sh) {
     EncodeTiledFn enc;
     FC_PROPAGATE(get_encoder(&enc));
     cuuint64_t dims[4] = {(cuuint64_t)icp, (cuuint64_t)iw, (cuuint64_t)ih, (cuuint64_t)n};
     cuuint64_t strides[3] = {(cuuint64_t)icp * 4, (cuuint64_t)icp * iw * 4, (cuuint64_t)icp * iw * ih * 4};
-    cuuint32_t box[4] = {BK, (cuuint32_t)bw, (cuuint32_t)bh, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint32_t box[4] = {BK, (cuuint32_t)(bw * sw), (cuuint32_t)(bh * sh), 1};
+    cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -295,12 +298,12 @@ int make_map_nhwc(CUtensorMap *map, const float *base, int icp, int iw, int ih, 
 
 static bool folds_taps(const fc_conv_desc &d) {  // ... and the staged rows of one output row fit shared memory
     const long long row_floats = (long long)d.ic * d.kh * (d.iw + d.pad_left + d.pad_right);
-    return d.kh * d.kw > 1 && d.ic * d.kh * d.kw <= BK && row_floats * 4 <= 160 * 1024 &&
+    return d.sh == 1 && d.sw == 1 && d.kh * d.kw > 1 && d.ic * d.kh * d.kw <= BK && row_floats * 4 <= 160 * 1024 &&
            (long long)d.batch * (d.ih + d.pad_top + d.pad_bottom) < (1ll << 31);
 }
 
 bool direct_tc_eligible(const fc_conv_desc &d) {
-    return d.sh == 1 && d.sw == 1 && d.group == 1 && d.iw <= (1 << 20) && d.ih <= (1 << 20);
+    return d.sh >= 1 && d.sh <= 2 && d.sw >= 1 && d.sw <= 2 && d.group == 1 && d.iw <= (1 << 20) && d.ih <= (1 << 20);
 }
 
 // patch of 128 output pixels: the shape that wastes the fewest pixels, the widest one among equals (longer runs in
@@ -315,13 +318,15 @@ static void direct_patch_shape(int oh, int ow, int *bh, int *bw) {
 }
 
 // Whether `-a auto` in the TF32 mode should take this kernel instead of the Winograd path (3x3) or the gathering
-// implicit GEMM (anything else of stride 1).  From per-layer timings of the VGG-16 and ResNet-50 layers at batch
+// implicit GEMM (anything else of stride 1 or 2).  From per-layer timings of the VGG-16 and ResNet-50 layers at batch
 // 1, 2, 8 and 64 on a B200:
 //  * against Winograd the kernel does 2.25x the multiplications but moves no V and M, so it wins where the
 //    channels are few -- ic*oc/(ic+oc) up to about 100 (128 -> 256 yes, 256 -> 256 a tie) -- provided the layer
 //    has a work item for every SM, or so few channels (up to about 48) that the transforms dominate anyway;
-//  * against the gathering kernel it wins by 1.5x to 3.5x as soon as there are 16 work items and 0.15 GFLOP;
-//    below that the extra launch of the layout pass decides.
+//  * against the gathering kernel (1x1 layers, stride-2 layers) it wins by 1.5x to 4x as soon as there are 16 work
+//    items and 0.15 GFLOP; below that the extra launch of the layout pass decides.  Not with a handful of channels
+//    and taps that do not fold (the 7x7 stride-2 stem: 3 real channels in every 32-wide k-block, 0.69 against 0.57 ms
+//    at batch 64).
 bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bool over_winograd) {
     if (!direct_tc_eligible(d)) return false;
     int bh = 8, bw = 16;
@@ -332,7 +337,7 @@ bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bo
         return h <= 100.0 && (items >= sm_count || h <= 48.0);
     }
     const double flops = 2.0 * d.batch * d.oc * d.ic * d.kh * d.kw * oh * ow;
-    return items >= 16 && flops >= 1.5e8;
+    return items >= 16 && flops >= 1.5e8 && (d.ic >= 16 || folds_taps(d));
 }
 
 size_t direct_nhwc_elems(const fc_conv_desc &d) {
@@ -361,7 +366,7 @@ int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_
 
 int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const float *d_wp, float *d_out,
                      const fc_conv_desc &full, int oh, int ow, const KernelCfg *cfg, const Epilogue &ep) {
-    FC_REQUIRE(direct_tc_eligible(full), FC_ERR_UNSUPPORTED, "the direct tensor-core path takes stride-1, ungrouped layers");
+    FC_REQUIRE(direct_tc_eligible(full), FC_ERR_UNSUPPORTED, "the direct tensor-core path takes ungrouped layers of stride 1 or 2");
     FC_REQUIRE(ctx->d_status != nullptr, FC_ERR_INVALID_ARG, "the tensor-core kernels need a context with a status word");
     fc_conv_desc d = full;
     if (folds_taps(full)) {
@@ -401,6 +406,7 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
     P.taps = d.kh * d.kw;
     P.kw = d.kw;
     P.pad_t = d.pad_top; P.pad_l = d.pad_left;
+    P.sh = d.sh; P.sw = d.sw;
     P.acc_cols = pow2_at_least(P.bn, 32);
     P.b_bytes = P.bn * BK * 4;
     const long long items = (long long)P.n_px * P.n_py * d.batch * P.n_oc_items;
@@ -419,7 +425,7 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
     if (ctas > P.n_items) ctas = P.n_items;
 
     CUtensorMap tmX, tmW;
-    FC_PROPAGATE(make_map_nhwc(&tmX, d_nhwc, icp, d.iw, d.ih, d.batch, bw, bh));
+    FC_PROPAGATE(make_map_nhwc(&tmX, d_nhwc, icp, d.iw, d.ih, d.batch, bw, bh, d.sw, d.sh));
     FC_PROPAGATE(make_map_3d(&tmW, d_wp, icp, d.oc, P.taps, P.bn));
     FC_CHECK_CUDA(cudaFuncSetAttribute(direct_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FC_CHECK_CUDA(launch_pdl(direct_tc_kernel, dim3((unsigned)ctas), dim3(TC_THREADS), smem, ctx->stream, tmX, tmW, P));

@@ -183,7 +183,7 @@ void igemm_fill_ktab(const fc_conv_desc &d, int *host_pairs);  // 2 ints per ent
 int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, float *d_out, const fc_conv_desc &d,
                     int oh, int ow, int mode, const KernelCfg *cfg = nullptr, const int *d_ktab = nullptr,
                     const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0);
-// direct convolution on the tensor cores (stride 1, TF32): NHWC copy of the input + shifted TMA boxes
+// direct convolution on the tensor cores (stride 1 or 2, TF32): NHWC copy of the input + shifted TMA boxes
 bool direct_tc_eligible(const fc_conv_desc &d);
 bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bool over_winograd);
 size_t direct_nhwc_elems(const fc_conv_desc &d);

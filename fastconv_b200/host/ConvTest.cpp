@@ -9,7 +9,7 @@
 // reference harness, all deliberate:
 //   * `-a auto` on a 1x1 stride-1 layer runs the implicit-GEMM layer (the reference's `direct` case is
 //     empty, ConvTest.cpp:369-371, so nothing ran);
-//   * `-a direct` runs ConvDirectLayer: the direct tensor-core kernel for stride-1 layers with `-m tf32`, the
+//   * `-a direct` runs ConvDirectLayer: the direct tensor-core kernel for layers of stride 1 or 2 with `-m tf32`, the
 //     implicit GEMM otherwise;
 //   * the self-check honours kernel size, stride and padding (the reference always checks against a
 //     3x3 / pad 1 naive layer, ConvTest.cpp:360) and also covers the im2col path;

@@ -1,7 +1,7 @@
 // Direct convolution layer for `-a direct`.  The reference parses the name but its case in main() is empty
 // (ConvTest.cpp:369-371), so there is no class to mirror; this one follows the shape of the im2col layer
 // (convLayer/im2colConv.h:9-53): same constructor arguments as ConvLayer, Init() and Forward() return 1.
-// On the GPU it is the direct tensor-core kernel for stride-1, ungrouped layers in the TF32 mode (shifted TMA boxes
+// On the GPU it is the direct tensor-core kernel for ungrouped layers of stride 1 or 2 in the TF32 mode (shifted TMA boxes
 // of an NHWC copy of the input, no Winograd transform); any other layer or mode runs as the implicit GEMM.
 #ifndef DIRECTCONV_H
 #define DIRECTCONV_H

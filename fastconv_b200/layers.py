@@ -399,7 +399,7 @@ class ConvIm2colLayer(ConvLayer):
 
 class ConvDirectLayer(ConvLayer):
     """`-a direct`: the reference parses the name but its case is empty (ConvTest.cpp:369-371).  Here it is the direct
-    convolution on the tensor cores: stride-1, ungrouped layers in mode "tf32" (shifted TMA boxes of an NHWC copy of
+    convolution on the tensor cores: ungrouped layers of stride 1 or 2 in mode "tf32" (shifted TMA boxes of an NHWC copy of
     the input, no Winograd transform, so single-pass TF32 keeps its plain accuracy); any other layer or mode runs as
     the implicit GEMM.  Init() and Forward() return 1 like the im2col layer's."""
 

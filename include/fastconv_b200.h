@@ -44,7 +44,7 @@ typedef enum fc_status {
 typedef enum fc_algorithm {
     FC_ALGO_AUTO = 0,
     FC_ALGO_DIRECT = 1, /* the reference's case is empty (ConvTest.cpp:369-371); here: direct convolution on the tensor
-                           cores for stride-1 ungrouped layers in FC_MATH_TF32, the implicit-GEMM kernel for anything else */
+                           cores for ungrouped layers of stride 1 or 2 in FC_MATH_TF32, the implicit-GEMM kernel for anything else */
     FC_ALGO_IM2COL = 2,
     FC_ALGO_WINOGRAD = 3
 } fc_algorithm;

@@ -1,4 +1,4 @@
-"""`-a direct`: direct convolution on the tensor cores (stride 1, TF32) against the oracle's convolution.
+"""`-a direct`: direct convolution on the tensor cores (stride 1 or 2, TF32) against the oracle's convolution.
 
 The reference has no code behind the name (ConvTest.cpp:369-371), so the expected values are those of its im2col
 layer restated by the oracle (im2colConv.cpp:285-309 + the sequential GEMM).  Tolerance: relative L2 <= 3e-3, the
@@ -58,6 +58,29 @@ def test_direct_tf32_within_tolerance(ctx, oracle, case):
     layer.release()
 
 
+STRIDED = [  # n, ic, oc, ih, iw, kh, kw, sh, sw, pad
+    (1, 8, 8, 15, 15, 3, 3, 2, 2, 1), (2, 64, 48, 28, 28, 1, 1, 2, 2, 0), (1, 32, 16, 20, 21, 3, 3, 2, 2, 1),
+    (4, 128, 128, 56, 56, 3, 3, 2, 2, 1), (1, 40, 24, 30, 30, 5, 5, 2, 2, 2), (1, 3, 16, 64, 64, 7, 7, 2, 2, 3),
+    (1, 16, 16, 21, 18, 3, 3, 2, 1, 1), (1, 16, 16, 18, 21, 3, 3, 1, 2, 1),  # a stride along one axis only
+]
+
+
+@pytest.mark.parametrize("case", STRIDED)
+def test_direct_strided_layers(ctx, oracle, case):
+    """Stride 2 is the element stride of the input's tensor map: same kernel, every second pixel of a twice larger box."""
+    n, ic, oc, ih, iw, kh, kw, sh, sw, pad = case
+    x = synth.conv_input(n, ic, ih, iw, 101)
+    w = synth.conv_weights(oc, ic, kh, kw, 102)
+    layer = fc.ConvDirectLayer(x, w, None, None, ic, ih, iw, oc, kh, kw, sh, sw, pad, pad, pad, pad, 1, False, 1, 1,
+                               batch=n, mode="tf32", ctx=ctx)
+    layer.Init(); layer.Forward()
+    assert layer.algorithm == _lib.ALGO_DIRECT
+    want = oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad)
+    assert layer.output_data.shape == want.shape
+    assert rel_l2(layer.output_data, want) <= 1e-3
+    layer.release()
+
+
 def test_direct_epilogue_and_repeatability(ctx, oracle):
     case = (2, 48, 72, 28, 28, 3, 3, 1, 1, 1, 1)
     n, ic, oc, ih, iw, kh, kw, pl, pr, pt, pb = case
@@ -77,13 +100,13 @@ def test_direct_epilogue_and_repeatability(ctx, oracle):
 
 
 def test_direct_falls_back_to_the_implicit_gemm(ctx, oracle, capsys):
-    """Strided layers and the other math modes have no direct kernel: they run as the im2col layer, bit-exact in fp32."""
+    """Strides above 2 and the other math modes have no direct kernel: they run as the im2col layer, bit-exact in fp32."""
     x = synth.conv_input(1, 8, 15, 15, 96)
     w = synth.conv_weights(8, 8, 3, 3, 97)
-    strided = fc.ConvDirectLayer(x, w, None, None, 8, 15, 15, 8, 3, 3, 2, 2, 1, 1, 1, 1, 1, False, 1, 1, mode="tf32", ctx=ctx)
+    strided = fc.ConvDirectLayer(x, w, None, None, 8, 15, 15, 8, 3, 3, 3, 3, 1, 1, 1, 1, 1, False, 1, 1, mode="tf32", ctx=ctx)
     strided.Init(); strided.Forward()
     assert strided.algorithm == _lib.ALGO_IM2COL
-    assert rel_l2(strided.output_data, oracle.im2col_gemm_forward(x, w, 2, 2, 1, 1, 1, 1)) <= 3e-3
+    assert rel_l2(strided.output_data, oracle.im2col_gemm_forward(x, w, 3, 3, 1, 1, 1, 1)) <= 3e-3
     strided.release()
     exact = fc.make_layer("direct", x, w, None, None, 8, 15, 15, 8, 3, 3, 1, 1, 1, 1, 1, 1, ctx=ctx)  # mode fp32
     assert isinstance(exact, fc.ConvDirectLayer)
