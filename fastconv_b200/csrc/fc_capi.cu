@@ -1101,6 +1101,8 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
     if (c->auto_requested && c->mode == FC_MATH_TF32 && direct_tc_eligible(c->desc) && c->algo != FC_ALGO_DIRECT &&
         conv_prepare(c, FC_ALGO_DIRECT) == FC_OK)
         enumerate_candidates(c, FC_ALGO_DIRECT, &cands);
+    if (c->auto_requested && c->algo == FC_ALGO_DIRECT && !c->wino_eligible && conv_prepare(c, FC_ALGO_IM2COL) == FC_OK)
+        enumerate_candidates(c, FC_ALGO_IM2COL, &cands);  // `auto` chose the direct kernel over the gathering one: time both
     const int start_algo = c->algo;
     const KernelCfg start_cfg = c->cfg;
     TuneCandidate best;

@@ -89,3 +89,31 @@ def test_im2col_tuning(ctx, oracle, tuning_log, capfd):
     layer.Forward()
     assert np.array_equal(layer.output_data, oracle.im2col_gemm_forward(x, w, 2, 2, 1, 1, 1, 1))
     layer.release()
+
+
+@pytest.mark.parametrize("case, rivals", [
+    ((4, 256, 128, 28, 1, 0), ("algo=direct", "algo=im2col")),     # 1x1: direct against the gathering kernel
+    ((1, 64, 64, 56, 3, 1), ("algo=direct", "algo=winograd")),     # 3x3, few channels: direct against Winograd
+])
+def test_auto_in_tf32_times_the_direct_kernel_against_its_rival(ctx, oracle, tuning_log, capfd, case, rivals):
+    n, ic, oc, hw, k, pad = case
+    lib = fc.load()
+    x = synth.conv_input(n, ic, hw, hw, 531)
+    w = synth.conv_weights(oc, ic, k, k, 532)
+    d = fc.make_desc(n, ic, hw, hw, oc, k, k, 1, 1, pad, pad, pad, pad)
+    h = C.c_void_p()
+    fc._lib.check(lib.fc_conv_create(ctx.handle, C.byref(d), fc.ALGO_AUTO, fc.MATH_TF32, C.c_void_p(w.ctypes.data), C.byref(h)),
+                  "create")
+    algo = C.c_int()
+    lib.fc_conv_algorithm(h, C.byref(algo))
+    assert algo.value == fc.ALGO_DIRECT  # the untuned choice for these shapes
+    fc._lib.check(lib.fc_conv_tune(h, 5, 1), "tune")
+    out = capfd.readouterr().out
+    for label in rivals:
+        assert label in out
+    y = np.empty((n, oc, hw, hw), np.float32)
+    fc._lib.check(lib.fc_conv_forward_host(h, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)), "forward")
+    lib.fc_conv_algorithm(h, C.byref(algo))
+    tol = 8e-3 if algo.value == fc.ALGO_WINOGRAD else 3e-3  # single-pass TF32 through F(6x6,3x3) is 6.4e-3
+    assert rel_l2(y, oracle.im2col_gemm_forward(x, w, 1, 1, pad, pad, pad, pad)) <= tol
+    lib.fc_conv_destroy(h)
