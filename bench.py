@@ -291,7 +291,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="fastconv", choices=["fastconv", "reference"])
-    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32"])
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-strict"],
+                    help="tf32-strict (with --algo auto): TF32 only where it stays within 3e-3 of fp32 -- per layer the direct "
+                         "tensor-core kernel or the bit-exact fp32 Winograd path")
     ap.add_argument("--batch", type=int, default=1, help="images per GPU")
     ap.add_argument("--layers", default="vgg16",
                     help="'vgg16' (the 13-layer stack) or a list 'C,K,H;C,K,H;...' of 3x3 s1 p1 layers")
@@ -461,8 +463,10 @@ def main():
         nl = C.c_int()
         lib.fc_conv_launches_per_forward(hdl, C.byref(nl))
         launches_per_step += nl.value
-        algo = C.c_int()
+        algo, resolved = C.c_int(), C.c_int()
         lib.fc_conv_algorithm(hdl, C.byref(algo))
+        lib.fc_conv_math_mode(hdl, C.byref(resolved))
+        layer_mode = {0: "fp32", 1: "3xtf32", 2: "tf32"}[resolved.value]  # tf32-strict resolves per layer
         is_wino = algo.value == _lib.ALGO_WINOGRAD
         t, tp, icp = wino_geometry(n, c, k, h)
         # roofline of a layer: the slower of its flops (Winograd-domain for a Winograd layer, direct otherwise) at the
@@ -472,11 +476,11 @@ def main():
         bytes_wino = 4.0 * (n * c * h * h + 64 * c * k + n * k * h * h) if is_wino else bytes_min
         wino_flops = 2.0 * 64 * t * c * k if is_wino else layer_flops(n, c, k, h)
         t_hbm_ms = bytes_wino / hbm_peak / 1e6
-        t_flop_ms = wino_flops / (MODE_PEAK_TFLOPS[args.mode] * 1e12) * 1e3
+        t_flop_ms = wino_flops / (MODE_PEAK_TFLOPS[layer_mode] * 1e12) * 1e3
         roof_ms = max(t_hbm_ms, t_flop_ms)
         roof_sum_ms += roof_ms
         per_layer.append({
-            "layer": f"{c}->{k}@{h}", "algo": {v: kk for kk, v in _lib.ALGO_NAMES.items()}[algo.value],
+            "layer": f"{c}->{k}@{h}", "algo": {v: kk for kk, v in _lib.ALGO_NAMES.items()}[algo.value], "math": layer_mode,
             "ms": round(one.value, 5),
             "gflops_direct_equiv": round(layer_flops(n, c, k, h) / one.value / 1e6, 1),
             "stage_ms": [round(float(v), 5) for v in ms],
@@ -503,10 +507,10 @@ def main():
         "kernel": "TensorGEMM (64 batched U*V products, one launch per layer)",
         "bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
         "frac": round(achieved_gbs / hbm_peak, 4), "peak_source": f"of {peak_kind}",
-        "traffic": NCU_GEMM_TRAFFIC_BYTES[args.mode] if (args.layers == "vgg16" and n == 1) else None,
+        "traffic": NCU_GEMM_TRAFFIC_BYTES.get(args.mode) if (args.layers == "vgg16" and n == 1 and args.algo == "winograd") else None,
         "algorithmic_bytes_per_launch": gemm_bytes / nl, "avg_launch_ms": gemm_ms / nl,
         "stack_roofline_ms": round(roof_sum_ms, 5), "stack_frac_of_roofline": round(roof_sum_ms / ms_step, 4),
-        "arithmetic_peak_tflops": round(MODE_PEAK_TFLOPS[args.mode], 1),
+        "arithmetic_peak_tflops": round(MODE_PEAK_TFLOPS.get(args.mode, TF32_TFLOPS), 1),
         "winograd_domain_tflops": round(gemm_flops / (gemm_ms / 1e3) / 1e12, 2) if gemm_ms > 0 else None,
         "share_of_step": {"InputTran": round(stage_tot[0] / stage_tot[4], 3), "TensorGEMM": round(stage_tot[2] / stage_tot[4], 3),
                           "OutputTran": round(stage_tot[3] / stage_tot[4], 3)},
@@ -532,7 +536,8 @@ def main():
             "metric": "conv GFLOP/s (direct-equiv), VGG-16 conv stack", "value": round(value, 1), "unit": "GFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32"}[args.mode], "data": "synthetic",
+            "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32", "tf32-strict": "tf32/f32 per layer"}[args.mode],
+            "data": "synthetic",
             "config": {"workload": f"{workload_name}, batch {n} per GPU, 224x224, 3x3 s1 p1, fp32 NCHW",
                        "algorithm": {"winograd": "winograd F(6x6,3x3)", "direct": "direct convolution on the tensor cores",
                                      "auto": "per layer: winograd F(6x6,3x3) or direct convolution on the tensor cores"}[args.algo],

@@ -14,8 +14,9 @@ FC_OK = 0
 (FC_ERR_INVALID_ARG, FC_ERR_UNSUPPORTED, FC_ERR_OUT_OF_MEMORY, FC_ERR_CUDA, FC_ERR_NO_DEVICE, FC_ERR_TIMEOUT,
  FC_ERR_COMM) = -1, -2, -3, -4, -5, -6, -7
 ALGO_AUTO, ALGO_DIRECT, ALGO_IM2COL, ALGO_WINOGRAD = 0, 1, 2, 3
-MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32 = 0, 1, 2
-MODE_NAMES = {"fp32": MATH_FP32_MIRRORED, "ffma": MATH_FP32_MIRRORED, "3xtf32": MATH_3XTF32, "tf32": MATH_TF32}
+MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32, MATH_TF32_STRICT = 0, 1, 2, 3
+MODE_NAMES = {"fp32": MATH_FP32_MIRRORED, "ffma": MATH_FP32_MIRRORED, "3xtf32": MATH_3XTF32, "tf32": MATH_TF32,
+              "tf32-strict": MATH_TF32_STRICT}
 ALGO_NAMES = {"auto": ALGO_AUTO, "direct": ALGO_DIRECT, "im2col": ALGO_IM2COL, "winograd": ALGO_WINOGRAD}
 
 
@@ -82,6 +83,7 @@ SIGNATURES = {
     "fc_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "fc_conv_destroy": (C.c_int, [_vp]),
     "fc_conv_algorithm": (C.c_int, [_vp, _ip]),
+    "fc_conv_math_mode": (C.c_int, [_vp, _ip]),
     "fc_conv_forward_device": (C.c_int, [_vp, _vp, _vp]),
     "fc_conv_forward_host": (C.c_int, [_vp, _vp, _vp]),
     "fc_conv_device_buffers": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),

@@ -111,6 +111,7 @@ struct fc_conv {
     KernelCfg cfg;        // all zero = launcher heuristics; set by fc_conv_tune
     bool auto_requested;  // created with FC_ALGO_AUTO: Tuning may switch between Winograd and im2col
     bool wino_eligible;   // 3x3, stride 1, symmetric padding
+    bool strict;          // created with FC_MATH_TF32_STRICT: `mode` is what that resolved to
 };
 
 extern "C" {
@@ -681,17 +682,34 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
                    fc_conv **out) {
     FC_REQUIRE(ctx && desc && h_kernel && out, FC_ERR_INVALID_ARG, "NULL argument");
     *out = nullptr;
-    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32, FC_ERR_INVALID_ARG, "unknown math mode %d",
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32_STRICT, FC_ERR_INVALID_ARG, "unknown math mode %d",
                mode);
     FC_REQUIRE(algo >= FC_ALGO_AUTO && algo <= FC_ALGO_WINOGRAD, FC_ERR_INVALID_ARG, "unknown algorithm %d", algo);
     int oh, ow;
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
     const bool auto_requested = algo == FC_ALGO_AUTO;
     if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const bool strict = mode == FC_MATH_TF32_STRICT;
+    if (strict) {
+        // TF32 only where it stays within 3e-3: never through F(6x6,3x3).  A layer headed for Winograd takes the direct
+        // tensor-core kernel, or stays on Winograd in the bit-exact fp32 arithmetic where that is the faster of the two
+        // (and whenever Winograd was asked for by name); every other layer is as accurate in TF32 as it is.
+        if (algo == FC_ALGO_WINOGRAD) {
+            if (auto_requested && direct_tc_preferred(*desc, oh, ow, sms, DIRECT_VS_WINOGRAD_FP32)) {
+                algo = FC_ALGO_DIRECT;
+                mode = FC_MATH_TF32;
+            } else {
+                mode = FC_MATH_FP32_MIRRORED;
+            }
+        } else {
+            mode = FC_MATH_TF32;
+        }
+    }
     // the TF32 mode states a tolerance, not an algorithm: where the direct tensor-core kernel is the faster way to
     // meet it, `auto` takes it (Tuning() still measures all of them)
     if (auto_requested && mode == FC_MATH_TF32 &&
-        direct_tc_preferred(*desc, oh, ow, ctx->sm_count > 0 ? ctx->sm_count : 148, algo == FC_ALGO_WINOGRAD))
+        direct_tc_preferred(*desc, oh, ow, sms, algo == FC_ALGO_WINOGRAD ? DIRECT_VS_WINOGRAD_TF32 : DIRECT_VS_GATHER))
         algo = FC_ALGO_DIRECT;
     // the direct tensor-core kernel is a TF32 kernel for ungrouped layers of stride 1 or 2; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
@@ -710,6 +728,7 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     c->ctx = ctx; c->desc = *desc; c->algo = algo; c->mode = mode; c->oh = oh; c->ow = ow; c->geom = g;
     c->auto_requested = auto_requested;
     c->wino_eligible = wino_eligible;
+    c->strict = strict;
 
     const size_t k_elems = (size_t)desc->oc * (desc->ic / desc->group) * desc->kh * desc->kw;  // [oc][ic/group][kh][kw]
     const size_t in_elems = (size_t)desc->batch * desc->ic * desc->ih * desc->iw;
@@ -739,6 +758,12 @@ int fc_conv_destroy(fc_conv *c) {
     cudaSetDevice(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
     conv_release(c);
+    return FC_OK;
+}
+
+int fc_conv_math_mode(const fc_conv *c, int *mode) {
+    FC_REQUIRE(c && mode, FC_ERR_INVALID_ARG, "NULL argument");
+    *mode = c->mode;
     return FC_OK;
 }
 
@@ -1032,7 +1057,7 @@ static const char *tuning_log_path() {
 // one log line: 17 key integers, then algo, bm, bn, skinny, smem_kb and the time in microseconds
 static void tuning_key(const fc_conv *c, int key[17]) {
     const fc_conv_desc &d = c->desc;
-    const int k[17] = {c->ctx->sm_count, c->auto_requested ? FC_ALGO_AUTO : c->algo, c->mode, d.batch, d.ic, d.ih, d.iw,
+    const int k[17] = {c->ctx->sm_count, c->auto_requested ? FC_ALGO_AUTO : c->algo, c->strict ? (int)FC_MATH_TF32_STRICT : c->mode, d.batch, d.ic, d.ih, d.iw,
                        d.oc, d.kh, d.kw, d.sh, d.sw, d.pad_left, d.pad_right, d.pad_top, d.pad_bottom, d.group};
     memcpy(key, k, sizeof k);
 }
@@ -1094,7 +1119,8 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
     std::vector<TuneCandidate> cands;
     enumerate_candidates(c, c->algo, &cands);
-    if (c->auto_requested && c->wino_eligible) {
+    // (a strict layer that runs in TF32 must not be moved onto the Winograd path, which misses its tolerance there)
+    if (c->auto_requested && c->wino_eligible && !(c->strict && c->mode == FC_MATH_TF32)) {
         const int other = c->algo == FC_ALGO_WINOGRAD ? FC_ALGO_IM2COL : FC_ALGO_WINOGRAD;
         if (conv_prepare(c, other) == FC_OK) enumerate_candidates(c, other, &cands);
     }

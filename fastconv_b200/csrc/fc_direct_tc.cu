@@ -327,15 +327,18 @@ static void direct_patch_shape(int oh, int ow, int *bh, int *bw) {
 //    items and 0.15 GFLOP; below that the extra launch of the layout pass decides.  Not with a handful of channels
 //    and taps that do not fold (the 7x7 stride-2 stem: 3 real channels in every 32-wide k-block, 0.69 against 0.57 ms
 //    at batch 64).
-bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bool over_winograd) {
+//  * against the bit-exact fp32 Winograd path (the alternative when single-pass TF32 through Winograd is not
+//    accurate enough): at batch 8 and 64 it wins on every VGG-16 layer (1.5x to 2.4x), at batch 1 up to 128 -> 128
+//    channels; it loses where a layer has both few work items and many channels (512 -> 512 at 14x14, batch 1:
+//    0.064 against 0.026 ms).
+bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, int rival) {
     if (!direct_tc_eligible(d)) return false;
     int bh = 8, bw = 16;
     direct_patch_shape(oh, ow, &bh, &bw);
     const double items = (double)ceil_div(oh, bh) * ceil_div(ow, bw) * d.batch * ceil_div(d.oc, 128);
-    if (over_winograd) {
-        const double h = (double)d.ic * d.oc / (d.ic + d.oc);
-        return h <= 100.0 && (items >= sm_count || h <= 48.0);
-    }
+    const double h = (double)d.ic * d.oc / (d.ic + d.oc);
+    if (rival == DIRECT_VS_WINOGRAD_TF32) return h <= 100.0 && (items >= sm_count || h <= 48.0);
+    if (rival == DIRECT_VS_WINOGRAD_FP32) return items >= 48 || h <= 64.0;
     const double flops = 2.0 * d.batch * d.oc * d.ic * d.kh * d.kw * oh * ow;
     return items >= 16 && flops >= 1.5e8 && (d.ic >= 16 || folds_taps(d));
 }

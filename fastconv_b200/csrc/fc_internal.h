@@ -185,7 +185,8 @@ int launch_igemm_tc(fc_context *ctx, const float *d_in, const float *d_packed, f
                     const Epilogue &ep = kNoEpilogue, size_t in_img_stride = 0, size_t out_img_stride = 0);
 // direct convolution on the tensor cores (stride 1 or 2, TF32): NHWC copy of the input + shifted TMA boxes
 bool direct_tc_eligible(const fc_conv_desc &d);
-bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, bool over_winograd);
+enum { DIRECT_VS_GATHER = 0, DIRECT_VS_WINOGRAD_TF32 = 1, DIRECT_VS_WINOGRAD_FP32 = 2 };  // what it would replace
+bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, int rival);
 size_t direct_nhwc_elems(const fc_conv_desc &d);
 size_t direct_packed_elems(const fc_conv_desc &d);
 int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_wp, const fc_conv_desc &d);

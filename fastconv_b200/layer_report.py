@@ -50,14 +50,15 @@ def peaks(mode: str):
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         hbm = float(json.loads(p.read_text())["hbm_gbs"])
-    flops = {"fp32": 63.7, "tf32": 759.9, "3xtf32": 759.9 / 3}[mode]
+    flops = {"fp32": 63.7, "tf32": 759.9, "3xtf32": 759.9 / 3, "tf32-strict": 759.9}[mode]
     return hbm, flops
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--set", default="resnet50", choices=sorted(SETS))
-    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32"])
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-strict"],
+                    help="tf32-strict: TF32 only where it stays within 3e-3 (direct kernel or fp32 Winograd per layer)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--tune", action="store_true", help="run Tuning() (timed configuration search) before measuring")
@@ -89,8 +90,11 @@ def main() -> None:
             ctx.upload(x, d_in.value)
             ms = C.c_float()
             _lib.check(lib.fc_conv_time_device(h, d_in, d_out, 5, args.iters, C.byref(ms)), "fc_conv_time_device")
-            algo = C.c_int()
+            algo, resolved = C.c_int(), C.c_int()
             lib.fc_conv_algorithm(h, C.byref(algo))
+            lib.fc_conv_math_mode(h, C.byref(resolved))  # what tf32-strict turned into for this layer
+            mode_name = {0: "fp32", 1: "3xtf32", 2: "tf32"}[resolved.value]
+            hbm, peak_tf = peaks(mode_name)
             oh = (hw + 2 * p - k) // s + 1
             direct = 2.0 * n * oc * ic * k * k * oh * oh
             if algo.value == _lib.ALGO_WINOGRAD:
@@ -100,7 +104,7 @@ def main() -> None:
                 flops, nbytes = direct, 4.0 * (n * ic * hw * hw + oc * ic * k * k + n * oc * oh * oh)
             roof_ms = max(flops / (peak_tf * 1e12), nbytes / (hbm * 1e9)) * 1e3
             print(json.dumps({
-                "layer": f"{ic}->{oc}@{hw} {k}x{k}s{s}", "batch": n, "mode": args.mode,
+                "layer": f"{ic}->{oc}@{hw} {k}x{k}s{s}", "batch": n, "mode": mode_name,
                 "algo": {v: k for k, v in _lib.ALGO_NAMES.items()}[algo.value], "ms": round(ms.value, 5),
                 "gflops_direct_equiv": round(direct / ms.value / 1e6, 1), "roofline_ms": round(roof_ms, 5),
                 "frac_of_roofline": round(roof_ms / ms.value, 4),

@@ -54,7 +54,12 @@ typedef enum fc_math_mode {
     FC_MATH_FP32_MIRRORED = 0, /* FFMA, one fused multiply-add per reduction step in ascending order:
                                   bit-identical to the reference's accumulation chain            */
     FC_MATH_3XTF32 = 1,        /* tcgen05 tensor cores, hi/lo TF32 split, fp32 accumulate         */
-    FC_MATH_TF32 = 2           /* tcgen05 tensor cores, single TF32 pass                          */
+    FC_MATH_TF32 = 2,          /* tcgen05 tensor cores, single TF32 pass                          */
+    FC_MATH_TF32_STRICT = 3    /* fc_conv_create only: TF32 wherever it stays within rel-L2 3e-3 of the fp32 result.
+                                  Single-pass TF32 through F(6x6,3x3) does not (6.4e-3), so a Winograd-eligible layer
+                                  runs the direct tensor-core kernel in TF32 or, where that is slower (few work items,
+                                  many channels), the Winograd path in FC_MATH_FP32_MIRRORED; other layers run as in
+                                  FC_MATH_TF32.  fc_conv_math_mode reports the mode the layer was planned with. */
 } fc_math_mode;
 
 typedef struct fc_conv_desc {
@@ -194,6 +199,9 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
                    fc_conv **out);
 int fc_conv_destroy(fc_conv *conv);
 int fc_conv_algorithm(const fc_conv *conv, int *algo);
+/* The arithmetic the layer runs in: the mode given to fc_conv_create, or what FC_MATH_TF32_STRICT resolved to
+ * (FC_MATH_TF32 or FC_MATH_FP32_MIRRORED).  No reference counterpart: the reference computes in fp32 only. */
+int fc_conv_math_mode(const fc_conv *conv, int *mode);
 /* Epilogue of the layer: every output element becomes relu(y + bias[oc]) before it is stored (both
  * parts optional: h_bias NULL = no bias, relu 0 = no clamp).  The reference carries a bias operand
  * (bias_term / bias_data, conv_layer.h:46-48,72-77) that only its general naive layer adds

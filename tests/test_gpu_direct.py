@@ -130,3 +130,40 @@ def test_direct_vgg_layer_and_tuner(ctx, oracle, tmp_path, monkeypatch):
     assert err <= 1e-3, err
     assert layer.kernel_launches == 2
     layer.release()
+
+
+def _create(ctx, desc, algo, mode, w):
+    import ctypes as C
+    lib = fc.load()
+    h = C.c_void_p()
+    _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), algo, mode, C.c_void_p(w.ctypes.data), C.byref(h)), "create")
+    a, m = C.c_int(), C.c_int()
+    lib.fc_conv_algorithm(h, C.byref(a))
+    lib.fc_conv_math_mode(h, C.byref(m))
+    return lib, h, a.value, m.value
+
+
+@pytest.mark.parametrize("shape, algo_in, want_algo, want_mode", [
+    # n, ic, oc, hw, k, pad
+    ((1, 64, 64, 56, 3, 1), "auto", "direct", "tf32"),          # few channels: the direct kernel
+    ((1, 512, 512, 14, 3, 1), "auto", "winograd", "fp32"),       # 8 work items, many channels: Winograd, bit-exact
+    ((8, 512, 512, 14, 3, 1), "auto", "direct", "tf32"),         # the same layer with 64 work items
+    ((1, 64, 64, 56, 3, 1), "winograd", "winograd", "fp32"),     # Winograd by name: only its fp32 arithmetic complies
+    ((4, 256, 128, 28, 1, 0), "auto", "direct", "tf32"),         # not a Winograd layer: as in the TF32 mode
+    ((1, 16, 12, 14, 1, 0), "auto", "im2col", "tf32"),
+])
+def test_strict_tf32_mode_never_runs_tf32_through_winograd(ctx, oracle, shape, algo_in, want_algo, want_mode):
+    import ctypes as C
+    n, ic, oc, hw, k, pad = shape
+    x = synth.conv_input(n, ic, hw, hw, 111)
+    w = synth.conv_weights(oc, ic, k, k, 112)
+    d = fc.make_desc(n, ic, hw, hw, oc, k, k, 1, 1, pad, pad, pad, pad)
+    lib, h, algo, mode = _create(ctx, d, _lib.ALGO_NAMES[algo_in], _lib.MATH_TF32_STRICT, w)
+    assert algo == _lib.ALGO_NAMES[want_algo] and mode == _lib.MODE_NAMES[want_mode]
+    y = np.empty((n, oc, hw, hw), np.float32)
+    _lib.check(lib.fc_conv_forward_host(h, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)), "forward")
+    if want_algo == "winograd":
+        assert np.array_equal(y, oracle.wino_forward(x, w, 1))
+    else:
+        assert rel_l2(y, oracle.im2col_gemm_forward(x, w, 1, 1, pad, pad, pad, pad)) <= 3e-3
+    lib.fc_conv_destroy(h)
