@@ -788,6 +788,11 @@ static bool igemm_on_fp32_pipe(const fc_conv *c) {
     return K <= (c->mode == FC_MATH_3XTF32 ? 512 : 256) && flops <= 500000000ll;  // short reduction AND a small problem
 }
 
+static int direct_launches(const fc_conv *c) {
+    return direct_tc_launches(c->desc, c->oh, c->ow, c->ctx->sm_count > 0 ? c->ctx->sm_count : 148, &c->cfg,
+                              c->d_bias != nullptr || c->relu);
+}
+
 // kernel launches of one forward of an implicit-GEMM layer
 static int igemm_launches(const fc_conv *c) {
     if (c->desc.group > 1) return c->desc.group == c->desc.ic ? 1 : c->desc.group;
@@ -1172,7 +1177,7 @@ int fc_conv_tune(fc_conv *c, int iters, int verbose) {
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : c->algo == FC_ALGO_DIRECT ? 2 : igemm_launches(c);
+    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : c->algo == FC_ALGO_DIRECT ? direct_launches(c) : igemm_launches(c);
     return FC_OK;
 }
 
@@ -1199,7 +1204,7 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
         launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i])
-                    : convs[i]->algo == FC_ALGO_DIRECT ? 2 : igemm_launches(convs[i]);
+                    : convs[i]->algo == FC_ALGO_DIRECT ? direct_launches(convs[i]) : igemm_launches(convs[i]);
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));
     // one eager pass first: kernel attributes are set and any error shows up outside the capture

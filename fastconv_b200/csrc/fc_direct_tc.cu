@@ -39,6 +39,7 @@ struct DirectParams {
     int pad_t, pad_l, sh, sw;
     int stages, acc_cols, n_items;
     int b_bytes;
+    int ksplit, kb_per_split;  // the taps*num_kb k-blocks of an output block are shared by ksplit work items
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
@@ -50,7 +51,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
 }
 
 // channel block fastest: CTAs next to each other read the same input patch
-__device__ __forceinline__ void item_coords(const DirectParams &P, int item, int &img, int &y0, int &x0, int &oc0) {
+__device__ __forceinline__ void item_coords(const DirectParams &P, int item, int &img, int &y0, int &x0, int &oc0,
+                                            int &k_lo, int &k_hi) {
+    const int part = item % P.ksplit;  // which share of the reduction
+    item /= P.ksplit;
+    k_lo = part * P.kb_per_split;
+    k_hi = min(P.taps * P.num_kb, k_lo + P.kb_per_split);
     oc0 = (item % P.n_oc_items) * P.bn;
     int patch = item / P.n_oc_items;
     x0 = (patch % P.n_px) * P.bw;
@@ -101,8 +107,6 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     pdl_trigger();
 
-    const int kb_per_item = P.taps * P.num_kb;
-
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -110,22 +114,21 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
             int g = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
-                int img, y0, x0, oc0;
-                item_coords(P, item, img, y0, x0, oc0);
-                for (int tap = 0; tap < P.taps && ok; ++tap) {
+                int img, y0, x0, oc0, k_lo, k_hi;
+                item_coords(P, item, img, y0, x0, oc0, k_lo, k_hi);
+                for (int k = k_lo; k < k_hi; ++k, ++g) {
+                    const int tap = k / P.num_kb, kb = k - tap * P.num_kb;
                     const int u = tap / P.kw, v = tap - u * P.kw;
-                    for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
-                        const int s = g % S;
-                        const uint32_t ph = (uint32_t)(g / S) & 1u;
-                        ok = mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status);
-                        if (!ok) break;
-                        const uint32_t dst = ring + s * stage_bytes;
-                        mbar_expect_tx(bar_full(s), stage_bytes);
-                        // innermost coordinate = channel block (a multiple of 32 floats); x and y may be negative or
-                        // past the image: those pixels read as zero
-                        tma_load_4d(dst, &tmX, bar_full(s), kb * BK, x0 * P.sw + v - P.pad_l, y0 * P.sh + u - P.pad_t, img);
-                        tma_load_3d(dst + A_BYTES, &tmW, bar_full(s), kb * BK, oc0, tap);
-                    }
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status);
+                    if (!ok) break;
+                    const uint32_t dst = ring + s * stage_bytes;
+                    mbar_expect_tx(bar_full(s), stage_bytes);
+                    // innermost coordinate = channel block (a multiple of 32 floats); x and y may be negative or
+                    // past the image: those pixels read as zero
+                    tma_load_4d(dst, &tmX, bar_full(s), kb * BK, x0 * P.sw + v - P.pad_l, y0 * P.sh + u - P.pad_t, img);
+                    tma_load_3d(dst + A_BYTES, &tmW, bar_full(s), kb * BK, oc0, tap);
                 }
             }
         }
@@ -142,6 +145,9 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.acc_cols);
+                int img, y0, x0, oc0, k_lo, k_hi;
+                item_coords(P, item, img, y0, x0, oc0, k_lo, k_hi);
+                const int kb_per_item = k_hi - k_lo;
                 for (int kb = 0; kb < kb_per_item; ++kb, ++g) {
                     const int s = g % S;
                     const uint32_t ph = (uint32_t)(g / S) & 1u;
@@ -167,8 +173,8 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
         int it = 0;
         bool ok = true, waited = false;
         for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
-            int img, y0, x0, oc0;
-            item_coords(P, item, img, y0, x0, oc0);
+            int img, y0, x0, oc0, k_lo, k_hi;
+            item_coords(P, item, img, y0, x0, oc0, k_lo, k_hi);
             if (!waited) {  // the output may still be read by whatever consumed the forward before this one
                 pdl_wait();
                 waited = true;
@@ -190,10 +196,14 @@ __global__ void __launch_bounds__(TC_THREADS) direct_tc_kernel(const __grid_cons
                     tc_fence_before();
                     mbar_arrive(bar_acc_empty(acc));
                 }
-                if (inside) {
+                if (inside && P.ksplit == 1) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         if (oc0 + c0 + j < P.oc) dst[(size_t)(c0 + j) * plane] = P.ep(va[j], oc0 + c0 + j);
+                } else if (inside) {  // a share of the reduction: added into the zeroed output (no epilogue then)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (oc0 + c0 + j < P.oc) atomicAdd(dst + (size_t)(c0 + j) * plane, va[j]);
                 }
             }
         }
@@ -233,6 +243,15 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restri
         const int p = p0 + ty + 8 * i;
         if (p < HW) out[(img * HW + p) * Cp + c0 + tx] = tile[tx][ty + 8 * i];
     }
+}
+
+// out[n][oc][plane] <- relu(out + bias[oc]): the epilogue of a layer whose reduction was shared by several work items
+__global__ void __launch_bounds__(256) bias_relu_kernel(float *__restrict__ out, Epilogue ep, int oc, int plane,
+                                                       size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = ep(out[i], (int)((i / plane) % oc));
 }
 
 // W[oc][ic][kh][kw] -> Wp[tap = u*kw + v][oc][icp], channels ic..icp-1 zero
@@ -355,6 +374,65 @@ size_t direct_packed_elems(const fc_conv_desc &d) {
     return folds_taps(d) ? (size_t)d.oc * BK : (size_t)d.kh * d.kw * d.oc * round_up(d.ic, BK);
 }
 
+// How a layer (taps already folded where they fold) is cut into work items.
+struct DirectPlan {
+    int bh, bw, n_px, n_py;   // patch of 128 output pixels and patches per image
+    int n_oc_items, bn;       // channel blocks
+    int ksplit, kb_per_split; // shares of the reduction per output block, k-blocks per share
+    long long blocks;         // output blocks = patches x channel blocks
+};
+
+static DirectPlan make_plan(const fc_conv_desc &d, int oh, int ow, int sm_count, const KernelCfg *cfg) {
+    DirectPlan p;
+    p.bh = 8; p.bw = 16;
+    direct_patch_shape(oh, ow, &p.bh, &p.bw);
+    p.n_px = (int)ceil_div(ow, p.bw);
+    p.n_py = (int)ceil_div(oh, p.bh);
+    const size_t patches = (size_t)p.n_px * p.n_py * d.batch;
+    // Channel blocks of up to 128, or of up to 256: then one CTA per SM holds all of TMEM and moves a quarter less
+    // operand bytes per flop.  Measured on the VGG-16 layers with 256 and 512 channels: 447 -> 472 and 481 -> 504
+    // TFLOP/s at batch 64, but 4 % slower at batch 8 where a 256-wide block leaves under two work items per SM.
+    int max_bn = d.oc >= 256 && patches * ceil_div(d.oc, 256) >= 4 * (size_t)sm_count ? 256 : 128;
+    // Fewer work items than SMs: channel blocks of 64 put the layer on more SMs (the pixels are then fetched once per
+    // block more, which idle SMs do for free).  cfg.bn = 128 or 256 (Tuning()) overrides.
+    while (max_bn > 64 && patches * ceil_div(d.oc, max_bn) < (size_t)sm_count) max_bn /= 2;
+    if (cfg && (cfg->bn == 128 || cfg->bn == 256)) max_bn = cfg->bn;
+    p.n_oc_items = (int)ceil_div(d.oc, max_bn);
+    p.bn = round_up((int)ceil_div(d.oc, p.n_oc_items), 16);  // balanced blocks of channels
+    p.blocks = (long long)patches * p.n_oc_items;
+    // Still no more output blocks than SMs (the 28x28 and 14x14 layers of one image, every ResNet-50 layer at batch 1):
+    // an SM pulls its operands at some 50 GB/s, so a long reduction on a few SMs is bound by that.  The reduction is
+    // then shared by several work items (two CTAs per SM in all, at least four k-blocks each) that add their partial
+    // sums into the zeroed output; a bias or ReLU follows in a pass of its own.  The order of the additions, hence
+    // the last bits of the result, may differ from run to run.  512 -> 512 at 14x14, one image: 0.064 -> 0.0145 ms.
+    const int kb_total = d.kh * d.kw * (round_up(d.ic, BK) / BK);
+    p.ksplit = 1;
+    if (p.blocks <= sm_count && kb_total >= 8) {
+        int want = (int)(2 * sm_count / p.blocks);
+        if (want > kb_total / 4) want = kb_total / 4;
+        if (want > 1) p.ksplit = want;
+    }
+    p.kb_per_split = (int)ceil_div(kb_total, p.ksplit);
+    p.ksplit = (int)ceil_div(kb_total, p.kb_per_split);
+    return p;
+}
+
+// the layer as the tensor-core kernel sees it: a 1x1, unpadded layer over 32 channels when the taps fold
+static fc_conv_desc kernel_view(const fc_conv_desc &full, int oh, int ow) {
+    fc_conv_desc d = full;
+    if (folds_taps(full)) {
+        d.ic = BK; d.ih = oh; d.iw = ow; d.kh = d.kw = 1;
+        d.pad_left = d.pad_right = d.pad_top = d.pad_bottom = 0;
+    }
+    return d;
+}
+
+// kernel launches of one forward: the layout pass, the tensor-core kernel, and the bias/ReLU pass of a shared reduction
+int direct_tc_launches(const fc_conv_desc &full, int oh, int ow, int sm_count, const KernelCfg *cfg, bool has_epilogue) {
+    const DirectPlan p = make_plan(kernel_view(full, oh, ow), oh, ow, sm_count, cfg);
+    return 2 + (p.ksplit > 1 && has_epilogue ? 1 : 0);
+}
+
 int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_wp, const fc_conv_desc &d) {
     // folded taps: a row of W (ic*kh*kw floats) padded to 32 is the one tap of a 1x1 layer over 32 channels
     const bool fold = folds_taps(d);
@@ -377,38 +455,25 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
         FC_CHECK_CUDA(cudaFuncSetAttribute(fold_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FC_CHECK_CUDA(launch_pdl(fold_taps_kernel, dim3((unsigned)(full.batch * oh)), dim3(256), smem, ctx->stream, d_in,
                                  d_nhwc, full.ic, full.ih, full.iw, full.kh, full.kw, full.pad_top, full.pad_left, oh, ow));
-        // from here on: a 1x1, unpadded layer over the 32 folded channels of an oh x ow image
-        d.ic = BK; d.ih = oh; d.iw = ow; d.kh = d.kw = 1;
-        d.pad_left = d.pad_right = d.pad_top = d.pad_bottom = 0;
+        d = kernel_view(full, oh, ow);  // from here on: a 1x1, unpadded layer over the 32 folded channels
     }
     const int icp = round_up(d.ic, BK), hw = d.ih * d.iw;
     if (!folds_taps(full)) {
         dim3 grid((unsigned)ceil_div(hw, 32), (unsigned)(icp / 32), (unsigned)d.batch), block(256);
         FC_CHECK_CUDA(launch_pdl(nchw_to_nhwc_kernel, grid, block, 0, ctx->stream, d_in, d_nhwc, d.ic, icp, hw));
     }
-    int bh = 8, bw = 16;
-    direct_patch_shape(oh, ow, &bh, &bw);
+    const DirectPlan plan = make_plan(d, oh, ow, ctx->sm_count, cfg);
+    const int bh = plan.bh, bw = plan.bw;
+    const bool late_epilogue = plan.ksplit > 1 && (ep.bias != nullptr || ep.relu);
     DirectParams P;
     P.out = d_out;
     P.status = ctx->d_status;
-    P.ep = ep;
+    P.ep = late_epilogue ? kNoEpilogue : ep;
     P.oc = d.oc; P.oh = oh; P.ow = ow;
     P.bh = bh; P.bw = bw;
-    P.n_px = ceil_div(ow, bw);
-    P.n_py = ceil_div(oh, bh);
-    // Channel blocks of up to 128, or of up to 256: then one CTA per SM holds all of TMEM and moves a quarter less
-    // operand bytes per flop.  Measured on the VGG-16 layers with 256 and 512 channels: 447 -> 472 and 481 -> 504
-    // TFLOP/s at batch 64, but 4 % slower at batch 8 where a 256-wide block leaves under two work items per SM.
-    // cfg.bn = 128 or 256 (Tuning()) overrides.
-    const size_t wide_items = (size_t)ceil_div(ow, bw) * ceil_div(oh, bh) * d.batch * ceil_div(d.oc, 256);
-    int max_bn = d.oc >= 256 && wide_items >= 4 * (size_t)ctx->sm_count ? 256 : 128;
-    // fewer work items than SMs: narrower channel blocks (down to 32) put the layer on more SMs; the pixels are then
-    // fetched once per block more, which idle SMs do for free (5-15 % on the batch-1 VGG-16 layers from 64 -> 128 on)
-    const size_t patches = (size_t)ceil_div(ow, bw) * ceil_div(oh, bh) * d.batch;
-    while (max_bn > 32 && patches * ceil_div(d.oc, max_bn) < (size_t)ctx->sm_count) max_bn /= 2;
-    if (cfg && (cfg->bn == 128 || cfg->bn == 256)) max_bn = cfg->bn;
-    P.n_oc_items = ceil_div(d.oc, max_bn);
-    P.bn = round_up(ceil_div(d.oc, P.n_oc_items), 16);  // balanced blocks of channels
+    P.n_px = plan.n_px; P.n_py = plan.n_py;
+    P.n_oc_items = plan.n_oc_items;
+    P.bn = plan.bn;
     P.num_kb = icp / BK;
     P.taps = d.kh * d.kw;
     P.kw = d.kw;
@@ -416,7 +481,12 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
     P.sh = d.sh; P.sw = d.sw;
     P.acc_cols = pow2_at_least(P.bn, 32);
     P.b_bytes = P.bn * BK * 4;
-    const long long items = (long long)P.n_px * P.n_py * d.batch * P.n_oc_items;
+    P.ksplit = plan.ksplit;
+    P.kb_per_split = plan.kb_per_split;
+    const long long blocks = plan.blocks;
+    if (P.ksplit > 1)
+        FC_CHECK_CUDA(cudaMemsetAsync(d_out, 0, (size_t)d.batch * d.oc * oh * ow * sizeof(float), ctx->stream));
+    const long long items = blocks * P.ksplit;
     FC_REQUIRE(items < (1ll << 31), FC_ERR_UNSUPPORTED, "too many work items");
     P.n_items = (int)items;
     const size_t stage_bytes = (size_t)A_BYTES + P.b_bytes;
@@ -436,6 +506,11 @@ int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const fl
     FC_PROPAGATE(make_map_3d(&tmW, d_wp, icp, d.oc, P.taps, P.bn));
     FC_CHECK_CUDA(cudaFuncSetAttribute(direct_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     FC_CHECK_CUDA(launch_pdl(direct_tc_kernel, dim3((unsigned)ctas), dim3(TC_THREADS), smem, ctx->stream, tmX, tmW, P));
+    if (late_epilogue) {
+        const size_t total = (size_t)d.batch * d.oc * oh * ow;
+        const unsigned nb = (unsigned)(ceil_div(total, 256) > (size_t)ctx->sm_count * 8 ? (size_t)ctx->sm_count * 8 : ceil_div(total, 256));
+        FC_CHECK_CUDA(launch_pdl(bias_relu_kernel, dim3(nb), dim3(256), 0, ctx->stream, d_out, ep, d.oc, oh * ow, total));
+    }
     return FC_OK;
 }
 

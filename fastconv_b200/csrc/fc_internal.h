@@ -189,6 +189,7 @@ enum { DIRECT_VS_GATHER = 0, DIRECT_VS_WINOGRAD_TF32 = 1, DIRECT_VS_WINOGRAD_FP3
 bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, int rival);
 size_t direct_nhwc_elems(const fc_conv_desc &d);
 size_t direct_packed_elems(const fc_conv_desc &d);
+int direct_tc_launches(const fc_conv_desc &d, int oh, int ow, int sm_count, const KernelCfg *cfg, bool has_epilogue);
 int launch_direct_pack_weights(fc_context *ctx, const float *d_kernel, float *d_wp, const fc_conv_desc &d);
 int launch_direct_tc(fc_context *ctx, const float *d_in, float *d_nhwc, const float *d_wp, float *d_out,
                      const fc_conv_desc &d, int oh, int ow, const KernelCfg *cfg = nullptr,

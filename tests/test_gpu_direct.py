@@ -81,8 +81,11 @@ def test_direct_strided_layers(ctx, oracle, case):
     layer.release()
 
 
-def test_direct_epilogue_and_repeatability(ctx, oracle):
-    case = (2, 48, 72, 28, 28, 3, 3, 1, 1, 1, 1)
+# a small layer (28 output blocks: its reduction is shared by several work items, bias and ReLU follow in a pass of
+# their own: 3 launches) and one with more output blocks than SMs (one accumulator per output, epilogue in the kernel)
+@pytest.mark.parametrize("case, launches", [((2, 48, 72, 28, 28, 3, 3, 1, 1, 1, 1), 3),
+                                            ((6, 48, 72, 56, 56, 3, 3, 1, 1, 1, 1), 2)])
+def test_direct_epilogue_and_repeatability(ctx, oracle, case, launches):
     n, ic, oc, ih, iw, kh, kw, pl, pr, pt, pb = case
     x = synth.conv_input(n, ic, ih, iw, 93)
     w = synth.conv_weights(oc, ic, kh, kw, 94)
@@ -90,12 +93,19 @@ def test_direct_epilogue_and_repeatability(ctx, oracle):
     layer = _layer(ctx, x, w, case)
     layer.set_epilogue(b, True)
     layer.Init(); layer.Forward()
+    assert layer.kernel_launches == launches
     first = layer.output_data.copy()
     want = np.maximum(oracle.im2col_gemm_forward(x, w, 1, 1, pl, pr, pt, pb) + b[None, :, None, None], 0).astype(np.float32)
     assert rel_l2(first, want) <= 1e-3
     assert (first >= 0).all()
     layer.Forward()
-    assert np.array_equal(layer.output_data, first)  # one accumulator per output, fixed order: no run-to-run noise
+    if launches == 2:
+        assert np.array_equal(layer.output_data, first)  # one accumulator per output, fixed order: no run-to-run noise
+    else:
+        assert rel_l2(layer.output_data, first) <= 1e-6  # partial sums are added in whatever order they arrive
+    layer.set_epilogue(None, False)
+    layer.Forward()
+    assert rel_l2(layer.output_data, oracle.im2col_gemm_forward(x, w, 1, 1, pl, pr, pt, pb)) <= 1e-3
     layer.release()
 
 
