@@ -336,30 +336,33 @@ static void direct_patch_shape(int oh, int ow, int *bh, int *bw) {
     }
 }
 
-// Whether `-a auto` in the TF32 mode should take this kernel instead of the Winograd path (3x3) or the gathering
-// implicit GEMM (anything else of stride 1 or 2).  From per-layer timings of the VGG-16 and ResNet-50 layers at batch
-// 1, 2, 8 and 64 on a B200:
-//  * against Winograd the kernel does 2.25x the multiplications but moves no V and M, so it wins where the
-//    channels are few -- ic*oc/(ic+oc) up to about 100 (128 -> 256 yes, 256 -> 256 a tie) -- provided the layer
-//    has a work item for every SM, or so few channels (up to about 48) that the transforms dominate anyway;
-//  * against the gathering kernel (1x1 layers, stride-2 layers) it wins by 1.5x to 4x as soon as there are 16 work
-//    items and 0.15 GFLOP; below that the extra launch of the layout pass decides.  Not with a handful of channels
-//    and taps that do not fold (the 7x7 stride-2 stem: 3 real channels in every 32-wide k-block, 0.69 against 0.57 ms
-//    at batch 64).
+// Whether `-a auto` should take this kernel instead of its rival.  From per-layer timings of the VGG-16 and ResNet-50
+// layers at batch 1, 2, 8 and 64 on a B200:
+//  * against Winograd in TF32 (3x3 stride 1) the kernel does 2.25x the multiplications but moves no V and M, so it
+//    wins where the channels are few -- ic*oc/(ic+oc) up to about 100 (128 -> 256 yes, 256 -> 256 a tie) -- provided the
+//    layer has a work item for every SM, or so few channels (up to about 48) that the transforms dominate anyway.
+//    Small layers (at most 8 patches and no more 64-channel output blocks than SMs: 28x28 maps and below of one
+//    image; with 16 patches -- 14x14 at batch 8 -- Winograd is 1.6x faster again) share their reduction among the SMs and then run within 0.8x to 1.15x of Winograd; they take this kernel
+//    too, because single-pass TF32 through F(6x6,3x3) misses the 3e-3 that the mode stands for and this kernel does not;
+//  * against the gathering kernel (1x1 layers, stride-2 layers) it wins by 1.3x to 4x from 50 MFLOP on.  Not with a
+//    handful of channels and taps that do not fold (the 7x7 stride-2 stem: 3 real channels in every 32-wide k-block,
+//    0.69 against 0.57 ms at batch 64);
 //  * against the bit-exact fp32 Winograd path (the alternative when single-pass TF32 through Winograd is not
-//    accurate enough): at batch 8 and 64 it wins on every VGG-16 layer (1.5x to 2.4x), at batch 1 up to 128 -> 128
-//    channels; it loses where a layer has both few work items and many channels (512 -> 512 at 14x14, batch 1:
-//    0.064 against 0.026 ms).
+//    accurate enough) it wins on every VGG-16 and ResNet-50 layer at every batch size measured (1.3x to 2.4x).
 bool direct_tc_preferred(const fc_conv_desc &d, int oh, int ow, int sm_count, int rival) {
     if (!direct_tc_eligible(d)) return false;
+    if (rival == DIRECT_VS_WINOGRAD_FP32) return true;
     int bh = 8, bw = 16;
     direct_patch_shape(oh, ow, &bh, &bw);
-    const double items = (double)ceil_div(oh, bh) * ceil_div(ow, bw) * d.batch * ceil_div(d.oc, 128);
-    const double h = (double)d.ic * d.oc / (d.ic + d.oc);
-    if (rival == DIRECT_VS_WINOGRAD_TF32) return h <= 100.0 && (items >= sm_count || h <= 48.0);
-    if (rival == DIRECT_VS_WINOGRAD_FP32) return items >= 48 || h <= 64.0;
+    const double patches = (double)ceil_div(oh, bh) * ceil_div(ow, bw) * d.batch;
+    const double items = patches * ceil_div(d.oc, 128);
+    if (rival == DIRECT_VS_WINOGRAD_TF32) {
+        const double h = (double)d.ic * d.oc / (d.ic + d.oc);
+        if (patches <= 8 && patches * ceil_div(d.oc, 64) <= sm_count) return true;
+        return h <= 100.0 && (items >= sm_count || h <= 48.0);
+    }
     const double flops = 2.0 * d.batch * d.oc * d.ic * d.kh * d.kw * oh * ow;
-    return items >= 16 && flops >= 1.5e8 && (d.ic >= 16 || folds_taps(d));
+    return flops >= 5e7 && (d.ic >= 16 || folds_taps(d));
 }
 
 size_t direct_nhwc_elems(const fc_conv_desc &d) {

@@ -156,8 +156,8 @@ def _create(ctx, desc, algo, mode, w):
 @pytest.mark.parametrize("shape, algo_in, want_algo, want_mode", [
     # n, ic, oc, hw, k, pad
     ((1, 64, 64, 56, 3, 1), "auto", "direct", "tf32"),          # few channels: the direct kernel
-    ((1, 512, 512, 14, 3, 1), "auto", "winograd", "fp32"),       # 8 work items, many channels: Winograd, bit-exact
-    ((8, 512, 512, 14, 3, 1), "auto", "direct", "tf32"),         # the same layer with 64 work items
+    ((1, 512, 512, 14, 3, 1), "auto", "direct", "tf32"),         # a small layer: its reduction is shared by the SMs
+    ((8, 512, 512, 14, 3, 1), "auto", "direct", "tf32"),
     ((1, 64, 64, 56, 3, 1), "winograd", "winograd", "fp32"),     # Winograd by name: only its fp32 arithmetic complies
     ((4, 256, 128, 28, 1, 0), "auto", "direct", "tf32"),         # not a Winograd layer: as in the TF32 mode
     ((1, 16, 12, 14, 1, 0), "auto", "im2col", "tf32"),
