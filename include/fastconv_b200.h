@@ -57,9 +57,9 @@ typedef enum fc_math_mode {
     FC_MATH_TF32 = 2,          /* tcgen05 tensor cores, single TF32 pass                          */
     FC_MATH_TF32_STRICT = 3    /* fc_conv_create only: TF32 wherever it stays within rel-L2 3e-3 of the fp32 result.
                                   Single-pass TF32 through F(6x6,3x3) does not (6.4e-3), so a Winograd-eligible layer
-                                  runs the direct tensor-core kernel in TF32 or, where that is slower (few work items,
-                                  many channels), the Winograd path in FC_MATH_FP32_MIRRORED; other layers run as in
-                                  FC_MATH_TF32.  fc_conv_math_mode reports the mode the layer was planned with. */
+                                  runs the direct tensor-core kernel in TF32 or, where that cannot run or Winograd
+                                  was asked for by name, the Winograd path in FC_MATH_FP32_MIRRORED; other layers run
+                                  as in FC_MATH_TF32.  fc_conv_math_mode reports the mode the layer was planned with. */
 } fc_math_mode;
 
 typedef struct fc_conv_desc {
