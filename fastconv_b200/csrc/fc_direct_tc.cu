@@ -17,6 +17,8 @@
 //     warp 0      TMA producer: per k-block (u,v, 32 channels) one 4-D box of the input and one 3-D box of Wp
 //     warp 1      tcgen05.mma kind::tf32, M = 128 pixels, N = channel block, two TMEM accumulators
 //     warps 2..5  epilogue: tcgen05.ld (lane = pixel), bias/ReLU, NCHW stores (a warp writes runs of bw pixels)
+//   fold_taps_kernel        replaces the layout pass when ic*kh*kw <= 32: the taps become channels of a 1x1 layer
+//   bias_relu_kernel        epilogue of a small layer whose reduction was shared by several work items (make_plan)
 //
 // There is no Winograd transform in the way, so single-pass TF32 keeps its plain accuracy (rel-L2 3e-4..8e-4 against
 // 6.4e-3 through F(6x6,3x3)).  Every mbarrier wait is bounded as in the other tensor-core kernels.
