@@ -8,9 +8,9 @@ from . import synth  # noqa: F401
 from ._lib import (ALGO_AUTO, ALGO_DIRECT, ALGO_IM2COL, ALGO_WINOGRAD, MATH_3XTF32, MATH_FP32_MIRRORED,  # noqa: F401
                    MATH_TF32, ConvDesc, FastConvError, load)
 from .layers import (Context, ConvDirectLayer, ConvIm2colLayer, ConvLayer, ConvWinoF63ZCLayer, LayerList, default_context, diff,  # noqa: F401
-                     make_desc, make_layer, output_size, select_algorithm)
+                     make_desc, make_layer, output_size, resolve_plan, select_algorithm)
 
 __all__ = [
     "Context", "LayerList", "ConvLayer", "ConvWinoF63ZCLayer", "ConvIm2colLayer", "ConvDirectLayer", "ConvDesc", "FastConvError", "make_desc",
-    "make_layer", "output_size", "select_algorithm", "diff", "default_context", "load", "synth",
+    "make_layer", "output_size", "select_algorithm", "resolve_plan", "diff", "default_context", "load", "synth",
 ]

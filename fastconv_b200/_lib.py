@@ -82,6 +82,7 @@ SIGNATURES = {
     "fc_igemm_forward": (C.c_int, [_vp, _vp, _vp, _vp, _dp, C.c_int]),
     "fc_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "fc_conv_destroy": (C.c_int, [_vp]),
+    "fc_resolve_plan": (C.c_int, [_dp, C.c_int, C.c_int, C.c_int, _ip, _ip]),
     "fc_conv_algorithm": (C.c_int, [_vp, _ip]),
     "fc_conv_math_mode": (C.c_int, [_vp, _ip]),
     "fc_conv_forward_device": (C.c_int, [_vp, _vp, _vp]),

@@ -678,10 +678,8 @@ static int conv_prepare(fc_conv *c, int algo) {
     return FC_OK;
 }
 
-int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode, const float *h_kernel,
-                   fc_conv **out) {
-    FC_REQUIRE(ctx && desc && h_kernel && out, FC_ERR_INVALID_ARG, "NULL argument");
-    *out = nullptr;
+int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, int *algo_out, int *mode_out) {
+    FC_REQUIRE(desc && algo_out && mode_out, FC_ERR_INVALID_ARG, "NULL argument");
     FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32_STRICT, FC_ERR_INVALID_ARG, "unknown math mode %d",
                mode);
     FC_REQUIRE(algo >= FC_ALGO_AUTO && algo <= FC_ALGO_WINOGRAD, FC_ERR_INVALID_ARG, "unknown algorithm %d", algo);
@@ -689,11 +687,10 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
     const bool auto_requested = algo == FC_ALGO_AUTO;
     if (algo == FC_ALGO_AUTO) FC_PROPAGATE(fc_select_algorithm(desc, &algo));
-    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
-    const bool strict = mode == FC_MATH_TF32_STRICT;
-    if (strict) {
+    const int sms = sm_count > 0 ? sm_count : 148;
+    if (mode == FC_MATH_TF32_STRICT) {
         // TF32 only where it stays within 3e-3: never through F(6x6,3x3).  A layer headed for Winograd takes the direct
-        // tensor-core kernel, or stays on Winograd in the bit-exact fp32 arithmetic where that is the faster of the two
+        // tensor-core kernel, or stays on Winograd in the bit-exact fp32 arithmetic where that kernel cannot run
         // (and whenever Winograd was asked for by name); every other layer is as accurate in TF32 as it is.
         if (algo == FC_ALGO_WINOGRAD) {
             if (auto_requested && direct_tc_preferred(*desc, oh, ow, sms, DIRECT_VS_WINOGRAD_FP32)) {
@@ -714,6 +711,20 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
     // the direct tensor-core kernel is a TF32 kernel for ungrouped layers of stride 1 or 2; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
     if (algo == FC_ALGO_DIRECT && !(mode == FC_MATH_TF32 && direct_tc_eligible(*desc))) algo = FC_ALGO_IM2COL;
+    *algo_out = algo;
+    *mode_out = mode;
+    return FC_OK;
+}
+
+int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode, const float *h_kernel,
+                   fc_conv **out) {
+    FC_REQUIRE(ctx && desc && h_kernel && out, FC_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    const bool auto_requested = algo == FC_ALGO_AUTO;
+    const bool strict = mode == FC_MATH_TF32_STRICT;
+    FC_PROPAGATE(fc_resolve_plan(desc, algo, mode, ctx->sm_count, &algo, &mode));
+    int oh, ow;
+    FC_PROPAGATE(fc_conv_output_size(desc, &oh, &ow));
     int auto_pick = FC_ALGO_IM2COL;
     fc_select_algorithm(desc, &auto_pick);
     const bool wino_eligible = auto_pick == FC_ALGO_WINOGRAD;

@@ -200,6 +200,19 @@ def select_algorithm(desc: ConvDesc) -> int:
     return a.value
 
 
+def resolve_plan(desc: ConvDesc, algorithm="auto", mode="tf32", sm_count: int = 0):
+    """(algorithm, math mode) that a layer planned with these arguments runs, as names; needs no GPU.
+
+    `auto` is select_algorithm of ConvTest.cpp:318-331 plus, in the TF32 modes, the direct tensor-core kernel where
+    the measured crossovers favour it; "tf32-strict" resolves to "tf32" or "fp32" per layer."""
+    algo = _lib.ALGO_NAMES[algorithm] if isinstance(algorithm, str) else int(algorithm)
+    m = _lib.MODE_NAMES[mode] if isinstance(mode, str) else int(mode)
+    a, r = C.c_int(), C.c_int()
+    check(_lib.load().fc_resolve_plan(C.byref(desc), algo, m, int(sm_count), C.byref(a), C.byref(r)), "fc_resolve_plan")
+    names = {v: k for k, v in _lib.ALGO_NAMES.items()}
+    return names[a.value], {0: "fp32", 1: "3xtf32", 2: "tf32"}[r.value]
+
+
 def diff(a: np.ndarray, b: np.ndarray) -> float:
     """diff() of utility/helper.cpp:74-89, printing the same line."""
     a = _as_f32(a, "a").ravel()

@@ -124,6 +124,11 @@ int fc_conv_output_size(const fc_conv_desc *desc, int *oh, int *ow);
 /* select_algorithm, ConvTest.cpp:318-331 -- except that 1x1 stride-1 ("direct", an empty case in
  * the reference) resolves to FC_ALGO_IM2COL so that something runs. */
 int fc_select_algorithm(const fc_conv_desc *desc, int *algo);
+/* What fc_conv_create plans for (desc, algo, mode) on a GPU with sm_count SMs (0 = 148): FC_ALGO_AUTO resolved --
+ * select_algorithm as above, then, in the TF32 modes, the direct tensor-core kernel where the measured crossovers
+ * favour it -- and FC_MATH_TF32_STRICT resolved to FC_MATH_TF32 or FC_MATH_FP32_MIRRORED.  Needs no GPU.  The reference
+ * has one arithmetic and a shape-only choice (ConvTest.cpp:318-331); this is that choice with the mode added. */
+int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, int *algo_out, int *mode_out);
 /* element counts (floats) of the Winograd-domain buffers for a descriptor */
 int fc_wino_buffer_elems(const fc_conv_desc *desc, int mode, size_t *u_elems, size_t *v_elems, size_t *m_elems);
 
