@@ -187,9 +187,12 @@ static void fillTestKernel(float *target, size_t count) {
     for (size_t i = 0; i < count; ++i) target[i] = (float)(1.0 * rand() / (double)RAND_MAX);
 }
 
-static enum nnp_convolution_algorithm select_algorithm(const fc_conv_desc &d) {
-    int a = FC_ALGO_IM2COL;
-    fc_select_algorithm(&d, &a);  // ConvTest.cpp:318-331, with 1x1 stride 1 resolved to the implicit GEMM
+// select_algorithm of ConvTest.cpp:318-331 (with 1x1 stride 1 resolved to the implicit GEMM); with -m tf32 or
+// tf32-strict the library may answer "direct" for layers where its tensor-core kernel is the faster or the only
+// accurate-enough TF32 path.
+static enum nnp_convolution_algorithm select_algorithm(const fc_conv_desc &d, int math_mode) {
+    int a = FC_ALGO_IM2COL, m = math_mode;
+    if (fc_resolve_plan(&d, FC_ALGO_AUTO, math_mode, 0, &a, &m) != FC_OK) fc_select_algorithm(&d, &a);
     return (enum nnp_convolution_algorithm)a;
 }
 
@@ -219,7 +222,7 @@ int main(int argc, char *argv[]) {
     fillTestInput(test_input, in_elems);
     fillTestKernel(test_kernel, k_elems);
 
-    if (options.algorithm == nnp_convolution_algorithm_auto) options.algorithm = select_algorithm(d);
+    if (options.algorithm == nnp_convolution_algorithm_auto) options.algorithm = select_algorithm(d, options.math_mode);
 
     if (fastconv_default_context() == NULL && options.gpu != 0) {
         fc_context *ctx = NULL;
