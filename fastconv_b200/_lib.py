@@ -14,9 +14,9 @@ FC_OK = 0
 (FC_ERR_INVALID_ARG, FC_ERR_UNSUPPORTED, FC_ERR_OUT_OF_MEMORY, FC_ERR_CUDA, FC_ERR_NO_DEVICE, FC_ERR_TIMEOUT,
  FC_ERR_COMM) = -1, -2, -3, -4, -5, -6, -7
 ALGO_AUTO, ALGO_DIRECT, ALGO_IM2COL, ALGO_WINOGRAD = 0, 1, 2, 3
-MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32, MATH_TF32_STRICT = 0, 1, 2, 3
+MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32, MATH_TF32_UNBOUNDED = 0, 1, 2, 3
 MODE_NAMES = {"fp32": MATH_FP32_MIRRORED, "ffma": MATH_FP32_MIRRORED, "3xtf32": MATH_3XTF32, "tf32": MATH_TF32,
-              "tf32-strict": MATH_TF32_STRICT}
+              "tf32-unbounded": MATH_TF32_UNBOUNDED}
 ALGO_NAMES = {"auto": ALGO_AUTO, "direct": ALGO_DIRECT, "im2col": ALGO_IM2COL, "winograd": ALGO_WINOGRAD}
 
 
@@ -98,11 +98,34 @@ SIGNATURES = {
     "fc_layer_list_launches": (C.c_int, [_vp, _ip]),
     "fc_layer_list_destroy": (C.c_int, [_vp]),
     "fc_conv_set_epilogue": (C.c_int, [_vp, _vp, C.c_int]),
+    "fc_context_info": (C.c_int, [_vp, _ip, _ip]),
+    "fc_conv_round_times": (C.c_int, [_vp, _fp, C.c_int, _ip]),
+    "fc_conv_work": (C.c_int, [_vp] + [C.POINTER(C.c_double)] * 4),
+    "fc_conv_set_kernel_config": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "fc_conv_get_kernel_config": (C.c_int, [_vp, _ip, _ip, _ip, _ip]),
     "fc_peer_export": (C.c_int, [_vp, _vp, _vp, _vp]),
     "fc_peer_open": (C.c_int, [_vp, _vp, _vp]),
     "fc_peer_close": (C.c_int, [_vp, _vp]),
     "fc_conv_forward_scatter": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "fc_peer_wait": (C.c_int, [_vp, _vp, C.c_int, C.c_int]),
+    "fc_context_set_wait_limit_ms": (C.c_int, [_vp, C.c_int]),
+    "fc_comm_init_all": (C.c_int, [C.c_int, _ip, C.c_size_t, C.POINTER(_vp)]),
+    "fc_comm_init_env": (C.c_int, [C.c_int, C.c_size_t, C.POINTER(_vp)]),
+    "fc_comm_destroy": (C.c_int, [_vp]),
+    "fc_comm_size": (C.c_int, [_vp, _ip, _ip, _ip]),
+    "fc_comm_context": (C.c_int, [_vp, C.c_int, C.POINTER(_vp)]),
+    "fc_comm_barrier": (C.c_int, [_vp]),
+    "fc_comm_allreduce_max": (C.c_int, [_vp, C.POINTER(C.c_double)]),
+    "fc_shard_range": (C.c_int, [C.c_int, C.c_int, C.c_int, _ip, _ip]),
+    "fc_sharded_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
+    "fc_sharded_conv_destroy": (C.c_int, [_vp]),
+    "fc_sharded_conv_part": (C.c_int, [_vp, C.c_int, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _ip, _ip]),
+    "fc_sharded_conv_upload": (C.c_int, [_vp, _vp]),
+    "fc_sharded_conv_forward": (C.c_int, [_vp]),
+    "fc_sharded_conv_wait": (C.c_int, [_vp]),
+    "fc_sharded_conv_download": (C.c_int, [_vp, _vp]),
+    "fc_sharded_conv_forward_host": (C.c_int, [_vp, _vp, _vp]),
+    "fc_sharded_conv_time_device": (C.c_int, [_vp, C.c_int, C.c_int, _fp]),
     "fc_diff": (C.c_float, [_vp, _vp, C.c_int]),
 }
 
@@ -119,10 +142,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     if _lib is not None:
         return _lib
     path = library_path()
-    if not path.exists():
-        if not build_if_missing:
-            raise FileNotFoundError(f"{path} is not built; run `python -m fastconv_b200.build`")
-        _build.build_library()
+    if build_if_missing:
+        _build.build_library()  # returns at once when the library is newer than every source and header
+    elif not path.exists():
+        raise FileNotFoundError(f"{path} is not built; run `python -m fastconv_b200.build`")
     lib = C.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here = header and library disagree

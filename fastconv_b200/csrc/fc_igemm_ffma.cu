@@ -480,7 +480,40 @@ __global__ void __launch_bounds__(256) depthwise_kernel(const float *__restrict_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// M, N and K all at most 32: the reference leaves its blocked SGEMM and runs the scalar triple loop
+// ConvIm2colLayer::GEMM (convLayer/im2colConv.cpp:400-432, chosen at im2colConv.h:30-31), whose statement
+// `C += temp * B` is a separate multiplication and addition, k ascending.  One thread per output element keeps
+// that chain: a rounded product, then a rounded sum.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) igemm_tiny_unfused_kernel(const float *__restrict__ in, const float *__restrict__ A,
+                                                                 float *__restrict__ out, IgemmParams P, Epilogue ep) {
+    const int ohw = P.oh * P.ow;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= P.n * P.oc * ohw) return;
+    const int rem = idx % ohw, r = idx / ohw, k = r % P.oc, img = r / P.oc;
+    const int oi = rem / P.ow, oj = rem - oi * P.ow;
+    const float *src = in + (size_t)img * P.in_img_stride;
+    const float *a = A + (size_t)k * P.K;
+    float acc = 0.0f;
+    int kk = 0;
+    for (int c = 0; c < P.ic; ++c)
+        for (int u = 0; u < P.kh; ++u)
+            for (int v = 0; v < P.kw; ++v, ++kk) {
+                const int row = oi * P.sh - P.pad_t + u, col = oj * P.sw - P.pad_l + v;
+                const float b = ((unsigned)row < (unsigned)P.ih && (unsigned)col < (unsigned)P.iw)
+                                    ? __ldg(src + ((size_t)c * P.ih + row) * P.iw + col) : 0.0f;
+                acc = __fadd_rn(acc, __fmul_rn(__ldg(a + kk), b));
+            }
+    out[(size_t)img * P.out_img_stride + (size_t)k * ohw + rem] = ep(acc, k);
+}
+
 }  // namespace
+
+// the reference's own switch to its scalar GEMM (convLayer/im2colConv.h:30-31), per image as the reference has no batch
+bool igemm_is_tiny(const fc_conv_desc &d, int oh, int ow) {
+    return d.oc <= 32 && oh * ow <= 32 && d.ic * d.kh * d.kw <= 32;
+}
 
 int launch_depthwise(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,
                      int oh, int ow, const Epilogue &ep) {
@@ -544,6 +577,12 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
     P.in_img_stride = in_img_stride ? (long long)in_img_stride : (long long)d.ic * d.ih * d.iw;
     P.out_img_stride = out_img_stride ? (long long)out_img_stride : (long long)d.oc * oh * ow;
     const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    if (igemm_is_tiny(d, oh, ow)) {  // the one shape class whose reference arithmetic is not a fused multiply-add
+        const int total = d.batch * d.oc * oh * ow;
+        FC_CHECK_CUDA(launch_pdl(igemm_tiny_unfused_kernel, dim3((unsigned)ceil_div(total, 256)), dim3(256), 0, ctx->stream,
+                                 d_in, d_kernel, d_out, P, ep));
+        return FC_OK;
+    }
     const int pick = cfg ? cfg->skinny : 0;
     const bool wide_m = cfg && cfg->bm ? cfg->bm == 128 : d.oc > 64;
     const bool wide_n = cfg && cfg->bn ? cfg->bn == 128 : P.npix > 64;

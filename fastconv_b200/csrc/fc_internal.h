@@ -15,6 +15,7 @@
 namespace fc {
 
 void set_error(const char *fmt, ...);
+unsigned default_peer_wait_polls();  // from $FASTCONV_PEER_WAIT_MS, else five seconds' worth
 
 #define FC_CHECK_CUDA(call)                                                                             \
     do {                                                                                                \
@@ -99,6 +100,18 @@ struct PeerOuts {
     int count;
 };
 
+// The same for a layer that is replayed without host involvement (a CUDA graph, a persistent stream of forwards):
+// the step number lives on the device.  `step` counts the forwards this rank has published; a forward with number
+// s = *step + 1 stores into the buffers of parity s & 1 and, when its last block is done, writes s into flag[rank]
+// of every rank and into *step.
+struct ScatterPublish {
+    float *base[2][FC_MAX_PEERS];  // [parity][rank]: this rank's first channel inside rank r's output buffer
+    int *flags[FC_MAX_PEERS];      // rank r's flag array int[world], as seen from this GPU
+    int *step;                     // this GPU's memory
+    unsigned *ticket;              // this GPU's memory, zero between launches: blocks of the launch that are done
+    int count, rank;
+};
+
 struct CommonSlot {
     size_t bytes;
     void *ptr;
@@ -117,6 +130,7 @@ struct fc_context {
     cudaEvent_t user_ev[FC_TIMER_SLOTS];
     int *d_status;  // device word kernels with bounded waits report into
     cudaStream_t copy_in, copy_out;  // created on first use by the pipelined host forward
+    unsigned peer_wait_polls;        // iteration limit of the flag waits of channel-split layers
 };
 
 // Programmatic dependent launch.  Every kernel of the forward path is launched with the
@@ -151,6 +165,10 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // kernel launchers (device pointers, context stream) ------------------------------------------
 namespace fc {
 
+// one forward of a channel-split Winograd layer whose output transform stores into every rank's buffer and publishes
+// the step itself (step number and buffer parity live on the device: the launch can be replayed by a CUDA graph)
+int conv_forward_scatter_publish(fc_conv *conv, const float *d_in, const ScatterPublish &pub);
+
 int launch_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
 int launch_filter_transform_rowmajor(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic);
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
@@ -159,8 +177,12 @@ int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, con
                             const Epilogue &ep = kNoEpilogue);
 int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g,
                                     const Epilogue &ep = kNoEpilogue);
+int launch_output_transform_scatter_publish(fc_context *ctx, const float *d_M, const ScatterPublish &dst,
+                                            const WinoGeom &g, const Epilogue &ep = kNoEpilogue);
 int launch_peer_publish(fc_context *ctx, int *const *flags, int world, int rank, int step);
 int launch_peer_wait(fc_context *ctx, const int *flags, int world, int step);
+// waits until every rank's flag has reached *d_step (this rank's own count of published forwards)
+int launch_peer_wait_published(fc_context *ctx, const int *flags, int world, const int *d_step);
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
                           const KernelCfg *cfg = nullptr);
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
@@ -174,6 +196,7 @@ int launch_igemm_ffma(fc_context *ctx, const float *d_in, const float *d_kernel,
                       float *d_bmat = nullptr);
 // scratch for the materialised gathered matrix of a few-pixel, long-reduction layer: K x igemm_matrix_ld floats
 bool igemm_wants_matrix(const fc_conv_desc &d, int oh, int ow);
+bool igemm_is_tiny(const fc_conv_desc &d, int oh, int ow);  // M, N, K <= 32: the reference's unfused scalar GEMM
 size_t igemm_matrix_ld(const fc_conv_desc &d, int oh, int ow);
 // group == ic: one thread per output element, reduction over the kh*kw taps only
 int launch_depthwise(fc_context *ctx, const float *d_in, const float *d_kernel, float *d_out, const fc_conv_desc &d,

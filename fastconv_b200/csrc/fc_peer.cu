@@ -13,6 +13,7 @@
 // and loads cross NVLink (no switch-side reduction or replication objects, nothing that needs a peer to stay alive).
 #include "fc_internal.h"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace fc {
@@ -32,13 +33,18 @@ __global__ void peer_publish_kernel(FlagPtrs flags, int world, int rank, int ste
     }
 }
 
-constexpr unsigned PEER_WAIT_POLLS = 1u << 22;  // x ~250 ns per poll: about a second
+// How long a wait polls before it gives up: fc_context_set_wait_limit_ms, initially $FASTCONV_PEER_WAIT_MS
+// milliseconds (default 5000), at about 250 ns per poll.  Generous on purpose: ranks may be seconds apart at start-up (module loading, one rank still planning or
+// tuning); the limit exists so that a rank whose peer has died returns an error instead of spinning for ever.  After
+// a timeout the gathered output buffer is undefined.
+constexpr long long POLLS_PER_MS = 4000;
 
-__global__ void peer_wait_kernel(const int *flags, int world, int step, int *status) {
+__global__ void peer_wait_kernel(const int *flags, int world, int step, const int *d_step, unsigned polls, int *status) {
     const int r = threadIdx.x;
     if (r >= world) return;
+    if (d_step != nullptr) step = *reinterpret_cast<const volatile int *>(d_step);  // this rank's own published count
     const volatile int *f = flags + r;
-    for (unsigned i = 0; i < PEER_WAIT_POLLS; ++i) {
+    for (unsigned i = 0; i < polls; ++i) {
         if (*f - step >= 0) {  // difference, so that a wrapped counter still compares
             __threadfence_system();
             return;
@@ -49,6 +55,14 @@ __global__ void peer_wait_kernel(const int *flags, int world, int step, int *sta
 }
 
 }  // namespace
+
+unsigned default_peer_wait_polls() {
+    const char *e = getenv("FASTCONV_PEER_WAIT_MS");
+    long long ms = e ? atoll(e) : 5000;
+    if (ms < 1) ms = 1;
+    if (ms > 600000) ms = 600000;
+    return (unsigned)(ms * POLLS_PER_MS);
+}
 
 int launch_peer_publish(fc_context *ctx, int *const *flags, int world, int rank, int step) {
     FlagPtrs f;
@@ -61,7 +75,14 @@ int launch_peer_publish(fc_context *ctx, int *const *flags, int world, int rank,
 }
 
 int launch_peer_wait(fc_context *ctx, const int *flags, int world, int step) {
-    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(flags, world, step, ctx->d_status);
+    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(flags, world, step, nullptr, ctx->peer_wait_polls, ctx->d_status);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+int launch_peer_wait_published(fc_context *ctx, const int *flags, int world, const int *d_step) {
+    // an ordinary launch: it starts after the scatter kernel before it has completed, *d_step included
+    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(flags, world, 0, d_step, ctx->peer_wait_polls, ctx->d_status);
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }
@@ -112,6 +133,13 @@ int fc_peer_close(fc_context *ctx, void *base) {
         cudaGetLastError();
         return FC_ERR_COMM;
     }
+    return FC_OK;
+}
+
+int fc_context_set_wait_limit_ms(fc_context *ctx, int ms) {
+    FC_REQUIRE(ctx != nullptr, FC_ERR_INVALID_ARG, "context is NULL");
+    FC_REQUIRE(ms >= 1 && ms <= 600000, FC_ERR_INVALID_ARG, "wait limit of %d ms outside 1..600000", ms);
+    ctx->peer_wait_polls = (unsigned)(ms * POLLS_PER_MS);
     return FC_OK;
 }
 

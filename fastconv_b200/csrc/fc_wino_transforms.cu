@@ -417,6 +417,43 @@ __global__ void __launch_bounds__(256) output_transform_scatter_kernel(const flo
     });
 }
 
+// Scatter with the step kept on the device and the publication folded into the kernel.  Every block stores its
+// results into the buffers of the parity of this forward; when a block is done, one of its threads orders the block's
+// stores before a device-wide ticket; the block that draws the last ticket issues ONE system-wide fence and writes the
+// step number into flag[rank] of every rank.  Nothing is passed by the host per forward, so a CUDA graph can replay
+// the launch, and no separate publishing kernel follows.
+template <int TPW>
+__global__ void __launch_bounds__(256) output_transform_scatter_publish_kernel(const float *__restrict__ M,
+                                                                               ScatterPublish dst, int n_tiles, int oc,
+                                                                               int tp, int oh, int ow, int th, int tw,
+                                                                               Epilogue ep) {
+    __shared__ int s_step;
+    // read after the predecessor in the stream has completed (the block helper waits for it before it touches M;
+    // the counter was last written by this layer's previous forward, which is older still)
+    pdl_wait();
+    if (threadIdx.x == 0) s_step = *reinterpret_cast<volatile int *>(dst.step) + 1;
+    __syncthreads();
+    const int step = s_step, parity = step & 1;
+    output_transform_block<TPW>(M, n_tiles, oc, tp, oh, ow, th, tw, [&dst, ep, parity](size_t at, int ch, float v) {
+        v = ep(v, ch);
+#pragma unroll
+        for (int r = 0; r < FC_MAX_PEERS; ++r)
+            if (r < dst.count) dst.base[parity][r][at] = v;
+    });
+    __syncthreads();  // every thread of the block has issued its stores
+    if (threadIdx.x == 0) {
+        __threadfence();  // ... and they are ordered before the ticket
+        const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(dst.ticket, 1u) == total - 1) {
+            *dst.ticket = 0;         // for the next launch
+            __threadfence_system();  // every block's stores, observed through its ticket, before the flags
+            for (int r = 0; r < dst.count; ++r) *reinterpret_cast<volatile int *>(dst.flags[r] + dst.rank) = step;
+            *reinterpret_cast<volatile int *>(dst.step) = step;
+            __threadfence_system();
+        }
+    }
+}
+
 // Many tiles (large feature maps or batches): throughput matters more than latency.  One thread per
 // (oc, tile) item keeps all 64 loads of M in flight at once and does both passes in registers; a warp
 // covers 32 consecutive tiles of one output channel and stages its 6 x 192 results so that the stores
@@ -522,6 +559,25 @@ int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const Pee
         dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
         FC_CHECK_CUDA(launch_pdl(output_transform_scatter_kernel<8>, grid, block, 0, ctx->stream, d_M, dst, g.tiles, g.oc,
                                  g.tp, g.oh, g.ow, g.th, g.tw, ep));
+    }
+    return FC_OK;
+}
+
+int launch_output_transform_scatter_publish(fc_context *ctx, const float *d_M, const ScatterPublish &dst,
+                                            const WinoGeom &g, const Epilogue &ep) {
+    dim3 block(256);
+    if (g.tiles > 16) {
+        dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)g.oc);
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_publish_kernel<32>, grid, block, 0, ctx->stream, d_M, dst, g.tiles,
+                                 g.oc, g.tp, g.oh, g.ow, g.th, g.tw, ep));
+    } else if (g.tiles > 8) {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 2));
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_publish_kernel<16>, grid, block, 0, ctx->stream, d_M, dst, g.tiles,
+                                 g.oc, g.tp, g.oh, g.ow, g.th, g.tw, ep));
+    } else {
+        dim3 grid(1, (unsigned)ceil_div(g.oc, 4));
+        FC_CHECK_CUDA(launch_pdl(output_transform_scatter_publish_kernel<8>, grid, block, 0, ctx->stream, d_M, dst, g.tiles,
+                                 g.oc, g.tp, g.oh, g.ow, g.th, g.tw, ep));
     }
     return FC_OK;
 }

@@ -13,7 +13,7 @@
 //     implicit GEMM otherwise;
 //   * the self-check honours kernel size, stride and padding (the reference always checks against a
 //     3x3 / pad 1 naive layer, ConvTest.cpp:360) and also covers the im2col path;
-//   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32|tf32-strict, -seed N (the reference seeds from
+//   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32|tf32-unbounded, -seed N (the reference seeds from
 //     the clock), -nc/--no-check, -g/--gpu INDEX.  -t is accepted and only sizes the host self-check.
 #include <math.h>
 #include <stdlib.h>
@@ -66,7 +66,7 @@ static void print_options_help(const char *program_name) {
            "  -i   --iterations         # iterations (default: 10)\n"
            "GPU additions:\n"
            "  -n   --batch              Images per forward (default: 1)\n"
-           "  -m   --math               fp32 (bit-identical accumulation), 3xtf32, tf32 or tf32-strict (default: fp32)\n"
+           "  -m   --math               fp32 (bit-identical accumulation), 3xtf32, tf32 (within 3e-3) or tf32-unbounded (default: fp32)\n"
            "  -seed                     Seed of the input/kernel generator (default: from the clock)\n"
            "  -nc  --no-check           Skip the naive host convolution and the difference line\n"
            "  -g   --gpu                CUDA device index (default: 0)\n",
@@ -157,7 +157,7 @@ static struct options parse_options(int argc, char **argv) {
                 if (strcmp(v, "fp32") == 0) o.math_mode = FC_MATH_FP32_MIRRORED;
                 else if (strcmp(v, "3xtf32") == 0) o.math_mode = FC_MATH_3XTF32;
                 else if (strcmp(v, "tf32") == 0) o.math_mode = FC_MATH_TF32;
-                else if (strcmp(v, "tf32-strict") == 0) o.math_mode = FC_MATH_TF32_STRICT;
+                else if (strcmp(v, "tf32-unbounded") == 0) o.math_mode = FC_MATH_TF32_UNBOUNDED;
                 else fail("invalid math mode %s", v);
             } else {
                 fprintf(stderr, "Error: unknown argument '%s'\n", a);
@@ -188,7 +188,7 @@ static void fillTestKernel(float *target, size_t count) {
 }
 
 // select_algorithm of ConvTest.cpp:318-331 (with 1x1 stride 1 resolved to the implicit GEMM); with -m tf32 or
-// tf32-strict the library may answer "direct" for layers where its tensor-core kernel is the faster or the only
+// tf32-unbounded the library may answer "direct" for layers where its tensor-core kernel is the faster or the only
 // accurate-enough TF32 path.
 static enum nnp_convolution_algorithm select_algorithm(const fc_conv_desc &d, int math_mode) {
     int a = FC_ALGO_IM2COL, m = math_mode;

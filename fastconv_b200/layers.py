@@ -204,7 +204,8 @@ def resolve_plan(desc: ConvDesc, algorithm="auto", mode="tf32", sm_count: int = 
     """(algorithm, math mode) that a layer planned with these arguments runs, as names; needs no GPU.
 
     `auto` is select_algorithm of ConvTest.cpp:318-331 plus, in the TF32 modes, the direct tensor-core kernel where
-    the measured crossovers favour it; "tf32-strict" resolves to "tf32" or "fp32" per layer."""
+    the measured crossovers favour it; "tf32" (the mode that keeps rel-L2 <= 3e-3) resolves to "tf32" or "3xtf32" per
+    layer, "tf32-unbounded" always to "tf32"."""
     algo = _lib.ALGO_NAMES[algorithm] if isinstance(algorithm, str) else int(algorithm)
     m = _lib.MODE_NAMES[mode] if isinstance(mode, str) else int(mode)
     a, r = C.c_int(), C.c_int()
@@ -312,6 +313,12 @@ class ConvLayer:
                 raise ValueError(f"bias has {b.size} values, the layer {self.desc.oc} output channels")
         check(self._lib.fc_conv_set_epilogue(self._conv, None if b is None else _ptr(b), 1 if relu else 0),
               "fc_conv_set_epilogue")
+
+    def set_kernel_config(self, bm: int = 0, bn: int = 0, variant: int = 0, smem_kb: int = 0) -> None:
+        """Fixes the kernel configuration by hand (what mc/nc/kc/row_batch/col_batch of the reference's im2col
+        constructor and the block members its Winograd Tuning() assigns are to the reference); zeros = heuristic."""
+        self._create()
+        check(self._lib.fc_conv_set_kernel_config(self._conv, bm, bn, variant, smem_kb), "fc_conv_set_kernel_config")
 
     @property
     def kernel_launches(self) -> int:
@@ -481,13 +488,19 @@ class LayerList:
 
 
 def make_layer(algorithm: str, *args, **kw) -> ConvLayer:
-    """The dispatch of ConvTest.cpp:365-413 (`-a auto|direct|im2col|winograd`)."""
+    """The dispatch of ConvTest.cpp:365-413 (`-a auto|direct|im2col|winograd`).
+
+    `auto` asks the library for the per-layer plan (fc_resolve_plan) and returns the matching layer class; the layer
+    itself is still created with the algorithm AUTO, so that the library records the request: the math mode then
+    resolves as for `-a auto` and Tuning() may time the rival algorithms too."""
     algo = _lib.ALGO_NAMES[algorithm]
-    if algo == _lib.ALGO_AUTO:
+    requested_auto = algo == _lib.ALGO_AUTO
+    if requested_auto:
         probe = ConvLayer(*args, **kw)
-        algo = select_algorithm(probe.desc)
-    if algo == _lib.ALGO_WINOGRAD:
-        return ConvWinoF63ZCLayer(*args, **kw)
-    if algo == _lib.ALGO_DIRECT:
-        return ConvDirectLayer(*args, **kw)
-    return ConvIm2colLayer(*args, **kw)
+        name, _ = resolve_plan(probe.desc, "auto", probe.mode)
+        algo = _lib.ALGO_NAMES[name]
+    cls = {_lib.ALGO_WINOGRAD: ConvWinoF63ZCLayer, _lib.ALGO_DIRECT: ConvDirectLayer}.get(algo, ConvIm2colLayer)
+    layer = cls(*args, **kw)
+    if requested_auto:
+        layer._algo = _lib.ALGO_AUTO  # instance attribute: fc_conv_create resolves it to the same plan
+    return layer

@@ -25,20 +25,31 @@ def _unit(idx: np.ndarray, seed: int) -> np.ndarray:
     return (_splitmix64(idx, seed) >> _U64(11)).astype(np.float64) * (1.0 / (1 << 53))
 
 
+_CHUNK = 1 << 16  # elements per pass: the temporaries of a pass stay in cache, which is what makes large tensors cheap
+
+
 def uniform(shape, seed: int, lo: float = -1.0, hi: float = 1.0) -> np.ndarray:
     n = int(np.prod(shape))
-    u = _unit(np.arange(n, dtype=_U64), seed)
-    return (lo + (hi - lo) * u).astype(np.float32).reshape(shape)
+    out = np.empty(n, np.float32)
+    for a in range(0, n, _CHUNK):
+        b = min(n, a + _CHUNK)
+        u = _unit(np.arange(a, b, dtype=_U64), seed)
+        out[a:b] = (lo + (hi - lo) * u).astype(np.float32)
+    return out.reshape(shape)
 
 
 def normal(shape, seed: int, std: float = 1.0) -> np.ndarray:
     """Box-Muller on two independent counter streams."""
     n = int(np.prod(shape))
-    idx = np.arange(n, dtype=_U64)
-    u1 = 1.0 - _unit(idx * _U64(2), seed)  # (0, 1]
-    u2 = _unit(idx * _U64(2) + _U64(1), seed)
-    z = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)
-    return (z * std).astype(np.float32).reshape(shape)
+    out = np.empty(n, np.float32)
+    for a in range(0, n, _CHUNK):
+        b = min(n, a + _CHUNK)
+        idx = np.arange(a, b, dtype=_U64)
+        u1 = 1.0 - _unit(idx * _U64(2), seed)  # (0, 1]
+        u2 = _unit(idx * _U64(2) + _U64(1), seed)
+        z = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)
+        out[a:b] = (z * std).astype(np.float32)
+    return out.reshape(shape)
 
 
 def conv_input(batch: int, ic: int, ih: int, iw: int, seed: int) -> np.ndarray:

@@ -54,12 +54,16 @@ typedef enum fc_math_mode {
     FC_MATH_FP32_MIRRORED = 0, /* FFMA, one fused multiply-add per reduction step in ascending order:
                                   bit-identical to the reference's accumulation chain            */
     FC_MATH_3XTF32 = 1,        /* tcgen05 tensor cores, hi/lo TF32 split, fp32 accumulate         */
-    FC_MATH_TF32 = 2,          /* tcgen05 tensor cores, single TF32 pass                          */
-    FC_MATH_TF32_STRICT = 3    /* fc_conv_create only: TF32 wherever it stays within rel-L2 3e-3 of the fp32 result.
-                                  Single-pass TF32 through F(6x6,3x3) does not (6.4e-3), so a Winograd-eligible layer
-                                  runs the direct tensor-core kernel in TF32 or, where that cannot run or Winograd
-                                  was asked for by name, the Winograd path in FC_MATH_FP32_MIRRORED; other layers run
-                                  as in FC_MATH_TF32.  fc_conv_math_mode reports the mode the layer was planned with. */
+    FC_MATH_TF32 = 2,          /* tcgen05 tensor cores, one TF32 pass per reduction step.  The stage entry points
+                                  (fc_wino_*, fc_igemm_*) run exactly that.  For a planned layer (fc_conv_create) the
+                                  mode stands for its tolerance, rel-L2 <= 3e-3 against the fp32 result: one TF32 pass
+                                  through F(6x6,3x3) measures 6.4e-3, so a Winograd-eligible layer runs the direct
+                                  tensor-core kernel in TF32 or, where that cannot run or Winograd was asked for by
+                                  name, the Winograd path in FC_MATH_3XTF32; every other layer runs in one TF32 pass.
+                                  fc_conv_math_mode reports the arithmetic the layer was planned with.             */
+    FC_MATH_TF32_UNBOUNDED = 3 /* fc_conv_create only: one TF32 pass on every path, F(6x6,3x3) included, whatever the
+                                  error (6.4e-3 rel-L2 on Winograd layers).  Faster than FC_MATH_TF32 on layers with
+                                  many channels at small batch; outside the stated tolerance, hence the extra name. */
 } fc_math_mode;
 
 typedef struct fc_conv_desc {
@@ -91,6 +95,10 @@ int fc_context_create(int device, size_t arena_bytes, fc_context **out);
 int fc_context_destroy(fc_context *ctx);
 int fc_context_synchronize(fc_context *ctx);
 int fc_context_device(const fc_context *ctx, int *device);
+/* What a roofline needs to know about the GPU behind a context: the number of SMs and the maximum SM clock in MHz
+ * (FP32 pipe peak = sm_count * 128 lanes * 2 flop * clock).  No reference counterpart; its nearest relative is
+ * get_cache_info, utility/common.cpp:56-181, which reads the cache sizes the reference's tuner blocks for. */
+int fc_context_info(const fc_context *ctx, int *sm_count, int *sm_clock_max_mhz);
 /* the context's cudaStream_t, for callers that enqueue their own work in order with the library's */
 int fc_context_stream(const fc_context *ctx, void **stream);
 /* PrivateMemPool::Alloc / GetSize / Free / FreeAll / PrintStats */
@@ -126,7 +134,8 @@ int fc_conv_output_size(const fc_conv_desc *desc, int *oh, int *ow);
 int fc_select_algorithm(const fc_conv_desc *desc, int *algo);
 /* What fc_conv_create plans for (desc, algo, mode) on a GPU with sm_count SMs (0 = 148): FC_ALGO_AUTO resolved --
  * select_algorithm as above, then, in the TF32 modes, the direct tensor-core kernel where the measured crossovers
- * favour it -- and FC_MATH_TF32_STRICT resolved to FC_MATH_TF32 or FC_MATH_FP32_MIRRORED.  Needs no GPU.  The reference
+ * favour it -- and the planned-layer meaning of FC_MATH_TF32 / FC_MATH_TF32_UNBOUNDED resolved to the arithmetic that
+ * runs (FC_MATH_TF32 or FC_MATH_3XTF32).  Needs no GPU.  The reference
  * has one arithmetic and a shape-only choice (ConvTest.cpp:318-331); this is that choice with the mode added. */
 int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, int *algo_out, int *mode_out);
 /* element counts (floats) of the Winograd-domain buffers for a descriptor */
@@ -146,7 +155,9 @@ int fc_wino_buffer_elems(const fc_conv_desc *desc, int mode, size_t *u_elems, si
  *                          floats and element (oc, ic) sits at (oc%128)*32 + ic%32 inside it -- one
  *                          box is one TMA load of the GEMM.
  * fc_wino_buffer_elems gives the float counts. */
-/* offline_kernel_transform_v1, winoF63ZC/winoF63ZC.h:14 (winoF63ZC.cpp:242-322) */
+/* offline_kernel_transform_v1, winoF63ZC/winoF63ZC.h:14 (winoF63ZC.cpp:242-322).  Synchronous: d_U is complete on
+ * return.  The forward entry points below read U before they wait for earlier work of the stream, so a caller that
+ * fills d_U by other means must have finished doing so before it enqueues a forward. */
 int fc_wino_filter_transform(fc_context *ctx, const float *d_kernel, float *d_U, int oc, int ic, int mode);
 /* input transform stage, winoF63ZC/winoF63ZC.cpp:512-813 */
 int fc_wino_input_transform(fc_context *ctx, const float *d_in, float *d_V, const fc_conv_desc *desc, int mode);
@@ -204,8 +215,9 @@ int fc_conv_create(fc_context *ctx, const fc_conv_desc *desc, int algo, int mode
                    fc_conv **out);
 int fc_conv_destroy(fc_conv *conv);
 int fc_conv_algorithm(const fc_conv *conv, int *algo);
-/* The arithmetic the layer runs in: the mode given to fc_conv_create, or what FC_MATH_TF32_STRICT resolved to
- * (FC_MATH_TF32 or FC_MATH_FP32_MIRRORED).  No reference counterpart: the reference computes in fp32 only. */
+/* The arithmetic the layer runs in: the mode given to fc_conv_create, or what FC_MATH_TF32 / FC_MATH_TF32_UNBOUNDED
+ * resolved to for this layer (FC_MATH_TF32 or FC_MATH_3XTF32).  No reference counterpart: the reference computes in
+ * fp32 only. */
 int fc_conv_math_mode(const fc_conv *conv, int *mode);
 /* Epilogue of the layer: every output element becomes relu(y + bias[oc]) before it is stored (both
  * parts optional: h_bias NULL = no bias, relu 0 = no clamp).  The reference carries a bias operand
@@ -230,9 +242,32 @@ int fc_conv_time_device(fc_conv *conv, const float *d_in, float *d_out, int warm
  * [0] InputTran / Im2colTran, [1] KernelTran (one-time, measured at create), [2] TensorGEMM / Gemm,
  * [3] OutputTran, [4] Total  (labels of convLayer/winoF63ConvZC.cpp:249-253, im2colConv.cpp:254-256) */
 int fc_conv_profile(fc_conv *conv, const float *d_in, float *d_out, int iters, float stage_ms[5]);
+/* Per-iteration device milliseconds of the most recent fc_conv_profile call: the "round time:" line the reference
+ * prints inside its -i loop (convLayer/winoF63ConvZC.cpp:227-247).  At most `capacity` values are written; *count
+ * receives how many iterations were recorded. */
+int fc_conv_round_times(const fc_conv *conv, float *ms, int capacity, int *count);
+/* Algorithmic work of one forward in the algorithm the layer runs, for throughput and roofline lines:
+ *   direct_flops  2*N*K*C/group*R*S*OH*OW (what the reference's benchmark scripts count)
+ *   algo_flops    Winograd: 2*64*T*C*K with T the tile count including overhang; otherwise direct_flops
+ *   algo_bytes    4*(input + filter as the kernels read it (64*C*K for Winograd, C*K*R*S otherwise) + output)
+ *   min_bytes     4*(input + raw filter + output)
+ * Any pointer may be NULL. */
+int fc_conv_work(const fc_conv *conv, double *direct_flops, double *algo_flops, double *algo_bytes, double *min_bytes);
 /* Tuning(): picks the kernel configuration (and, for FC_ALGO_AUTO, the algorithm) from measured
  * device time (convLayer/winoF63ConvZC.cpp:25-174, convLayer/im2colConv.cpp:261-283). */
 int fc_conv_tune(fc_conv *conv, int iters, int verbose);
+/* The kernel configuration fixed by hand instead of by Tuning(): what the blocking arguments of the reference
+ * constructors are to its layers (mc, nc, kc, row_batch, col_batch of ConvIm2colLayer, convLayer/im2colConv.h:16-18;
+ * the members ocBlock / tileBlock / icBlock that ConvWinoF63ZCLayer::Tuning assigns, convLayer/winoF63ConvZC.cpp:151-161).
+ * Every field 0 = the launcher's heuristic.  bm x bn: block of output channels x tiles or pixels (FFMA kernels: 64 or
+ * 128 each for Winograd, 128x128 ... 8x32 for the table-driven implicit GEMM; tcgen05 kernels: bn = accumulator
+ * width, a multiple of 16 up to 256).  variant: 1 / 2 select between the two kernels a path has (Winograd fp32 with
+ * at most 32 tiles: 1 = the few-tile kernel, 2 = the blocked one; implicit GEMM: 1 = table-driven FFMA kernel,
+ * 2 = the 16x16-thread FFMA kernel in fp32 mode and the tcgen05 kernel in the tensor-core modes).  smem_kb: size of
+ * the operand ring of the tcgen05 kernels.  A combination the layer's kernels do not offer is reported by the next
+ * forward (FC_ERR_INVALID_ARG / FC_ERR_UNSUPPORTED).  A layer list that captured the layer must be rebuilt. */
+int fc_conv_set_kernel_config(fc_conv *conv, int bm, int bn, int variant, int smem_kb);
+int fc_conv_get_kernel_config(const fc_conv *conv, int *bm, int *bn, int *variant, int *smem_kb);
 /* number of kernel launches one forward issues (for launch accounting) */
 int fc_conv_launches_per_forward(const fc_conv *conv, int *launches);
 
@@ -267,7 +302,8 @@ int fc_layer_list_destroy(fc_layer_list *list);
  * ranks have published `step`, after which this rank's buffer holds the whole [oc_total][oh][ow]
  * output.  `step` must grow by one per forward; a caller that lets ranks run ahead of each other
  * alternates between two output buffers.  A wait that gives up reports FC_ERR_TIMEOUT at the next
- * fc_context_synchronize. */
+ * fc_context_synchronize; the gathered output is then undefined.  The limit is fc_context_set_wait_limit_ms
+ * (initially $FASTCONV_PEER_WAIT_MS, else 5000 ms: ranks may be seconds apart while one of them still plans or tunes). */
 #define FC_MAX_PEERS 8
 #define FC_PEER_HANDLE_BYTES 64
 /* handle of the context's arena allocation and the offset of `dptr` inside it */
@@ -280,6 +316,65 @@ int fc_peer_close(fc_context *ctx, void *base);
 int fc_conv_forward_scatter(fc_conv *conv, const float *d_in, float *const *outs, int *const *flags, int world,
                             int rank, int k0, int oc_total, int step);
 int fc_peer_wait(fc_context *ctx, const int *d_flags, int world, int step);
+int fc_context_set_wait_limit_ms(fc_context *ctx, int ms);
+
+/* ---- several GPUs of one machine ------------------------------------------------
+ * No counterpart in the reference either (same nearest relative: the OpenMP split over output channels,
+ * winoF63ZC/winoF63ZC.cpp:1486-1544, whose threads share one address space as the GPUs here share NVLink).
+ * A communicator owns one context per local rank.  Two ways to run:
+ *   fc_comm_init_all   ONE process drives `ndev` GPUs (devices[] or 0..ndev-1); ranks = positions in that list.
+ *   fc_comm_init_env   one process per GPU under a launcher: RANK, WORLD_SIZE, LOCAL_RANK (device < 0 = LOCAL_RANK)
+ *                      and MASTER_PORT are read from the environment; rank 0 hands the NCCL id to the others through
+ *                      a file under /tmp named after the launcher's process id and the port (or $FASTCONV_COMM_ID_FILE).
+ * Every entry point acts on the ranks local to the calling process; with several processes all of them must make
+ * the same calls in the same order.  NCCL is loaded at run time (libnccl.so.2 or $FASTCONV_NCCL_LIB) and only
+ * where it is needed: several processes, or the NCCL gather. */
+typedef struct fc_comm fc_comm;
+int fc_comm_init_all(int ndev, const int *devices, size_t arena_bytes, fc_comm **out);
+int fc_comm_init_env(int device, size_t arena_bytes, fc_comm **out);
+/* every sharded layer of the communicator must be destroyed first */
+int fc_comm_destroy(fc_comm *comm);
+int fc_comm_size(const fc_comm *comm, int *world, int *local_count, int *first_rank);
+int fc_comm_context(fc_comm *comm, int local_index, fc_context **ctx);
+/* all device work of every rank complete and every rank arrived */
+int fc_comm_barrier(fc_comm *comm);
+/* values[local_count] in; each replaced by the maximum over all ranks (how a job's time is taken: the slowest rank) */
+int fc_comm_allreduce_max(fc_comm *comm, double *values);
+/* balanced contiguous split of range(total): the first total % world ranks get one item more */
+int fc_shard_range(int total, int world, int rank, int *begin, int *end);
+
+/* A layer sharded over the communicator.
+ *   FC_SHARD_BATCH     rank r runs images [b0, b1) of desc->batch; full weights on every rank; NO collective.
+ *   FC_SHARD_CHANNELS  single image; rank r owns output channels [k0, k1): its slice of the weights only, the whole
+ *                      input, and afterwards every rank holds the whole output.  gather = FC_GATHER_PEER: the Winograd
+ *                      output transform stores each result into every rank's buffer over NVLink and its last block
+ *                      publishes a step number (one kernel, no collective launch; fc_sharded_conv_wait enqueues the
+ *                      bounded wait for the other ranks' slabs).  FC_GATHER_NCCL: one ncclAllGather after the layer.
+ * The reduction over input channels is never split: the result is bit-equal to the unsharded layer's.
+ * h_kernel is the whole layer's [oc][ic/group][kh][kw].  Host tensors of upload / download / forward_host:
+ *   batch split    the images of THIS process's ranks back to back (the whole batch when one process owns all ranks)
+ *   channel split  the one input image; the whole [oc][oh][ow] output (delivered by the first local rank)
+ * forward / wait are asynchronous on the ranks' streams; two output buffers alternate from forward to forward, so a
+ * rank that is one forward ahead never overwrites what a peer still reads.  The peer gather keeps its step number
+ * on the device: a captured forward can be replayed. */
+enum { FC_SHARD_BATCH = 0, FC_SHARD_CHANNELS = 1 };
+enum { FC_GATHER_PEER = 0, FC_GATHER_NCCL = 1 };
+typedef struct fc_sharded_conv fc_sharded_conv;
+int fc_sharded_conv_create(fc_comm *comm, const fc_conv_desc *desc, int algo, int mode, int shard, int gather,
+                           const float *h_kernel, fc_sharded_conv **out);
+int fc_sharded_conv_destroy(fc_sharded_conv *sc);
+/* the planned layer of one local rank (NULL when the rank owns nothing), its device input / current output and its
+ * range of images or channels; any pointer may be NULL */
+int fc_sharded_conv_part(fc_sharded_conv *sc, int local_index, fc_conv **conv, float **d_in, float **d_out, int *begin,
+                         int *end);
+int fc_sharded_conv_upload(fc_sharded_conv *sc, const float *h_in);
+int fc_sharded_conv_forward(fc_sharded_conv *sc);
+int fc_sharded_conv_wait(fc_sharded_conv *sc);
+int fc_sharded_conv_download(fc_sharded_conv *sc, float *h_out);
+int fc_sharded_conv_forward_host(fc_sharded_conv *sc, const float *h_in, float *h_out);
+/* `iters` forwards (+ waits) timed with CUDA events on every rank's stream after a barrier; the result is the
+ * maximum over all ranks of the mean per forward */
+int fc_sharded_conv_time_device(fc_sharded_conv *sc, int warmup, int iters, float *ms_per_iter);
 
 /* ---- error metrics on the host ---------------------------------------------- */
 /* diff(), utility/helper.cpp:74-89: mean |a-b| over the elements with |a-b| > 1e-5 */

@@ -7,7 +7,7 @@
  *
  * Parity pin: every function below is validated bit-for-bit against the
  * reference's own sources compiled on this host (oracle/_ref, see
- * oracle/Makefile) by tests/test_oracle_vs_reference.py, and against the
+ * oracle/Makefile) by tests/test_oracle_golden.py, and against the
  * golden vectors under tests/golden/ that were generated from that build.
  * The reference itself ships no tests, fixtures or known-answer vectors.
  *
@@ -281,14 +281,19 @@ void oracle_im2col(float *B, const float *in, int ic, int ih, int iw, int kh, in
  * fused multiply-add per k starting from C = 0.  This is the accumulation
  * order of the reference's register kernels (im2col/gemm_kernel.cpp:350-420,
  * `fmla` per k with C loaded first; kc blocks continue the chain through C,
- * convLayer/im2colConv.cpp:465-557).  The reference never zeroes C
- * (conv_layer.h:79); the restatement starts from zero.
+ * convLayer/im2colConv.cpp:465-557).  When M = oc, N = oh*ow and K are all at
+ * most 32 the reference runs its scalar GEMM instead (convLayer/im2colConv.h:30-31,
+ * im2colConv.cpp:400-432): `C += temp * B`, a separate multiplication and
+ * addition per k.  The reference never zeroes C (conv_layer.h:79); the
+ * restatement starts from zero.  Bit-equal to the reference's sgemm() run
+ * through oracle/_ref (tests/test_oracle_golden.py).
  * in is [n][ic][ih][iw], kernel [oc][ic][kh][kw], out [n][oc][oh][ow]. */
 int oracle_im2col_gemm_forward(float *out, const float *in, const float *kernel, int n, int ic, int oc, int ih,
                                int iw, int kh, int kw, int sh, int sw, int pad_l, int pad_r, int pad_t, int pad_b) {
     const int ow = (iw + pad_l + pad_r - kw) / sw + 1;
     const int oh = (ih + pad_t + pad_b - kh) / sh + 1;
     if (oh < 1 || ow < 1) return -1;
+    const int scalar_gemm = oc <= 32 && oh * ow <= 32 && ic * kh * kw <= 32;
 #pragma omp parallel for collapse(2)
     for (int img = 0; img < n; ++img) {
         for (int k = 0; k < oc; ++k) {
@@ -304,7 +309,8 @@ int oracle_im2col_gemm_forward(float *out, const float *in, const float *kernel,
                                 const float b = (row < 0 || row >= ih || col < 0 || col >= iw)
                                                     ? 0.0f
                                                     : src[(size_t)row * iw + col];
-                                acc = fmaf(a[(c * kh + u) * kw + v], b, acc);
+                                const float av = a[(c * kh + u) * kw + v];
+                                acc = scalar_gemm ? acc + av * b : fmaf(av, b, acc);
                             }
                     }
                     out[(((size_t)img * oc + k) * oh + i) * ow + j] = acc;

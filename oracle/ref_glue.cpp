@@ -12,6 +12,10 @@
  *   ref_naive_conv3x3      -> ConvNaiveLayer::Forward     convLayer/naiveConv.h:24-64
  *   ref_im2col / _v1       -> ConvIm2colLayer::im2col()   convLayer/im2colConv.cpp:285-309
  *                             ConvIm2colLayer::im2col_v1()                      :311-382
+ *   ref_im2col_sgemm       -> ConvIm2colLayer::Init(), im2col_v1(), sgemm()
+ *                             convLayer/im2colConv.cpp:224-235, 311-382, 384-398: GEMM_v2 (:434-565) with the
+ *                             8x8 register kernel for one thread, GEMM_multithread (:568-703) for more, the
+ *                             scalar GEMM (:400-432) when M, N, K <= 32
  *   ref_diff               -> diff()                      utility/helper.cpp:74-89
  *
  * The Winograd driver is called with tileRegBlock = 5, ocRegBlock = 4 and
@@ -123,6 +127,29 @@ int ref_im2col(float *gathered, const float *in, int ic, int ih, int iw, int kh,
         memcpy(gathered, layer.gathered(), n * sizeof(float));
     }
     free(dummy_kernel);
+    return 0;
+}
+
+/*
+ * One forward of the reference's im2col layer: gather, then sgemm().  The reference never zeroes its
+ * output and every register kernel computes C += A*B (im2col/gemm_kernel.cpp:350-400), so C is cleared
+ * here first -- the one liberty taken.  Constructor defaults otherwise (mc 8, nc 256, kc 384, 8x8 kernel,
+ * C in place; convLayer/im2colConv.h:16-18).  The register kernels run through their intrinsic branches:
+ * the library is built from a copy of im2col/gemm_kernel.cpp and im2col/gemm_pack.cpp in which the one
+ * line `#define __ARM_ASM` is blanked (oracle/Makefile), nothing else changed.
+ */
+int ref_im2col_sgemm(float *out, const float *in, const float *kernel, int ic, int oc, int ih, int iw, int kh, int kw,
+                     int sh, int sw, int pad_l, int pad_r, int pad_t, int pad_b, int threads) {
+    if (threads < 1) return -1;
+    omp_set_num_threads(threads);
+    Im2colProbe layer((float *)in, (float *)kernel, NULL, NULL, ic, ih, iw, oc, kh, kw, sh, sw, pad_l, pad_r, pad_t,
+                      pad_b, 1, false, threads, 1);
+    const size_t n = (size_t)oc * layer.get_output_height() * layer.get_output_width();
+    layer.Init();
+    memset(layer.output_data, 0, (n + 128) * sizeof(float));
+    layer.im2col_v1();
+    layer.sgemm();
+    memcpy(out, layer.output_data, n * sizeof(float));
     return 0;
 }
 

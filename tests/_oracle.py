@@ -132,6 +132,16 @@ class Reference:
         assert self.lib.ref_naive_conv3x3(P(out), P(x), P(w), ic, oc, ih, iw, pad) == 0
         return out
 
+    def im2col_sgemm(self, x, w, sh, sw, pad):
+        """im2col_v1() + sgemm() of the reference's im2col layer on one thread, C cleared first."""
+        x, w = f32(x), f32(w)
+        ic, ih, iw = x.shape[-3:]
+        oc, _, kh, kw = w.shape
+        oh, ow = (ih + 2 * pad - kh) // sh + 1, (iw + 2 * pad - kw) // sw + 1
+        out = np.zeros((oc, oh, ow), np.float32)
+        assert self.lib.ref_im2col_sgemm(P(out), P(x), P(w), ic, oc, ih, iw, kh, kw, sh, sw, pad, pad, pad, pad, 1) == 0
+        return out
+
     def im2col(self, x, kh, kw, sh, sw, pad, which=0):
         x = f32(x)
         ic, ih, iw = x.shape[-3:]

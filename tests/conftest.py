@@ -56,6 +56,6 @@ def golden():
 @pytest.fixture(scope="session")
 def ctx():
     import fastconv_b200 as fc
-    c = fc.Context(0, arena_bytes=6 << 30)
+    c = fc.Context(0, arena_bytes=10 << 30)
     yield c
     c.close()

@@ -2,7 +2,7 @@
 
 Run where the reference tree is present (its location is the REF variable of oracle/Makefile):
 
-    make -C oracle ref && python tests/golden/make_golden.py
+    make -C oracle ref [REF=...] && python tests/golden/make_golden.py
 
 It loads oracle/_ref/libfastconv_ref.so -- the reference's own sources compiled through the NEON
 stand-in header (oracle/Makefile) -- and records, for seeded inputs from fastconv_b200.synth:
@@ -11,7 +11,10 @@ stand-in header (oracle/Makefile) -- and records, for seeded inputs from fastcon
     threads than output-channel register blocks the reference's OpenMP driver mis-computes, e.g.
     oc <= 4 at 8 threads, so the pins are taken single-threaded),
   * the output of the reference's naive layers (ConvNaiveLayer, both variants),
-  * SHA-256 digests of the matrices gathered by ConvIm2colLayer::im2col() and im2col_v1().
+  * SHA-256 digests of the matrices gathered by ConvIm2colLayer::im2col() and im2col_v1(),
+  * the output of the reference's im2col layer -- im2col_v1() then sgemm() -- with the constructor's default
+    blocking on one thread: GEMM_v2 with the 8x8 register kernel and its corner kernels, across several kc and
+    nc blocks, and the scalar GEMM that the reference switches to when M, N and K are all at most 32.
 
 Small cases are stored whole; the two full-size layers are stored as digests plus a strided sample.
 The reference ships no golden vectors of its own, so these files are the pins.
@@ -39,6 +42,15 @@ GENERAL = [  # ic, oc, ih, iw, kh, kw, sh, sw, pad
     (3, 8, 30, 30, 7, 7, 2, 2, 3), (16, 12, 14, 14, 1, 1, 1, 1, 0), (8, 8, 15, 15, 3, 3, 2, 2, 1),
     (12, 6, 14, 14, 1, 1, 2, 2, 0), (5, 7, 9, 11, 3, 3, 1, 1, 1), (4, 4, 8, 8, 5, 3, 1, 2, 2),
 ]
+
+
+SGEMM = [  # ic, oc, ih, iw, kh, kw, sh, sw, pad -- M % 8 corners, N % 8 tails, K > kc = 384, N > nc = 256, tiny
+    (3, 8, 30, 30, 7, 7, 2, 2, 3), (16, 12, 14, 14, 1, 1, 1, 1, 0), (8, 8, 15, 15, 3, 3, 2, 2, 1),
+    (12, 6, 14, 14, 1, 1, 2, 2, 0), (5, 7, 9, 11, 3, 3, 1, 1, 1), (4, 4, 8, 8, 5, 3, 1, 2, 2),
+    (100, 37, 13, 13, 3, 3, 1, 1, 1), (130, 9, 10, 10, 5, 5, 1, 1, 2), (64, 19, 23, 17, 1, 1, 1, 1, 0),
+    (2, 3, 4, 4, 3, 3, 1, 1, 1), (3, 32, 6, 5, 3, 3, 1, 1, 1), (32, 5, 4, 8, 1, 1, 1, 1, 0), (33, 5, 4, 8, 1, 1, 1, 1, 0),
+]
+SGEMM_LARGE = [(3, 64, 224, 224, 7, 7, 2, 2, 3), (256, 128, 28, 28, 3, 3, 2, 2, 1), (512, 128, 28, 28, 1, 1, 1, 1, 0)]
 
 
 def P(a):
@@ -85,6 +97,22 @@ def main() -> None:
         meta["general"].append({"idx": idx, "ic": ic, "oc": oc, "ih": ih, "iw": iw, "kh": kh, "kw": kw, "sh": sh,
                                 "sw": sw, "pad": pad, "seed_in": 1000 + idx, "seed_w": 2000 + idx, "sha_in": sha(x),
                                 "sha_w": sha(w), "sha_gather": sha(g0), "sha_naive": sha(naive)})
+    meta["sgemm"], meta["sgemm_large"] = [], []
+    for j, (ic, oc, ih, iw, kh, kw, sh, sw, pad) in enumerate(SGEMM + SGEMM_LARGE):
+        idx = 200 + j
+        x = synth.conv_input(1, ic, ih, iw, 1000 + idx)
+        w = synth.conv_weights(oc, ic, kh, kw, 2000 + idx)
+        oh, ow = (ih + 2 * pad - kh) // sh + 1, (iw + 2 * pad - kw) // sw + 1
+        out = np.zeros((oc, oh, ow), np.float32)
+        assert ref.ref_im2col_sgemm(P(out), P(x), P(w), ic, oc, ih, iw, kh, kw, sh, sw, pad, pad, pad, pad, 1) == 0
+        rec = {"idx": idx, "ic": ic, "oc": oc, "ih": ih, "iw": iw, "kh": kh, "kw": kw, "sh": sh, "sw": sw, "pad": pad,
+               "seed_in": 1000 + idx, "seed_w": 2000 + idx, "sha_in": sha(x), "sha_w": sha(w), "sha_sgemm": sha(out)}
+        if j < len(SGEMM):
+            arrays[f"sgemm_{idx}"] = out
+            meta["sgemm"].append(rec)
+        else:
+            arrays[f"sgemm_sample_{idx}"] = out.ravel()[::997].copy()
+            meta["sgemm_large"].append(rec)
     out_path = Path(__file__).with_name("fastconv_golden.npz")
     np.savez_compressed(out_path, meta=np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8), **arrays)
     print(out_path, out_path.stat().st_size, "bytes")

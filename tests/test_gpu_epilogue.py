@@ -68,7 +68,7 @@ def test_implicit_gemm_epilogue_bit_exact(ctx, oracle, case):
 
 @pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
 def test_tensor_core_modes_apply_the_epilogue(ctx, oracle, mode):
-    tol = 2e-5 if mode == "3xtf32" else 8e-3
+    tol = 2e-5 if mode == "3xtf32" else 3e-3
     x = synth.conv_input(1, 64, 28, 28, 77)
     b = _bias(96, 78)
     w3 = synth.conv_weights(96, 64, 3, 3, 79)

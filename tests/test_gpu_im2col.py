@@ -1,5 +1,7 @@
 """Parity of the im2col / implicit-GEMM path: the gathered matrix is bit-exact with the reference's
-index map; the mirrored fp32 GEMM is bit-exact with the oracle's one-FMA-per-k chain."""
+index map -- as dumped by the inspection entry point AND as the forward kernels' own operand producers gather it
+(identity weights turn a layer's output into its gathered matrix); the mirrored fp32 GEMM is bit-exact with the
+oracle's one-FMA-per-k chain, which is pinned to the reference's sgemm() by the golden vectors."""
 import hashlib
 
 import numpy as np
@@ -59,6 +61,62 @@ def test_mirrored_gemm_bit_exact(ctx, oracle, case):
     assert layer.Init() == 1 and layer.Forward() == 1  # return values of im2colConv.cpp:234, :258
     want = oracle.im2col_gemm_forward(x, w, sh, sw, pad, pad, pad, pad)
     assert np.array_equal(layer.output_data, want)
+    layer.release()
+
+
+def test_mirrored_gemm_matches_reference_sgemm_vectors(ctx, golden):
+    """Outputs of the reference's own im2col_v1() + sgemm() (GEMM_v2 with its 8x8 register kernels, and the scalar
+    GEMM of the M, N, K <= 32 case), recorded in tests/golden: the CUDA layer reproduces them bit for bit."""
+    meta, z = golden
+    for rec in meta["sgemm"] + meta["sgemm_large"]:
+        x = synth.conv_input(1, rec["ic"], rec["ih"], rec["iw"], rec["seed_in"])
+        w = synth.conv_weights(rec["oc"], rec["ic"], rec["kh"], rec["kw"], rec["seed_w"])
+        layer = make(ctx, x, w, rec["sh"], rec["sw"], rec["pad"])
+        layer.Init()
+        layer.Forward()
+        assert sha(layer.output_data[0]) == rec["sha_sgemm"], rec
+        layer.release()
+
+
+def _tf32_exact(a):
+    """Values with 10 explicit mantissa bits: a tensor-core product of such a value with 1.0 is exact."""
+    return (np.ascontiguousarray(a, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+# n, ic, ih, iw, kh, kw, sh, sw, (left, right, top, bottom)
+IDENTITY_SHAPES = {
+    "3x3": (2, 8, 13, 11, 3, 3, 1, 1, (1, 1, 1, 1)),
+    "5x3s2": (1, 6, 17, 14, 5, 3, 2, 2, (2, 1, 0, 2)),
+    "7x7s2": (1, 3, 40, 36, 7, 7, 2, 2, (3, 3, 3, 3)),
+    "few-pixels": (1, 64, 14, 14, 3, 3, 2, 2, (1, 1, 1, 1)),  # 49 pixels, K = 576: the gathered matrix is written once
+}
+# mode, bm, bn, variant (see fc_conv_set_kernel_config)
+IDENTITY_KERNELS = (
+    [("fp32", bm, bn, 1) for bm, bn in [(128, 128), (128, 64), (64, 128), (64, 64), (32, 64), (32, 32), (16, 32), (8, 32)]]
+    + [("fp32", 0, 0, 0), ("fp32", 64, 64, 2), ("fp32", 128, 128, 2)]
+    + [(m, 0, bn, 2) for m in ("3xtf32", "tf32") for bn in (0, 32, 64, 128)])
+
+
+@pytest.mark.parametrize("kernel", IDENTITY_KERNELS, ids=lambda k: "%s-%dx%d-v%d" % k)
+@pytest.mark.parametrize("shape", sorted(IDENTITY_SHAPES))
+def test_forward_kernels_gather_what_im2col_gathers(ctx, oracle, shape, kernel):
+    """The gather that RUNS in a forward -- the table-driven cp.async producer of every FFMA block shape, the
+    materialised-matrix route of few-pixel layers, the 16x16-thread kernel, the gather warps of the tcgen05 kernel --
+    checked element by element: with oc = K and the identity as weight matrix, output row k IS row k of the gathered
+    matrix (1*x + 0 is exact; in the tensor-core modes the inputs are TF32-representable so that it stays exact)."""
+    n, ic, ih, iw, kh, kw, sh, sw, (pl, pr, pt, pb) = IDENTITY_SHAPES[shape]
+    mode, bm, bn, variant = kernel
+    K = ic * kh * kw
+    x = _tf32_exact(synth.conv_input(n, ic, ih, iw, 23))
+    w = np.eye(K, dtype=np.float32).reshape(K, ic, kh, kw)
+    layer = fc.ConvIm2colLayer(x, w, None, None, ic, ih, iw, K, kh, kw, sh, sw, pl, pr, pt, pb, 1, False, 1, 1,
+                               batch=n, mode=mode, ctx=ctx)
+    layer.Init()
+    layer.set_kernel_config(bm, bn, variant, 0)
+    layer.Forward()
+    for img in range(n):
+        want = oracle.im2col(x[img], kh, kw, sh, sw, pl, pr, pt, pb)
+        assert np.array_equal(layer.output_data[img].reshape(K, -1), want), (shape, kernel, img)
     layer.release()
 
 

@@ -1,7 +1,7 @@
 """Every distinct conv layer of VGG-16 and ResNet-50 v1.5 (batch 1, 224x224) under `-a auto`, at full size:
 fp32 mirrored mode bit-equal to the oracle of the algorithm that `auto` selects, tensor-core modes within
 the stated tolerances (3xTF32: rel-L2 <= 1e-5 up to 256 input channels, <= 1.5e-5 above, see
-test_gpu_winograd.py; im2col path TF32 <= 3e-3).
+test_gpu_winograd.py; TF32 <= 3e-3 on every layer).
 
 On the im2col path the 3xTF32 error grows linearly with the reduction length K = ic*kh*kw (measured
 1.4e-5 at K=2048, 1.6e-5 at K=2304, 3.2e-5 at K=4608): the tensor core's fp32 accumulator rounds toward
@@ -40,7 +40,10 @@ def _run(ctx, oracle, spec, idx, mode):
     layer.Init()
     layer.Forward()
     wino = isinstance(layer, fc.ConvWinoF63ZCLayer)
-    assert wino == (k == 3 and s == 1)  # select_algorithm, ConvTest.cpp:318-331
+    if mode != "tf32":  # select_algorithm, ConvTest.cpp:318-331; "tf32" sends Winograd-eligible layers to the direct kernel
+        assert wino == (k == 3 and s == 1)
+    else:
+        assert not wino
     want = oracle.wino_forward(x, w, p) if wino else oracle.im2col_gemm_forward(x, w, s, s, p, p, p, p)
     got = layer.output_data.copy()
     layer.release()
@@ -74,5 +77,5 @@ def test_resnet50_layers_tensor_core(ctx, oracle, idx):
         if mode == "3xtf32":
             bound = (1e-5 if ic <= 256 else 1.5e-5) if wino else max(1e-5, 8e-9 * ic * k * k)
         else:
-            bound = 8e-3 if wino else 3e-3  # single-pass TF32 through F(6x6,3x3) measures 6.4e-3
+            bound = 3e-3  # the tolerance the mode stands for, on every path
         assert rel_l2(got, want) <= bound, (mode, RESNET50[idx], rel_l2(got, want))

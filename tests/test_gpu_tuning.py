@@ -91,19 +91,20 @@ def test_im2col_tuning(ctx, oracle, tuning_log, capfd):
     layer.release()
 
 
-@pytest.mark.parametrize("case, rivals", [
-    ((4, 256, 128, 28, 1, 0), ("algo=direct", "algo=im2col")),     # 1x1: direct against the gathering kernel
-    ((1, 64, 64, 56, 3, 1), ("algo=direct", "algo=winograd")),     # 3x3, few channels: direct against Winograd
+@pytest.mark.parametrize("case, mode, rivals", [
+    ((4, 256, 128, 28, 1, 0), "tf32", ("algo=direct", "algo=im2col")),     # 1x1: direct against the gathering kernel
+    # 3x3, few channels: direct against Winograd -- only where one TF32 pass through Winograd is allowed at all
+    ((1, 64, 64, 56, 3, 1), "tf32-unbounded", ("algo=direct", "algo=winograd")),
 ])
-def test_auto_in_tf32_times_the_direct_kernel_against_its_rival(ctx, oracle, tuning_log, capfd, case, rivals):
+def test_auto_in_tf32_times_the_direct_kernel_against_its_rival(ctx, oracle, tuning_log, capfd, case, mode, rivals):
     n, ic, oc, hw, k, pad = case
     lib = fc.load()
     x = synth.conv_input(n, ic, hw, hw, 531)
     w = synth.conv_weights(oc, ic, k, k, 532)
     d = fc.make_desc(n, ic, hw, hw, oc, k, k, 1, 1, pad, pad, pad, pad)
     h = C.c_void_p()
-    fc._lib.check(lib.fc_conv_create(ctx.handle, C.byref(d), fc.ALGO_AUTO, fc.MATH_TF32, C.c_void_p(w.ctypes.data), C.byref(h)),
-                  "create")
+    fc._lib.check(lib.fc_conv_create(ctx.handle, C.byref(d), fc.ALGO_AUTO, fc._lib.MODE_NAMES[mode], C.c_void_p(w.ctypes.data),
+                                     C.byref(h)), "create")
     algo = C.c_int()
     lib.fc_conv_algorithm(h, C.byref(algo))
     assert algo.value == fc.ALGO_DIRECT  # the untuned choice for these shapes

@@ -3,10 +3,11 @@
 fp32 "mirrored" mode is held to BIT equality with the oracle (which is itself bit-equal to the
 reference build).  3xTF32 is held to rel-L2 <= 1e-5 and max-abs <= 1e-4*||out||inf up to 256 input
 channels; at 512 channels it measures 1.3e-5, which is the size of the reference's own
-accumulation-order noise (1.06e-5), so the bound there is 1.5e-5.  Single-pass TF32 measures
-6.4e-3 on every layer: F(6x6,3x3) amplifies the 2^-11 operand rounding about 16x, so the 3e-3
-target of the fast mode is NOT met by one TF32 pass; the test pins the measured level (<= 8e-3)
-and a strict xfail records the unmet target.
+accumulation-order noise (1.06e-5), so the bound there is 1.5e-5.  The mode "tf32" stands for
+rel-L2 <= 3e-3 and is held to it: a Winograd layer asked for by name then runs the split
+arithmetic, because one TF32 pass through F(6x6,3x3) measures 6.4e-3 (the transform amplifies the
+2^-11 operand rounding about 16x).  That single pass is the mode "tf32-unbounded": the test pins
+its measured level (<= 8e-3) and a strict xfail records that it misses 3e-3.
 """
 import ctypes as C
 import hashlib
@@ -194,7 +195,7 @@ def test_reference_self_check_line(ctx, oracle, capsys):
     layer.release()
 
 
-@pytest.mark.parametrize("mode, tol_l2, tol_max", [("3xtf32", 1e-5, 1e-4), ("tf32", 8e-3, 4e-2)])
+@pytest.mark.parametrize("mode, tol_l2, tol_max", [("3xtf32", 1e-5, 1e-4), ("tf32", 3e-3, 1.5e-2), ("tf32-unbounded", 8e-3, 4e-2)])
 @pytest.mark.parametrize("shape", [(1, 64, 64, 56, 56, 1), (1, 256, 256, 56, 56, 1), (2, 37, 70, 20, 23, 1),
                                    (1, 3, 64, 40, 40, 1), (1, 128, 128, 14, 14, 1), (1, 8, 8, 6, 6, 1),
                                    (1, 200, 136, 30, 30, 1), (3, 40, 300, 13, 13, 1)])
@@ -221,10 +222,10 @@ def test_3xtf32_at_512_channels_is_at_the_reference_noise_floor(ctx, oracle):
 
 @pytest.mark.xfail(strict=True, reason="one TF32 pass through F(6x6,3x3) measures 6.4e-3 rel-L2; the 3e-3 target "
                                        "needs more than single-pass TF32 operands")
-def test_single_pass_tf32_meets_3e_3(ctx, oracle):
+def test_single_pass_tf32_through_winograd_meets_3e_3(ctx, oracle):
     x = synth.conv_input(1, 64, 56, 56, 95)
     w = synth.conv_weights(64, 64, 3, 3, 96)
-    assert rel_l2(run_layer(ctx, x, w, 1, mode="tf32"), oracle.wino_forward(x, w, 1)) <= 3e-3
+    assert rel_l2(run_layer(ctx, x, w, 1, mode="tf32-unbounded"), oracle.wino_forward(x, w, 1)) <= 3e-3
 
 
 def test_tensor_core_kernel_reports_no_timeouts(ctx):

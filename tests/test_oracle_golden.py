@@ -65,6 +65,37 @@ def test_general_paths_match_golden(oracle, golden):
         assert rel_l2(gemm, naive) < 2e-6
 
 
+def test_sgemm_oracle_matches_golden(oracle, golden):
+    """The one-FMA-per-k chain of the oracle (and the unfused chain of the M, N, K <= 32 case) against the output of
+    the reference's own im2col_v1() + sgemm(): GEMM_v2 with its 8x8 register and corner kernels over several kc and
+    nc blocks, and the scalar GEMM."""
+    meta, z = golden
+    assert len(meta["sgemm"]) >= 12 and len(meta["sgemm_large"]) >= 3
+    for rec in meta["sgemm"] + meta["sgemm_large"]:
+        x, w = _inputs(rec, rec["kh"], rec["kw"])
+        p = rec["pad"]
+        got = oracle.im2col_gemm_forward(x, w, rec["sh"], rec["sw"], p, p, p, p)[0]
+        assert sha(got) == rec["sha_sgemm"], f"SGEMM chain differs from the reference for {rec}"
+        key = f"sgemm_{rec['idx']}"
+        if key in z:
+            assert np.array_equal(got, z[key])
+        else:
+            assert np.array_equal(got.ravel()[::997], z[f"sgemm_sample_{rec['idx']}"])
+
+
+@pytest.mark.parametrize("g", [(3, 8, 30, 7, 2, 3), (16, 12, 14, 1, 1, 0), (100, 37, 13, 3, 1, 1), (130, 9, 10, 5, 1, 2),
+                               (64, 64, 56, 1, 1, 0), (2, 3, 4, 3, 1, 1), (3, 32, 6, 3, 1, 1), (33, 5, 5, 1, 1, 0),
+                               (40, 50, 20, 3, 1, 1)])
+def test_sgemm_oracle_bit_equal_to_reference_build(oracle, reference, g):
+    if reference is None:
+        pytest.skip("oracle/_ref is not built in this checkout (needs the reference tree)")
+    ic, oc, hw, k, s, pad = g
+    x = synth.conv_input(1, ic, hw, hw, 13)
+    w = synth.conv_weights(oc, ic, k, k, 14)
+    assert np.array_equal(oracle.im2col_gemm_forward(x, w, s, s, pad, pad, pad, pad)[0],
+                          reference.im2col_sgemm(x[0], w, s, s, pad))
+
+
 @pytest.mark.parametrize("shape", [(3, 5, 7, 9, 1), (8, 8, 12, 12, 1), (17, 6, 23, 20, 1), (5, 3, 6, 6, 0),
                                    (6, 7, 13, 8, 2), (4, 4, 1, 1, 1), (64, 48, 28, 28, 1), (128, 128, 14, 14, 1)])
 def test_oracle_bit_equal_to_reference_build(oracle, reference, shape):

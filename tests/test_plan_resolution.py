@@ -22,7 +22,9 @@ def test_exact_modes_keep_the_reference_choice(mode):
     assert plan(8, 64, 64, 224, 3, algo="direct", mode=mode) == ("im2col", mode)  # no direct kernel in these modes
 
 
-def test_tf32_auto_on_the_vgg16_layers():
+def test_unbounded_tf32_auto_on_the_vgg16_layers():
+    def plan(*a, **k):
+        return globals()["plan"](*a, mode="tf32-unbounded", **k)
     # batch 1: few channels -> direct; small maps (shared reduction) -> direct; the middle of the network -> Winograd
     assert plan(1, 3, 64, 224, 3)[0] == "direct"
     assert plan(1, 64, 128, 112, 3)[0] == "direct"
@@ -44,16 +46,32 @@ def test_tf32_auto_on_1x1_and_strided_layers():
     assert plan(1, 128, 128, 56, 3, s=2)[0] == "direct"   # stride 2 = element stride of the tensor map
     assert plan(64, 3, 64, 224, 7, s=2)[0] == "im2col"    # the stem: 3 real channels per k-block, 49 taps that do not fold
     assert plan(1, 64, 64, 56, 3, s=3)[0] == "im2col"     # stride 3: no direct kernel
-    assert plan(1, 64, 64, 56, 3, algo="winograd") == ("winograd", "tf32")  # an algorithm asked for by name is kept
+    assert plan(1, 64, 64, 56, 3, algo="winograd") == ("winograd", "3xtf32")  # the algorithm asked for by name is kept
+    assert plan(1, 64, 64, 56, 3, algo="winograd", mode="tf32-unbounded") == ("winograd", "tf32")
 
 
-def test_strict_tf32_never_runs_tf32_through_winograd():
+def test_tf32_never_runs_one_pass_through_winograd():
+    """"tf32" stands for rel-L2 <= 3e-3, which one TF32 pass through F(6x6,3x3) misses."""
     for n in (1, 8, 64):
         for ic, oc, hw in [(3, 64, 224), (128, 128, 112), (256, 256, 56), (512, 512, 28), (512, 512, 14), (512, 512, 7)]:
-            assert plan(n, ic, oc, hw, 3, mode="tf32-strict") == ("direct", "tf32")
-    assert plan(1, 256, 256, 56, 3, algo="winograd", mode="tf32-strict") == ("winograd", "fp32")
-    assert plan(1, 256, 64, 56, 1, mode="tf32-strict")[1] == "tf32"
-    assert plan(1, 3, 64, 224, 7, s=2, mode="tf32-strict") == ("im2col", "tf32")
+            assert plan(n, ic, oc, hw, 3) == ("direct", "tf32")
+    assert plan(1, 256, 256, 56, 3, algo="winograd") == ("winograd", "3xtf32")
+    assert plan(1, 256, 64, 56, 1)[1] == "tf32"
+    assert plan(1, 3, 64, 224, 7, s=2) == ("im2col", "tf32")
+
+
+def test_make_layer_auto_follows_the_plan():
+    """The Python front end, the CLI and the library agree on what `auto` means in every mode."""
+    import numpy as np
+    for mode in ("fp32", "3xtf32", "tf32", "tf32-unbounded"):
+        for ic, oc, hw, k, s in [(64, 64, 56, 3, 1), (256, 256, 56, 3, 1), (64, 256, 56, 1, 1), (128, 128, 56, 3, 2)]:
+            p = k // 2
+            x = np.zeros((1, ic, hw, hw), np.float32)
+            w = np.zeros((oc, ic, k, k), np.float32)
+            layer = fc.make_layer("auto", x, w, None, None, ic, hw, hw, oc, k, k, s, s, p, p, p, p, mode=mode)
+            name = {fc.ConvWinoF63ZCLayer: "winograd", fc.ConvDirectLayer: "direct", fc.ConvIm2colLayer: "im2col"}[type(layer)]
+            assert name == plan(1, ic, oc, hw, k, s=s, mode=mode)[0]
+            assert layer._algo == 0  # created as AUTO, so the library records the request
 
 
 def test_bad_arguments_are_refused():
