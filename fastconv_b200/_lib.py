@@ -116,6 +116,7 @@ SIGNATURES = {
     "fc_comm_context": (C.c_int, [_vp, C.c_int, C.POINTER(_vp)]),
     "fc_comm_barrier": (C.c_int, [_vp]),
     "fc_comm_allreduce_max": (C.c_int, [_vp, C.POINTER(C.c_double)]),
+    "fc_comm_allgather": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
     "fc_shard_range": (C.c_int, [C.c_int, C.c_int, C.c_int, _ip, _ip]),
     "fc_sharded_conv_create": (C.c_int, [_vp, _dp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "fc_sharded_conv_destroy": (C.c_int, [_vp]),

@@ -397,6 +397,11 @@ int fc_comm_allreduce_max(fc_comm *c, double *values) {
     return FC_OK;
 }
 
+int fc_comm_allgather(fc_comm *c, const void *mine, void *all, size_t bytes) {
+    FC_REQUIRE(c && mine && all && bytes > 0, FC_ERR_INVALID_ARG, "bad argument");
+    return comm_allgather_bytes(c, mine, all, bytes);
+}
+
 int fc_comm_destroy(fc_comm *c) {
     if (!c) return FC_OK;
     // an exporter must not free memory that a peer still maps: everyone stops, unmaps, and only then frees

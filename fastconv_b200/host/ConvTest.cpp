@@ -14,7 +14,10 @@
 //   * the self-check honours kernel size, stride and padding (the reference always checks against a
 //     3x3 / pad 1 naive layer, ConvTest.cpp:360) and also covers the im2col path;
 //   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32|tf32-unbounded, -seed N (the reference seeds from
-//     the clock), -nc/--no-check, -g/--gpu INDEX.  -t is accepted and only sizes the host self-check.
+//     the clock), -nc/--no-check, -dev INDEX, and for several GPUs of one machine driven by this one process
+//     -g/--gpus N with -shard batch|k (images or output channels split over the GPUs) and -gather peer|nccl.
+//     -t is accepted and only sizes the host self-check;
+//   * after the reference's lines: one "Throughput:" line and one machine-readable JSON line per layer.
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -46,7 +49,10 @@ struct options {
     int math_mode;
     long seed;
     bool check;
-    int gpu;
+    int device;  // CUDA device index of a one-GPU run
+    int gpus;    // number of GPUs (ranks) of a sharded run
+    int shard;   // FC_SHARD_BATCH or FC_SHARD_CHANNELS
+    int gather;  // FC_GATHER_PEER or FC_GATHER_NCCL
 };
 
 static void print_options_help(const char *program_name) {
@@ -69,7 +75,10 @@ static void print_options_help(const char *program_name) {
            "  -m   --math               fp32 (bit-identical accumulation), 3xtf32, tf32 (within 3e-3) or tf32-unbounded (default: fp32)\n"
            "  -seed                     Seed of the input/kernel generator (default: from the clock)\n"
            "  -nc  --no-check           Skip the naive host convolution and the difference line\n"
-           "  -g   --gpu                CUDA device index (default: 0)\n",
+           "  -dev --device             CUDA device index of a one-GPU run (default: 0)\n"
+           "  -g   --gpus               Number of GPUs the layer is sharded over (default: 1)\n"
+           "  -shard                    batch (images split, no collective) or k (output channels split; one image) (default: batch)\n"
+           "  -gather                   with -shard k: peer (stores of the output transform over NVLink) or nccl (default: peer)\n",
            program_name);
 }
 
@@ -108,7 +117,10 @@ static struct options parse_options(int argc, char **argv) {
     o.math_mode = FC_MATH_FP32_MIRRORED;
     o.seed = -1;
     o.check = true;
-    o.gpu = 0;
+    o.device = 0;
+    o.gpus = 1;
+    o.shard = FC_SHARD_BATCH;
+    o.gather = FC_GATHER_PEER;
 
     for (int i = 1; i < argc; ++i) {
         const char *a = argv[i];
@@ -137,7 +149,17 @@ static struct options parse_options(int argc, char **argv) {
             else if (is_flag(a, "--threads", "-t")) o.threads = parse_positive(v, "the number of threads");
             else if (is_flag(a, "--iterations", "-i")) o.iterations = parse_positive(v, "the number of iterations");
             else if (is_flag(a, "--batch", "-n")) o.batch = parse_positive(v, "the batch size");
-            else if (is_flag(a, "--gpu", "-g")) o.gpu = (int)parse_positive(v, "the GPU index", true);
+            else if (is_flag(a, "--device", "-dev")) o.device = (int)parse_positive(v, "the GPU index", true);
+            else if (is_flag(a, "--gpus", "-g")) o.gpus = (int)parse_positive(v, "the number of GPUs");
+            else if (is_flag(a, "--shard", "-shard")) {
+                if (strcmp(v, "batch") == 0) o.shard = FC_SHARD_BATCH;
+                else if (strcmp(v, "k") == 0) o.shard = FC_SHARD_CHANNELS;
+                else fail("invalid partitioning %s", v);
+            } else if (is_flag(a, "--gather", "-gather")) {
+                if (strcmp(v, "peer") == 0) o.gather = FC_GATHER_PEER;
+                else if (strcmp(v, "nccl") == 0) o.gather = FC_GATHER_NCCL;
+                else fail("invalid gather %s", v);
+            }
             else if (strcmp(a, "-seed") == 0 || strcmp(a, "--seed") == 0) o.seed = (long)parse_positive(v, "the seed", true);
             else if (is_flag(a, "--algorithm", "-a")) {
                 if (strcmp(v, "auto") == 0) o.algorithm = nnp_convolution_algorithm_auto;
@@ -196,6 +218,92 @@ static enum nnp_convolution_algorithm select_algorithm(const fc_conv_desc &d, in
     return (enum nnp_convolution_algorithm)a;
 }
 
+static const char *algorithm_name(int a) {
+    return a == FC_ALGO_WINOGRAD ? "winograd" : a == FC_ALGO_DIRECT ? "direct" : "im2col";
+}
+static const char *math_name(int m) { return m == FC_MATH_3XTF32 ? "3xtf32" : m == FC_MATH_TF32 ? "tf32" : "fp32"; }
+
+// One JSON line per layer: what ran, how long it took, and how far that is from the layer's roofline -- the slower of
+// its algorithmic flops at the arithmetic peak of the mode and its algorithmic bytes at the HBM bandwidth.  Peaks: FP32
+// = SMs x 128 lanes x 2 x the maximum SM clock; TF32 = $FASTCONV_TF32_TFLOPS, else 759.9 (a library GEMM of 8192^3 on a
+// B200), a third of it for 3xTF32; HBM = $FASTCONV_HBM_GBS, else 6538.3 (a device-to-device copy on a B200).
+static void print_json_line(fc_context *ctx, fc_conv *conv, const fc_conv_desc &d, double ms, int gpus, const char *shard) {
+    double direct = 0, flops = 0, bytes = 0, min_bytes = 0;
+    int algo = 0, mode = 0, sms = 148, mhz = 1965;
+    fc_conv_work(conv, &direct, &flops, &bytes, &min_bytes);
+    fc_conv_algorithm(conv, &algo);
+    fc_conv_math_mode(conv, &mode);
+    fc_context_info(ctx, &sms, &mhz);
+    const char *e_tf32 = getenv("FASTCONV_TF32_TFLOPS"), *e_hbm = getenv("FASTCONV_HBM_GBS");
+    const double tf32 = e_tf32 ? atof(e_tf32) : 759.9, hbm = e_hbm ? atof(e_hbm) : 6538.3;
+    const double fp32 = sms * 128.0 * 2.0 * mhz * 1e-6;
+    const double peak = mode == FC_MATH_FP32_MIRRORED ? fp32 : mode == FC_MATH_TF32 ? tf32 : tf32 / 3.0;
+    // a sharded layer: `conv` is one rank's share, and every rank has its own peaks
+    const double t_flop = flops / (peak * 1e12) * 1e3, t_hbm = bytes / (hbm * 1e9) * 1e3;
+    const double roof = t_flop > t_hbm ? t_flop : t_hbm;
+    const double whole = 2.0 * d.batch * d.oc * (double)(d.ic / d.group) * d.kh * d.kw *
+                         (double)((d.ih + d.pad_top + d.pad_bottom - d.kh) / d.sh + 1) *
+                         (double)((d.iw + d.pad_left + d.pad_right - d.kw) / d.sw + 1);
+    printf("{\"layer\": \"%d->%d@%dx%d %dx%ds%d\", \"batch\": %d, \"gpus\": %d, \"shard\": \"%s\", \"algo\": \"%s\", "
+           "\"math\": \"%s\", \"ms\": %.6f, \"gflops_direct_equiv\": %.1f, \"roofline_ms\": %.6f, "
+           "\"frac_of_roofline\": %.4f, \"bound\": \"%s\", \"peak_tflops\": %.1f, \"hbm_gbs\": %.1f}\n",
+           d.ic, d.oc, d.ih, d.iw, d.kh, d.kw, d.sh, d.batch, gpus, shard, algorithm_name(algo), math_name(mode), ms,
+           whole / (ms * 1e-3) / 1e9, roof, roof / ms, t_flop > t_hbm ? "math" : "hbm", peak, hbm);
+}
+
+void ConvLayer::print_json(const fc_conv_desc &d) {
+    if (conv) print_json_line(ctx, conv, d, stage_ms[4], 1, "none");
+}
+
+// -g N: the layer sharded over N GPUs that this process drives (fc_comm_init_all, fc_sharded_conv_*).
+static int run_sharded(const struct options &options, const fc_conv_desc &d, int oh, int ow, float *test_input,
+                       float *test_kernel, float *ref) {
+    fc_comm *comm = NULL;
+    const size_t act = ((size_t)d.batch * d.ic * d.ih * d.iw + (size_t)d.batch * d.oc * oh * ow) * sizeof(float);
+    const size_t wts = (size_t)d.ic * d.oc * d.kh * d.kw * sizeof(float);
+    const size_t tiles = (size_t)d.batch * ((oh + 5) / 6) * ((ow + 5) / 6) + 8;
+    const size_t wino = 64 * sizeof(float) * ((size_t)(d.oc + 8) * (d.ic + 8) + tiles * (d.ic + 8) + tiles * (d.oc + 8));
+    if (fc_comm_init_all(options.gpus, NULL, 2 * (act + 8 * wts + wino) + (256u << 20), &comm) != FC_OK) {
+        fprintf(stderr, "Error: %s\n", fc_last_error());
+        return EXIT_FAILURE;
+    }
+    fc_sharded_conv *sc = NULL;
+    const int algo = options.algorithm == nnp_convolution_algorithm_auto ? FC_ALGO_AUTO : (int)options.algorithm;
+    if (fc_sharded_conv_create(comm, &d, algo, options.math_mode, options.shard, options.gather, test_kernel, &sc) != FC_OK) {
+        fprintf(stderr, "Error: %s\n", fc_last_error());
+        fc_comm_destroy(comm);
+        return EXIT_FAILURE;
+    }
+    fc_conv *part = NULL;
+    fc_sharded_conv_part(sc, 0, &part, NULL, NULL, NULL, NULL);
+    int ran = FC_ALGO_IM2COL;
+    if (part) fc_conv_algorithm(part, &ran);
+    printf("Algorithm: %s\n", ran == FC_ALGO_WINOGRAD ? "winograd F63" : algorithm_name(ran));
+    printf("Sharding: %s over %d GPUs%s\n", options.shard == FC_SHARD_BATCH ? "images" : "output channels", options.gpus,
+           options.shard == FC_SHARD_BATCH ? ", no collective"
+                                           : options.gather == FC_GATHER_PEER ? ", gathered by the output transform's stores"
+                                                                              : ", NCCL all-gather");
+    const size_t out_elems = (size_t)d.batch * d.oc * oh * ow;
+    float *out = (float *)malloc(out_elems * sizeof(float));
+    float ms = 0.f;
+    if (fc_sharded_conv_forward_host(sc, test_input, out) != FC_OK ||
+        fc_sharded_conv_time_device(sc, 2, options.iterations > 0 ? (int)options.iterations : 1, &ms) != FC_OK) {
+        fprintf(stderr, "Error: %s\n", fc_last_error());
+        return EXIT_FAILURE;
+    }
+    printf("Total time: %lfms\n", (double)ms);
+    if (ref != NULL) diff(ref, out, (int)out_elems);
+    const double flops = 2.0 * d.batch * d.oc * d.ic * d.kh * d.kw * oh * ow;
+    printf("Throughput: %.1f GFLOP/s (direct-equivalent, %.6f ms per forward)\n", flops / (ms * 1e-3) / 1e9, ms);
+    fc_context *ctx0 = NULL;
+    fc_comm_context(comm, 0, &ctx0);
+    if (part) print_json_line(ctx0, part, d, ms, options.gpus, options.shard == FC_SHARD_BATCH ? "batch" : "k");
+    free(out);
+    fc_sharded_conv_destroy(sc);
+    fc_comm_destroy(comm);
+    return 0;
+}
+
 int main(int argc, char *argv[]) {
     struct options options = parse_options(argc, argv);
     srand(options.seed >= 0 ? (unsigned)options.seed : (unsigned)time(NULL));
@@ -224,9 +332,9 @@ int main(int argc, char *argv[]) {
 
     if (options.algorithm == nnp_convolution_algorithm_auto) options.algorithm = select_algorithm(d, options.math_mode);
 
-    if (fastconv_default_context() == NULL && options.gpu != 0) {
+    if (fastconv_default_context() == NULL && options.device != 0 && options.gpus == 1) {
         fc_context *ctx = NULL;
-        if (fc_context_create(options.gpu, (size_t)8 << 30, &ctx) != FC_OK) {
+        if (fc_context_create(options.device, (size_t)8 << 30, &ctx) != FC_OK) {
             fprintf(stderr, "Error: %s\n", fc_last_error());
             return EXIT_FAILURE;
         }
@@ -241,6 +349,14 @@ int main(int argc, char *argv[]) {
         conv_reference->Forward();
     }
     float *ref = conv_reference ? conv_reference->output_data : NULL;
+
+    if (options.gpus > 1) {
+        const int rc = run_sharded(options, d, oh, ow, test_input, test_kernel, ref);
+        delete conv_reference;
+        free(test_input);
+        free(test_kernel);
+        return rc;
+    }
 
     ConvLayer *conv = NULL;
     if (options.algorithm == nnp_convolution_algorithm_winograd)
@@ -264,6 +380,7 @@ int main(int argc, char *argv[]) {
     const float *ms = conv->stage_milliseconds();
     const double flops = 2.0 * options.batch * oc * ic * ks.height * ks.width * oh * ow;
     printf("Throughput: %.1f GFLOP/s (direct-equivalent, %.6f ms per forward)\n", flops / (ms[4] * 1e-3) / 1e9, ms[4]);
+    conv->print_json(d);
 
     delete conv;
     delete conv_reference;

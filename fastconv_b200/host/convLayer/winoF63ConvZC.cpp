@@ -23,10 +23,8 @@ int ConvWinoF63ZCLayer::Tuning() {
 
 int ConvWinoF63ZCLayer::Init() {
     printf("Algorithm: winograd F63\n");
-    const int tiles = (int)(batch * ((output_height + 5) / 6) * ((output_width + 5) / 6));
-    printf("Testing ic=%d oc=%d width=%d tiles=%d batch=%d threads=%d\n", (int)input_channels, (int)output_channels,
-           (int)input_width, tiles, (int)batch, (int)num_threads);
     plan(FC_ALGO_WINOGRAD);
+    print_testing_line();
     return -1;  // as convLayer/winoF63ConvZC.cpp:212
 }
 

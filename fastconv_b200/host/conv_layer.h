@@ -82,6 +82,8 @@ public:
     void set_math_mode(int mode) { math_mode = mode; }
     void set_context(fc_context *c) { ctx = c; }
     const float *stage_milliseconds() const { return stage_ms; }
+    // one machine-readable line for the layer (see print_json_line in ConvTest.cpp)
+    void print_json(const fc_conv_desc &d);
 
     float *output_data;
 
@@ -133,10 +135,29 @@ protected:
         }
         float *d_in = NULL, *d_out = NULL;
         fc_conv_device_buffers(conv, &d_in, &d_out);
-        if (fc_conv_profile(conv, d_in, d_out, iterations > 0 ? (int)iterations : 1, stage_ms) != FC_OK) {
+        const int iters = iterations > 0 ? (int)iterations : 1;
+        if (fc_conv_profile(conv, d_in, d_out, iters, stage_ms) != FC_OK) {
             fprintf(stderr, "fastconv: %s\n", fc_last_error());
             exit(EXIT_FAILURE);
         }
+        // the reference prints one "round time:" line per iteration of its -i loop (convLayer/winoF63ConvZC.cpp:245)
+        float *rounds = (float *)malloc(iters * sizeof(float));
+        int count = 0;
+        if (rounds && fc_conv_round_times(conv, rounds, iters, &count) == FC_OK)
+            for (int i = 0; i < count && i < iters; ++i) printf("round time: %lfms\n", (double)rounds[i]);
+        free(rounds);
+    }
+
+    // The reference's line (convLayer/winoF63ConvZC.cpp:191-192) with this library's blocking in the three block
+    // fields: tile block, channel block (0 = chosen per launch by the library) and the k-step of the kernels' operand
+    // ring (16 floats in the fp32 mode, 32 in the tensor-core modes); then the tile count and the batch.
+    void print_testing_line() {
+        int bm = 0, bn = 0;
+        if (conv) fc_conv_get_kernel_config(conv, &bm, &bn, NULL, NULL);
+        const int tiles = (int)(batch * ((output_height + 5) / 6) * ((output_width + 5) / 6));
+        printf("Testing ic=%d oc=%d width=%d tileBlock=%d ocBlock=%d icBlock=%d threads=%d tiles=%d batch=%d\n",
+               (int)input_channels, (int)output_channels, (int)input_width, bn, bm,
+               math_mode == FC_MATH_FP32_MIRRORED ? 16 : 32, (int)num_threads, tiles, (int)batch);
     }
 
     size_t input_channels, input_width, input_height;

@@ -37,10 +37,17 @@ def _ptr(a: np.ndarray) -> C.c_void_p:
 class Context:
     """One GPU, one stream, one device arena (fc_context)."""
 
-    def __init__(self, device: int = 0, arena_bytes: int = 1 << 30):
+    def __init__(self, device: int = 0, arena_bytes: int = 1 << 30, *, _borrowed: Optional[C.c_void_p] = None):
         self._lib = _lib.load()
-        h = C.c_void_p()
-        check(self._lib.fc_context_create(device, arena_bytes, C.byref(h)), "fc_context_create")
+        self._owned = _borrowed is None
+        if _borrowed is None:
+            h = C.c_void_p()
+            check(self._lib.fc_context_create(device, arena_bytes, C.byref(h)), "fc_context_create")
+        else:  # a context that belongs to a communicator (fc_comm_context): used here, destroyed there
+            h = _borrowed
+            dev = C.c_int()
+            check(self._lib.fc_context_device(h, C.byref(dev)), "fc_context_device")
+            device = dev.value
         self._h = h
         self.device = device
         self._pinned = []
@@ -67,7 +74,8 @@ class Context:
             for p in self._pinned:
                 self._lib.fc_host_free_pinned(p)
             self._pinned = []
-            self._lib.fc_context_destroy(self._h)
+            if self._owned:
+                self._lib.fc_context_destroy(self._h)
             self._h = None
 
     def __enter__(self):

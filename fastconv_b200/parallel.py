@@ -1,4 +1,5 @@
-"""Multi-GPU partitioning of the convolution path: one process per GPU, torch.distributed for the plumbing.
+"""Several GPUs of one machine: thin ctypes front end of the communicator and the sharded layers of the C ABI
+(fc_comm_*, fc_sharded_conv_*), plus the partition arithmetic as plain functions.
 
 The reference has no distributed code (its only parallelism is OpenMP inside one process), so nothing here
 mirrors a reference interface; the two partitionings are the ones the path offers naturally:
@@ -8,20 +9,34 @@ mirrors a reference interface; the two partitionings are the ones the path offer
 * K sharding      -- output channels are independent: rank r owns channels [k0, k1) of a single-image
   wide layer, i.e. transforms and keeps only its slice of the weights (which is what shrinks the
   dominant 64*C*K weight stream), reads the whole (small) input, and produces the slab
-  out[:, k0:k1] -- contiguous in NCHW for one image -- which one all-gather reassembles on every
-  rank.  The reduction over input channels is never split, so every output element is computed by
+  out[:, k0:k1] -- contiguous in NCHW for one image.  The slabs reach every rank either through the stores of
+  the output transform itself (peer memory over NVLink, step flags, bounded wait) or through one NCCL
+  all-gather.  The reduction over input channels is never split, so every output element is computed by
   exactly the arithmetic of the unsharded layer: sharded == unsharded bit for bit.
+
+Nothing here computes and nothing here needs torch: process groups, collectives and peer mappings live in the
+library.  `KShardedConv` is the exception, kept for CPU tests of the partition logic: it all-gathers slabs that
+any callable produced, over a torch.distributed group of any backend.
 """
 from __future__ import annotations
 
 import ctypes as C
-from typing import Callable, Optional, Tuple
+from typing import Callable, List, Optional, Tuple
 
 import numpy as np
 
+from . import _lib
+from .layers import Context, make_desc
+
+SHARD_BATCH, SHARD_CHANNELS = 0, 1
+GATHER_PEER, GATHER_NCCL = 0, 1
+SHARD_NAMES = {"batch": SHARD_BATCH, "k": SHARD_CHANNELS, "channels": SHARD_CHANNELS}
+GATHER_NAMES = {"peer": GATHER_PEER, "nccl": GATHER_NCCL}
+
 
 def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
-    """Contiguous balanced split of range(total): the first total % world ranks get one extra item."""
+    """Contiguous balanced split of range(total): the first total % world ranks get one extra item
+    (the same arithmetic as fc_shard_range)."""
     if world < 1 or not 0 <= rank < world:
         raise ValueError(f"bad rank {rank} of {world}")
     if total < 0:
@@ -40,6 +55,150 @@ def shard_channels(oc: int, world: int, rank: int, multiple: int = 1) -> Tuple[i
     blocks = -(-oc // multiple)
     b0, b1 = shard_range(blocks, world, rank)
     return min(b0 * multiple, oc), min(b1 * multiple, oc)
+
+
+class Comm:
+    """fc_comm: the GPUs of one machine as ranks.  `Comm.all(n)` drives n GPUs from this process; `Comm.from_env()`
+    is one rank of a job started by a launcher (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_PORT in the environment)."""
+
+    def __init__(self, handle: C.c_void_p):
+        self._lib = _lib.load()
+        self._h = handle
+        w, n, f = C.c_int(), C.c_int(), C.c_int()
+        _lib.check(self._lib.fc_comm_size(handle, C.byref(w), C.byref(n), C.byref(f)), "fc_comm_size")
+        self.world, self.local_count, self.first_rank = w.value, n.value, f.value
+        self.contexts: List[Context] = []
+        for i in range(self.local_count):
+            c = C.c_void_p()
+            _lib.check(self._lib.fc_comm_context(handle, i, C.byref(c)), "fc_comm_context")
+            self.contexts.append(Context(_borrowed=c))
+        self._layers = []
+
+    @classmethod
+    def all(cls, ndev: int, arena_bytes: int = 1 << 30, devices=None) -> "Comm":
+        lib = _lib.load()
+        h = C.c_void_p()
+        arr = None if devices is None else (C.c_int * ndev)(*devices)
+        _lib.check(lib.fc_comm_init_all(ndev, arr, arena_bytes, C.byref(h)), "fc_comm_init_all")
+        return cls(h)
+
+    @classmethod
+    def from_env(cls, device: int = -1, arena_bytes: int = 1 << 30) -> "Comm":
+        lib = _lib.load()
+        h = C.c_void_p()
+        _lib.check(lib.fc_comm_init_env(device, arena_bytes, C.byref(h)), "fc_comm_init_env")
+        return cls(h)
+
+    @property
+    def handle(self) -> C.c_void_p:
+        if not self._h:
+            raise RuntimeError("communicator is closed")
+        return self._h
+
+    def barrier(self) -> None:
+        _lib.check(self._lib.fc_comm_barrier(self.handle), "fc_comm_barrier")
+
+    def max(self, value: float) -> float:
+        """Maximum over all ranks of `value` (taken as the value of every local rank)."""
+        arr = (C.c_double * self.local_count)(*([float(value)] * self.local_count))
+        _lib.check(self._lib.fc_comm_allreduce_max(self.handle, arr), "fc_comm_allreduce_max")
+        return float(arr[0])
+
+    def allgather(self, values) -> np.ndarray:
+        """One row of float64 values per rank, gathered to every rank: [world][len(values)].  With several local ranks
+        the same row stands for each of them."""
+        row = np.ascontiguousarray(values, dtype=np.float64).reshape(1, -1)
+        mine = np.ascontiguousarray(np.repeat(row, self.local_count, axis=0))
+        out = np.empty((self.world, row.shape[1]), np.float64)
+        _lib.check(self._lib.fc_comm_allgather(self.handle, C.c_void_p(mine.ctypes.data), C.c_void_p(out.ctypes.data),
+                                               row.nbytes), "fc_comm_allgather")
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            for layer in list(self._layers):
+                layer.release()
+            for c in self.contexts:
+                c.close()  # layer lists, pinned buffers; the contexts themselves belong to the communicator
+            self._lib.fc_comm_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class ShardedConv:
+    """fc_sharded_conv: one layer split over the ranks of a communicator by images ("batch") or by output channels
+    ("k", single image; gather "peer" = stores of the output transform into every rank's buffer, "nccl" = one
+    all-gather after the layer)."""
+
+    def __init__(self, comm: Comm, weights: np.ndarray, batch: int, ih: int, iw: int, *, stride=1, pad=1, shard="batch",
+                 gather="peer", algorithm="auto", mode="fp32"):
+        self._lib, self.comm = _lib.load(), comm
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        oc, ic, kh, kw = w.shape
+        self.desc = make_desc(batch, ic, ih, iw, oc, kh, kw, stride, stride, pad, pad, pad, pad)
+        self.oh, self.ow = (ih + 2 * pad - kh) // stride + 1, (iw + 2 * pad - kw) // stride + 1
+        self.shard = SHARD_NAMES[shard] if isinstance(shard, str) else int(shard)
+        h = C.c_void_p()
+        _lib.check(self._lib.fc_sharded_conv_create(comm.handle, C.byref(self.desc), _lib.ALGO_NAMES[algorithm],
+                                                    _lib.MODE_NAMES[mode], self.shard,
+                                                    GATHER_NAMES[gather] if isinstance(gather, str) else int(gather),
+                                                    C.c_void_p(w.ctypes.data), C.byref(h)), "fc_sharded_conv_create")
+        self._h = h
+        comm._layers.append(self)
+
+    def part(self, local_index: int = 0):
+        """(fc_conv handle or None, device input, device output, begin, end) of one local rank."""
+        conv, d_in, d_out, b, e = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_int(), C.c_int()
+        _lib.check(self._lib.fc_sharded_conv_part(self._h, local_index, C.byref(conv), C.byref(d_in), C.byref(d_out),
+                                                  C.byref(b), C.byref(e)), "fc_sharded_conv_part")
+        return (conv if conv.value else None), d_in.value, d_out.value, b.value, e.value
+
+    def local_images(self) -> Tuple[int, int]:
+        """Batch split: the range of images this process's ranks own together."""
+        first, last = self.part(0), self.part(self.comm.local_count - 1)
+        return first[3], last[4]
+
+    def upload(self, x: np.ndarray) -> None:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        _lib.check(self._lib.fc_sharded_conv_upload(self._h, C.c_void_p(x.ctypes.data)), "fc_sharded_conv_upload")
+
+    def forward(self) -> None:
+        _lib.check(self._lib.fc_sharded_conv_forward(self._h), "fc_sharded_conv_forward")
+
+    def wait(self) -> None:
+        _lib.check(self._lib.fc_sharded_conv_wait(self._h), "fc_sharded_conv_wait")
+
+    def download(self) -> np.ndarray:
+        if self.shard == SHARD_BATCH:
+            b0, b1 = self.local_images()
+            out = np.empty((b1 - b0, self.desc.oc, self.oh, self.ow), np.float32)
+        else:
+            out = np.empty((1, self.desc.oc, self.oh, self.ow), np.float32)
+        _lib.check(self._lib.fc_sharded_conv_download(self._h, C.c_void_p(out.ctypes.data)), "fc_sharded_conv_download")
+        return out
+
+    def forward_host(self, x: np.ndarray) -> np.ndarray:
+        self.upload(x)
+        self.forward()
+        self.wait()
+        return self.download()
+
+    def time_device(self, warmup: int = 3, iters: int = 20) -> float:
+        ms = C.c_float()
+        _lib.check(self._lib.fc_sharded_conv_time_device(self._h, warmup, iters, C.byref(ms)), "fc_sharded_conv_time_device")
+        return float(ms.value)
+
+    def release(self) -> None:
+        if self._h:
+            self._lib.fc_sharded_conv_destroy(self._h)
+            self._h = None
+            if self in self.comm._layers:
+                self.comm._layers.remove(self)
 
 
 def allgather_channel_slabs(local, oc: int, group=None):
@@ -69,11 +228,8 @@ def allgather_channel_slabs(local, oc: int, group=None):
 
 
 class KShardedConv:
-    """One single-image layer with its output channels split over the ranks of a process group.
-
-    `forward_slab(x, w_slice) -> ndarray/tensor [n][k_r][oh][ow]` computes this rank's channels; on a GPU
-    it is a planned fastconv layer built from the weight slice (see `gpu`), in CPU tests any convolution.
-    """
+    """CPU-test stand-in for the channel split: `forward_slab(x, w_slice) -> [n][k_r][oh][ow]` computes this
+    rank's channels (any convolution), and the slabs are all-gathered over a torch.distributed group."""
 
     def __init__(self, weights: np.ndarray, forward_slab: Callable, group=None):
         import torch.distributed as dist
@@ -93,150 +249,3 @@ class KShardedConv:
         if not isinstance(slab, torch.Tensor):
             slab = torch.from_numpy(np.ascontiguousarray(slab))
         return allgather_channel_slabs(slab, self.oc, self.group)
-
-    @classmethod
-    def gpu(cls, ctx, weights: np.ndarray, ih: int, iw: int, pad: int = 1, mode: str = "fp32", group=None):
-        """K-sharded Winograd layer on this rank's GPU: the slab is written straight into a torch CUDA
-        tensor by the library, then all-gathered over NCCL."""
-        import torch
-
-        from . import _lib
-        from .layers import make_desc
-
-        lib = _lib.load()
-        state = {}
-
-        def forward_slab(x, w_slice):
-            if "conv" not in state:
-                x = np.ascontiguousarray(x, dtype=np.float32)
-                n, ic = x.shape[:2]
-                desc = make_desc(n, ic, ih, iw, w_slice.shape[0], 3, 3, 1, 1, pad, pad, pad, pad)
-                h = C.c_void_p()
-                _lib.check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, _lib.MODE_NAMES[mode],
-                                              C.c_void_p(w_slice.ctypes.data), C.byref(h)), "fc_conv_create")
-                d_in, d_out = C.c_void_p(), C.c_void_p()
-                _lib.check(lib.fc_conv_device_buffers(h, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
-                oh, ow = ih + 2 * pad - 2, iw + 2 * pad - 2
-                state.update(conv=h, d_in=d_in, slab=torch.empty((n, w_slice.shape[0], oh, ow), dtype=torch.float32,
-                                                                  device=f"cuda:{ctx.device}"))
-            if x is not None:
-                ctx.upload(x, state["d_in"].value)
-            _lib.check(lib.fc_conv_forward_device(state["conv"], state["d_in"], C.c_void_p(state["slab"].data_ptr())),
-                       "fc_conv_forward_device")
-            return state["slab"]
-
-        def release():
-            if "conv" in state:
-                lib.fc_conv_destroy(state.pop("conv"))
-
-        obj = cls(weights, forward_slab, group)
-        obj._state = state
-        obj.release = release
-        ctx.adopt(obj)
-        # torch sees the library's stream as an external stream: with it current, the all-gather is ordered
-        # after the kernels without a host synchronisation, and CUDA events on it time both
-        obj.stream = torch.cuda.ExternalStream(ctx.stream.value, device=f"cuda:{ctx.device}")
-        plain_forward = obj.forward
-
-        def forward_on_library_stream(x):
-            with torch.cuda.stream(obj.stream):
-                return plain_forward(x)
-
-        obj.forward = forward_on_library_stream
-        return obj
-
-
-class PeerKShardedConv:
-    """K-sharded Winograd layer whose all-gather is fused into the output transform: the kernel of each rank
-    stores its channel slab into the output buffer of every rank through peer-mapped pointers over NVLink
-    (`fc_conv_forward_scatter`), publishes a step flag, and a bounded wait kernel on every rank makes the
-    stream wait for all slabs.  No NCCL call in the data path; torch.distributed only carries the CUDA IPC
-    handles at construction.  Two output buffers alternate by step, so a rank that runs one step ahead never
-    overwrites what a peer is still reading; `forward` returns the device address of the buffer just filled.
-    """
-
-    def __init__(self, ctx, weights: np.ndarray, ih: int, iw: int, pad: int = 1, mode: str = "fp32", group=None):
-        import torch.distributed as dist
-
-        from . import _lib
-        from .layers import make_desc
-
-        self._lib, self._check = _lib.load(), _lib.check
-        lib, check = self._lib, self._check
-        self.ctx, self.group = ctx, group
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        if self.world > 8:
-            raise ValueError("at most 8 ranks")
-        self.oc = int(weights.shape[0])
-        ic = int(weights.shape[1])
-        self.k0, self.k1 = shard_channels(self.oc, self.world, self.rank)
-        if self.k1 <= self.k0:
-            raise ValueError("a rank would own no output channel")
-        w_slice = np.ascontiguousarray(weights[self.k0:self.k1], dtype=np.float32)
-        self.oh, self.ow = ih + 2 * pad - 2, iw + 2 * pad - 2
-        desc = make_desc(1, ic, ih, iw, self.k1 - self.k0, 3, 3, 1, 1, pad, pad, pad, pad)
-        h = C.c_void_p()
-        check(lib.fc_conv_create(ctx.handle, C.byref(desc), _lib.ALGO_WINOGRAD, _lib.MODE_NAMES[mode],
-                                 C.c_void_p(w_slice.ctypes.data), C.byref(h)), "fc_conv_create")
-        self._conv = h
-        d_in = C.c_void_p()
-        check(lib.fc_conv_device_buffers(h, C.byref(d_in), None), "fc_conv_device_buffers")
-        self._d_in = d_in
-        self.out_bytes = 4 * self.oc * self.oh * self.ow
-        self._outs = [ctx.alloc(self.out_bytes), ctx.alloc(self.out_bytes)]  # alternate by step
-        self._flags = ctx.zeros(4 * 8)
-        ctx.synchronize()  # the flags are zero before any peer can learn their address
-        self.step = 0
-
-        # exchange the IPC handle of this rank's arena and the offsets of its three buffers
-        handle = (C.c_ubyte * 64)()
-        offs = []
-        for p in (*self._outs, self._flags):
-            off = C.c_size_t()
-            check(lib.fc_peer_export(ctx.handle, C.c_void_p(p), handle, C.byref(off)), "fc_peer_export")
-            offs.append(off.value)
-        mine = (bytes(handle), offs)
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        self._peer_outs = [[0] * self.world, [0] * self.world]
-        self._peer_flags = [0] * self.world
-        opened = ctx._peer_arenas
-        for r, (hbytes, roffs) in enumerate(everyone):
-            if r == self.rank:
-                base = None
-            else:
-                if hbytes not in opened:  # one mapping per peer arena and process
-                    b = C.c_void_p()
-                    buf = (C.c_ubyte * 64).from_buffer_copy(hbytes)
-                    check(lib.fc_peer_open(ctx.handle, buf, C.byref(b)), "fc_peer_open")
-                    opened[hbytes] = b.value
-                base = opened[hbytes]
-            for i in range(2):
-                self._peer_outs[i][r] = self._outs[i] if base is None else base + roffs[i]
-            self._peer_flags[r] = self._flags if base is None else base + roffs[2]
-        dist.barrier(group=group)
-        ctx.adopt(self)
-
-    def upload(self, x: np.ndarray) -> None:
-        self.ctx.upload(np.ascontiguousarray(x, dtype=np.float32), self._d_in.value)
-
-    def forward(self) -> int:
-        """Enqueues one forward on the context stream; returns the device address of the full output."""
-        self.step += 1
-        which = self.step & 1
-        vp = C.c_void_p * self.world
-        outs, flags = vp(*self._peer_outs[which]), vp(*self._peer_flags)
-        self._check(self._lib.fc_conv_forward_scatter(self._conv, self._d_in, outs, flags, self.world, self.rank,
-                                                      self.k0, self.oc, self.step), "fc_conv_forward_scatter")
-        self._check(self._lib.fc_peer_wait(self.ctx.handle, C.c_void_p(self._flags), self.world, self.step),
-                    "fc_peer_wait")
-        return self._outs[which]
-
-    def result(self, dptr: int) -> np.ndarray:
-        self.ctx.synchronize()
-        return self.ctx.download(dptr, (1, self.oc, self.oh, self.ow))
-
-    def release(self) -> None:
-        if self._conv is not None:
-            self._lib.fc_conv_destroy(self._conv)
-            self._conv = None

@@ -340,6 +340,9 @@ int fc_comm_context(fc_comm *comm, int local_index, fc_context **ctx);
 int fc_comm_barrier(fc_comm *comm);
 /* values[local_count] in; each replaced by the maximum over all ranks (how a job's time is taken: the slowest rank) */
 int fc_comm_allreduce_max(fc_comm *comm, double *values);
+/* `bytes` of every rank to every rank through host memory (small records: timings, handles): mine = one record per
+ * local rank, all = one per rank of the world, in rank order */
+int fc_comm_allgather(fc_comm *comm, const void *mine, void *all, size_t bytes);
 /* balanced contiguous split of range(total): the first total % world ranks get one item more */
 int fc_shard_range(int total, int world, int rank, int *begin, int *end);
 

@@ -94,3 +94,57 @@ def test_direct_runs_the_tensor_core_kernel_in_tf32_and_the_implicit_gemm_otherw
     assert "Algorithm: direct" in fast.stdout
     # outputs are ~1e4 (inputs in [0,256), 144 taps): a mean absolute difference of a few units is TF32 rounding (3e-4)
     assert float(re.search(r"The difference is ([0-9.]+)", fast.stdout).group(1)) < 10.0
+
+
+@pytest.mark.gpu
+def test_round_times_testing_line_and_json_line(binary):
+    """The reference prints one `round time:` per -i iteration (convLayer/winoF63ConvZC.cpp:245) and a `Testing ic=...
+    tileBlock=... ocBlock=... icBlock=... threads=...` line (:191-192); the harness adds one JSON line per layer."""
+    import json
+    r = run(binary, "-ic", "16", "-oc", "32", "-is", "18", "18", "-ks", "3", "3", "-i", "4", "-seed", "3")
+    assert r.returncode == 0, r.stderr
+    assert len(re.findall(r"^round time: [0-9.]+ms$", r.stdout, re.M)) == 4
+    assert re.search(r"^Testing ic=16 oc=32 width=18 tileBlock=\d+ ocBlock=\d+ icBlock=\d+ threads=1 tiles=9 batch=1$",
+                     r.stdout, re.M)
+    rec = json.loads([line for line in r.stdout.splitlines() if line.startswith("{")][-1])
+    assert rec["layer"] == "16->32@18x18 3x3s1" and rec["algo"] == "winograd" and rec["math"] == "fp32"
+    assert rec["ms"] > 0 and rec["gflops_direct_equiv"] > 0 and 0 < rec["frac_of_roofline"] <= 1.5
+    assert rec["bound"] in ("hbm", "math")
+
+
+def _gpu_count():
+    import ctypes
+    import fastconv_b200
+    n = ctypes.c_int(0)
+    fastconv_b200.load().fc_device_count(ctypes.byref(n))
+    return n.value
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shard", [["-shard", "batch", "-n", "4"], ["-shard", "k"], ["-shard", "k", "-gather", "nccl"]])
+def test_two_gpus_print_the_difference_line_of_one(binary, shard):
+    """`-g 2` shards the layer over two GPUs driven by the one process; the self-check line is the one-GPU line."""
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    base = ["-ic", "32", "-oc", "64", "-is", "20", "20", "-ks", "3", "3", "-i", "3", "-seed", "1", *shard]
+    one = run(binary, *base)
+    two = run(binary, *base, "-g", "2")
+    assert one.returncode == 0 and two.returncode == 0, one.stderr + two.stderr
+    line = re.compile(r"The difference is ([0-9.]+)")
+    assert line.search(one.stdout).group(0) == line.search(two.stdout).group(0)
+    assert "Sharding:" in two.stdout and "over 2 GPUs" in two.stdout
+
+
+@pytest.mark.gpu
+def test_more_gpus_than_the_box_has_is_refused(binary):
+    r = run(binary, "-ic", "8", "-oc", "8", "-is", "8", "8", "-ks", "3", "3", "-g", "64")
+    assert r.returncode != 0 and "GPUs asked for" in r.stderr
+
+
+@pytest.mark.gpu
+def test_feather_layer_blob_and_pools_chain_two_convolutions(binary):
+    """The FeatherCNN-style interface the reference carries (layer.h, utility/blob.h, utility/mempool.h) instantiated
+    over the GPU library: two convolutions with fused bias + ReLU chained on device blobs, checked on the host."""
+    r = subprocess.run([str(HOST / "feather_chain_test")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "feather chain ok" in r.stdout

@@ -1,8 +1,14 @@
-"""Two GPUs, one process each, NCCL: K-sharded and batch-sharded layers against the single-GPU result.
-Skipped on a box with fewer than two GPUs."""
+"""Layers sharded over a communicator (fc_comm_*, fc_sharded_conv_*) against the single-GPU result, bit for bit.
+
+  * one rank (runs on any box): the same entry points with a world of one, where the peer gather stores into local
+    memory only;
+  * two GPUs driven by ONE process (fc_comm_init_all: peer pointers inside the process);
+  * two GPUs, one process each (fc_comm_init_env: NCCL id through a file, CUDA IPC mappings of the arenas).
+The two-GPU tests are skipped on a box with fewer than two GPUs.
+"""
 import ctypes
 import os
-import socket
+import tempfile
 
 import numpy as np
 import pytest
@@ -12,6 +18,8 @@ from fastconv_b200 import parallel, synth
 
 pytestmark = pytest.mark.gpu
 
+IC, OC, HW = 96, 256, 14
+
 
 def _gpus():
     n = ctypes.c_int(0)
@@ -19,72 +27,119 @@ def _gpus():
     return n.value
 
 
-def _worker(rank, world, port, ret):
-    import torch
-    import torch.distributed as dist
+def _reference_outputs(ctx, x, w, xb, modes):
+    """The unsharded layer on one GPU: per mode the single-image output, and the fp32 output of the batch."""
+    one = {}
+    for mode in modes:
+        layer = fc.ConvWinoF63ZCLayer(x, w, None, None, IC, HW, HW, OC, iter=1, mode=mode, ctx=ctx)
+        layer.Init(); layer.Forward()
+        one[mode] = layer.output_data.copy()
+        layer.release()
+    full = fc.ConvWinoF63ZCLayer(xb, w, None, None, IC, HW, HW, OC, batch=xb.shape[0], iter=1, ctx=ctx)
+    full.Init(); full.Forward()
+    batch = full.output_data.copy()
+    full.release()
+    return one, batch
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+
+def _check_sharded(comm, forwards=12):
+    """Runs on every process of the job; returns True when every sharded result equals the unsharded one."""
+    x = synth.conv_input(1, IC, HW, HW, 700)
+    w = synth.conv_weights(OC, IC, 3, 3, 701)
+    xb = synth.conv_input(5, IC, HW, HW, 702)  # 5 images: an uneven split over two ranks
+    one, batch = _reference_outputs(comm.contexts[0], x, w, xb, ("fp32", "3xtf32"))
     ok = True
-    try:
-        with fc.Context(rank, arena_bytes=2 << 30) as ctx:
-            ic, oc, hw = 96, 256, 14
-            x = synth.conv_input(1, ic, hw, hw, 700)
-            w = synth.conv_weights(oc, ic, 3, 3, 701)
-            whole = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, hw, hw, oc, iter=1, ctx=ctx)
-            whole.Init(); whole.Forward()
-            sharded = parallel.KShardedConv.gpu(ctx, w, hw, hw, 1, "fp32")
-            got = sharded.forward(x)
-            torch.cuda.synchronize()
-            ok = ok and np.array_equal(got.cpu().numpy(), whole.output_data)  # bit for bit, on every rank
-            got2 = sharded.forward(None)  # second call: same device input, same answer
-            torch.cuda.synchronize()
-            ok = ok and np.array_equal(got2.cpu().numpy(), whole.output_data)
-            # batch sharding: this rank's images only, no collective
-            xb = synth.conv_input(4, ic, hw, hw, 702)
-            b0, b1 = parallel.shard_batch(4, world, rank)
-            mine = fc.ConvWinoF63ZCLayer(xb[b0:b1], w, None, None, ic, hw, hw, oc, batch=b1 - b0, iter=1, ctx=ctx)
-            mine.Init(); mine.Forward()
-            full = fc.ConvWinoF63ZCLayer(xb, w, None, None, ic, hw, hw, oc, batch=4, iter=1, ctx=ctx)
-            full.Init(); full.Forward()
-            ok = ok and np.array_equal(mine.output_data, full.output_data[b0:b1])
-            # K sharding with the all-gather fused into the output transform (peer stores over NVLink, flags,
-            # bounded wait): every rank ends with the whole output, bit-equal to the one-GPU layer, on both of
-            # the alternating output buffers and in both operand layouts
-            for mode, ref in (("fp32", whole.output_data), ("3xtf32", None)):
-                peer = parallel.PeerKShardedConv(ctx, w, hw, hw, 1, mode)
-                peer.upload(x)
-                if ref is None:
-                    one = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, hw, hw, oc, iter=1, mode=mode, ctx=ctx)
-                    one.Init(); one.Forward()
-                    ref = one.output_data
-                for _ in range(3):
-                    ok = ok and np.array_equal(peer.result(peer.forward()), ref)
-                dist.barrier()
-            ctx.close_peer_mappings()
-            dist.barrier()
-        flag = torch.tensor([1 if ok else 0], device=f"cuda:{rank}")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if rank == 0:
-            ret.put(int(flag.item()))
-    finally:
-        dist.destroy_process_group()
+    # output channels split, gathered by the output transform's own stores: many forwards in a row, so that both of
+    # the alternating buffers and the device-side step counter are exercised and a missing fence would show
+    for mode in ("fp32", "3xtf32"):
+        for gather in ("peer", "nccl"):
+            sc = parallel.ShardedConv(comm, w, 1, HW, HW, shard="k", gather=gather, algorithm="winograd", mode=mode)
+            sc.upload(x)
+            for _ in range(forwards):
+                sc.forward()
+                sc.wait()
+                ok = ok and np.array_equal(sc.download(), one[mode])
+            ok = ok and np.array_equal(sc.forward_host(x), one[mode])
+            ok = ok and sc.time_device(2, 5) > 0.0
+            sc.release()
+    # images split: no collective; this process's ranks return their images back to back
+    sb = parallel.ShardedConv(comm, w, xb.shape[0], HW, HW, shard="batch", algorithm="winograd")
+    b0, b1 = sb.local_images()
+    ok = ok and np.array_equal(sb.forward_host(xb[b0:b1]), batch[b0:b1])
+    # an uneven channel split (255 channels) goes through the broadcast form of the NCCL gather
+    w_odd = np.ascontiguousarray(w[:255])
+    so = parallel.ShardedConv(comm, w_odd, 1, HW, HW, shard="k", gather="nccl", algorithm="winograd")
+    ok = ok and np.array_equal(so.forward_host(x), one["fp32"][:, :255])
+    so.release()
+    sb.release()
+    return bool(ok)
 
 
-def test_two_gpu_sharding_is_bit_equal_to_one_gpu():
+def test_one_rank_communicator_runs_the_sharded_entry_points():
+    with parallel.Comm.all(1, arena_bytes=1 << 30) as comm:
+        assert (comm.world, comm.local_count, comm.first_rank) == (1, 1, 0)
+        assert comm.max(3.5) == 3.5
+        comm.barrier()
+        x = synth.conv_input(1, IC, HW, HW, 700)
+        w = synth.conv_weights(OC, IC, 3, 3, 701)
+        xb = synth.conv_input(3, IC, HW, HW, 702)
+        one, batch = _reference_outputs(comm.contexts[0], x, w, xb, ("fp32",))
+        sc = parallel.ShardedConv(comm, w, 1, HW, HW, shard="k", gather="peer", algorithm="winograd")
+        sc.upload(x)
+        for _ in range(5):
+            sc.forward()
+            sc.wait()
+            assert np.array_equal(sc.download(), one["fp32"])
+        sb = parallel.ShardedConv(comm, w, 3, HW, HW, shard="batch")
+        assert sb.local_images() == (0, 3)
+        assert np.array_equal(sb.forward_host(xb), batch)
+        with pytest.raises(fc.FastConvError):  # the channel split takes one image
+            parallel.ShardedConv(comm, w, 2, HW, HW, shard="k")
+    lib = fc.load()
+    h = ctypes.c_void_p()
+    assert lib.fc_comm_init_all(99, None, 1 << 20, ctypes.byref(h)) == fc._lib.FC_ERR_INVALID_ARG
+
+
+def test_two_gpus_one_process_sharding_is_bit_equal_to_one_gpu():
     if _gpus() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
+    with parallel.Comm.all(2, arena_bytes=2 << 30) as comm:
+        assert (comm.world, comm.local_count) == (2, 2)
+        assert _check_sharded(comm)
+
+
+def _worker(rank, world, id_file, ret):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), FASTCONV_COMM_ID_FILE=id_file,
+                      NCCL_NVLS_ENABLE="0")
+    ok, err = False, ""
+    comm = None
+    try:
+        comm = parallel.Comm.from_env(arena_bytes=2 << 30)
+        ok = (comm.world, comm.local_count, comm.first_rank) == (world, 1, rank) and _check_sharded(comm)
+    except Exception as exc:  # reported through the queue; the peer is not left waiting for ever (bounded waits)
+        err = repr(exc)
+    finally:
+        try:
+            if comm is not None:
+                comm.close()
+        except Exception as exc:
+            err = err or repr(exc)
+    ret.put((rank, bool(ok), err))
+
+
+def test_two_gpus_two_processes_sharding_is_bit_equal_to_one_gpu():
+    if _gpus() < 2:
+        pytest.skip("needs two GPUs")
+    import multiprocessing as mp
     mpc = mp.get_context("spawn")
     ret = mpc.Queue()
-    procs = [mpc.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
-    assert ret.get(timeout=10) == 1
+    with tempfile.TemporaryDirectory() as tmp:
+        id_file = os.path.join(tmp, "nccl.id")
+        procs = [mpc.Process(target=_worker, args=(r, 2, id_file, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        results = [ret.get(timeout=600) for _ in procs]
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results), results
