@@ -820,12 +820,20 @@ int fc_conv_algorithm(const fc_conv *c, int *algo) {
 // barriers, the gather's look-ahead) exceeds the whole FFMA kernel, whose exact fp32 result is inside any tensor-core
 // tolerance.  Measured at batch 1 (ResNet-50 1x1 layers): K = 64..256 -> FFMA 6-18 us against 10-25 us; from K = 512 on
 // the tensor cores win in TF32, from K = 1024 on in 3xTF32 (three MMAs and a split pass per k-step).  Tuning() decides by measurement (cfg.skinny 1 = FFMA, 2 = tcgen05).
+//
+// 3xTF32 stands for rel-L2 <= 1e-5.  The tensor core's fp32 accumulate rounds toward zero, which adds a bias of about
+// 7e-9 per reduction step to a sum kept in TMEM (measured 1.4e-5 at K = 2048, 3.2e-5 at K = 4608); the implicit GEMM
+// keeps its whole reduction there, so from K = 1024 on the mode runs the FFMA kernel, whose result is the reference's
+// bit for bit.  (The Winograd GEMM takes its sum over into registers every 128 channels instead: fc_gemm_tc.cu.)
+constexpr long long IGEMM_3XTF32_MAX_K = 1024;
+
 static bool igemm_on_fp32_pipe(const fc_conv *c) {
     if (c->mode == FC_MATH_FP32_MIRRORED) return true;
-    if (c->cfg.skinny == 1) return true;
-    if (c->cfg.skinny == 2 || c->cfg.bn || c->cfg.smem_kb) return false;
     const fc_conv_desc gd = group_desc(c);
     const long long K = (long long)gd.ic * gd.kh * gd.kw;
+    if (c->mode == FC_MATH_3XTF32 && K > IGEMM_3XTF32_MAX_K) return true;
+    if (c->cfg.skinny == 1) return true;
+    if (c->cfg.skinny == 2 || c->cfg.bn || c->cfg.smem_kb) return false;
     const long long flops = 2ll * gd.batch * gd.oc * K * c->oh * c->ow;
     return K <= (c->mode == FC_MATH_3XTF32 ? 512 : 256) && flops <= 500000000ll;  // short reduction AND a small problem
 }
@@ -1114,7 +1122,11 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
         push(0, 256, 0, 0);
         return;
     }
-    if (c->mode == FC_MATH_FP32_MIRRORED) {
+    const fc_conv_desc gd = group_desc(c);
+    const bool ffma_only = c->mode == FC_MATH_FP32_MIRRORED ||  // ... or a 3xTF32 implicit GEMM too long for TMEM accumulation
+                           (algo == FC_ALGO_IM2COL && c->mode == FC_MATH_3XTF32 &&
+                            (long long)gd.ic * gd.kh * gd.kw > IGEMM_3XTF32_MAX_K);
+    if (ffma_only) {
         if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
         if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its eight block shapes
             const int small_tiles[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};

@@ -23,6 +23,11 @@
 //
 // U is constant, so the producer fills the ring's U halves before griddepcontrol.wait (the kernel may
 // have been launched while the input transform is still running) and adds V afterwards.
+// The tensor core's fp32 accumulate rounds toward zero, so a sum kept in TMEM drifts by a bias that grows with the
+// number of accumulation steps.  In the 3xTF32 mode (the accuracy mode) a long reduction is therefore cut into chunks
+// of kb_chunk k-blocks: each chunk accumulates in one of the two TMEM buffers from zero, and the epilogue warps add the
+// finished chunk to a running sum in registers with ordinary round-to-nearest additions while the MMA warp already
+// fills the other buffer.  The bias then stops growing with the reduction length.
 // Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
 // context's status word, all roles drain, TMEM is released and the kernel returns.
 #include "fc_tc_common.cuh"
@@ -42,6 +47,7 @@ struct TcParams {
     int n_oc_items;  // work items along the output channels: n_oc_blk blocks of 128, or blocks of `bn` with exchanged roles
     int b_bytes;     // bytes of the second operand slot of a stage
     int u_loads;     // exchanged roles: 128-row boxes of U per stage (1 or 2)
+    int kb_chunk;    // k-blocks accumulated in TMEM before the sum is taken over into registers (>= num_kb: never)
 };
 
 // row coordinate of U box (p, ocb, kb) in the packed filter viewed as a [boxes*128][32] matrix
@@ -156,16 +162,21 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_tf32(BM, P.bn);
-            int g = 0, it = 0;
+            int g = 0, it = 0;  // it counts accumulator hand-overs: one per chunk of a work item
             bool ok = true;
-            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
-                const int acc = it & 1;
-                const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
-                ok = mbar_wait(bar_acc_empty(acc), acc_ph ^ 1u, abort_flag, P.status);  // epilogue drained it
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.acc_cols);
+            for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+                uint32_t d_tmem = 0;
+                int acc = 0;
                 for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
+                    const bool chunk_start = kb % P.kb_chunk == 0;
+                    if (chunk_start) {
+                        acc = it & 1;
+                        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                        ok = mbar_wait(bar_acc_empty(acc), acc_ph ^ 1u, abort_flag, P.status);  // epilogue drained it
+                        if (!ok) break;
+                        tc_fence_after();
+                        d_tmem = tmem_base + (uint32_t)(acc * P.acc_cols);
+                    }
                     const int s = g % S;
                     const uint32_t ph = (uint32_t)(g / S) & 1u;
                     ok = mbar_wait(kSplit ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
@@ -176,7 +187,7 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ++ks) {
                         const uint32_t koff = ks * 32;  // 8 tf32 = 32 bytes further along K inside the swizzle span
-                        const uint32_t accum = (kb == 0 && ks == 0) ? 0u : 1u;
+                        const uint32_t accum = (chunk_start && ks == 0) ? 0u : 1u;
                         if (kSplit) {
                             tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_lo + koff), umma_desc_k_sw128(b_hi + koff), idesc, accum);
                             tc_mma_tf32(d_tmem, umma_desc_k_sw128(a_hi + koff), umma_desc_k_sw128(b_lo + koff), idesc, 1u);
@@ -186,8 +197,11 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
                         }
                     }
                     tc_commit(bar_empty(s));  // arrives once the MMAs above have finished reading the stage
+                    if ((kb + 1) % P.kb_chunk == 0 || kb + 1 == P.num_kb) {  // the chunk is complete: hand it over
+                        tc_commit(bar_acc_full(acc));
+                        ++it;
+                    }
                 }
-                if (ok) tc_commit(bar_acc_full(acc));
             }
         }
     } else if (warp >= 6) {
@@ -226,12 +240,61 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int it = 0;
         bool ok = true, waited = false;
-        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x, ++it) {
+        const int n_chunks = (P.num_kb + P.kb_chunk - 1) / P.kb_chunk;
+        for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
             int p, oc0, t0;
             item_coords<kSwap>(P, item, p, oc0, t0);
             if (!waited) {  // M may still be read by the output transform of the forward before this one
                 pdl_wait();
                 waited = true;
+            }
+            if constexpr (kSplit) {
+                if (n_chunks > 1) {
+                    // running sum of the chunks in registers: accumulator row of this lane, up to 128 columns
+                    float sum[128];
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) sum[j] = 0.0f;
+                    for (int c = 0; c < n_chunks; ++c, ++it) {
+                        const int acc = it & 1;
+                        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+                        ok = mbar_wait(bar_acc_full(acc), acc_ph, abort_flag, P.status);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * P.acc_cols);
+#pragma unroll
+                        for (int c0 = 0; c0 < 128; c0 += 16) {
+                            if (c0 < P.bn) {
+                                float va[16];
+                                tc_ld16(t_addr + (uint32_t)c0, va);
+                                // (the first chunk is added to +0, which leaves its bits alone)
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) sum[c0 + j] = __fadd_rn(sum[c0 + j], va[j]);
+                            }
+                        }
+                        tc_fence_before();
+                        mbar_arrive(bar_acc_empty(acc));  // the MMA warp may start the chunk after next in this buffer
+                    }
+                    if (!ok) break;
+                    if constexpr (kSwap) {
+                        const int tile = t0 + q * 32 + lane;
+                        float *dst = P.M + ((size_t)p * P.oc + oc0) * P.tp + tile;
+                        if (tile < P.tp) {
+#pragma unroll
+                            for (int j = 0; j < 128; ++j)
+                                if (j < P.bn && oc0 + j < P.oc) dst[(size_t)j * P.tp] = sum[j];
+                        }
+                    } else {
+                        const int row = oc0 + q * 32 + lane;
+                        float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
+                        if (row < P.oc) {
+#pragma unroll
+                            for (int j = 0; j < 128; j += 4)
+                                if (j < P.bn && t0 + j < P.tp)  // tp is a multiple of 8: a float4 never straddles the end
+                                    *reinterpret_cast<float4 *>(dst + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+                        }
+                    }
+                    continue;
+                }
             }
             const int acc = it & 1;
             const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
@@ -283,6 +346,7 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
                     }
                 }
             }
+            ++it;
         }
     }
 
@@ -341,6 +405,10 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.n_oc_items = n_oc_items;
     P.b_bytes = b_bytes;
     P.u_loads = u_loads;
+    // 3xTF32: at most four k-blocks (128 input channels, 48 accumulation steps) per TMEM chunk; accumulator blocks wider
+    // than 128 columns (a tuned configuration) keep the whole reduction in TMEM, their sum would not fit the registers
+    P.kb_chunk = split && bn <= 128 ? 4 : P.num_kb;
+    if (P.kb_chunk < 1) P.kb_chunk = 1;
     P.n_items = P.n_tile_blk * P.n_oc_items * 64;
     const size_t stage_bytes = (size_t)(A_BYTES + b_bytes) * (split ? 2 : 1);
     // More work items than SMs: size the ring so that two CTAs share an SM (one CTA's loads then overlap the

@@ -155,6 +155,112 @@ __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tile counts between the block widths: 72 tiles (14x14 maps of 8 images) fill 56 % of two 64-wide blocks, 200 tiles
+// (28x28 of 8 images) 78 % of two 128-wide ones.  Here a thread owns 8 output channels x TN tiles with TN = 5, 6 or 7,
+// so a block is 128 x 80, 96 or 112 and the launcher picks the width that pads least.  The tiles of a thread are
+// 16 apart (tx, tx + 16, ...), read from shared memory one float at a time (a half-warp reads 16 consecutive floats,
+// the other half the same ones: one wavefront); everything else -- cp.async ring, one accumulator per output, one
+// fused multiply-add per input channel in ascending order, packed pairs -- is the kernel above.
+// ---------------------------------------------------------------------------------------------
+template <int TN>
+__global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_flex_kernel(const float *__restrict__ U,
+                                                                         const float *__restrict__ V, float *__restrict__ M,
+                                                                         int oc, int ocp, int tp, int icp) {
+    constexpr int BM = 128, BN = 16 * TN, TM = 8;
+    constexpr int A_CHUNKS = BK * BM / 4 / THREADS, B_TOTAL = BK * BN / 4, TP2 = TN / 2;
+    extern __shared__ __align__(16) float smem[];
+    float(*As)[BK][BM] = reinterpret_cast<float(*)[BK][BM]>(smem);
+    float(*Bs)[BK][BN] = reinterpret_cast<float(*)[BK][BN]>(smem + STAGES * BK * BM);
+
+    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * BN;
+    const float *Up = U + (size_t)p * icp * ocp;
+    const float *Vp = V + (size_t)p * icp * tp;
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+
+    auto load_stage = [&](int stage, int k0) {
+#pragma unroll
+        for (int i = 0; i < A_CHUNKS; ++i) {
+            const int idx = tid + i * THREADS;
+            const int kr = idx / (BM / 4), c4 = (idx % (BM / 4)) * 4;
+            const int k = k0 + kr, col = oc0 + c4;
+            const bool ok = k < icp && col < ocp;
+            cp_async_16(&As[stage][kr][c4], Up + (ok ? (size_t)k * ocp + col : 0), ok);
+        }
+        for (int idx = tid; idx < B_TOTAL; idx += THREADS) {
+            const int kr = idx / (BN / 4), c4 = (idx % (BN / 4)) * 4;
+            const int k = k0 + kr, col = t0 + c4;
+            const bool ok = k < icp && col < tp;  // tp is a multiple of 8 and so is t0: a 16-byte piece never straddles
+            cp_async_16(&Bs[stage][kr][c4], Vp + (ok ? (size_t)k * tp + col : 0), ok);
+        }
+    };
+
+    uint64_t acc2[TM][TP2 > 0 ? TP2 : 1];
+    float acc1[TM];  // the odd tile of a thread, when TN is odd
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        acc1[i] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < TP2; ++j) acc2[i][j] = 0ull;
+    }
+
+    pdl_trigger();
+    pdl_wait();  // V comes from the input transform launched just before
+
+    const int n_slabs = (icp + BK - 1) / BK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_slabs) load_stage(s, s * BK);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < n_slabs; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        const int next = kt + STAGES - 1;
+        if (next < n_slabs) load_stage(next % STAGES, next * BK);
+        cp_async_commit();
+        const int buf = kt % STAGES;
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int g = 0; g < TM / 4; ++g) {
+                const float4 v = *reinterpret_cast<const float4 *>(&As[buf][k][g * 64 + ty * 4]);
+                a[g * 4 + 0] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = Bs[buf][k][tx + 16 * j];
+            uint64_t bp[TP2 > 0 ? TP2 : 1];
+#pragma unroll
+            for (int j = 0; j < TP2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+                const uint64_t ap = pack2(a[i], a[i]);
+#pragma unroll
+                for (int j = 0; j < TP2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+                if constexpr (TN % 2 == 1) acc1[i] = __fmaf_rn(a[i], b[TN - 1], acc1[i]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    float *Mp = M + (size_t)p * oc * tp;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = oc0 + (i / 4) * 64 + ty * 4 + (i % 4);
+        if (r >= oc) continue;
+        float res[TN];
+#pragma unroll
+        for (int j = 0; j < TP2; ++j) unpack2(acc2[i][j], res[2 * j], res[2 * j + 1]);
+        if constexpr (TN % 2 == 1) res[TN - 1] = acc1[i];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int c = t0 + tx + 16 * j;
+            if (c < tp) Mp[(size_t)r * tp + c] = res[j];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Few tiles (small feature maps at batch 1: 28x28 -> 25 tiles, 14x14 -> 9, 7x7 -> 4).  The GEMM is a
 // stream over U with a short N, so the blocked kernel above would multiply mostly padding.  Here a CTA
 // owns 128 output channels and all tiles of one position.  A producer warp keeps a ring of stages in
@@ -438,6 +544,17 @@ int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_
     return FC_OK;
 }
 
+template <int TN>
+int launch_flex(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    constexpr int BN = 16 * TN;
+    const size_t smem = (size_t)STAGES * BK * (128 + BN) * sizeof(float);
+    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_flex_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)ceil_div(g.tp, BN), (unsigned)ceil_div(g.oc, 128), 64), block(THREADS);
+    FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_flex_kernel<TN>, grid, block, smem, ctx->stream, d_U, d_V, d_M, g.oc, g.ocp,
+                              g.tp, g.icp)));
+    return FC_OK;
+}
+
 template <int BM, int BN>
 int launch_blocked(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
     const size_t smem = (size_t)STAGES * BK * (BM + BN) * sizeof(float);
@@ -469,6 +586,21 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
     // configuration: the largest block that still gives every SM about one and a half CTAs (at batch 1 the
     // GEMMs are small and a 128x128 grid would leave the machine half empty), else the one with most CTAs.
     bool wide_m = g.oc > 64, wide_n = g.tp > 64;
+    // block widths of 80, 96 and 112 tiles: by name (bn), or where they pad at least a tenth less than 64 / 128 do
+    // (their inner loop is a little slower per multiplication: scalar operand reads)
+    int flex = 0;
+    if (cfg && (cfg->bn == 80 || cfg->bn == 96 || cfg->bn == 112)) {
+        flex = cfg->bn;
+    } else if (!(cfg && (cfg->bm || cfg->bn)) && g.oc > 64) {
+        auto padded = [&](int bn) { return (double)ceil_div(g.tp, bn) * bn; };
+        double best = padded(128) < padded(64) ? padded(128) : padded(64);
+        const int widths[3] = {112, 96, 80};
+        for (int bn : widths)
+            if (padded(bn) * 1.1 < best) { best = padded(bn) * 1.1; flex = bn; }
+    }
+    if (flex == 80) return launch_flex<5>(ctx, d_U, d_V, d_M, g);
+    if (flex == 96) return launch_flex<6>(ctx, d_U, d_V, d_M, g);
+    if (flex == 112) return launch_flex<7>(ctx, d_U, d_V, d_M, g);
     if (cfg && (cfg->bm || cfg->bn)) {
         if (cfg->bm) wide_m = cfg->bm == 128;
         if (cfg->bn) wide_n = cfg->bn == 128;

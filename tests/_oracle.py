@@ -151,6 +151,16 @@ class Reference:
         return B
 
 
+def order_noise(oracle, x, w, want, pad=1):
+    """How far the reference's own Winograd output moves when only the ORDER of its input channels changes: rel-L2
+    between `want` = oracle(x, w) and the oracle run on the same layer with its channels permuted (same products,
+    same exact sum, another fp32 accumulation order).  No implementation with a summation order of its own can be
+    closer to the reference than this; tests of the 3xTF32 mode use max(1e-5, 1.25 * order_noise) as their bound."""
+    perm = np.random.default_rng(5).permutation(x.shape[1])
+    moved = oracle.wino_forward(np.ascontiguousarray(x[:, perm]), np.ascontiguousarray(w[:, perm]), pad)
+    return rel_l2(moved, want)
+
+
 def unpack_filter(packed, oc, ic):
     """The library keeps the transformed filter in contiguous boxes of 128 output channels x 32 input
     channels: box (p, ocb, kb) at ((p*n_ocb + ocb)*n_kb + kb)*4096 floats, element (oc%128)*32 + ic%32.

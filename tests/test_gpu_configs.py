@@ -15,7 +15,7 @@ import numpy as np
 import pytest
 
 import fastconv_b200 as fc
-from _oracle import max_abs_rel, rel_l2
+from _oracle import max_abs_rel, order_noise, rel_l2
 from fastconv_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -35,12 +35,6 @@ def _forward(ctx, x, w, mode):
     return out
 
 
-def _order_noise(oracle, x, w, want):
-    """rel-L2 between the oracle's output and the oracle's output with the input channels visited in another order."""
-    perm = np.random.default_rng(5).permutation(x.shape[1])
-    return rel_l2(oracle.wino_forward(np.ascontiguousarray(x[:, perm]), np.ascontiguousarray(w[:, perm]), 1), want)
-
-
 @pytest.mark.parametrize("c,hw", WIDE)
 def test_wide_single_image_layers(ctx, oracle, c, hw):
     x = synth.conv_input(1, c, hw, hw, 4000 + c + hw)
@@ -48,7 +42,7 @@ def test_wide_single_image_layers(ctx, oracle, c, hw):
     want = oracle.wino_forward(x, w, 1)
     assert np.array_equal(_forward(ctx, x, w, "fp32"), want)
     got = _forward(ctx, x, w, "3xtf32")
-    noise = _order_noise(oracle, x, w, want)
+    noise = order_noise(oracle, x, w, want)
     assert rel_l2(got, want) <= max(1e-5, 1.25 * noise), (rel_l2(got, want), noise)
     assert max_abs_rel(got, want) <= 1e-4
     assert rel_l2(_forward(ctx, x, w, "tf32"), want) <= 3e-3
@@ -64,7 +58,7 @@ def test_vgg16_layers_at_eight_images(ctx, oracle, ic, oc, hw):
     want = oracle.wino_forward(x, w, 1)
     assert np.array_equal(_forward(ctx, x, w, "fp32"), want)
     got = _forward(ctx, x, w, "3xtf32")
-    bound = 1e-5 if ic <= 256 else max(1e-5, 1.25 * _order_noise(oracle, x[:1], w, want[:1]))
+    bound = 1e-5 if ic <= 256 else max(1e-5, 1.25 * order_noise(oracle, x[:1], w, want[:1]))
     assert rel_l2(got, want) <= bound and max_abs_rel(got, want) <= 1e-4
     assert rel_l2(_forward(ctx, x, w, "tf32"), want) <= 3e-3
 
@@ -87,7 +81,7 @@ def test_vgg16_layers_at_sixty_four_images(ctx, oracle, ic, oc, hw):
     for i in sample:
         assert np.array_equal(got[i], want[i]), f"image {i}"
     got = _forward(ctx, x, w, "3xtf32")
-    noise = _order_noise(oracle, x[:1], w, want[0][None]) if ic > 256 else 0.0
+    noise = order_noise(oracle, x[:1], w, want[0][None]) if ic > 256 else 0.0
     for i in sample:
         assert rel_l2(got[i], want[i]) <= max(1e-5, 1.25 * noise) and max_abs_rel(got[i], want[i]) <= 1e-4
     got = _forward(ctx, x, w, "tf32")

@@ -2,8 +2,8 @@
 
 fp32 "mirrored" mode is held to BIT equality with the oracle (which is itself bit-equal to the
 reference build).  3xTF32 is held to rel-L2 <= 1e-5 and max-abs <= 1e-4*||out||inf up to 256 input
-channels; at 512 channels it measures 1.3e-5, which is the size of the reference's own
-accumulation-order noise (1.06e-5), so the bound there is 1.5e-5.  The mode "tf32" stands for
+channels; at 512 channels the reference's own output moves by 1.06e-5 when only the order of its
+accumulation changes, so the bound there is that movement (measured in the test) times 1.25.  The mode "tf32" stands for
 rel-L2 <= 3e-3 and is held to it: a Winograd layer asked for by name then runs the split
 arithmetic, because one TF32 pass through F(6x6,3x3) measures 6.4e-3 (the transform amplifies the
 2^-11 operand rounding about 16x).  That single pass is the mode "tf32-unbounded": the test pins
@@ -16,7 +16,7 @@ import numpy as np
 import pytest
 
 import fastconv_b200 as fc
-from _oracle import max_abs_rel, rel_l2
+from _oracle import max_abs_rel, order_noise, rel_l2
 from fastconv_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -215,7 +215,8 @@ def test_3xtf32_at_512_channels_is_at_the_reference_noise_floor(ctx, oracle):
     want = oracle.wino_forward(x, w, 1)
     got = run_layer(ctx, x, w, 1, mode="3xtf32")
     truth = oracle.direct_f64(x, w, 1, 1, 1, 1, 1, 1)
-    assert rel_l2(got, want) <= 1.5e-5 and max_abs_rel(got, want) <= 1e-4
+    # 1e-5, or what the reference's own output moves by when only its accumulation order changes (1.06e-5 here)
+    assert rel_l2(got, want) <= max(1e-5, 1.25 * order_noise(oracle, x, w, want)) and max_abs_rel(got, want) <= 1e-4
     # against the exact result it is as accurate as the reference's own fp32 arithmetic (within 30 %)
     assert rel_l2(got, truth) <= 1.3 * rel_l2(want, truth)
 
