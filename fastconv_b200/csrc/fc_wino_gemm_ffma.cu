@@ -12,6 +12,8 @@
 // ring, and the inner product reads 128-bit rows without bank conflicts.  No register staging, no
 // transposition, two CTAs per SM.  The FMAs of two neighbouring tiles are issued as one packed instruction
 // (fma.rn.f32x2): each half rounds like a scalar FMA, so the chains are unchanged.
+#include <cstdlib>
+
 #include "fc_tc_common.cuh"
 
 namespace fc {
@@ -544,6 +546,16 @@ int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_
     return FC_OK;
 }
 
+// FASTCONV_FFMA_FLEX=0 in the environment keeps the heuristic on the 64- and 128-wide blocks (for comparisons).
+bool flex_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_FFMA_FLEX");
+        state = (e && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
 template <int TN>
 int launch_flex(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
     constexpr int BN = 16 * TN;
@@ -586,17 +598,20 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
     // configuration: the largest block that still gives every SM about one and a half CTAs (at batch 1 the
     // GEMMs are small and a 128x128 grid would leave the machine half empty), else the one with most CTAs.
     bool wide_m = g.oc > 64, wide_n = g.tp > 64;
-    // block widths of 80, 96 and 112 tiles: by name (bn), or where they pad at least a tenth less than 64 / 128 do
-    // (their inner loop is a little slower per multiplication: scalar operand reads)
+    // block widths of 80, 96 and 112 tiles: by name (bn), or where they pad at least a fifth less than 64 / 128 do.
+    // Their inner loop is slower per multiplication (scalar operand reads): measured on 8 images, 72 tiles in one
+    // 80-wide block 0.074 ms against 0.096 ms in two 64-wide ones, but 200 tiles in two 112-wide blocks 0.188 ms
+    // against 0.184 ms in two 128-wide ones.  (Keeping 8 x 8 outputs per thread and dropping thread columns instead --
+    // blocks of 128 x 72 ... 120 with 144 ... 240 threads -- measured slower than both: too few warps per SM.)
     int flex = 0;
     if (cfg && (cfg->bn == 80 || cfg->bn == 96 || cfg->bn == 112)) {
         flex = cfg->bn;
-    } else if (!(cfg && (cfg->bm || cfg->bn)) && g.oc > 64) {
+    } else if (!(cfg && (cfg->bm || cfg->bn)) && g.oc > 64 && flex_enabled()) {
         auto padded = [&](int bn) { return (double)ceil_div(g.tp, bn) * bn; };
         double best = padded(128) < padded(64) ? padded(128) : padded(64);
         const int widths[3] = {112, 96, 80};
         for (int bn : widths)
-            if (padded(bn) * 1.1 < best) { best = padded(bn) * 1.1; flex = bn; }
+            if (padded(bn) * 1.25 < best) { best = padded(bn) * 1.25; flex = bn; }
     }
     if (flex == 80) return launch_flex<5>(ctx, d_U, d_V, d_M, g);
     if (flex == 96) return launch_flex<6>(ctx, d_U, d_V, d_M, g);

@@ -309,3 +309,20 @@ def test_random_shapes_3xtf32_within_tolerance(ctx, oracle, shape):
     got = run_layer(ctx, x, w, pad, "3xtf32")
     assert rel_l2(got, want) <= 1e-5
     assert max_abs_rel(got, want) <= 1e-4
+
+
+@pytest.mark.parametrize("bn", [80, 96, 112])
+@pytest.mark.parametrize("shape", [(8, 136, 200, 14, 14), (3, 64, 130, 30, 31), (1, 40, 129, 55, 50)])
+def test_ffma_block_widths_between_64_and_128_are_bit_exact(ctx, oracle, bn, shape):
+    """The FFMA TensorGEMM in blocks of 128 channels x 80 / 96 / 112 tiles (what 72 or 200 tiles take by default),
+    forced by hand on tile counts that leave ragged blocks in both directions."""
+    n, ic, oc, ih, iw = shape
+    x = synth.conv_input(n, ic, ih, iw, 141)
+    w = synth.conv_weights(oc, ic, 3, 3, 142)
+    layer = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, ih, iw, oc, 3, 3, 1, 1, 1, 1, 1, 1, 1, False, 1, 1,
+                                  batch=n, ctx=ctx)
+    layer.Init()
+    layer.set_kernel_config(0, bn, 2, 0)
+    layer.Forward()
+    assert np.array_equal(layer.output_data, oracle.wino_forward(x, w, 1))
+    layer.release()
