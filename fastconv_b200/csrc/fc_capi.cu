@@ -1135,6 +1135,8 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
             for (auto &t : small_tiles) push(t[0], t[1], 1, 0);
         }
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
+        if (algo == FC_ALGO_WINOGRAD && c->desc.oc > 64)  // block widths between 64 and 128 tiles
+            for (int bn : {80, 96, 112}) push(128, bn, 2, 0);
     } else {
         const int widths[5] = {32, 64, 96, 128, 256};
         const int budgets[3] = {72, 104, 200};

@@ -637,8 +637,10 @@ int fc_sharded_conv_forward(fc_sharded_conv *s) {
 int fc_sharded_conv_wait(fc_sharded_conv *s) {
     FC_REQUIRE(s != nullptr, FC_ERR_INVALID_ARG, "layer is NULL");
     if (s->shard != FC_SHARD_CHANNELS || s->gather != FC_GATHER_PEER) return FC_OK;  // stream order is enough
-    for (ShardPart &p : s->parts)
+    for (ShardPart &p : s->parts) {
+        FC_CHECK_CUDA(cudaSetDevice(s->comm->ctx[p.local]->device));  // one process may drive several GPUs
         FC_PROPAGATE(launch_peer_wait_published(s->comm->ctx[p.local], p.flags, s->comm->world, p.step));
+    }
     return FC_OK;
 }
 

@@ -30,6 +30,8 @@
 // fills the other buffer.  The bias then stops growing with the reduction length.
 // Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
 // context's status word, all roles drain, TMEM is released and the kernel returns.
+#include <cstdlib>
+
 #include "fc_tc_common.cuh"
 
 namespace fc {
@@ -427,6 +429,13 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     const int per_sm = (2 * P.acc_cols > 256 || smem > 113 * 1024) ? 1 : 2;
     int ctas = ctx->sm_count * per_sm;
     if (ctas > P.n_items) ctas = P.n_items;
+    // FASTCONV_TC_MAX_CTAS caps the persistent grid (experiments: how fast a given number of SMs can pull the filter
+    // stream -- the question a kernel that needs all 64 positions of a tile block in ONE CTA has to answer)
+    static const int cta_cap = [] {
+        const char *e = getenv("FASTCONV_TC_MAX_CTAS");
+        return e && atoi(e) > 0 ? atoi(e) : 0;
+    }();
+    if (cta_cap > 0 && ctas > cta_cap) ctas = cta_cap;
 
     CUtensorMap tmU, tmV;  // box rows: the 128-row operand and the bn-row operand
     FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap && bn < U_BOX_ROWS ? bn : U_BOX_ROWS));
