@@ -288,7 +288,7 @@ class Stack:
             algo, resolved = C.c_int(), C.c_int()
             self.lib.fc_conv_algorithm(hdl, C.byref(algo))
             self.lib.fc_conv_math_mode(hdl, C.byref(resolved))
-            layer_mode = {0: "fp32", 1: "3xtf32", 2: "tf32"}[resolved.value]  # "tf32" resolves per layer
+            layer_mode = {0: "fp32", 1: "3xtf32", 2: "tf32", 4: "tf32"}[resolved.value]  # "tf32" resolves per layer
             work = [C.c_double() for _ in range(4)]
             self._lib.check(self.lib.fc_conv_work(hdl, *[C.byref(v) for v in work]), "fc_conv_work")
             direct, algo_flops, algo_bytes, min_bytes = (v.value for v in work)
@@ -455,7 +455,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="fastconv", choices=["fastconv", "reference"])
-    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-unbounded"],
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-unbounded", "tf32-u16"],
                     help="arithmetic of `value`: fp32 = bit-identical to the reference (default); tf32 keeps rel-L2 <= 3e-3 "
                          "on every layer; tf32-unbounded also runs one TF32 pass through Winograd (6.4e-3)")
     ap.add_argument("--batch", type=int, default=64, help="images IN ALL, split by image over the GPUs")
@@ -566,7 +566,7 @@ def main():
         gemm_tflops = agg["gemm_flops"] / (agg["gemm_ms"] / 1e3) / 1e12
         gemm_gbs = agg["gemm_bytes"] / (agg["gemm_ms"] / 1e3) / 1e9
         # the arithmetic the Winograd layers of this run use ("tf32" runs them in the split arithmetic)
-        gemm_mode = {"fp32": "fp32", "3xtf32": "3xtf32", "tf32": "3xtf32", "tf32-unbounded": "tf32"}[args.mode]
+        gemm_mode = {"fp32": "fp32", "3xtf32": "3xtf32", "tf32": "3xtf32", "tf32-unbounded": "tf32", "tf32-u16": "tf32"}[args.mode]
         mode_peak = peak_tflops[gemm_mode]
         t_math = agg["gemm_flops"] / (mode_peak * 1e12)
         t_hbm = agg["gemm_bytes"] / (hbm_peak * 1e9)
@@ -600,7 +600,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"fp32": "f32", "3xtf32": "3xtf32", "tf32": "tf32 (3xtf32 where one pass misses 3e-3)",
-                      "tf32-unbounded": "tf32"}[args.mode],
+                      "tf32-unbounded": "tf32", "tf32-u16": "tf32 (fp16 filter)"}[args.mode],
             "data": "synthetic",
             "config": {"workload": workload,
                        "images_per_gpu": n,

@@ -14,9 +14,10 @@ FC_OK = 0
 (FC_ERR_INVALID_ARG, FC_ERR_UNSUPPORTED, FC_ERR_OUT_OF_MEMORY, FC_ERR_CUDA, FC_ERR_NO_DEVICE, FC_ERR_TIMEOUT,
  FC_ERR_COMM) = -1, -2, -3, -4, -5, -6, -7
 ALGO_AUTO, ALGO_DIRECT, ALGO_IM2COL, ALGO_WINOGRAD = 0, 1, 2, 3
-MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32, MATH_TF32_UNBOUNDED = 0, 1, 2, 3
+MATH_FP32_MIRRORED, MATH_3XTF32, MATH_TF32, MATH_TF32_UNBOUNDED, MATH_TF32_U16 = 0, 1, 2, 3, 4
+MODE_LABELS = {0: "fp32", 1: "3xtf32", 2: "tf32", 4: "tf32-u16"}  # what fc_conv_math_mode / fc_resolve_plan report
 MODE_NAMES = {"fp32": MATH_FP32_MIRRORED, "ffma": MATH_FP32_MIRRORED, "3xtf32": MATH_3XTF32, "tf32": MATH_TF32,
-              "tf32-unbounded": MATH_TF32_UNBOUNDED}
+              "tf32-unbounded": MATH_TF32_UNBOUNDED, "tf32-u16": MATH_TF32_U16}
 ALGO_NAMES = {"auto": ALGO_AUTO, "direct": ALGO_DIRECT, "im2col": ALGO_IM2COL, "winograd": ALGO_WINOGRAD}
 
 

@@ -421,6 +421,7 @@ int fc_select_algorithm(const fc_conv_desc *d, int *algo) {
 }
 
 static size_t u_elems_for(const WinoGeom &g, int mode) {
+    if (mode == FC_MATH_TF32_U16) return filter_u16_floats(g);
     return rowmajor_layout(mode) ? (size_t)64 * g.icp * g.ocp : (size_t)64 * g.n_ocb * g.n_kb * U_BOX_ELEMS;
 }
 
@@ -469,6 +470,7 @@ static int wino_gemm_dispatch(fc_context *ctx, const float *d_U, const float *d_
         case FC_MATH_FP32_MIRRORED: return launch_wino_gemm_ffma(ctx, d_U, d_V, d_M, g, cfg);
         case FC_MATH_3XTF32:
         case FC_MATH_TF32: return launch_wino_gemm_tc(ctx, d_U, d_V, d_M, g, mode, cfg);
+        case FC_MATH_TF32_U16: return launch_wino_gemm_tc(ctx, d_U, d_V, d_M, g, mode, cfg, filter_u16_scales(d_U, g));
         default: set_error("unknown math mode %d", mode); return FC_ERR_INVALID_ARG;
     }
 }
@@ -647,8 +649,17 @@ static int conv_prepare(fc_conv *c, int algo) {
         if (st == FC_OK) st = grab(ctx, &c->d_M, (size_t)64 * g.oc * g.tp);
         if (st == FC_OK && fresh) {
             cudaEventRecord(ctx->ev[0], ctx->stream);
-            st = rowmajor_layout(c->mode) ? launch_filter_transform_rowmajor(ctx, c->d_kernel, c->d_U, g.oc, g.ic)
-                                          : launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic);
+            if (c->mode == FC_MATH_TF32_U16) {  // the packed fp32 filter into a scratch allocation, then its fp16 copy
+                float *tmp = nullptr;
+                st = grab(ctx, &tmp, u_elems_for(g, FC_MATH_TF32));
+                if (st == FC_OK) st = launch_filter_transform(ctx, c->d_kernel, tmp, g.oc, g.ic);
+                if (st == FC_OK) st = launch_filter_to_u16(ctx, tmp, c->d_U, g);
+                cudaStreamSynchronize(ctx->stream);
+                drop(ctx, &tmp);
+            } else {
+                st = rowmajor_layout(c->mode) ? launch_filter_transform_rowmajor(ctx, c->d_kernel, c->d_U, g.oc, g.ic)
+                                              : launch_filter_transform(ctx, c->d_kernel, c->d_U, g.oc, g.ic);
+            }
             cudaEventRecord(ctx->ev[1], ctx->stream);
             timed = true;
         }
@@ -711,7 +722,7 @@ static int conv_prepare(fc_conv *c, int algo) {
 
 int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, int *algo_out, int *mode_out) {
     FC_REQUIRE(desc && algo_out && mode_out, FC_ERR_INVALID_ARG, "NULL argument");
-    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32_UNBOUNDED, FC_ERR_INVALID_ARG, "unknown math mode %d",
+    FC_REQUIRE(mode >= FC_MATH_FP32_MIRRORED && mode <= FC_MATH_TF32_U16, FC_ERR_INVALID_ARG, "unknown math mode %d",
                mode);
     FC_REQUIRE(algo >= FC_ALGO_AUTO && algo <= FC_ALGO_WINOGRAD, FC_ERR_INVALID_ARG, "unknown algorithm %d", algo);
     int oh, ow;
@@ -733,12 +744,18 @@ int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, 
         } else if (auto_requested && direct_tc_preferred(*desc, oh, ow, sms, DIRECT_VS_GATHER)) {
             algo = FC_ALGO_DIRECT;
         }
-    } else if (mode == FC_MATH_TF32_UNBOUNDED) {
+    } else if (mode == FC_MATH_TF32_UNBOUNDED || mode == FC_MATH_TF32_U16) {
         // one TF32 pass everywhere; `auto` takes the direct kernel where the measured crossovers favour it
+        const bool u16 = mode == FC_MATH_TF32_U16;
         mode = FC_MATH_TF32;
         if (auto_requested &&
             direct_tc_preferred(*desc, oh, ow, sms, algo == FC_ALGO_WINOGRAD ? DIRECT_VS_WINOGRAD_TF32 : DIRECT_VS_GATHER))
             algo = FC_ALGO_DIRECT;
+        // the fp16 filter: Winograd layers whose accumulator rows are channels (more than 64 of them, under 128 tiles)
+        if (u16 && algo == FC_ALGO_WINOGRAD) {
+            WinoGeom g;
+            if (wino_geom(desc, &g) == FC_OK && wino_gemm_tc_rows_are_channels(g)) mode = FC_MATH_TF32_U16;
+        }
     }
     // the direct tensor-core kernel is a TF32 kernel for ungrouped layers of stride 1 or 2; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)

@@ -28,9 +28,16 @@
 // of kb_chunk k-blocks: each chunk accumulates in one of the two TMEM buffers from zero, and the epilogue warps add the
 // finished chunk to a running sum in registers with ordinary round-to-nearest additions while the MMA warp already
 // fills the other buffer.  The bias then stops growing with the reduction length.
+// Reduced-precision filter (kMode 2): the transformed filter is kept in HBM as fp16 -- the significand TF32 reads
+// anyway -- scaled per position by a power of two, so the dominant stream of a single-image layer is half as long.
+// The producer lands a box of 128 x 32 halves (8 KB) beside the stage, the four helper warps expand it into the
+// swizzled fp32 operand slot (exact), the MMAs are the single-pass TF32 ones, and the epilogue multiplies the
+// accumulator by the position's scale (exact).
 // Every wait on an mbarrier is bounded: after the limit the kernel records FC_ERR_TIMEOUT in the
 // context's status word, all roles drain, TMEM is released and the kernel returns.
 #include <cstdlib>
+
+#include <cuda_fp16.h>
 
 #include "fc_tc_common.cuh"
 
@@ -50,6 +57,7 @@ struct TcParams {
     int b_bytes;     // bytes of the second operand slot of a stage
     int u_loads;     // exchanged roles: 128-row boxes of U per stage (1 or 2)
     int kb_chunk;    // k-blocks accumulated in TMEM before the sum is taken over into registers (>= num_kb: never)
+    const float *scales;  // fp16 filter: the power of two every position's values were divided by, [64]
 };
 
 // row coordinate of U box (p, ocb, kb) in the packed filter viewed as a [boxes*128][32] matrix
@@ -67,12 +75,25 @@ __device__ __forceinline__ void item_coords(const TcParams &P, int item, int &p,
     p = rest / P.n_oc_items;
 }
 
-constexpr int TC_SPLIT_THREADS = TC_THREADS + 128;  // 3xTF32: four more warps that do nothing but split stages
+// two fp16 values in one 32-bit word -> two floats (exact)
+__device__ __forceinline__ float2 half2_bits_to_float2(uint32_t v) {
+    float2 f;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}"
+        : "=f"(f.x), "=f"(f.y)
+        : "r"(v));
+    return f;
+}
 
-template <bool kSplit, bool kSwap>
-__global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
+constexpr int TC_SPLIT_THREADS = TC_THREADS + 128;  // 3xTF32 / fp16 filter: four more warps that only prepare stages
+constexpr int A16_BYTES = BM * BK * 2;               // a filter box in fp16
+
+// kMode: 0 = one TF32 pass, 1 = 3xTF32 (hi/lo split of every landed stage), 2 = one TF32 pass over an fp16 filter
+template <int kMode, bool kSwap>
+__global__ void __launch_bounds__(kMode != 0 ? TC_SPLIT_THREADS : TC_THREADS) wino_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmU,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const TcParams P) {
+    constexpr bool kSplit = kMode == 1, kU16 = kMode == 2, kHelpers = kMode != 0;
+    static_assert(!(kU16 && kSwap), "the fp16 filter is built for rows = channels");
     extern __shared__ uint8_t smem_raw[];
     // carve: [barriers + flags | 1024-aligned stage ring]
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[8] empty[8] split[8] acc_full[2] acc_empty[2]
@@ -82,7 +103,8 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
     const uint32_t ring = (smem_u32(smem_raw) + 512 + 1023) & ~1023u;
     const uint32_t b_bytes = (uint32_t)P.b_bytes;
     const uint32_t part_bytes = A_BYTES + b_bytes;  // one (A,B) pair
-    const uint32_t stage_bytes = part_bytes * (kSplit ? 2 : 1);
+    const uint32_t stage_bytes = kSplit ? 2 * part_bytes : kU16 ? part_bytes + A16_BYTES : part_bytes;
+    const uint32_t tx_bytes = kU16 ? b_bytes + A16_BYTES : part_bytes;  // what the producer lands per stage
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -123,6 +145,10 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
         if (lane == 0) {
             // the first slot of a stage (A operand, 128 rows) and the second (B operand, bn rows): U, V or V, U
             auto load_u = [&](uint32_t stage, uint32_t bar, int p, int oc0, int kb) {
+                if (kU16) {  // the fp16 box lands behind the operand slots; the helper warps expand it into slot A
+                    tma_load_3d(stage + part_bytes, &tmU, bar, 0, u_box_row(P, p, oc0, kb), 0);
+                    return;
+                }
                 tma_load_3d(stage + (kSwap ? A_BYTES : 0), &tmU, bar, 0, u_box_row(P, p, oc0, kb), 0);
                 if (kSwap && P.u_loads == 2)  // channels oc0+128.. of a 256-wide block: the next packed box
                     tma_load_3d(stage + 2 * A_BYTES, &tmU, bar, 0, u_box_row(P, p, oc0 + BM, kb), 0);
@@ -140,7 +166,7 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
                     // the ring is empty: fill it with U boxes before waiting for the producer of V
                     const int pre = P.num_kb < S ? P.num_kb : S;
                     for (; kb < pre; ++kb) {
-                        mbar_expect_tx(bar_full(kb), part_bytes);
+                        mbar_expect_tx(bar_full(kb), tx_bytes);
                         load_u(ring + kb * stage_bytes, bar_full(kb), p, oc0, kb);
                     }
                     pdl_wait();
@@ -154,7 +180,7 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
                     ok = mbar_wait(bar_empty(s), ph ^ 1u, abort_flag, P.status);
                     if (!ok) break;
                     const uint32_t a_dst = ring + s * stage_bytes;
-                    mbar_expect_tx(bar_full(s), part_bytes);
+                    mbar_expect_tx(bar_full(s), tx_bytes);
                     load_u(a_dst, bar_full(s), p, oc0, kb);
                     load_v(a_dst, bar_full(s), p, t0, kb);
                 }
@@ -181,7 +207,7 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
                     }
                     const int s = g % S;
                     const uint32_t ph = (uint32_t)(g / S) & 1u;
-                    ok = mbar_wait(kSplit ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
+                    ok = mbar_wait(kHelpers ? bar_split(s) : bar_full(s), ph, abort_flag, P.status);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_hi = ring + s * stage_bytes, b_hi = a_hi + A_BYTES;
@@ -214,7 +240,31 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
         int g = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
-            {
+            if constexpr (kU16) {
+                for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (uint32_t)(g / S) & 1u;
+                    ok = mbar_wait(bar_full(s), ph, abort_flag, P.status);
+                    if (!ok) break;
+                    uint8_t *a32 = smem_raw + (ring - smem_u32(smem_raw)) + s * stage_bytes;
+                    const uint8_t *a16 = a32 + part_bytes;  // 128 rows x 32 halves, rows of 64 bytes
+                    for (int c = et; c < BM * 4; c += 128) {  // 16 bytes = 8 halves = two 16-byte pieces of floats
+                        const int r = c >> 2, q = c & 3;
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(a16 + (size_t)c * 16);
+                        const float2 f0 = half2_bits_to_float2(raw.x), f1 = half2_bits_to_float2(raw.y);
+                        const float2 f2 = half2_bits_to_float2(raw.z), f3 = half2_bits_to_float2(raw.w);
+                        // K-major, 128-byte swizzle: 16-byte piece index XOR row-in-group
+                        const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+                        const uint32_t sw = (uint32_t)(r & 7);
+                        *reinterpret_cast<float4 *>(a32 + row_off + ((((uint32_t)(2 * q)) ^ sw) << 4)) =
+                            make_float4(f0.x, f0.y, f1.x, f1.y);
+                        *reinterpret_cast<float4 *>(a32 + row_off + ((((uint32_t)(2 * q + 1)) ^ sw) << 4)) =
+                            make_float4(f2.x, f2.y, f3.x, f3.y);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
+                    mbar_arrive(bar_split(s));
+                }
+            } else {
                 const int all_chunks = (int)(part_bytes / 16);
                 for (int kb = 0; kb < P.num_kb; ++kb, ++g) {
                     const int s = g % S;
@@ -324,11 +374,19 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
             } else {
                 const int row = oc0 + q * 32 + lane;
                 float *dst = P.M + ((size_t)p * P.oc + row) * P.tp + t0;
+                const float scale = kU16 ? __ldg(P.scales + p) : 1.0f;  // a power of two: the product is exact
                 for (int c0 = 0; c0 < P.bn; c0 += 32) {
                     float va[16], vb[16];
                     tc_ld16(t_addr + (uint32_t)c0, va);
                     const bool second = c0 + 16 < P.bn;
                     if (second) tc_ld16(t_addr + (uint32_t)(c0 + 16), vb);
+                    if (kU16) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            va[j] *= scale;
+                            if (second) vb[j] *= scale;
+                        }
+                    }
                     if (c0 + 32 >= P.bn) {  // last columns read: the MMA warp may overwrite this accumulator
                         tc_fence_before();
                         mbar_arrive(bar_acc_empty(acc));
@@ -367,9 +425,30 @@ __global__ void __launch_bounds__(kSplit ? TC_SPLIT_THREADS : TC_THREADS) wino_g
 
 }  // namespace
 
+// The fp16 filter as a matrix [boxes*128][32 halves]; box = 128 rows x 32 halves, no swizzle (the helper warps place
+// the expanded floats themselves).
+static int make_map_u16(CUtensorMap *map, const void *base, size_t rows) {
+    EncodeTiledFn enc;
+    FC_PROPAGATE(get_encoder(&enc));
+    cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, 1};
+    cuuint64_t strides[2] = {(cuuint64_t)BK * 2, (cuuint64_t)BK * 2 * rows};
+    cuuint32_t box[3] = {BK, (cuuint32_t)BM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled (fp16 filter) failed with %d", (int)r);
+    return FC_OK;
+}
+
+// rows = channels, columns = tiles: the layout the fp16 filter is built for
+bool wino_gemm_tc_rows_are_channels(const WinoGeom &g) { return !(g.oc <= 64 || g.tp >= 128); }
+
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g, int mode,
-                        const KernelCfg *cfg) {
-    const bool split = mode == FC_MATH_3XTF32;
+                        const KernelCfg *cfg, const float *d_scales) {
+    const bool split = mode == FC_MATH_3XTF32, u16 = mode == FC_MATH_TF32_U16;
+    FC_REQUIRE(!u16 || (d_scales != nullptr && wino_gemm_tc_rows_are_channels(g)), FC_ERR_INVALID_ARG,
+               "the fp16 filter needs its scales and a layer whose accumulator rows are channels");
     // Exchanged roles (rows = 128 tiles, columns = a block of at most 128 output channels, a multiple of 16) when no
     // accumulator row is left empty by it: at most 64 channels, or at least 128 tiles.  Measured on the batch-8
     // VGG-16 stack: TF32 1.233 ms with rows = channels everywhere, 1.143 ms with this rule (3xTF32: 1.624 -> 1.577 ms);
@@ -407,12 +486,13 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     P.n_oc_items = n_oc_items;
     P.b_bytes = b_bytes;
     P.u_loads = u_loads;
+    P.scales = d_scales;
     // 3xTF32: at most four k-blocks (128 input channels, 48 accumulation steps) per TMEM chunk; accumulator blocks wider
     // than 128 columns (a tuned configuration) keep the whole reduction in TMEM, their sum would not fit the registers
     P.kb_chunk = split && bn <= 128 ? 4 : P.num_kb;
     if (P.kb_chunk < 1) P.kb_chunk = 1;
     P.n_items = P.n_tile_blk * P.n_oc_items * 64;
-    const size_t stage_bytes = (size_t)(A_BYTES + b_bytes) * (split ? 2 : 1);
+    const size_t stage_bytes = split ? (size_t)2 * (A_BYTES + b_bytes) : (size_t)(A_BYTES + b_bytes) + (u16 ? A16_BYTES : 0);
     // More work items than SMs: size the ring so that two CTAs share an SM (one CTA's loads then overlap the
     // other's epilogue); otherwise one CTA takes the whole SM.  512 TMEM columns cannot be shared.
     const bool two_per_sm = P.n_items > ctx->sm_count && 2 * P.acc_cols <= 256;
@@ -438,17 +518,21 @@ int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, flo
     if (cta_cap > 0 && ctas > cta_cap) ctas = cta_cap;
 
     CUtensorMap tmU, tmV;  // box rows: the 128-row operand and the bn-row operand
-    FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap && bn < U_BOX_ROWS ? bn : U_BOX_ROWS));
+    if (u16)
+        FC_PROPAGATE(make_map_u16(&tmU, d_U, (size_t)64 * g.n_ocb * g.n_kb * U_BOX_ROWS));
+    else
+        FC_PROPAGATE(make_map_3d(&tmU, d_U, U_BOX_COLS, 64 * g.n_ocb * g.n_kb * U_BOX_ROWS, 1, swap && bn < U_BOX_ROWS ? bn : U_BOX_ROWS));
     FC_PROPAGATE(make_map_3d(&tmV, d_V, g.icp, g.tp, 64, swap ? BM : bn));
 
-    dim3 grid((unsigned)ctas), block(split ? TC_SPLIT_THREADS : TC_THREADS);
+    dim3 grid((unsigned)ctas), block(split || u16 ? TC_SPLIT_THREADS : TC_THREADS);
     auto launch = [&](auto kernel) -> int {
         FC_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         FC_CHECK_CUDA(launch_pdl(kernel, grid, block, smem, ctx->stream, tmU, tmV, P));
         return FC_OK;
     };
-    if (split) FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<true, true>) : launch(wino_gemm_tc_kernel<true, false>));
-    else FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<false, true>) : launch(wino_gemm_tc_kernel<false, false>));
+    if (u16) FC_PROPAGATE(launch(wino_gemm_tc_kernel<2, false>));
+    else if (split) FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<1, true>) : launch(wino_gemm_tc_kernel<1, false>));
+    else FC_PROPAGATE(swap ? launch(wino_gemm_tc_kernel<0, true>) : launch(wino_gemm_tc_kernel<0, false>));
     FC_CHECK_CUDA(cudaGetLastError());
     return FC_OK;
 }

@@ -186,7 +186,15 @@ int launch_peer_wait_published(fc_context *ctx, const int *flags, int world, con
 int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
                           const KernelCfg *cfg = nullptr);
 int launch_wino_gemm_tc(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g,
-                        int mode, const KernelCfg *cfg = nullptr);
+                        int mode, const KernelCfg *cfg = nullptr, const float *d_scales = nullptr);
+// FC_MATH_TF32_U16: whether the layer runs with accumulator rows = channels (the layout the fp16 filter is built for),
+// and the one-time conversion of the packed fp32 filter to fp16 boxes + 64 per-position scales (behind the boxes)
+bool wino_gemm_tc_rows_are_channels(const WinoGeom &g);
+size_t filter_u16_floats(const WinoGeom &g);  // floats the fp16 boxes and the scales occupy together
+int launch_filter_to_u16(fc_context *ctx, const float *d_U32, float *d_U16, const WinoGeom &g);
+inline const float *filter_u16_scales(const float *d_U16, const WinoGeom &g) {
+    return d_U16 + (size_t)64 * g.n_ocb * g.n_kb * U_BOX_ELEMS / 2;
+}
 int launch_im2col_gather(fc_context *ctx, const float *d_in, float *d_B, const fc_conv_desc &d, int oh, int ow,
                          int image);
 // d_ktab: per-layer k -> (offset, u:v) table (igemm_fill_ktab), or NULL outside a planned layer

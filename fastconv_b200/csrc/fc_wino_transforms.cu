@@ -8,6 +8,10 @@
 //
 // Layouts (ic contiguous, padded with zeros to icp = roundup(ic, 8)):
 //   U: packed 128 x 32 boxes (upack_index)   V[p][tp][icp]   M[p][oc][tp]     p = col*8 + row
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "fc_internal.h"
 
 namespace fc {
@@ -519,9 +523,70 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// fp16 copy of the packed filter (FC_MATH_TF32_U16).  Per position p the largest magnitude picks a power of two 2^e
+// with max|U_p| / 2^e in [2^13, 2^14): every value is divided by it (exact) and rounded to fp16, which keeps TF32's 11
+// significant bits for everything within 2^-27 of the largest value; the scale goes into scales[p] and is multiplied
+// back onto the accumulator.  The boxes keep their order and shape (128 channels x 32 input channels, now 8 KB).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) filter_u16_max_kernel(const float *__restrict__ U, unsigned *__restrict__ maxbits,
+                                                             size_t per_pos) {
+    const int p = blockIdx.y;
+    const float *src = U + (size_t)p * per_pos;
+    float m = 0.0f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < per_pos; i += (size_t)gridDim.x * blockDim.x)
+        m = fmaxf(m, fabsf(src[i]));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(maxbits + p, __float_as_uint(m));  // non-negative floats order like their bits
+}
+
+__global__ void __launch_bounds__(256) filter_u16_convert_kernel(const float *__restrict__ U, __half *__restrict__ H,
+                                                                 float *__restrict__ scales,
+                                                                 const unsigned *__restrict__ maxbits, size_t per_pos) {
+    const int p = blockIdx.y;
+    const float mx = __uint_as_float(maxbits[p]);
+    int e = 0;
+    if (mx > 0.0f) {
+        frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
+        e -= 14;         // mx / 2^e in [2^13, 2^14)
+    }
+    const float inv = ldexpf(1.0f, -e);
+    if (blockIdx.x == 0 && threadIdx.x == 0) scales[p] = ldexpf(1.0f, e);
+    const float *src = U + (size_t)p * per_pos;
+    __half *dst = H + (size_t)p * per_pos;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < per_pos; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __float2half_rn(src[i] * inv);
+}
+
+// the fp16 boxes, then 64 scales, then 64 words the maxima are gathered in
+size_t filter_u16_floats(const WinoGeom &g) { return (size_t)64 * g.n_ocb * g.n_kb * U_BOX_ELEMS / 2 + 128; }
+
+int launch_filter_to_u16(fc_context *ctx, const float *d_U32, float *d_U16, const WinoGeom &g) {
+    const size_t per_pos = (size_t)g.n_ocb * g.n_kb * U_BOX_ELEMS;
+    float *scales = const_cast<float *>(filter_u16_scales(d_U16, g));
+    unsigned *maxbits = reinterpret_cast<unsigned *>(scales + 64);
+    FC_CHECK_CUDA(cudaMemsetAsync(maxbits, 0, 64 * sizeof(unsigned), ctx->stream));
+    const unsigned blocks = (unsigned)(ceil_div(per_pos, 256) > 64 ? 64 : ceil_div(per_pos, 256));
+    filter_u16_max_kernel<<<dim3(blocks, 64), 256, 0, ctx->stream>>>(d_U32, maxbits, per_pos);
+    filter_u16_convert_kernel<<<dim3(blocks, 64), 256, 0, ctx->stream>>>(d_U32, reinterpret_cast<__half *>(d_U16), scales,
+                                                                        maxbits, per_pos);
+    FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+// tile count from which the throughput-oriented output transform is taken ($FASTCONV_OT_WIDE_MIN overrides it)
+static int wide_min_tiles() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("FASTCONV_OT_WIDE_MIN");
+        v = e && atoi(e) > 0 ? atoi(e) : 64;  // measured on 8 images: 200 tiles 25 -> 16 us, 72 tiles 14 -> 12 us
+    }
+    return v;
+}
+
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g, const Epilogue &ep) {
     dim3 block(256);
-    if (g.tiles >= 256) {
+    if (g.tiles >= wide_min_tiles()) {
         dim3 wblock(32 * OTW_WARPS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
         FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
                                  g.oh, g.ow, g.th, g.tw, ep));

@@ -13,7 +13,7 @@
 //     implicit GEMM otherwise;
 //   * the self-check honours kernel size, stride and padding (the reference always checks against a
 //     3x3 / pad 1 naive layer, ConvTest.cpp:360) and also covers the im2col path;
-//   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32|tf32-unbounded, -seed N (the reference seeds from
+//   * optional additions: -n/--batch, -m/--math fp32|3xtf32|tf32|tf32-unbounded|tf32-u16, -seed N (the reference seeds from
 //     the clock), -nc/--no-check, -dev INDEX, and for several GPUs of one machine driven by this one process
 //     -g/--gpus N with -shard batch|k (images or output channels split over the GPUs) and -gather peer|nccl.
 //     -t is accepted and only sizes the host self-check;
@@ -72,7 +72,7 @@ static void print_options_help(const char *program_name) {
            "  -i   --iterations         # iterations (default: 10)\n"
            "GPU additions:\n"
            "  -n   --batch              Images per forward (default: 1)\n"
-           "  -m   --math               fp32 (bit-identical accumulation), 3xtf32, tf32 (within 3e-3) or tf32-unbounded (default: fp32)\n"
+           "  -m   --math               fp32 (bit-identical accumulation), 3xtf32, tf32 (within 3e-3), tf32-unbounded or tf32-u16 (default: fp32)\n"
            "  -seed                     Seed of the input/kernel generator (default: from the clock)\n"
            "  -nc  --no-check           Skip the naive host convolution and the difference line\n"
            "  -dev --device             CUDA device index of a one-GPU run (default: 0)\n"
@@ -180,6 +180,7 @@ static struct options parse_options(int argc, char **argv) {
                 else if (strcmp(v, "3xtf32") == 0) o.math_mode = FC_MATH_3XTF32;
                 else if (strcmp(v, "tf32") == 0) o.math_mode = FC_MATH_TF32;
                 else if (strcmp(v, "tf32-unbounded") == 0) o.math_mode = FC_MATH_TF32_UNBOUNDED;
+                else if (strcmp(v, "tf32-u16") == 0) o.math_mode = FC_MATH_TF32_U16;
                 else fail("invalid math mode %s", v);
             } else {
                 fprintf(stderr, "Error: unknown argument '%s'\n", a);
@@ -221,7 +222,9 @@ static enum nnp_convolution_algorithm select_algorithm(const fc_conv_desc &d, in
 static const char *algorithm_name(int a) {
     return a == FC_ALGO_WINOGRAD ? "winograd" : a == FC_ALGO_DIRECT ? "direct" : "im2col";
 }
-static const char *math_name(int m) { return m == FC_MATH_3XTF32 ? "3xtf32" : m == FC_MATH_TF32 ? "tf32" : "fp32"; }
+static const char *math_name(int m) {
+    return m == FC_MATH_3XTF32 ? "3xtf32" : m == FC_MATH_TF32 ? "tf32" : m == FC_MATH_TF32_U16 ? "tf32-u16" : "fp32";
+}
 
 // One JSON line per layer: what ran, how long it took, and how far that is from the layer's roofline -- the slower of
 // its algorithmic flops at the arithmetic peak of the mode and its algorithmic bytes at the HBM bandwidth.  Peaks: FP32
@@ -237,7 +240,7 @@ static void print_json_line(fc_context *ctx, fc_conv *conv, const fc_conv_desc &
     const char *e_tf32 = getenv("FASTCONV_TF32_TFLOPS"), *e_hbm = getenv("FASTCONV_HBM_GBS");
     const double tf32 = e_tf32 ? atof(e_tf32) : 759.9, hbm = e_hbm ? atof(e_hbm) : 6538.3;
     const double fp32 = sms * 128.0 * 2.0 * mhz * 1e-6;
-    const double peak = mode == FC_MATH_FP32_MIRRORED ? fp32 : mode == FC_MATH_TF32 ? tf32 : tf32 / 3.0;
+    const double peak = mode == FC_MATH_FP32_MIRRORED ? fp32 : mode == FC_MATH_3XTF32 ? tf32 / 3.0 : tf32;
     // a sharded layer: `conv` is one rank's share, and every rank has its own peaks
     const double t_flop = flops / (peak * 1e12) * 1e3, t_hbm = bytes / (hbm * 1e9) * 1e3;
     const double roof = t_flop > t_hbm ? t_flop : t_hbm;

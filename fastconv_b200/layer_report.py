@@ -9,8 +9,9 @@ JSON line per layer carries the algorithm, milliseconds, direct-equivalent GFLOP
 the layer's roofline  max(flops / peak, bytes / HBM bandwidth)  with
     Winograd:  flops = 2*64*T*C*K,  bytes = 4*(N*C*H*W + 64*C*K + N*K*OH*OW)
     im2col:    flops = 2*N*K*C*R*S*OH*OW,  bytes = 4*(N*C*H*W + K*C*R*S + N*K*OH*OW)
-Peaks: HBM from MEASURED_PEAKS.json (copy bandwidth); FP32 63.7 and TF32 759.9 TFLOP/s measured with an
-8192^3 library GEMM on a B200, 3xTF32 a third of the TF32 figure.
+Peaks: HBM from MEASURED_PEAKS.json (copy bandwidth); FP32 = SMs x 128 lanes x 2 flop x the maximum SM clock
+(74.5 TFLOP/s on a B200; a library SGEMM of 8192^3 reaches 63.7); TF32 759.9 TFLOP/s measured with an 8192^3
+library GEMM on a B200, 3xTF32 a third of it.
 """
 from __future__ import annotations
 
@@ -43,22 +44,28 @@ WIDE = [(c, c, h, 3, 1, 1) for c in (512, 1024, 2048) for h in (14, 28, 56)]
 SETS = {"vgg16": VGG16, "resnet50": RESNET50, "wide": WIDE}
 
 
+FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1965e-6  # replaced by the context's own SM count and clock in main()
+
+
 def peaks(mode: str):
     """HBM GB/s (measured copy bandwidth when the file is there) and the arithmetic peak of the mode in TFLOP/s:
-    TF32 759.9 and FP32 63.7 measured with an 8192^3 library GEMM on a B200; 3xTF32 is a third of TF32."""
+    FP32 from the SM count and maximum clock, TF32 759.9 measured with an 8192^3 library GEMM on a B200, 3xTF32 a
+    third of TF32."""
     hbm = 6650.0
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         hbm = float(json.loads(p.read_text())["hbm_gbs"])
-    flops = {"fp32": 63.7, "tf32": 759.9, "3xtf32": 759.9 / 3, "tf32-strict": 759.9}[mode]
+    flops = {"fp32": FP32_PEAK_TFLOPS, "tf32": 759.9, "3xtf32": 759.9 / 3, "tf32-unbounded": 759.9, "tf32-u16": 759.9}[mode]
     return hbm, flops
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--set", default="resnet50", choices=sorted(SETS))
-    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-strict"],
-                    help="tf32-strict: TF32 only where it stays within 3e-3 (direct kernel or fp32 Winograd per layer)")
+    ap.add_argument("--mode", default="fp32", choices=["fp32", "3xtf32", "tf32", "tf32-unbounded", "tf32-u16"],
+                    help="tf32 keeps rel-L2 <= 3e-3 on every layer (direct kernel, or Winograd in the split arithmetic); "
+                         "tf32-unbounded also runs one TF32 pass through Winograd (6.4e-3); tf32-u16 does the same "
+                         "over a filter stored as fp16")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--tune", action="store_true", help="run Tuning() (timed configuration search) before measuring")
@@ -73,6 +80,10 @@ def main() -> None:
     n = args.batch
     total_ms = total_flops = 0.0
     with Context(args.device, arena_bytes=12 << 30) as ctx:
+        global FP32_PEAK_TFLOPS
+        sms, mhz = C.c_int(), C.c_int()
+        _lib.check(lib.fc_context_info(ctx.handle, C.byref(sms), C.byref(mhz)), "fc_context_info")
+        FP32_PEAK_TFLOPS = sms.value * 128 * 2 * mhz.value * 1e-6
         for idx, (ic, oc, hw, k, s, p) in enumerate(SETS[args.set]):
             if args.only is not None and idx != args.only:
                 continue
@@ -92,14 +103,15 @@ def main() -> None:
             _lib.check(lib.fc_conv_time_device(h, d_in, d_out, 5, args.iters, C.byref(ms)), "fc_conv_time_device")
             algo, resolved = C.c_int(), C.c_int()
             lib.fc_conv_algorithm(h, C.byref(algo))
-            lib.fc_conv_math_mode(h, C.byref(resolved))  # what tf32-strict turned into for this layer
-            mode_name = {0: "fp32", 1: "3xtf32", 2: "tf32"}[resolved.value]
+            lib.fc_conv_math_mode(h, C.byref(resolved))  # what "tf32" turned into for this layer
+            mode_name = _lib.MODE_LABELS[resolved.value]
             hbm, peak_tf = peaks(mode_name)
             oh = (hw + 2 * p - k) // s + 1
             direct = 2.0 * n * oc * ic * k * k * oh * oh
             if algo.value == _lib.ALGO_WINOGRAD:
                 tiles = n * ((oh + 5) // 6) ** 2
-                flops, nbytes = 2.0 * 64 * tiles * ic * oc, 4.0 * (n * ic * hw * hw + 64 * ic * oc + n * oc * oh * oh)
+                u_bytes = 2.0 if mode_name == "tf32-u16" else 4.0  # the filter as the kernel reads it
+                flops, nbytes = 2.0 * 64 * tiles * ic * oc, 4.0 * (n * ic * hw * hw + n * oc * oh * oh) + u_bytes * 64 * ic * oc
             else:
                 flops, nbytes = direct, 4.0 * (n * ic * hw * hw + oc * ic * k * k + n * oc * oh * oh)
             roof_ms = max(flops / (peak_tf * 1e12), nbytes / (hbm * 1e9)) * 1e3

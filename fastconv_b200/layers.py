@@ -219,7 +219,7 @@ def resolve_plan(desc: ConvDesc, algorithm="auto", mode="tf32", sm_count: int = 
     a, r = C.c_int(), C.c_int()
     check(_lib.load().fc_resolve_plan(C.byref(desc), algo, m, int(sm_count), C.byref(a), C.byref(r)), "fc_resolve_plan")
     names = {v: k for k, v in _lib.ALGO_NAMES.items()}
-    return names[a.value], {0: "fp32", 1: "3xtf32", 2: "tf32"}[r.value]
+    return names[a.value], _lib.MODE_LABELS[r.value]
 
 
 def diff(a: np.ndarray, b: np.ndarray) -> float:

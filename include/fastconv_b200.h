@@ -61,6 +61,13 @@ typedef enum fc_math_mode {
                                   tensor-core kernel in TF32 or, where that cannot run or Winograd was asked for by
                                   name, the Winograd path in FC_MATH_3XTF32; every other layer runs in one TF32 pass.
                                   fc_conv_math_mode reports the arithmetic the layer was planned with.             */
+    FC_MATH_TF32_U16 = 4,      /* fc_conv_create only; a reduced-precision mode outside every stated tolerance, like
+                                  FC_MATH_TF32_UNBOUNDED (same 6.4e-3 on Winograd layers): the transformed filter of a
+                                  Winograd layer is STORED as fp16 (TF32's own 11-bit significand) scaled per position by
+                                  a power of two, which halves the stream that bounds single-image layers with many
+                                  channels; it is expanded in shared memory and multiplied in one TF32 pass.  Layers it
+                                  does not fit (at most 64 output channels, 128 tiles or more, other algorithms) run as
+                                  in FC_MATH_TF32_UNBOUNDED; fc_conv_math_mode tells which.                          */
     FC_MATH_TF32_UNBOUNDED = 3 /* fc_conv_create only: one TF32 pass on every path, F(6x6,3x3) included, whatever the
                                   error (6.4e-3 rel-L2 on Winograd layers).  Faster than FC_MATH_TF32 on layers with
                                   many channels at small batch; outside the stated tolerance, hence the extra name. */

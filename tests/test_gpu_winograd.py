@@ -326,3 +326,42 @@ def test_ffma_block_widths_between_64_and_128_are_bit_exact(ctx, oracle, bn, sha
     layer.Forward()
     assert np.array_equal(layer.output_data, oracle.wino_forward(x, w, 1))
     layer.release()
+
+
+@pytest.mark.parametrize("shape", [(1, 512, 512, 14, 14), (1, 256, 256, 28, 28), (1, 128, 200, 30, 30), (2, 96, 129, 13, 13),
+                                   (1, 40, 72, 56, 56)])
+def test_fp16_filter_mode_is_as_accurate_as_one_tf32_pass(ctx, oracle, shape):
+    """"tf32-u16": the transformed filter stored as scaled fp16 (TF32's own significand), expanded in shared memory,
+    one TF32 pass.  A reduced-precision mode outside the stated tolerances -- its error against the reference is
+    that of one TF32 pass through F(6x6,3x3) (6.4e-3), which is what the test pins, together with its distance to
+    the fp32-filter result of the same arithmetic (the fp16 rounding of values TF32 would have rounded anyway)."""
+    n, ic, oc, ih, iw = shape
+    x = synth.conv_input(n, ic, ih, iw, 151)
+    w = synth.conv_weights(oc, ic, 3, 3, 152)
+    want = oracle.wino_forward(x, w, 1)
+    layer = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, ih, iw, oc, batch=n, iter=1, mode="tf32-u16", ctx=ctx)
+    layer.Init()
+    mode = C.c_int()
+    fc.load().fc_conv_math_mode(layer._conv, C.byref(mode))
+    assert mode.value == fc._lib.MATH_TF32_U16
+    layer.Forward()
+    got = layer.output_data.copy()
+    layer.release()
+    one_pass = run_layer(ctx, x, w, 1, mode="tf32-unbounded")
+    assert rel_l2(got, want) <= 8e-3, rel_l2(got, want)
+    assert rel_l2(got, one_pass) <= 6e-3, rel_l2(got, one_pass)
+
+
+def test_fp16_filter_mode_falls_back_where_it_does_not_fit(ctx, oracle):
+    lib = fc.load()
+    for n, ic, oc, hw in [(1, 32, 64, 28), (8, 128, 128, 28)]:  # at most 64 channels; 128 tiles or more
+        x = synth.conv_input(n, ic, hw, hw, 153)
+        w = synth.conv_weights(oc, ic, 3, 3, 154)
+        layer = fc.ConvWinoF63ZCLayer(x, w, None, None, ic, hw, hw, oc, batch=n, iter=1, mode="tf32-u16", ctx=ctx)
+        layer.Init()
+        mode = C.c_int()
+        lib.fc_conv_math_mode(layer._conv, C.byref(mode))
+        assert mode.value == fc._lib.MATH_TF32
+        layer.Forward()
+        assert rel_l2(layer.output_data, oracle.wino_forward(x, w, 1)) <= 8e-3
+        layer.release()

@@ -60,6 +60,16 @@ def test_tf32_never_runs_one_pass_through_winograd():
     assert plan(1, 3, 64, 224, 7, s=2) == ("im2col", "tf32")
 
 
+def test_fp16_filter_mode_resolves_per_layer():
+    """"tf32-u16" keeps the fp16 filter for Winograd layers with more than 64 channels and under 128 tiles."""
+    assert plan(1, 512, 512, 14, 3, algo="winograd", mode="tf32-u16") == ("winograd", "tf32-u16")
+    assert plan(1, 256, 256, 56, 3, algo="winograd", mode="tf32-u16") == ("winograd", "tf32-u16")   # 100 tiles
+    assert plan(64, 512, 512, 14, 3, algo="winograd", mode="tf32-u16") == ("winograd", "tf32")      # 576 tiles
+    assert plan(1, 64, 64, 56, 3, algo="winograd", mode="tf32-u16") == ("winograd", "tf32")         # 64 channels
+    assert plan(1, 256, 64, 56, 1, mode="tf32-u16")[1] == "tf32"                                    # not a Winograd layer
+    assert plan(1, 256, 256, 56, 3, mode="tf32-u16") == plan(1, 256, 256, 56, 3, mode="tf32-unbounded")[:1] + ("tf32-u16",)
+
+
 def test_make_layer_auto_follows_the_plan():
     """The Python front end, the CLI and the library agree on what `auto` means in every mode."""
     import numpy as np
