@@ -349,7 +349,8 @@ def test_fp16_filter_mode_is_as_accurate_as_one_tf32_pass(ctx, oracle, shape):
     layer.release()
     one_pass = run_layer(ctx, x, w, 1, mode="tf32-unbounded")
     assert rel_l2(got, want) <= 8e-3, rel_l2(got, want)
-    assert rel_l2(got, one_pass) <= 6e-3, rel_l2(got, one_pass)
+    # the two round the filter differently (fp16 to nearest, the tensor core by truncation): independent errors
+    assert rel_l2(got, one_pass) <= 1e-2, rel_l2(got, one_pass)
 
 
 def test_fp16_filter_mode_falls_back_where_it_does_not_fit(ctx, oracle):
