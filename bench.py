@@ -46,6 +46,11 @@ HBM_FALLBACK_GBS = 6650.0
 TF32_LIBRARY_TFLOPS = 759.9
 FP32_LIBRARY_TFLOPS = 63.7
 
+# DRAM bytes (read + write) per TensorGEMM launch, averaged over the 13 launches of one step of the default workload
+# (VGG-16, 64 images, fp32 mode, one GPU), from one ncu capture of `dram__bytes_read.sum + dram__bytes_write.sum`
+# (profiles/tensorgemm_dram_traffic_vgg16_batch64.md).  None for any other workload.
+NCU_GEMM_TRAFFIC_BYTES_DEFAULT = 905.96e6
+
 
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
@@ -583,7 +588,8 @@ def main():
                             if math_bound and gemm_mode == "fp32" else
                             "TF32 library GEMM (8192^3) measured on a B200" + (" / 3 passes" if gemm_mode == "3xtf32" else "")
                             if math_bound else f"copy bandwidth of MEASURED_PEAKS.json, of {peak_kind}"),
-            "traffic": None,
+            "traffic": NCU_GEMM_TRAFFIC_BYTES_DEFAULT if (args.layers == "vgg16" and args.batch == 64 and world == 1 and
+                                                          args.mode == "fp32" and args.algo == "winograd" and not args.chain) else None,
             "algorithmic_flops_per_launch": agg["gemm_flops"] / nl, "algorithmic_bytes_per_launch": agg["gemm_bytes"] / nl,
             "avg_launch_ms": agg["gemm_ms"] / nl,
             "winograd_domain_tflops": round(gemm_tflops, 2), "operand_gbs": round(gemm_gbs, 1),
