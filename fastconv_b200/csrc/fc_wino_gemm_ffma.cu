@@ -52,7 +52,7 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int BM, int BN>
+template <int BM, int BN, int BK = 16, int STAGES = 4>
 __global__ void __launch_bounds__(THREADS, 2) wino_gemm_ffma_kernel(const float *__restrict__ U,
                                                                     const float *__restrict__ V, float *__restrict__ M,
                                                                     int oc, int ocp, int tp, int icp) {
@@ -567,12 +567,12 @@ int launch_flex(fc_context *ctx, const float *d_U, const float *d_V, float *d_M,
     return FC_OK;
 }
 
-template <int BM, int BN>
+template <int BM, int BN, int BKT = BK, int NST = STAGES>
 int launch_blocked(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
-    const size_t smem = (size_t)STAGES * BK * (BM + BN) * sizeof(float);
-    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t smem = (size_t)NST * BKT * (BM + BN) * sizeof(float);
+    FC_CHECK_CUDA(cudaFuncSetAttribute(wino_gemm_ffma_kernel<BM, BN, BKT, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)ceil_div(g.tp, BN), (unsigned)ceil_div(g.oc, BM), 64), block(THREADS);
-    FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<BM, BN>, grid, block, smem, ctx->stream, d_U, d_V, d_M, g.oc, g.ocp,
+    FC_CHECK_CUDA((launch_pdl(wino_gemm_ffma_kernel<BM, BN, BKT, NST>, grid, block, smem, ctx->stream, d_U, d_V, d_M, g.oc, g.ocp,
                               g.tp, g.icp)));
     return FC_OK;
 }
@@ -638,6 +638,8 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
             }
         }
     }
+    if (wide_m && wide_n && cfg && cfg->smem_kb == 1) return launch_blocked<128, 128, 32, 3>(ctx, d_U, d_V, d_M, g);  // experiment
+    if (wide_m && wide_n && cfg && cfg->smem_kb == 2) return launch_blocked<128, 128, 8, 6>(ctx, d_U, d_V, d_M, g);   // experiment
     if (wide_m && wide_n) return launch_blocked<128, 128>(ctx, d_U, d_V, d_M, g);
     if (wide_m) return launch_blocked<128, 64>(ctx, d_U, d_V, d_M, g);
     if (wide_n) return launch_blocked<64, 128>(ctx, d_U, d_V, d_M, g);
