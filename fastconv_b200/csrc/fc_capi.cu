@@ -867,6 +867,27 @@ static int igemm_launches(const fc_conv *c) {
     return c->d_bmat != nullptr && igemm_on_fp32_pipe(c) && tile_kernel ? 2 : 1;
 }
 
+// fp32 layers with at most 4 input channels run the TensorGEMM inside the output transform (two kernels, M never
+// stored); $FASTCONV_FUSE_SMALL_IC=0 keeps the three-kernel form for comparison.
+static bool wino_pass_fuses_gemm(const fc_conv *c, const WinoGeom &g) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char *e = getenv("FASTCONV_FUSE_SMALL_IC");
+        enabled = e && atoi(e) == 0 ? 0 : 1;
+    }
+    return enabled && c->mode == FC_MATH_FP32_MIRRORED && output_transform_can_fuse_gemm(g);
+}
+
+static int wino_launches(const fc_conv *c) {
+    const int passes = conv_passes(c);
+    int n = 0;
+    for (int p = 0; p < passes; ++p) {
+        const bool tail = (p + 1) * c->pass_imgs > c->desc.batch;
+        n += wino_pass_fuses_gemm(c, tail ? c->tail_geom : c->pass_geom) ? 2 : 3;
+    }
+    return n;
+}
+
 // One pass of a Winograd layer: images [pass*pass_imgs, ...) of the batch through the three kernels.
 static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_out, bool timed) {
     fc_context *ctx = c->ctx;
@@ -878,6 +899,12 @@ static int wino_enqueue_pass(fc_conv *c, int pass, const float *d_in, float *d_o
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[0], ctx->stream));
     FC_PROPAGATE(input_transform_dispatch(ctx, in, c->d_V, g, c->mode));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[1], ctx->stream));
+    if (wino_pass_fuses_gemm(c, g)) {  // no TensorGEMM stage of its own: its time shows under the output transform
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
+        FC_PROPAGATE(launch_output_transform_fused_gemm(ctx, c->d_U, c->d_V, out, g, Epilogue{c->d_bias, c->relu}));
+        if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[3], ctx->stream));
+        return FC_OK;
+    }
     FC_PROPAGATE(wino_gemm_dispatch(ctx, c->d_U, c->d_V, c->d_M, g, c->mode, &c->cfg));
     if (timed) FC_CHECK_CUDA(cudaEventRecord(ctx->ev[2], ctx->stream));
     FC_PROPAGATE(launch_output_transform(ctx, c->d_M, out, g, Epilogue{c->d_bias, c->relu}));
@@ -1154,6 +1181,7 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
         for (auto &t : ffma_tiles) push(t[0], t[1], 2, 0);
         if (algo == FC_ALGO_WINOGRAD && c->desc.oc > 64)  // block widths between 64 and 128 tiles
             for (int bn : {80, 96, 112}) push(128, bn, 2, 0);
+        if (algo == FC_ALGO_WINOGRAD && c->desc.oc <= 64) push(64, 256, 2, 0);  // 4 channels x 16 tiles per thread
     } else {
         const int widths[5] = {32, 64, 96, 128, 256};
         const int budgets[3] = {72, 104, 200};
@@ -1305,7 +1333,7 @@ int fc_conv_get_kernel_config(const fc_conv *c, int *bm, int *bn, int *variant, 
 
 int fc_conv_launches_per_forward(const fc_conv *c, int *launches) {
     FC_REQUIRE(c && launches, FC_ERR_INVALID_ARG, "NULL argument");
-    *launches = c->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(c) : c->algo == FC_ALGO_DIRECT ? direct_launches(c) : igemm_launches(c);
+    *launches = c->algo == FC_ALGO_WINOGRAD ? wino_launches(c) : c->algo == FC_ALGO_DIRECT ? direct_launches(c) : igemm_launches(c);
     return FC_OK;
 }
 
@@ -1331,7 +1359,7 @@ int fc_layer_list_create(fc_context *ctx, fc_conv *const *convs, const float *co
     for (int i = 0; i < count; ++i) {
         FC_REQUIRE(convs[i] && d_ins[i] && d_outs[i], FC_ERR_INVALID_ARG, "layer %d has a NULL member", i);
         FC_REQUIRE(convs[i]->ctx == ctx, FC_ERR_INVALID_ARG, "layer %d belongs to another context", i);
-        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? 3 * conv_passes(convs[i])
+        launches += convs[i]->algo == FC_ALGO_WINOGRAD ? wino_launches(convs[i])
                     : convs[i]->algo == FC_ALGO_DIRECT ? direct_launches(convs[i]) : igemm_launches(convs[i]);
     }
     FC_CHECK_CUDA(cudaSetDevice(ctx->device));

@@ -75,7 +75,8 @@ int wino_geom(const fc_conv_desc *d, WinoGeom *g);  // validates and fills
 // Kernel configuration of the multiply-accumulate stage; every field 0 = let the launcher's heuristic decide.
 // This is what Tuning() searches (the counterpart of the reference's ocBlock/tileBlock/icBlock and mc/nc/kc).
 struct KernelCfg {
-    int bm, bn;     // block rows (output channels) / columns (tiles or pixels): 64 or 128 for FFMA, bn a multiple of 16 for tcgen05
+    int bm, bn;     // block rows (output channels) / columns (tiles or pixels): 64 or 128 for FFMA (Winograd also 64 x 256
+                    // and 128 x 80/96/112), bn a multiple of 16 for tcgen05
     int skinny;     // FFMA TensorGEMM with <= 32 tiles: 1 = one-thread-per-channel kernel, 2 = blocked kernel
     int smem_kb;    // tcgen05 kernels: shared-memory budget of the operand ring (sets the stage count / CTAs per SM)
 };
@@ -175,6 +176,11 @@ int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d
 int launch_input_transform(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g);
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g,
                             const Epilogue &ep = kNoEpilogue);
+// fp32 layers with at most 4 input channels and a warp's worth of tiles: the TensorGEMM inside the output transform
+// (same accumulation chain, M never stored)
+bool output_transform_can_fuse_gemm(const WinoGeom &g);
+int launch_output_transform_fused_gemm(fc_context *ctx, const float *d_U, const float *d_V, float *d_out,
+                                       const WinoGeom &g, const Epilogue &ep);
 int launch_output_transform_scatter(fc_context *ctx, const float *d_M, const PeerOuts &dst, const WinoGeom &g,
                                     const Epilogue &ep = kNoEpilogue);
 int launch_output_transform_scatter_publish(fc_context *ctx, const float *d_M, const ScatterPublish &dst,

@@ -524,6 +524,146 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Layers with at most 4 input channels (the first layer of an image network): the TensorGEMM costs 64 x ic fused
+// multiply-adds per (output channel, tile) item, far less than writing the item's 64 values of M and reading them
+// back.  So the output transform computes them itself, straight from U[p][ic][ocp] and V[p][ic][tp], with the
+// same chain as the TensorGEMM (one accumulator from +0, one fused multiply-add per input channel in ascending order:
+// bit-identical values of M), and M never exists in memory.
+//
+// A block owns 32 consecutive tiles x FUSED_OCC output channels.  Its slice of the filter sits in shared memory as one
+// float4 (channels 0..3, zero past ic) per (position, output channel), its slab of V as [position, channel][tile]; a
+// thread owns one tile and two output channels at a time, so that every value of V read feeds two chains.  The rest is
+// output_transform_wide_kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int FUSED_OCC = 16, FUSED_WARPS = 4;
+
+template <int IC, bool EPI>
+__global__ void __launch_bounds__(32 * FUSED_WARPS, 3) output_transform_fused_gemm_kernel(
+    const float *__restrict__ U, const float *__restrict__ V, float *__restrict__ out, int n_tiles, int oc, int ocp,
+    int icp, int tp, int oh, int ow, int th, int tw, Epilogue ep) {
+    constexpr int ROW = 32 * 6 + 2, THREADS = 32 * FUSED_WARPS;
+    extern __shared__ __align__(16) float fused_smem[];
+    float4(*s_u)[FUSED_OCC] = reinterpret_cast<float4(*)[FUSED_OCC]>(fused_smem);
+    float(*s_v)[32] = reinterpret_cast<float(*)[32]>(fused_smem + 64 * FUSED_OCC * 4);  // [p * IC + c][tile of the block]
+    float(*stage)[6][ROW] = reinterpret_cast<float(*)[6][ROW]>(fused_smem + 64 * FUSED_OCC * 4 + 64 * IC * 32);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 32 + lane, k_base = blockIdx.y * FUSED_OCC;
+    // the filter does not depend on the preceding kernel: fetch it before waiting for V
+    {
+        constexpr int P_STEP = THREADS / FUSED_OCC;  // positions covered by one sweep of the block
+        const int kl = threadIdx.x % FUSED_OCC, p0 = threadIdx.x / FUSED_OCC, k = k_base + kl;
+        const float *ub = U + (size_t)p0 * icp * ocp + k;
+#pragma unroll
+        for (int i = 0; i < 64 / P_STEP; ++i) {
+            float u[4] = {0.f, 0.f, 0.f, 0.f};
+            if (k < oc) {
+#pragma unroll
+                for (int c = 0; c < IC; ++c) u[c] = __ldg(ub + ((size_t)(i * P_STEP) * icp + c) * ocp);
+            }
+            s_u[p0 + i * P_STEP][kl] = make_float4(u[0], u[1], u[2], u[3]);
+        }
+    }
+    pdl_trigger();
+    pdl_wait();  // V comes from the input transform launched just before
+    // the block's slab of V, every load in flight at once: one round trip to memory per block
+    {   // warp w brings positions [16w, 16w + 16)
+        constexpr int ROWS = 64 / FUSED_WARPS * IC;
+        const float *vb = V + (size_t)(warp * (64 / FUSED_WARPS)) * icp * tp + t;
+        float v[ROWS];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) v[i] = t < n_tiles ? __ldg(vb + ((size_t)(i / IC) * icp + i % IC) * tp) : 0.f;
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) s_v[warp * ROWS + i][lane] = v[i];
+    }
+    __syncthreads();
+
+    // Where this lane stores: element e = lane + 32*it of every staged row belongs to tile e/6, column e%6.  None of it
+    // depends on the output channel, so it is worked out once: offset inside a channel's page, image, valid rows.
+    const size_t out_page = (size_t)oh * ow;
+    int st_off[6], st_img[6], st_rows[6];
+    {
+        int my_org = -1, my_img = 0;  // y0 << 16 | x0 of the tile's first output, -1 past the end
+        if (t < n_tiles) {
+            const int per_img = th * tw;
+            const int img = t / per_img, tt = t - img * per_img;
+            my_org = ((tt / tw) * 6) << 16 | ((tt % tw) * 6);
+            my_img = img;
+        }
+#pragma unroll
+        for (int it = 0; it < 6; ++it) {
+            const int e = lane + it * 32;
+            const int te = e / 6, j = e - te * 6;
+            const int org = __shfl_sync(0xffffffffu, my_org, te);
+            st_img[it] = __shfl_sync(0xffffffffu, my_img, te);
+            const int y0 = org >> 16, x = (org & 0xffff) + j;
+            st_off[it] = y0 * ow + x;
+            st_rows[it] = org < 0 || x >= ow ? 0 : min(6, oh - y0);
+        }
+    }
+    constexpr int PER_WARP = FUSED_OCC / FUSED_WARPS;
+#pragma unroll 1
+    for (int pair = 0; pair < PER_WARP / 2; ++pair) {
+        const int kl0 = warp * PER_WARP + pair * 2, k0 = k_base + kl0;
+        if (k0 >= oc) break;  // whole warp
+        float h0[8][6], h1[8][6];
+#pragma unroll
+        for (int row = 0; row < 8; ++row) {
+            float m0[8], m1[8];
+#pragma unroll
+            for (int col = 0; col < 8; ++col) {
+                const int p = col * 8 + row;
+                const float4 u0 = s_u[p][kl0], u1 = s_u[p][kl0 + 1];
+                const float a0[4] = {u0.x, u0.y, u0.z, u0.w}, a1[4] = {u1.x, u1.y, u1.z, u1.w};
+                float x0 = 0.f, x1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < IC; ++c) {
+                    const float v = s_v[p * IC + c][lane];
+                    x0 = __fmaf_rn(a0[c], v, x0);
+                    x1 = __fmaf_rn(a1[c], v, x1);
+                }
+                m0[col] = x0;
+                m1[col] = x1;
+            }
+            output_transform_1d(m0[0], m0[1], m0[2], m0[3], m0[4], m0[5], m0[6], m0[7], h0[row]);
+            output_transform_1d(m1[0], m1[1], m1[2], m1[3], m1[4], m1[5], m1[6], m1[7], h1[row]);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int k = k0 + half;
+            if (k >= oc) break;  // whole warp
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                float s[6];
+                if (half == 0)
+                    output_transform_1d(h0[0][j], h0[1][j], h0[2][j], h0[3][j], h0[4][j], h0[5][j], h0[6][j], h0[7][j], s);
+                else
+                    output_transform_1d(h1[0][j], h1[1][j], h1[2][j], h1[3][j], h1[4][j], h1[5][j], h1[6][j], h1[7][j], s);
+#pragma unroll
+                for (int i = 0; i < 6; ++i) stage[warp][i][lane * 6 + j] = s[i];
+            }
+            __syncwarp();
+            float b = 0.f;
+            if (EPI && ep.bias != nullptr) b = __ldg(ep.bias + k);
+#pragma unroll
+            for (int it = 0; it < 6; ++it) {
+                float *dst = out + ((size_t)st_img[it] * oc + k) * out_page + st_off[it];
+#pragma unroll
+                for (int i = 0; i < 6; ++i) {
+                    if (i >= st_rows[it]) break;
+                    float v = stage[warp][i][lane + it * 32];
+                    if (EPI) {
+                        if (ep.bias != nullptr) v = __fadd_rn(v, b);
+                        if (ep.relu) v = fmaxf(v, 0.0f);
+                    }
+                    dst[(size_t)i * ow] = v;
+                }
+            }
+            __syncwarp();  // the staged rows are free again
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // fp16 copy of the packed filter (FC_MATH_TF32_U16).  Per position p the largest magnitude picks a power of two 2^e
 // with max|U_p| / 2^e in [2^13, 2^14): every value is divided by it (exact) and rounded to fp16, which keeps TF32's 11
 // significant bits for everything within 2^-27 of the largest value; the scale goes into scales[p] and is multiplied
@@ -606,6 +746,30 @@ int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, con
                                  g.oh, g.ow, g.th, g.tw, ep));
     }
     FC_CHECK_CUDA(cudaGetLastError());
+    return FC_OK;
+}
+
+bool output_transform_can_fuse_gemm(const WinoGeom &g) { return g.ic <= 4 && g.tiles >= 32; }
+
+int launch_output_transform_fused_gemm(fc_context *ctx, const float *d_U, const float *d_V, float *d_out,
+                                       const WinoGeom &g, const Epilogue &ep) {
+    FC_REQUIRE(output_transform_can_fuse_gemm(g), FC_ERR_UNSUPPORTED, "fused TensorGEMM: %d input channels, %d tiles",
+               g.ic, g.tiles);
+    dim3 block(32 * FUSED_WARPS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, FUSED_OCC));
+    const size_t smem = sizeof(float) * (64 * FUSED_OCC * 4 + 64 * (size_t)g.ic * 32 + FUSED_WARPS * 6 * (32 * 6 + 2));
+    auto go = [&](auto kern) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        return launch_pdl(kern, grid, block, smem, ctx->stream, d_U, d_V, d_out, g.tiles, g.oc, g.ocp, g.icp, g.tp, g.oh,
+                          g.ow, g.th, g.tw, ep);
+    };
+    const bool epi = ep.bias != nullptr || ep.relu;
+    switch (g.ic) {
+        case 1: FC_CHECK_CUDA(epi ? go(output_transform_fused_gemm_kernel<1, true>) : go(output_transform_fused_gemm_kernel<1, false>)); break;
+        case 2: FC_CHECK_CUDA(epi ? go(output_transform_fused_gemm_kernel<2, true>) : go(output_transform_fused_gemm_kernel<2, false>)); break;
+        case 3: FC_CHECK_CUDA(epi ? go(output_transform_fused_gemm_kernel<3, true>) : go(output_transform_fused_gemm_kernel<3, false>)); break;
+        default: FC_CHECK_CUDA(epi ? go(output_transform_fused_gemm_kernel<4, true>) : go(output_transform_fused_gemm_kernel<4, false>)); break;
+    }
     return FC_OK;
 }
 

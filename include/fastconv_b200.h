@@ -267,7 +267,7 @@ int fc_conv_tune(fc_conv *conv, int iters, int verbose);
  * constructors are to its layers (mc, nc, kc, row_batch, col_batch of ConvIm2colLayer, convLayer/im2colConv.h:16-18;
  * the members ocBlock / tileBlock / icBlock that ConvWinoF63ZCLayer::Tuning assigns, convLayer/winoF63ConvZC.cpp:151-161).
  * Every field 0 = the launcher's heuristic.  bm x bn: block of output channels x tiles or pixels (FFMA kernels: 64 or
- * 128 each for Winograd, 128x128 ... 8x32 for the table-driven implicit GEMM; tcgen05 kernels: bn = accumulator
+ * 128 each for Winograd, also 64x256 and 128x80/96/112; 128x128 ... 8x32 for the table-driven implicit GEMM; tcgen05 kernels: bn = accumulator
  * width, a multiple of 16 up to 256).  variant: 1 / 2 select between the two kernels a path has (Winograd fp32 with
  * at most 32 tiles: 1 = the few-tile kernel, 2 = the blocked one; implicit GEMM: 1 = table-driven FFMA kernel,
  * 2 = the 16x16-thread FFMA kernel in fp32 mode and the tcgen05 kernel in the tensor-core modes).  smem_kb: size of

@@ -26,8 +26,9 @@ def _bias(oc, seed):
     return (synth.conv_input(1, 1, 1, oc, seed).reshape(oc) * np.float32(0.5)).astype(np.float32)
 
 
-# n, ic, oc, hw: 4 / 25 / 100 / 400 tiles -> the three latency-oriented shapes and the wide output transform
-WINO = [(1, 8, 12, 7), (1, 16, 20, 30), (1, 24, 40, 56), (4, 16, 24, 56)]
+# n, ic, oc, hw: 4 / 25 / 100 / 400 tiles -> the three latency-oriented shapes and the wide output transform;
+# 3 input channels -> the output transform that holds the multiply-accumulate
+WINO = [(1, 8, 12, 7), (1, 16, 20, 30), (1, 24, 40, 56), (4, 16, 24, 56), (2, 3, 18, 56)]
 
 
 @pytest.mark.parametrize("shape", WINO)

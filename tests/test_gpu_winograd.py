@@ -366,3 +366,40 @@ def test_fp16_filter_mode_falls_back_where_it_does_not_fit(ctx, oracle):
         layer.Forward()
         assert rel_l2(layer.output_data, oracle.wino_forward(x, w, 1)) <= 8e-3
         layer.release()
+
+
+# n, ic, oc, ih, iw, pad: at most 4 input channels and 32+ tiles -- the TensorGEMM runs inside the output transform
+FEW_CHANNELS = [(1, 3, 64, 224, 224, 1), (2, 3, 16, 40, 37, 1), (1, 1, 7, 36, 36, 1), (3, 2, 33, 25, 31, 0),
+                (1, 4, 20, 48, 30, 2), (5, 3, 5, 19, 20, 1), (1, 4, 130, 34, 34, 1)]
+
+
+@pytest.mark.parametrize("shape", FEW_CHANNELS)
+def test_few_input_channels_two_kernels_bit_exact(ctx, oracle, shape):
+    """Two launches (input transform, output transform with the multiply-accumulate inside) and the oracle's bits."""
+    n, ic, oc, ih, iw, pad = shape
+    x = synth.conv_input(n, ic, ih, iw, 141)
+    w = synth.conv_weights(oc, ic, 3, 3, 142)
+    assert np.array_equal(run_layer(ctx, x, w, pad, launches=2), oracle.wino_forward(x, w, pad))
+
+
+def test_few_input_channels_same_bits_as_three_kernels(ctx, monkeypatch):
+    """Full-size first layer on 4 images: the two-kernel form against the three-kernel form of the same library."""
+    import subprocess, sys, os, textwrap
+    code = textwrap.dedent("""
+        import hashlib, numpy as np, fastconv_b200 as fc
+        from fastconv_b200 import synth
+        x = synth.conv_input(4, 3, 224, 224, 7); w = synth.conv_weights(64, 3, 3, 3, 8)
+        with fc.Context(0, arena_bytes=3 << 30) as ctx:
+            l = fc.ConvWinoF63ZCLayer(x, w, None, None, 3, 224, 224, 64, batch=4, ctx=ctx)
+            l.Init(); l.Forward()
+            print(l.kernel_launches, hashlib.sha256(l.output_data.tobytes()).hexdigest())
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = []
+    for flag in ("1", "0"):
+        env = dict(os.environ, FASTCONV_FUSE_SMALL_IC=flag, PYTHONPATH=root)
+        r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(r.stdout.split()[-2:])  # the layer's own "Algorithm:" line comes first
+    assert outs[0][0] == "2" and outs[1][0] == "3"
+    assert outs[0][1] == outs[1][1]
