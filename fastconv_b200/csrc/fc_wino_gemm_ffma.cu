@@ -497,12 +497,12 @@ __global__ void __launch_bounds__(SK_THREADS) wino_gemm_ffma_skinny_kernel(const
 }
 
 // U[p][icp][ocp] as a 3-D tensor (oc, ic, p), box = 128 oc x 32 ic, no swizzle, zero fill outside
-int make_map_u_rowmajor(CUtensorMap *map, const float *base, int ocp, int icp) {
+int make_map_u_rowmajor(CUtensorMap *map, const float *base, int ocp, int icp, int box_oc = 128, int box_ic = 32) {
     tc::EncodeTiledFn enc;
     FC_PROPAGATE(tc::get_encoder(&enc));
     cuuint64_t dims[3] = {(cuuint64_t)ocp, (cuuint64_t)icp, 64};
     cuuint64_t strides[2] = {(cuuint64_t)ocp * 4, (cuuint64_t)ocp * icp * 4};
-    cuuint32_t box[3] = {128, 32, 1};
+    cuuint32_t box[3] = {(cuuint32_t)box_oc, (cuuint32_t)box_ic, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -512,17 +512,170 @@ int make_map_u_rowmajor(CUtensorMap *map, const float *base, int ocp, int icp) {
 }
 
 // V[p][icp][tp] as a 3-D tensor (tile, ic, p), box = tp tiles x 32 ic, no swizzle, zero fill outside
-int make_map_v_rowmajor(CUtensorMap *map, const float *base, int tp, int icp) {
+int make_map_v_rowmajor(CUtensorMap *map, const float *base, int tp, int icp, int box_t = 0, int box_ic = 32) {
     tc::EncodeTiledFn enc;
     FC_PROPAGATE(tc::get_encoder(&enc));
     cuuint64_t dims[3] = {(cuuint64_t)tp, (cuuint64_t)icp, 64};
     cuuint64_t strides[2] = {(cuuint64_t)tp * 4, (cuuint64_t)tp * icp * 4};
-    cuuint32_t box[3] = {(cuuint32_t)tp, 32, 1};
+    cuuint32_t box[3] = {(cuuint32_t)(box_t ? box_t : tp), (cuuint32_t)box_ic, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     FC_REQUIRE(r == CUDA_SUCCESS, FC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (tp %d icp %d)", (int)r, tp, icp);
+    return FC_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// The blocked kernel fed by TMA.  Same block, same thread tile, same inner product as wino_gemm_ffma_kernel; what
+// changes is how the slabs arrive and how the warps meet.  One thread asks for a whole BK x BM box of U and a BK x BN
+// box of V per slab (cp.async.bulk.tensor, zero fill past the edges), the boxes land in a ring of TB_STAGES stages and
+// complete the stage's "full" mbarrier; each warp waits for that barrier by itself, multiplies, and arrives on the
+// stage's "empty" barrier.  No thread issues per-slab copy instructions, and no block-wide barrier sits in the loop:
+// a warp may run a slab ahead of its neighbours.  The stage refilled while slab kt is multiplied is the one slab kt-2
+// used, so the requesting warp waits only for warps that are two slabs behind.
+// ---------------------------------------------------------------------------------------------
+constexpr int TB_STAGES = 5;
+
+template <int BM, int BN, int MAP>
+__global__ void __launch_bounds__(THREADS, 2)
+    wino_gemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
+                              float *__restrict__ M, int *status, int oc, int tp, int icp) {
+    using namespace tc;
+    constexpr int TM = BM / 16, TN = BN / 16;
+    constexpr uint32_t A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4, STAGE = A_STAGE + B_STAGE;
+    extern __shared__ uint8_t smem_raw[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[TB_STAGES], empty[TB_STAGES]
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * TB_STAGES);
+    const uint32_t ring = (smem_u32(smem_raw) + 128 + 127) & ~127u;
+    const uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    auto bar_full = [&](int s) { return smem_u32(bars + s); };
+    auto bar_empty = [&](int s) { return smem_u32(bars + TB_STAGES + s); };
+
+    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tx = MAP == 0 ? tid % 16 : (tid / 32 % 2) * 8 + tid % 8;
+    const int ty = MAP == 0 ? tid / 16 : (tid / 64) * 4 + tid % 32 / 8;
+    const int n_slabs = (icp + BK - 1) / BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < TB_STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), THREADS / 32);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_trigger();
+    if (tid == 0) {
+        // U is constant: its first boxes are requested before the input transform that writes V is known to be complete
+        const int head = n_slabs < TB_STAGES - 1 ? n_slabs : TB_STAGES - 1;
+        for (int kt = 0; kt < head; ++kt) {
+            mbar_expect_tx(bar_full(kt), STAGE);
+            tma_load_3d(ring + kt * STAGE, &tmU, bar_full(kt), oc0, kt * BK, p);
+        }
+        pdl_wait();
+        for (int kt = 0; kt < head; ++kt) tma_load_3d(ring + kt * STAGE + A_STAGE, &tmV, bar_full(kt), t0, kt * BK, p);
+    }
+
+    uint64_t acc2[TM][TN / 2];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN / 2; ++j) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
+
+    bool ok = true;
+    for (int kt = 0; kt < n_slabs; ++kt) {
+        const int s = kt % TB_STAGES;
+        if (tid == 0 && kt >= 1) {  // request slab kt + TB_STAGES - 2 into the stage slab kt - 2 used
+            const int kn = kt + TB_STAGES - 2;
+            if (kn < n_slabs) {
+                const int sn = kn % TB_STAGES;
+                bool free_stage = true;
+                if (kt >= 2) free_stage = mbar_wait(bar_empty(sn), (uint32_t)((kt - 2) / TB_STAGES) & 1u, abort_flag, status);
+                if (free_stage) {
+                    mbar_expect_tx(bar_full(sn), STAGE);
+                    tma_load_3d(ring + sn * STAGE, &tmU, bar_full(sn), oc0, kn * BK, p);
+                    tma_load_3d(ring + sn * STAGE + A_STAGE, &tmV, bar_full(sn), t0, kn * BK, p);
+                }
+            }
+        }
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), (uint32_t)(kt / TB_STAGES) & 1u, abort_flag, status));
+        if (!ok) break;
+        const float(*As)[BM] = reinterpret_cast<const float(*)[BM]>(ring_ptr + (size_t)s * STAGE);
+        const float(*Bs)[BN] = reinterpret_cast<const float(*)[BN]>(ring_ptr + (size_t)s * STAGE + A_STAGE);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int g = 0; g < TM / 4; ++g) {
+                const float4 v = *reinterpret_cast<const float4 *>(&As[k][g * 64 + ty * 4]);
+                a[g * 4 + 0] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int g = 0; g < TN / 4; ++g) {
+                const float4 v = *reinterpret_cast<const float4 *>(&Bs[k][g * 64 + tx * 4]);
+                b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
+            }
+            uint64_t bp[TN / 2];
+#pragma unroll
+            for (int j = 0; j < TN / 2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+                const uint64_t ap = pack2(a[i], a[i]);
+#pragma unroll
+                for (int j = 0; j < TN / 2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty(s));  // this warp no longer reads the stage
+    }
+    if (ok) {
+        float *Mp = M + (size_t)p * oc * tp;
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int r = oc0 + (i / 4) * 64 + ty * 4 + (i % 4);
+            if (r >= oc) continue;
+#pragma unroll
+            for (int g = 0; g < TN / 4; ++g) {
+                const int c = t0 + g * 64 + tx * 4;
+                if (c < tp) {  // tp is a multiple of 8, so a float4 never straddles the end
+                    float4 v;
+                    unpack2(acc2[i][g * 2 + 0], v.x, v.y);
+                    unpack2(acc2[i][g * 2 + 1], v.z, v.w);
+                    *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) = v;
+                }
+            }
+        }
+    }
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let boxes still in flight land before the CTA goes
+    }
+}
+
+// $FASTCONV_FFMA_TMA=0 keeps the blocked kernel on per-thread asynchronous copies (for comparisons).
+static bool tma_blocked_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_FFMA_TMA");
+        state = (e && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
+template <int BM, int BN, int MAP>
+int launch_blocked_tma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    CUtensorMap tmU, tmV;
+    FC_PROPAGATE(make_map_u_rowmajor(&tmU, d_U, g.ocp, g.icp, BM, BK));
+    FC_PROPAGATE(make_map_v_rowmajor(&tmV, d_V, g.tp, g.icp, BN, BK));
+    const size_t smem = 128 + 128 + (size_t)TB_STAGES * BK * (BM + BN) * sizeof(float);
+    auto kern = wino_gemm_ffma_tma_kernel<BM, BN, MAP>;
+    FC_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)ceil_div(g.tp, BN), (unsigned)ceil_div(g.oc, BM), 64), block(THREADS);
+    FC_CHECK_CUDA((launch_pdl(kern, grid, block, smem, ctx->stream, tmU, tmV, d_M, ctx->d_status, g.oc, g.tp, g.icp)));
     return FC_OK;
 }
 
@@ -642,6 +795,9 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
             }
         }
     }
+    // (boxes no larger than the tensor: at least one full block of channels and of tiles)
+    if (wide_m && wide_n && g.ocp >= 128 && g.tp >= 128 && ctx->d_status != nullptr && tma_blocked_enabled())
+        return launch_blocked_tma<128, 128, 1>(ctx, d_U, d_V, d_M, g);
     if (wide_m && wide_n) return launch_blocked<128, 128, 1>(ctx, d_U, d_V, d_M, g);
     if (wide_m) return launch_blocked<128, 64>(ctx, d_U, d_V, d_M, g);
     // at most 64 output channels: a 256-wide block gives a thread 4 channels x 16 tiles, the 64 outputs of the 128 x 128

@@ -303,8 +303,78 @@ __global__ void __launch_bounds__(256) input_transform_rowmajor_kernel(const flo
     dst[4 * 8 * plane] = r4; dst[5 * 8 * plane] = r5; dst[6 * 8 * plane] = r6; dst[7 * 8 * plane] = r7;
 }
 
+// Many tiles (large feature maps or batches): throughput matters more than latency, and the three-phase kernel above
+// is bound by instruction issue (0.72 of the issue slots used, DRAM at 29 %), not by memory.  Here one thread owns a
+// whole (channel, tile) item: 64 loads in flight, both passes in registers, 64 stores; no shared memory, no barrier,
+// about half the instructions per item.  Lanes run along consecutive tiles, warps along channels.
+constexpr int ITW_WARPS = 4;
+
+__global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_kernel(
+    const float *__restrict__ in, float *__restrict__ V, int n_tiles, int ic, int icp, int tp, int ih, int iw, int pad,
+    int th, int tw) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tile = blockIdx.x * 32 + lane, c = blockIdx.y * ITW_WARPS + warp;
+    pdl_trigger();
+    pdl_wait();  // the input may be the previous layer's output; V may still be read by an earlier GEMM
+    if (c >= icp || tile >= tp) return;
+    float r[8][8];  // [y][x]
+    unsigned rows = 0, cols = 0;  // bit y / bit x set: inside the image
+    const float *src = in;
+    if (c < ic && tile < n_tiles) {
+        const int per_img = th * tw;
+        const int img = tile / per_img, tt = tile - img * per_img;
+        const int y0 = (tt / tw) * 6 - pad, x0 = (tt % tw) * 6 - pad;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            rows |= (unsigned)(y0 + i >= 0 && y0 + i < ih) << i;
+            cols |= (unsigned)(x0 + i >= 0 && x0 + i < iw) << i;
+        }
+        src = in + (((ptrdiff_t)img * ic + c) * ih + y0) * iw + x0;
+    }
+    if (rows == 0xffu && cols == 0xffu) {
+#pragma unroll
+        for (int y = 0; y < 8; ++y)
+#pragma unroll
+            for (int x = 0; x < 8; ++x) r[y][x] = __ldg(src + (ptrdiff_t)y * iw + x);
+    } else {
+#pragma unroll
+        for (int y = 0; y < 8; ++y)
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+                r[y][x] = ((rows >> y) & (cols >> x) & 1u) ? __ldg(src + (ptrdiff_t)y * iw + x) : 0.0f;
+    }
+#pragma unroll
+    for (int x = 0; x < 8; ++x)  // along y, for every column
+        input_transform_1d(r[0][x], r[1][x], r[2][x], r[3][x], r[4][x], r[5][x], r[6][x], r[7][x]);
+#pragma unroll
+    for (int y = 0; y < 8; ++y)  // along x, for every row
+        input_transform_1d(r[y][0], r[y][1], r[y][2], r[y][3], r[y][4], r[y][5], r[y][6], r[y][7]);
+    const size_t plane = (size_t)icp * tp;
+    float *dst = V + (size_t)c * tp + tile;
+#pragma unroll
+    for (int x = 0; x < 8; ++x)
+#pragma unroll
+        for (int y = 0; y < 8; ++y) dst[(size_t)(x * 8 + y) * plane] = r[y][x];  // p = x*8 + y
+}
+
+// tile count from which the throughput-oriented input transform is taken ($FASTCONV_IT_WIDE_MIN overrides it)
+static int it_wide_min_tiles() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("FASTCONV_IT_WIDE_MIN");
+        v = e && atoi(e) > 0 ? atoi(e) : 64;
+    }
+    return v;
+}
+
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
     dim3 block(256);
+    if (g.tiles >= it_wide_min_tiles()) {
+        dim3 wblock(32 * ITW_WARPS), grid((unsigned)ceil_div(g.tp, 32), (unsigned)ceil_div(g.icp, ITW_WARPS));
+        FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles, g.ic,
+                                 g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+        return FC_OK;
+    }
     if (g.tiles > 16) {
         dim3 grid((unsigned)ceil_div(g.tp, 32), (unsigned)g.icp);
         FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_kernel<32>, grid, block, 0, ctx->stream, d_in, d_V, g.tiles,
@@ -548,33 +618,34 @@ __global__ void __launch_bounds__(32 * FUSED_WARPS, 3) output_transform_fused_ge
     float(*stage)[6][ROW] = reinterpret_cast<float(*)[6][ROW]>(fused_smem + 64 * FUSED_OCC * 4 + 64 * IC * 32);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 32 + lane, k_base = blockIdx.y * FUSED_OCC;
-    // the filter does not depend on the preceding kernel: fetch it before waiting for V
+    // Both operand slices travel through registers with every load in flight at once: the filter's first (it does not
+    // depend on the preceding kernel), then, after the wait for the input transform, the slab of V; only then are they
+    // parked in shared memory -- one round trip to memory per block.
+    constexpr int P_STEP = THREADS / FUSED_OCC;  // positions covered by one sweep of the block over the filter
+    constexpr int ROWS = 64 / FUSED_WARPS * IC;  // rows of V per warp: warp w brings positions [16w, 16w + 16)
+    const int kl = threadIdx.x % FUSED_OCC, p0 = threadIdx.x / FUSED_OCC;
+    float u[64 / P_STEP][4], v[ROWS];
     {
-        constexpr int P_STEP = THREADS / FUSED_OCC;  // positions covered by one sweep of the block
-        const int kl = threadIdx.x % FUSED_OCC, p0 = threadIdx.x / FUSED_OCC, k = k_base + kl;
+        const int k = k_base + kl;
         const float *ub = U + (size_t)p0 * icp * ocp + k;
 #pragma unroll
-        for (int i = 0; i < 64 / P_STEP; ++i) {
-            float u[4] = {0.f, 0.f, 0.f, 0.f};
-            if (k < oc) {
+        for (int i = 0; i < 64 / P_STEP; ++i)
 #pragma unroll
-                for (int c = 0; c < IC; ++c) u[c] = __ldg(ub + ((size_t)(i * P_STEP) * icp + c) * ocp);
-            }
-            s_u[p0 + i * P_STEP][kl] = make_float4(u[0], u[1], u[2], u[3]);
-        }
+            for (int c = 0; c < 4; ++c)
+                u[i][c] = c < IC && k < oc ? __ldg(ub + ((size_t)(i * P_STEP) * icp + c) * ocp) : 0.f;
     }
     pdl_trigger();
-    pdl_wait();  // V comes from the input transform launched just before
-    // the block's slab of V, every load in flight at once: one round trip to memory per block
-    {   // warp w brings positions [16w, 16w + 16)
-        constexpr int ROWS = 64 / FUSED_WARPS * IC;
+    pdl_wait();
+    {
         const float *vb = V + (size_t)(warp * (64 / FUSED_WARPS)) * icp * tp + t;
-        float v[ROWS];
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) v[i] = t < n_tiles ? __ldg(vb + ((size_t)(i / IC) * icp + i % IC) * tp) : 0.f;
-#pragma unroll
-        for (int i = 0; i < ROWS; ++i) s_v[warp * ROWS + i][lane] = v[i];
     }
+#pragma unroll
+    for (int i = 0; i < 64 / P_STEP; ++i)
+        s_u[p0 + i * P_STEP][kl] = make_float4(u[i][0], u[i][1], u[i][2], u[i][3]);
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) s_v[warp * ROWS + i][lane] = v[i];
     __syncthreads();
 
     // Where this lane stores: element e = lane + 32*it of every staged row belongs to tile e/6, column e%6.  None of it
