@@ -536,13 +536,17 @@ int make_map_v_rowmajor(CUtensorMap *map, const float *base, int tp, int icp, in
 // a warp may run a slab ahead of its neighbours.  The stage refilled while slab kt is multiplied is the one slab kt-2
 // used, so the requesting warp waits only for warps that are two slabs behind.
 // ---------------------------------------------------------------------------------------------
-template <int BM, int BN, int MAP, int BK = 16, int TB_STAGES = 5>
+// FLEX = 0: a thread owns TM channels x TN tiles read as 128-bit rows (BN a multiple of 64).  FLEX = 1: BN = 80, 96 or
+// 112 and a thread's TN = BN / 16 tiles are 16 apart, read one float at a time (wino_gemm_ffma_flex_kernel's form).
+template <int BM, int BN, int MAP, int BK = 16, int TB_STAGES = 5, int FLEX = 0>
 __global__ void __launch_bounds__(THREADS, 2)
     wino_gemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
                               float *__restrict__ M, int *status, int oc, int tp, int icp) {
     using namespace tc;
-    constexpr int TM = BM / 16, TN = BN / 16;
+    constexpr int TM = BM / 16, TN = BN / 16, TP2 = TN / 2;
+    static_assert(FLEX == 1 || (TM % 4 == 0 && TN % 4 == 0), "block shape");
     constexpr uint32_t A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4, STAGE = A_STAGE + B_STAGE;
+    static_assert(STAGE % 128 == 0, "stages stay 128-byte aligned");
     static_assert(2 * TB_STAGES * 8 + 4 <= 128, "barriers and the abort flag live in the 128 bytes ahead of the ring");
     extern __shared__ uint8_t smem_raw[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);  // full[TB_STAGES], empty[TB_STAGES]
@@ -553,7 +557,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     auto bar_empty = [&](int s) { return smem_u32(bars + TB_STAGES + s); };
 
     const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * BN;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
     const int tx = MAP == 0 ? tid % 16 : (tid / 32 % 2) * 8 + tid % 8;
     const int ty = MAP == 0 ? tid / 16 : (tid / 64) * 4 + tid % 32 / 8;
     const int n_slabs = (icp + BK - 1) / BK;
@@ -579,11 +583,14 @@ __global__ void __launch_bounds__(THREADS, 2)
         for (int kt = 0; kt < head; ++kt) tma_load_3d(ring + kt * STAGE + A_STAGE, &tmV, bar_full(kt), t0, kt * BK, p);
     }
 
-    uint64_t acc2[TM][TN / 2];
+    uint64_t acc2[TM][TP2];
+    float acc1[TM];  // FLEX with an odd TN: the last tile of a thread
 #pragma unroll
-    for (int i = 0; i < TM; ++i)
+    for (int i = 0; i < TM; ++i) {
+        acc1[i] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < TN / 2; ++j) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
+        for (int j = 0; j < TP2; ++j) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
+    }
 
     bool ok = true;
     for (int kt = 0; kt < n_slabs; ++kt) {
@@ -614,19 +621,25 @@ __global__ void __launch_bounds__(THREADS, 2)
                 const float4 v = *reinterpret_cast<const float4 *>(&As[k][g * 64 + ty * 4]);
                 a[g * 4 + 0] = v.x; a[g * 4 + 1] = v.y; a[g * 4 + 2] = v.z; a[g * 4 + 3] = v.w;
             }
+            if constexpr (FLEX == 0) {
 #pragma unroll
-            for (int g = 0; g < TN / 4; ++g) {
-                const float4 v = *reinterpret_cast<const float4 *>(&Bs[k][g * 64 + tx * 4]);
-                b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
+                for (int g = 0; g < TN / 4; ++g) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&Bs[k][g * 64 + tx * 4]);
+                    b[g * 4 + 0] = v.x; b[g * 4 + 1] = v.y; b[g * 4 + 2] = v.z; b[g * 4 + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < TN; ++j) b[j] = Bs[k][tx + 16 * j];
             }
-            uint64_t bp[TN / 2];
+            uint64_t bp[TP2];
 #pragma unroll
-            for (int j = 0; j < TN / 2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
+            for (int j = 0; j < TP2; ++j) bp[j] = pack2(b[2 * j], b[2 * j + 1]);
 #pragma unroll
             for (int i = 0; i < TM; ++i) {
                 const uint64_t ap = pack2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < TN / 2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+                for (int j = 0; j < TP2; ++j) acc2[i][j] = fma2(ap, bp[j], acc2[i][j]);
+                if constexpr (TN % 2 == 1) acc1[i] = __fmaf_rn(a[i], b[TN - 1], acc1[i]);
             }
         }
         __syncwarp();
@@ -638,14 +651,26 @@ __global__ void __launch_bounds__(THREADS, 2)
         for (int i = 0; i < TM; ++i) {
             const int r = oc0 + (i / 4) * 64 + ty * 4 + (i % 4);
             if (r >= oc) continue;
+            if constexpr (FLEX == 0) {
 #pragma unroll
-            for (int g = 0; g < TN / 4; ++g) {
-                const int c = t0 + g * 64 + tx * 4;
-                if (c < tp) {  // tp is a multiple of 8, so a float4 never straddles the end
-                    float4 v;
-                    unpack2(acc2[i][g * 2 + 0], v.x, v.y);
-                    unpack2(acc2[i][g * 2 + 1], v.z, v.w);
-                    *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) = v;
+                for (int g = 0; g < TN / 4; ++g) {
+                    const int c = t0 + g * 64 + tx * 4;
+                    if (c < tp) {  // tp is a multiple of 8, so a float4 never straddles the end
+                        float4 v;
+                        unpack2(acc2[i][g * 2 + 0], v.x, v.y);
+                        unpack2(acc2[i][g * 2 + 1], v.z, v.w);
+                        *reinterpret_cast<float4 *>(Mp + (size_t)r * tp + c) = v;
+                    }
+                }
+            } else {
+                float res[TN];
+#pragma unroll
+                for (int j = 0; j < TP2; ++j) unpack2(acc2[i][j], res[2 * j], res[2 * j + 1]);
+                if constexpr (TN % 2 == 1) res[TN - 1] = acc1[i];
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    const int c = t0 + tx + 16 * j;
+                    if (c < tp) Mp[(size_t)r * tp + c] = res[j];
                 }
             }
         }
@@ -665,13 +690,13 @@ static bool tma_blocked_enabled() {
     return state == 1;
 }
 
-template <int BM, int BN, int MAP, int BKT = 16, int NST = 5>
+template <int BM, int BN, int MAP, int BKT = 16, int NST = 5, int FLEX = 0>
 int launch_blocked_tma(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
     CUtensorMap tmU, tmV;
     FC_PROPAGATE(make_map_u_rowmajor(&tmU, d_U, g.ocp, g.icp, BM, BKT));
     FC_PROPAGATE(make_map_v_rowmajor(&tmV, d_V, g.tp, g.icp, BN, BKT));
     const size_t smem = 128 + 128 + (size_t)NST * BKT * (BM + BN) * sizeof(float);
-    auto kern = wino_gemm_ffma_tma_kernel<BM, BN, MAP, BKT, NST>;
+    auto kern = wino_gemm_ffma_tma_kernel<BM, BN, MAP, BKT, NST, FLEX>;
     FC_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)ceil_div(g.tp, BN), (unsigned)ceil_div(g.oc, BM), 64), block(THREADS);
     FC_CHECK_CUDA((launch_pdl(kern, grid, block, smem, ctx->stream, tmU, tmV, d_M, ctx->d_status, g.oc, g.tp, g.icp)));
@@ -768,6 +793,11 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
         const int widths[3] = {112, 96, 80};
         for (int bn : widths)
             if (padded(bn) * 1.25 < best) { best = padded(bn) * 1.25; flex = bn; }
+    }
+    if (flex && ctx->d_status != nullptr && tma_blocked_enabled() && g.ocp >= 128 && g.tp >= flex) {
+        if (flex == 80) return launch_blocked_tma<128, 80, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
+        if (flex == 96) return launch_blocked_tma<128, 96, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
+        if (flex == 112) return launch_blocked_tma<128, 112, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
     }
     if (flex == 80) return launch_flex<5>(ctx, d_U, d_V, d_M, g);
     if (flex == 96) return launch_flex<6>(ctx, d_U, d_V, d_M, g);

@@ -309,11 +309,14 @@ __global__ void __launch_bounds__(256) input_transform_rowmajor_kernel(const flo
 // about half the instructions per item.  Lanes run along consecutive tiles, warps along channels.
 constexpr int ITW_WARPS = 4;
 
+template <bool ALONG_TILES>
 __global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_kernel(
     const float *__restrict__ in, float *__restrict__ V, int n_tiles, int ic, int icp, int tp, int ih, int iw, int pad,
     int th, int tw) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tile = blockIdx.x * 32 + lane, c = blockIdx.y * ITW_WARPS + warp;
+    // the warps of a block: ITW_WARPS channels of the same 32 tiles, or one channel of 32 * ITW_WARPS consecutive tiles
+    const int tile = ALONG_TILES ? blockIdx.x * 32 * ITW_WARPS + threadIdx.x : blockIdx.x * 32 + lane;
+    const int c = ALONG_TILES ? blockIdx.y : blockIdx.y * ITW_WARPS + warp;
     pdl_trigger();
     pdl_wait();  // the input may be the previous layer's output; V may still be read by an earlier GEMM
     if (c >= icp || tile >= tp) return;
@@ -370,9 +373,18 @@ static int it_wide_min_tiles() {
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
     dim3 block(256);
     if (g.tiles >= it_wide_min_tiles()) {
-        dim3 wblock(32 * ITW_WARPS), grid((unsigned)ceil_div(g.tp, 32), (unsigned)ceil_div(g.icp, ITW_WARPS));
-        FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles, g.ic,
-                                 g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+        // a block of four warps along the tile axis writes runs of 512 bytes per (position, channel) instead of 128:
+        // measured 1-4 % faster at 64 images
+        dim3 wblock(32 * ITW_WARPS);
+        if (g.tiles >= 32 * ITW_WARPS) {
+            dim3 grid((unsigned)ceil_div(g.tp, 32 * ITW_WARPS), (unsigned)g.icp);
+            FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel<true>, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles,
+                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+        } else {
+            dim3 grid((unsigned)ceil_div(g.tp, 32), (unsigned)ceil_div(g.icp, ITW_WARPS));
+            FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel<false>, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles,
+                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+        }
         return FC_OK;
     }
     if (g.tiles > 16) {
@@ -534,6 +546,7 @@ __global__ void __launch_bounds__(256) output_transform_scatter_publish_kernel(c
 // run along the output rows.  No block-wide synchronisation.
 constexpr int OTW_WARPS = 4;
 
+template <bool ALONG_TILES>
 __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(const float *__restrict__ M,
                                                                               float *__restrict__ out, int n_tiles,
                                                                               int oc, int tp, int oh, int ow, int th,
@@ -541,8 +554,9 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
     constexpr int ROW = 32 * 6 + 2;
     __shared__ float stage[OTW_WARPS][6][ROW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t_base = blockIdx.x * 32;
-    const int t = t_base + lane, k = blockIdx.y * OTW_WARPS + warp;
+    // the warps of a block: OTW_WARPS channels of the same 32 tiles, or one channel of 32 * OTW_WARPS consecutive tiles
+    const int t_base = ALONG_TILES ? (blockIdx.x * OTW_WARPS + warp) * 32 : blockIdx.x * 32;
+    const int t = t_base + lane, k = ALONG_TILES ? blockIdx.y : blockIdx.y * OTW_WARPS + warp;
     const size_t plane = (size_t)oc * tp;
     pdl_trigger();
     pdl_wait();  // M comes from the GEMM launched just before
@@ -798,9 +812,16 @@ static int wide_min_tiles() {
 int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, const WinoGeom &g, const Epilogue &ep) {
     dim3 block(256);
     if (g.tiles >= wide_min_tiles()) {
-        dim3 wblock(32 * OTW_WARPS), grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
-        FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp,
-                                 g.oh, g.ow, g.th, g.tw, ep));
+        dim3 wblock(32 * OTW_WARPS);
+        if (g.tiles >= 32 * OTW_WARPS) {  // four warps along the tile axis: reads of 512 bytes per position (1 % faster)
+            dim3 grid((unsigned)ceil_div(g.tiles, 32 * OTW_WARPS), (unsigned)g.oc);
+            FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel<true>, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc,
+                                     g.tp, g.oh, g.ow, g.th, g.tw, ep));
+        } else {
+            dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
+            FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel<false>, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc,
+                                     g.tp, g.oh, g.ow, g.th, g.tw, ep));
+        }
         return FC_OK;
     }
     if (g.tiles > 16) {
