@@ -18,12 +18,14 @@ group, barrier and max-over-ranks all go through the library's communicator (fc_
 from __future__ import annotations
 
 import argparse
+import atexit
 import ctypes as C
 import json
 import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 from pathlib import Path
@@ -208,7 +210,7 @@ class Stack:
     """The layer stack planned for `n` images on one context, with device-resident inputs and (optionally) pinned
     host buffers for the end-to-end path."""
 
-    def __init__(self, fc, ctx, layers, n, first_image, mode, algo, chain=False, host=True):
+    def __init__(self, fc, ctx, layers, n, first_image, mode, algo, chain=False, host=True, tune=False):
         from fastconv_b200 import _lib, synth
         self.fc, self.ctx, self.lib, self._lib = fc, ctx, fc.load(), _lib
         self.layers, self.n = layers, n
@@ -224,6 +226,8 @@ class Stack:
             d_in, d_out = C.c_void_p(), C.c_void_p()
             _lib.check(self.lib.fc_conv_device_buffers(hdl, C.byref(d_in), C.byref(d_out)), "fc_conv_device_buffers")
             ctx.upload(x, d_in.value)
+            if tune:  # Tuning(): the layer's kernel configuration by measured device time, before anything is timed
+                _lib.check(self.lib.fc_conv_tune(hdl, 3, 0), "fc_conv_tune")
             if host:
                 px = ctx.pinned(x.shape)
                 px[...] = x
@@ -481,6 +485,8 @@ def main():
                          "tensor-core kernel for every layer (tf32 modes)")
     ap.add_argument("--repeats", type=int, default=25, help="further timed regions of K steps, for median/min/max")
     ap.add_argument("--ref-images", type=int, default=4, help="--impl reference: images of the batch run per step")
+    ap.add_argument("--no-tuning", dest="tuning", action="store_false",
+                    help="keep the launchers' heuristics instead of running Tuning() on every layer first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-subrecords", action="store_true", help="skip the TF32 and batch-1 sub-records")
     args = ap.parse_args()
@@ -505,6 +511,13 @@ def main():
     import fastconv_b200 as fc
     from fastconv_b200 import parallel
 
+    if args.tuning and "FASTCONV_TUNING_LOG" not in os.environ:
+        # a log of this run only: an entry left by another GPU, clock state or library build must not decide a layer
+        fd, log_path = tempfile.mkstemp(prefix=f"fastconv_tuning_r{rank}_", suffix=".log")
+        os.close(fd)
+        os.environ["FASTCONV_TUNING_LOG"] = log_path
+        atexit.register(lambda: os.path.exists(log_path) and os.remove(log_path))
+
     n0, n1 = shard_range(args.batch, world, rank)
     n = n1 - n0
     if n < 1:
@@ -528,7 +541,7 @@ def main():
     sampler.wait_first()
 
     # ---- `value`: device-resident throughput of the whole job --------------------------------------------
-    stack = Stack(fc, ctx, layers, n, n0, args.mode, args.algo, chain=args.chain)
+    stack = Stack(fc, ctx, layers, n, n0, args.mode, args.algo, chain=args.chain, tune=args.tuning)
     for _ in range(args.warmup):
         stack.step_device()
     sampler.mark()
@@ -615,6 +628,8 @@ def main():
                        "math_mode": args.mode,
                        "launch": "all layers of a step replayed as one CUDA graph",
                        "chain": bool(args.chain),
+                       "tuning": ("Tuning() per layer before the timed region (block shapes by measured device time, the "
+                                  "reference's -tn tuning)" if args.tuning else "no_tuning (launcher heuristics)"),
                        "parallelism": f"images sharded over {world} GPU(s), no collective in the data path; barrier and "
                                       f"max-over-ranks through the library's communicator",
                        "l2": f"inputs larger than L2: the stack touches {stack.footprint / 1e6:.0f} MB per step and GPU"},
@@ -636,7 +651,7 @@ def main():
     subs = {}
     if not args.no_subrecords and args.mode == "fp32" and not args.chain:
         for name, mode, algo in (("tf32", "tf32", "auto"), ("3xtf32", "3xtf32", "winograd")):
-            s = Stack(fc, ctx, layers, n, n0, mode, algo, host=False)
+            s = Stack(fc, ctx, layers, n, n0, mode, algo, host=False, tune=args.tuning)
             first, many = measure_stack(comm, ctx, s, args, 4)
             rows, _ = s.per_layer(max(3, args.steps), hbm_peak, peak_tflops)
             subs[name] = {"math_mode": mode, "algorithm": algo, "value": round(total_flops / first / 1e6, 1),
@@ -645,7 +660,7 @@ def main():
                           "layers": [{k: r[k] for k in ("layer", "algo", "math", "ms", "frac_of_roofline", "bound")} for r in rows]}
             s.close()
         if world == 1:
-            s = Stack(fc, ctx, layers, 1, 0, "fp32", "winograd")
+            s = Stack(fc, ctx, layers, 1, 0, "fp32", "winograd", tune=args.tuning)
             first, many = measure_stack(comm, ctx, s, args, 24)
             e2e1 = measure_e2e(comm, ctx, s, args.steps)
             rows, agg1 = s.per_layer(max(3, args.steps), hbm_peak, peak_tflops)
