@@ -1171,6 +1171,7 @@ static void enumerate_candidates(const fc_conv *c, int algo, std::vector<TuneCan
                            (algo == FC_ALGO_IM2COL && c->mode == FC_MATH_3XTF32 &&
                             (long long)gd.ic * gd.kh * gd.kw > IGEMM_3XTF32_MAX_K);
     if (ffma_only) {
+        if (algo == FC_ALGO_WINOGRAD) push(0, 0, 0, 0);  // the launcher's own choice (it alone mixes block widths in one launch)
         if (algo == FC_ALGO_WINOGRAD && (c->pass_imgs ? c->pass_geom : c->geom).tiles <= 32) push(0, 0, 1, 0);
         if (algo == FC_ALGO_IM2COL) {  // table-driven kernel in its eight block shapes
             const int small_tiles[5][2] = {{64, 64}, {32, 64}, {32, 32}, {16, 32}, {8, 32}};

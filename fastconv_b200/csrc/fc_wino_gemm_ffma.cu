@@ -538,10 +538,9 @@ int make_map_v_rowmajor(CUtensorMap *map, const float *base, int tp, int icp, in
 // ---------------------------------------------------------------------------------------------
 // FLEX = 0: a thread owns TM channels x TN tiles read as 128-bit rows (BN a multiple of 64).  FLEX = 1: BN = 80, 96 or
 // 112 and a thread's TN = BN / 16 tiles are 16 apart, read one float at a time (wino_gemm_ffma_flex_kernel's form).
-template <int BM, int BN, int MAP, int BK = 16, int TB_STAGES = 5, int FLEX = 0>
-__global__ void __launch_bounds__(THREADS, 2)
-    wino_gemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
-                              float *__restrict__ M, int *status, int oc, int tp, int icp) {
+template <int BM, int BN, int MAP, int BK, int TB_STAGES, int FLEX>
+__device__ __forceinline__ void tma_block_body(const CUtensorMap *tmU_p, const CUtensorMap *tmV_p, float *__restrict__ M,
+                                               int *status, int oc, int tp, int icp, int oc0, int t0, int p) {
     using namespace tc;
     constexpr int TM = BM / 16, TN = BN / 16, TP2 = TN / 2;
     static_assert(FLEX == 1 || (TM % 4 == 0 && TN % 4 == 0), "block shape");
@@ -556,7 +555,6 @@ __global__ void __launch_bounds__(THREADS, 2)
     auto bar_full = [&](int s) { return smem_u32(bars + s); };
     auto bar_empty = [&](int s) { return smem_u32(bars + TB_STAGES + s); };
 
-    const int p = blockIdx.z, oc0 = blockIdx.y * BM, t0 = blockIdx.x * BN;
     const int tid = threadIdx.x, lane = tid & 31;
     const int tx = MAP == 0 ? tid % 16 : (tid / 32 % 2) * 8 + tid % 8;
     const int ty = MAP == 0 ? tid / 16 : (tid / 64) * 4 + tid % 32 / 8;
@@ -577,10 +575,10 @@ __global__ void __launch_bounds__(THREADS, 2)
         const int head = n_slabs < TB_STAGES - 1 ? n_slabs : TB_STAGES - 1;
         for (int kt = 0; kt < head; ++kt) {
             mbar_expect_tx(bar_full(kt), STAGE);
-            tma_load_3d(ring + kt * STAGE, &tmU, bar_full(kt), oc0, kt * BK, p);
+            tma_load_3d(ring + kt * STAGE, tmU_p, bar_full(kt), oc0, kt * BK, p);
         }
         pdl_wait();
-        for (int kt = 0; kt < head; ++kt) tma_load_3d(ring + kt * STAGE + A_STAGE, &tmV, bar_full(kt), t0, kt * BK, p);
+        for (int kt = 0; kt < head; ++kt) tma_load_3d(ring + kt * STAGE + A_STAGE, tmV_p, bar_full(kt), t0, kt * BK, p);
     }
 
     uint64_t acc2[TM][TP2];
@@ -603,8 +601,8 @@ __global__ void __launch_bounds__(THREADS, 2)
                 if (kt >= 2) free_stage = mbar_wait(bar_empty(sn), (uint32_t)((kt - 2) / TB_STAGES) & 1u, abort_flag, status);
                 if (free_stage) {
                     mbar_expect_tx(bar_full(sn), STAGE);
-                    tma_load_3d(ring + sn * STAGE, &tmU, bar_full(sn), oc0, kn * BK, p);
-                    tma_load_3d(ring + sn * STAGE + A_STAGE, &tmV, bar_full(sn), t0, kn * BK, p);
+                    tma_load_3d(ring + sn * STAGE, tmU_p, bar_full(sn), oc0, kn * BK, p);
+                    tma_load_3d(ring + sn * STAGE + A_STAGE, tmV_p, bar_full(sn), t0, kn * BK, p);
                 }
             }
         }
@@ -680,11 +678,46 @@ __global__ void __launch_bounds__(THREADS, 2)
     }
 }
 
+template <int BM, int BN, int MAP, int BK = 16, int TB_STAGES = 5, int FLEX = 0>
+__global__ void __launch_bounds__(THREADS, 2)
+    wino_gemm_ffma_tma_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
+                              float *__restrict__ M, int *status, int oc, int tp, int icp) {
+    tma_block_body<BM, BN, MAP, BK, TB_STAGES, FLEX>(&tmU, &tmV, M, status, oc, tp, icp, blockIdx.y * BM, blockIdx.x * BN,
+                                                     blockIdx.z);
+}
+
+// Tile counts that are not a multiple of 128: the first n_main block columns are 128 tiles wide, the last one only as
+// wide as the rest needs (32 ... 112 tiles), so that almost nothing but real tiles is multiplied -- 200 tiles (28x28 maps
+// of 8 images) are 128 + 80 instead of 2 x 128, 576 (14x14 of 64 images) are 4 x 128 + 64.  One launch, two block shapes:
+// the branch is uniform per block.
+template <int TAIL_BN, int TAIL_FLEX>
+__global__ void __launch_bounds__(THREADS, 2)
+    wino_gemm_ffma_tma_mixed_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
+                                    const __grid_constant__ CUtensorMap tmVtail, float *__restrict__ M, int *status, int oc,
+                                    int tp, int icp, int n_main) {
+    if ((int)blockIdx.x < n_main)
+        tma_block_body<128, 128, 1, 32, 3, 0>(&tmU, &tmV, M, status, oc, tp, icp, blockIdx.y * 128, blockIdx.x * 128,
+                                              blockIdx.z);
+    else
+        tma_block_body<128, TAIL_BN, 0, 32, 3, TAIL_FLEX>(&tmU, &tmVtail, M, status, oc, tp, icp, blockIdx.y * 128,
+                                                          n_main * 128, blockIdx.z);
+}
+
 // $FASTCONV_FFMA_TMA=0 keeps the blocked kernel on per-thread asynchronous copies (for comparisons).
 static bool tma_blocked_enabled() {
     static int state = -1;
     if (state < 0) {
         const char *e = getenv("FASTCONV_FFMA_TMA");
+        state = (e && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
+// $FASTCONV_FFMA_MIXED=0 keeps every block column 128 tiles wide (for comparisons).
+static bool mixed_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char *e = getenv("FASTCONV_FFMA_MIXED");
         state = (e && e[0] == '0') ? 0 : 1;
     }
     return state == 1;
@@ -702,6 +735,23 @@ int launch_blocked_tma(fc_context *ctx, const float *d_U, const float *d_V, floa
     FC_CHECK_CUDA((launch_pdl(kern, grid, block, smem, ctx->stream, tmU, tmV, d_M, ctx->d_status, g.oc, g.tp, g.icp)));
     return FC_OK;
 }
+
+template <int TAIL_BN, int TAIL_FLEX>
+int launch_blocked_tma_mixed(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
+    CUtensorMap tmU, tmV, tmVtail;
+    FC_PROPAGATE(make_map_u_rowmajor(&tmU, d_U, g.ocp, g.icp, 128, 32));
+    FC_PROPAGATE(make_map_v_rowmajor(&tmV, d_V, g.tp, g.icp, 128, 32));
+    FC_PROPAGATE(make_map_v_rowmajor(&tmVtail, d_V, g.tp, g.icp, TAIL_BN, 32));
+    const size_t smem = 128 + 128 + (size_t)3 * 32 * (128 + 128) * sizeof(float);
+    auto kern = wino_gemm_ffma_tma_mixed_kernel<TAIL_BN, TAIL_FLEX>;
+    FC_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int n_main = g.tp / 128;
+    dim3 grid((unsigned)n_main + 1, (unsigned)ceil_div(g.oc, 128), 64), block(THREADS);
+    FC_CHECK_CUDA((launch_pdl(kern, grid, block, smem, ctx->stream, tmU, tmV, tmVtail, d_M, ctx->d_status, g.oc, g.tp, g.icp,
+                              n_main)));
+    return FC_OK;
+}
+
 
 template <int TN>
 int launch_skinny(fc_context *ctx, const float *d_U, const float *d_V, float *d_M, const WinoGeom &g) {
@@ -835,7 +885,17 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
     const bool tma = ctx->d_status != nullptr && tma_blocked_enabled();
     const bool wide256 = !wide_m && wide_n && (named ? cfg->bn == 256 : ceil_div(g.tp, 256) * ceil_div(g.oc, 64) * 64 >= (size_t)8 * 148);
     if (tma) {
-        if (wide_m && wide_n && g.ocp >= 128 && g.tp >= 128) return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
+        if (wide_m && wide_n && g.ocp >= 128 && g.tp >= 128) {
+            const int tail = g.tp % 128;  // a multiple of 8
+            if (tail == 0 || named || !mixed_enabled()) return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 32) return launch_blocked_tma_mixed<32, 1>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 48) return launch_blocked_tma_mixed<48, 1>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 64) return launch_blocked_tma_mixed<64, 0>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 80) return launch_blocked_tma_mixed<80, 1>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 96) return launch_blocked_tma_mixed<96, 1>(ctx, d_U, d_V, d_M, g);
+            if (tail <= 112) return launch_blocked_tma_mixed<112, 1>(ctx, d_U, d_V, d_M, g);
+            return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
+        }
         if (wide_m && !wide_n && g.ocp >= 128 && g.tp >= 64) return launch_blocked_tma<128, 64, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
         if (wide256 && g.ocp >= 64 && g.tp >= 256) return launch_blocked_tma<64, 256, 0, 16, 5>(ctx, d_U, d_V, d_M, g);
         if (!wide_m && wide_n && !wide256 && g.ocp >= 64 && g.tp >= 128) return launch_blocked_tma<64, 128, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
