@@ -844,7 +844,7 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
         for (int bn : widths)
             if (padded(bn) * 1.25 < best) { best = padded(bn) * 1.25; flex = bn; }
     }
-    if (flex && ctx->d_status != nullptr && tma_blocked_enabled() && g.ocp >= 128 && g.tp >= flex) {
+    if (flex && ctx->d_status != nullptr && tma_blocked_enabled()) {
         if (flex == 80) return launch_blocked_tma<128, 80, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
         if (flex == 96) return launch_blocked_tma<128, 96, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
         if (flex == 112) return launch_blocked_tma<128, 112, 0, 16, 5, 1>(ctx, d_U, d_V, d_M, g);
@@ -878,16 +878,16 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
     // block (measured 7 % faster than 64 x 128 on 64 -> 64 channels at 224 x 224, 64 images), once there are blocks
     // enough for several waves
     const bool named = cfg && cfg->bn;
-    // The TMA-fed kernel wherever a context stands behind the call (its waits report into the context's status word)
-    // and the boxes are no larger than the tensor: at least one full block of channels and of tiles.  Slabs of 32
+    // The TMA-fed kernel wherever a context stands behind the call (its waits report into the context's status word); a
+    // box may be wider than the tensor, what lies outside reads as zero.  Slabs of 32
     // channels in a ring of 3 measured 1 % faster than 16 x 5 or 16 x 6 on the 128 x 128 block; the 64 x 256 block keeps
     // 16 x 5 so that two CTAs fit an SM.
     const bool tma = ctx->d_status != nullptr && tma_blocked_enabled();
     const bool wide256 = !wide_m && wide_n && (named ? cfg->bn == 256 : ceil_div(g.tp, 256) * ceil_div(g.oc, 64) * 64 >= (size_t)8 * 148);
     if (tma) {
-        if (wide_m && wide_n && g.ocp >= 128 && g.tp >= 128) {
+        if (wide_m && wide_n) {
             const int tail = g.tp % 128;  // a multiple of 8
-            if (tail == 0 || named || !mixed_enabled()) return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
+            if (tail == 0 || g.tp < 128 || named || !mixed_enabled()) return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
             if (tail <= 32) return launch_blocked_tma_mixed<32, 1>(ctx, d_U, d_V, d_M, g);
             if (tail <= 48) return launch_blocked_tma_mixed<48, 1>(ctx, d_U, d_V, d_M, g);
             if (tail <= 64) return launch_blocked_tma_mixed<64, 0>(ctx, d_U, d_V, d_M, g);
@@ -896,10 +896,10 @@ int launch_wino_gemm_ffma(fc_context *ctx, const float *d_U, const float *d_V, f
             if (tail <= 112) return launch_blocked_tma_mixed<112, 1>(ctx, d_U, d_V, d_M, g);
             return launch_blocked_tma<128, 128, 1, 32, 3>(ctx, d_U, d_V, d_M, g);
         }
-        if (wide_m && !wide_n && g.ocp >= 128 && g.tp >= 64) return launch_blocked_tma<128, 64, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
-        if (wide256 && g.ocp >= 64 && g.tp >= 256) return launch_blocked_tma<64, 256, 0, 16, 5>(ctx, d_U, d_V, d_M, g);
-        if (!wide_m && wide_n && !wide256 && g.ocp >= 64 && g.tp >= 128) return launch_blocked_tma<64, 128, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
-        if (!wide_m && !wide_n && g.ocp >= 64 && g.tp >= 64) return launch_blocked_tma<64, 64, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
+        if (wide_m && !wide_n) return launch_blocked_tma<128, 64, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
+        if (wide256) return launch_blocked_tma<64, 256, 0, 16, 5>(ctx, d_U, d_V, d_M, g);
+        if (!wide_m && wide_n && !wide256) return launch_blocked_tma<64, 128, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
+        if (!wide_m && !wide_n) return launch_blocked_tma<64, 64, 0, 32, 3>(ctx, d_U, d_V, d_M, g);
     }
     if (wide_m && wide_n) return launch_blocked<128, 128, 1>(ctx, d_U, d_V, d_M, g);
     if (wide_m) return launch_blocked<128, 64>(ctx, d_U, d_V, d_M, g);
