@@ -7,11 +7,13 @@
 // sums, no reordering -- that is what makes the layer bit-identical to the reference.
 //
 // Operands arrive in the row-major layouts U[p][icp][ocp] / V[p][icp][tp] (row index contiguous), so a
-// BK x BM slab of U and a BK x BN slab of V are sets of contiguous runs: they go to shared memory as
-// [k][row] with 16-byte asynchronous copies (cp.async, zero-filled past the edges) through a 4-stage
-// ring, and the inner product reads 128-bit rows without bank conflicts.  No register staging, no
-// transposition, two CTAs per SM.  The FMAs of two neighbouring tiles are issued as one packed instruction
-// (fma.rn.f32x2): each half rounds like a scalar FMA, so the chains are unchanged.
+// BK x BM slab of U and a BK x BN slab of V are sets of contiguous runs: they go to shared memory as [k][row]
+// and the inner product reads 128-bit rows without bank conflicts.  No register staging, no transposition, two
+// CTAs per SM.  Behind a context the slabs are TMA boxes in a ring of mbarrier-guarded stages
+// (wino_gemm_ffma_tma_kernel, further down); callers without one get the same blocks on 16-byte asynchronous
+// copies (cp.async, zero-filled past the edges) through a 4-stage ring with a block-wide barrier per slab.  The
+// FMAs of two neighbouring tiles are issued as one packed instruction (fma.rn.f32x2): each half rounds like a
+// scalar FMA, so the chains are unchanged.
 #include <cstdlib>
 
 #include "fc_tc_common.cuh"
