@@ -403,3 +403,43 @@ def test_few_input_channels_same_bits_as_three_kernels(ctx, monkeypatch):
         outs.append(r.stdout.split()[-2:])  # the layer's own "Algorithm:" line comes first
     assert outs[0][0] == "2" and outs[1][0] == "3"
     assert outs[0][1] == outs[1][1]
+
+
+# th, tw: 128 tiles and a rest of 8, 32, 40, 48, 56, 64, 72, 80, 96, 104, 112, 120 -- every width of the last block column
+OFF_WIDTH = [(8, 17), (10, 16), (12, 14), (11, 16), (8, 23), (12, 16), (10, 20), (13, 16), (14, 16), (8, 29), (15, 16),
+             (8, 31)]
+
+
+@pytest.mark.parametrize("th,tw", OFF_WIDTH)
+def test_tile_counts_off_the_block_width_are_bit_exact(ctx, oracle, th, tw):
+    """One launch with 128-wide block columns and a narrower last one; 130 output channels make the second row of
+    blocks nearly empty, 40 input channels end the reduction inside a slab."""
+    x = synth.conv_input(1, 40, 6 * th, 6 * tw - 2, 151)
+    w = synth.conv_weights(130, 40, 3, 3, 152)
+    assert np.array_equal(run_layer(ctx, x, w, 1), oracle.wino_forward(x, w, 1))
+
+
+def test_copy_fed_kernels_give_the_bits_of_the_tma_fed_ones():
+    """The blocked TensorGEMM on per-thread asynchronous copies (what callers without a context get) against the
+    TMA-fed default, and the uniform launch against the one with a narrower last column: same bits."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import hashlib, numpy as np, fastconv_b200 as fc
+        from fastconv_b200 import synth
+        out = []
+        with fc.Context(0, arena_bytes=2 << 30) as ctx:
+            for n, ic, oc, h, w in [(2, 40, 130, 48, 100), (1, 64, 64, 56, 56), (4, 96, 200, 14, 14), (1, 24, 72, 112, 112)]:
+                x = synth.conv_input(n, ic, h, w, 161); k = synth.conv_weights(oc, ic, 3, 3, 162)
+                l = fc.ConvWinoF63ZCLayer(x, k, None, None, ic, h, w, oc, batch=n, ctx=ctx)
+                l.Init(); l.Forward()
+                out.append(hashlib.sha256(l.output_data.tobytes()).hexdigest()); l.release()
+        print("HASHES", " ".join(out))
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    got = []
+    for extra in ({}, {"FASTCONV_FFMA_TMA": "0"}, {"FASTCONV_FFMA_MIXED": "0"}):
+        r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, PYTHONPATH=root, **extra), capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        got.append([line for line in r.stdout.splitlines() if line.startswith("HASHES")][0])
+    assert got[0] == got[1] == got[2]
