@@ -360,19 +360,23 @@ __global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_
         for (int y = 0; y < 8; ++y) dst[(size_t)(x * 8 + y) * plane] = r[y][x];  // p = x*8 + y
 }
 
-// tile count from which the throughput-oriented input transform is taken ($FASTCONV_IT_WIDE_MIN overrides it)
-static int it_wide_min_tiles() {
+// Which layers take the throughput-oriented input transform: one thread per item needs many items to fill the machine
+// (8 images, whole VGG-16 stack: 1.700 ms with it from 64 tiles on, 1.683 ms from 1024 tiles on; 64 images, 576 tiles x
+// 512 channels: 0.035 against 0.037 ms in its favour).  $FASTCONV_IT_WIDE_MIN=<tiles> replaces the rule by a plain
+// threshold.
+static bool it_wide(const WinoGeom &g) {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("FASTCONV_IT_WIDE_MIN");
-        v = e && atoi(e) > 0 ? atoi(e) : 64;
+        v = e && atoi(e) > 0 ? atoi(e) : 0;
     }
-    return v;
+    if (v > 0) return g.tiles >= v;
+    return g.tiles >= 1024 || (g.tiles >= 512 && (long long)g.tiles * g.icp >= 256 * 1024);
 }
 
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
     dim3 block(256);
-    if (g.tiles >= it_wide_min_tiles()) {
+    if (it_wide(g)) {
         // a block of four warps along the tile axis writes runs of 512 bytes per (position, channel) instead of 128:
         // measured 1-4 % faster at 64 images
         dim3 wblock(32 * ITW_WARPS);
