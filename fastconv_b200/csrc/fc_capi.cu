@@ -757,6 +757,16 @@ int fc_resolve_plan(const fc_conv_desc *desc, int algo, int mode, int sm_count, 
             if (wino_geom(desc, &g) == FC_OK && wino_gemm_tc_rows_are_channels(g)) mode = FC_MATH_TF32_U16;
         }
     }
+    // The split arithmetic stands for rel-L2 <= 1e-5, which the fp32 kernels meet with room to spare (they are
+    // bit-identical to the reference).  With at most 64 input channels the reduction is too short to pay for the
+    // tensor-core kernel's operand splitting: on every such layer measured (1, 8 and 64 images; 3 -> 64 @224 0.40
+    // against 1.75 ms, 64 -> 64 @224 1.92 against 2.14 ms, 64 -> 128 @112 0.77 against 0.89 ms at 64 images) the FFMA
+    // path is the faster one, so the accuracy mode runs it there.  $FASTCONV_3XTF32_MIN_IC moves the border (0: never).
+    if (mode == FC_MATH_3XTF32 && algo == FC_ALGO_WINOGRAD) {
+        const char *e = getenv("FASTCONV_3XTF32_MIN_IC");
+        const int min_ic = e ? atoi(e) : 65;
+        if (desc->ic < min_ic) mode = FC_MATH_FP32_MIRRORED;
+    }
     // the direct tensor-core kernel is a TF32 kernel for ungrouped layers of stride 1 or 2; anything else asked for as
     // "direct" runs as the implicit GEMM (the reference's own case for the name is empty)
     if (algo == FC_ALGO_DIRECT && !(mode == FC_MATH_TF32 && direct_tc_eligible(*desc))) algo = FC_ALGO_IM2COL;

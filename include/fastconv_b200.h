@@ -53,7 +53,10 @@ typedef enum fc_algorithm {
 typedef enum fc_math_mode {
     FC_MATH_FP32_MIRRORED = 0, /* FFMA, one fused multiply-add per reduction step in ascending order:
                                   bit-identical to the reference's accumulation chain            */
-    FC_MATH_3XTF32 = 1,        /* tcgen05 tensor cores, hi/lo TF32 split, fp32 accumulate         */
+    FC_MATH_3XTF32 = 1,        /* tcgen05 tensor cores, hi/lo TF32 split, fp32 accumulate: rel-L2 <= 1e-5.  The stage
+                                  entry points run exactly that; a planned Winograd layer of at most 64 input channels
+                                  runs the fp32 kernels instead (exact, and faster on so short a reduction;
+                                  $FASTCONV_3XTF32_MIN_IC moves the border), fc_conv_math_mode says which       */
     FC_MATH_TF32 = 2,          /* tcgen05 tensor cores, one TF32 pass per reduction step.  The stage entry points
                                   (fc_wino_*, fc_igemm_*) run exactly that.  For a planned layer (fc_conv_create) the
                                   mode stands for its tolerance, rel-L2 <= 3e-3 against the fp32 result: one TF32 pass

@@ -443,3 +443,21 @@ def test_copy_fed_kernels_give_the_bits_of_the_tma_fed_ones():
         assert r.returncode == 0, r.stderr[-2000:]
         got.append([line for line in r.stdout.splitlines() if line.startswith("HASHES")][0])
     assert got[0] == got[1] == got[2]
+
+
+def test_accuracy_mode_on_a_short_reduction_is_the_fp32_path(ctx, oracle, monkeypatch):
+    """Library default (the variable the test session sets is removed): 64 input channels in 3xTF32 run the fp32
+    kernels -- the reported arithmetic says so and the result is the oracle's, bit for bit."""
+    monkeypatch.delenv("FASTCONV_3XTF32_MIN_IC")
+    lib = fc.load()
+    x = synth.conv_input(2, 64, 30, 30, 171)
+    w = synth.conv_weights(48, 64, 3, 3, 172)
+    d = fc.make_desc(2, 64, 30, 30, 48)
+    h, m = C.c_void_p(), C.c_int()
+    fc._lib.check(lib.fc_conv_create(ctx.handle, C.byref(d), fc.ALGO_WINOGRAD, 1, C.c_void_p(w.ctypes.data), C.byref(h)), "create")
+    lib.fc_conv_math_mode(h, C.byref(m))
+    assert m.value == 0
+    y = np.empty((2, 48, 30, 30), np.float32)
+    fc._lib.check(lib.fc_conv_forward_host(h, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)), "forward")
+    assert np.array_equal(y, oracle.wino_forward(x, w, 1))
+    lib.fc_conv_destroy(h)

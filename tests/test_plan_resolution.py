@@ -84,6 +84,20 @@ def test_make_layer_auto_follows_the_plan():
             assert layer._algo == 0  # created as AUTO, so the library records the request
 
 
+def test_accuracy_mode_runs_the_fp32_kernels_on_short_reductions(monkeypatch):
+    """By default a Winograd layer of at most 64 input channels asked for in 3xTF32 (or in "tf32" with Winograd named)
+    is planned in the fp32 arithmetic: faster there, and inside the mode's tolerance by being exact."""
+    monkeypatch.delenv("FASTCONV_3XTF32_MIN_IC")
+    assert plan(64, 3, 64, 224, 3, mode="3xtf32") == ("winograd", "fp32")
+    assert plan(1, 64, 128, 112, 3, mode="3xtf32") == ("winograd", "fp32")
+    assert plan(1, 65, 128, 112, 3, mode="3xtf32") == ("winograd", "3xtf32")
+    assert plan(8, 512, 512, 28, 3, mode="3xtf32") == ("winograd", "3xtf32")
+    assert plan(1, 64, 64, 56, 3, algo="winograd", mode="tf32") == ("winograd", "fp32")
+    assert plan(1, 64, 64, 56, 1, mode="3xtf32") == ("im2col", "3xtf32")   # the rule is about Winograd layers only
+    monkeypatch.setenv("FASTCONV_3XTF32_MIN_IC", "200")
+    assert plan(1, 128, 128, 56, 3, mode="3xtf32") == ("winograd", "fp32")
+
+
 def test_bad_arguments_are_refused():
     d = fc.make_desc(1, 8, 8, 8, 8)
     with pytest.raises(fc.FastConvError):
