@@ -663,7 +663,9 @@ def main():
             rows, _ = s.per_layer(max(3, args.steps), hbm_peak, peak_tflops)
             subs[name] = {"math_mode": mode, "algorithm": algo, "value": round(total_flops / first / 1e6, 1),
                           "unit": "GFLOP/s", "ms_per_step": round(first, 4), "repeat_stats": repeat_stats(many, args.steps),
-                          "tolerance": "rel-L2 <= 3e-3 on every layer" if mode == "tf32" else "rel-L2 <= 1e-5 (see tests)",
+                          "tolerance": "rel-L2 <= 3e-3 on every layer" if mode == "tf32" else
+                                       "rel-L2 <= 1e-5 (see tests); the `math` of a layer says whether it ran the split "
+                                       "tensor-core arithmetic or, with at most 64 input channels, the fp32 kernels",
                           "layers": [{k: r[k] for k in ("layer", "algo", "math", "ms", "frac_of_roofline", "bound")} for r in rows]}
             s.close()
         if world == 1:
