@@ -312,7 +312,7 @@ constexpr int ITW_WARPS = 4;
 template <bool ALONG_TILES>
 __global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_kernel(
     const float *__restrict__ in, float *__restrict__ V, int n_tiles, int ic, int icp, int tp, int ih, int iw, int pad,
-    int th, int tw) {
+    int th, int tw, bool allow_pairs) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // the warps of a block: ITW_WARPS channels of the same 32 tiles, or one channel of 32 * ITW_WARPS consecutive tiles
     const int tile = ALONG_TILES ? blockIdx.x * 32 * ITW_WARPS + threadIdx.x : blockIdx.x * 32 + lane;
@@ -334,7 +334,33 @@ __global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_
         }
         src = in + (((ptrdiff_t)img * ic + c) * ih + y0) * iw + x0;
     }
-    if (rows == 0xffu && cols == 0xffu) {
+    // An even row length and an 8-byte aligned image let the window rows travel as aligned pairs: the window starts
+    // at x0 = 6*tx - pad, whose parity is the padding's, so the pair grid starts `shift` = pad & 1 elements to its left
+    // and 4 (or, shifted, 5) pairs cover it; with an even row length a pair lies wholly inside or wholly outside the
+    // image.  37 % fewer load instructions than element by element, which is what this kernel is short of.
+    const bool pairs = allow_pairs && (iw & 1) == 0 && (reinterpret_cast<uintptr_t>(in) & 7) == 0;
+    if (pairs) {
+        const int shift = pad & 1;
+        // pair j holds window elements 2j - shift and 2j + 1 - shift; the one of them that always belongs to the window
+        // (element 2j, or 7 for the fifth pair) says whether the pair lies inside the image
+        unsigned pair_ok = 0;
+#pragma unroll
+        for (int j = 0; j < 5; ++j) pair_ok |= ((cols >> (j < 4 ? 2 * j : 7)) & 1u) << j;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) {
+            const float2 *rp = reinterpret_cast<const float2 *>(src + (ptrdiff_t)y * iw - shift);
+            float f[10];
+#pragma unroll
+            for (int j = 0; j < 5; ++j) {
+                float2 q = make_float2(0.f, 0.f);
+                if ((j < 4 || shift) && ((rows >> y) & (pair_ok >> j) & 1u)) q = __ldg(rp + j);
+                f[2 * j] = q.x;
+                f[2 * j + 1] = q.y;
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) r[y][x] = shift ? f[x + 1] : f[x];
+        }
+    } else if (rows == 0xffu && cols == 0xffu) {
 #pragma unroll
         for (int y = 0; y < 8; ++y)
 #pragma unroll
@@ -377,17 +403,18 @@ static bool it_wide(const WinoGeom &g) {
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
     dim3 block(256);
     if (it_wide(g)) {
+        static const bool pairs_on = !(getenv("FASTCONV_IT_PAIRS") && atoi(getenv("FASTCONV_IT_PAIRS")) == 0);
         // a block of four warps along the tile axis writes runs of 512 bytes per (position, channel) instead of 128:
         // measured 1-4 % faster at 64 images
         dim3 wblock(32 * ITW_WARPS);
         if (g.tiles >= 32 * ITW_WARPS) {
             dim3 grid((unsigned)ceil_div(g.tp, 32 * ITW_WARPS), (unsigned)g.icp);
             FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel<true>, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles,
-                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw, pairs_on));
         } else {
             dim3 grid((unsigned)ceil_div(g.tp, 32), (unsigned)ceil_div(g.icp, ITW_WARPS));
             FC_CHECK_CUDA(launch_pdl(input_transform_rowmajor_wide_kernel<false>, grid, wblock, 0, ctx->stream, d_in, d_V, g.tiles,
-                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw));
+                                     g.ic, g.icp, g.tp, g.ih, g.iw, g.pad, g.th, g.tw, pairs_on));
         }
         return FC_OK;
     }
@@ -550,8 +577,8 @@ __global__ void __launch_bounds__(256) output_transform_scatter_publish_kernel(c
 // run along the output rows.  No block-wide synchronisation.
 constexpr int OTW_WARPS = 4;
 
-template <bool ALONG_TILES>
-__global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(const float *__restrict__ M,
+template <bool ALONG_TILES, bool UPFRONT>
+__global__ void __launch_bounds__(32 * OTW_WARPS, UPFRONT ? 4 : 1) output_transform_wide_kernel(const float *__restrict__ M,
                                                                               float *__restrict__ out, int n_tiles,
                                                                               int oc, int tp, int oh, int ow, int th,
                                                                               int tw, Epilogue ep) {
@@ -568,12 +595,24 @@ __global__ void __launch_bounds__(32 * OTW_WARPS) output_transform_wide_kernel(c
     if (t < n_tiles) {
         const float *src = M + (size_t)k * tp + t;
         float h[8][6];
+        if constexpr (UPFRONT) {
+            // all 64 values of the item requested before the first is used: the kernel lives on loads in flight
+            float m[8][8];
 #pragma unroll
-        for (int row = 0; row < 8; ++row) {
-            float m[8];
+            for (int row = 0; row < 8; ++row)
 #pragma unroll
-            for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
-            output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
+                for (int col = 0; col < 8; ++col) m[row][col] = __ldg(src + (size_t)(col * 8 + row) * plane);
+#pragma unroll
+            for (int row = 0; row < 8; ++row)
+                output_transform_1d(m[row][0], m[row][1], m[row][2], m[row][3], m[row][4], m[row][5], m[row][6], m[row][7], h[row]);
+        } else {
+#pragma unroll
+            for (int row = 0; row < 8; ++row) {
+                float m[8];
+#pragma unroll
+                for (int col = 0; col < 8; ++col) m[col] = __ldg(src + (size_t)(col * 8 + row) * plane);
+                output_transform_1d(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], h[row]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < 6; ++j) {
@@ -817,14 +856,16 @@ int launch_output_transform(fc_context *ctx, const float *d_M, float *d_out, con
     dim3 block(256);
     if (g.tiles >= wide_min_tiles()) {
         dim3 wblock(32 * OTW_WARPS);
+        static const bool upfront_off = getenv("FASTCONV_OT_UPFRONT") && atoi(getenv("FASTCONV_OT_UPFRONT")) == 0;
+        const bool upfront = !upfront_off && (size_t)g.tiles * g.oc >= 512 * 1024;
         if (g.tiles >= 32 * OTW_WARPS) {  // four warps along the tile axis: reads of 512 bytes per position (1 % faster)
             dim3 grid((unsigned)ceil_div(g.tiles, 32 * OTW_WARPS), (unsigned)g.oc);
-            FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel<true>, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc,
-                                     g.tp, g.oh, g.ow, g.th, g.tw, ep));
+            FC_CHECK_CUDA(launch_pdl(upfront ? output_transform_wide_kernel<true, true> : output_transform_wide_kernel<true, false>,
+                                     grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc, g.tp, g.oh, g.ow, g.th, g.tw, ep));
         } else {
             dim3 grid((unsigned)ceil_div(g.tiles, 32), (unsigned)ceil_div(g.oc, OTW_WARPS));
-            FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel<false>, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles, g.oc,
-                                     g.tp, g.oh, g.ow, g.th, g.tw, ep));
+            FC_CHECK_CUDA(launch_pdl(output_transform_wide_kernel<false, false>, grid, wblock, 0, ctx->stream, d_M, d_out, g.tiles,
+                                     g.oc, g.tp, g.oh, g.ow, g.th, g.tw, ep));
         }
         return FC_OK;
     }
