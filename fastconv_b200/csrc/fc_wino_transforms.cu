@@ -386,10 +386,10 @@ __global__ void __launch_bounds__(32 * ITW_WARPS) input_transform_rowmajor_wide_
         for (int y = 0; y < 8; ++y) dst[(size_t)(x * 8 + y) * plane] = r[y][x];  // p = x*8 + y
 }
 
-// Which layers take the throughput-oriented input transform: one thread per item needs many items to fill the machine
-// (8 images, whole VGG-16 stack: 1.700 ms with it from 64 tiles on, 1.683 ms from 1024 tiles on; 64 images, 576 tiles x
-// 512 channels: 0.035 against 0.037 ms in its favour).  $FASTCONV_IT_WIDE_MIN=<tiles> replaces the rule by a plain
-// threshold.
+// Which layers take the throughput-oriented input transform: one thread per item needs items enough to fill the
+// machine.  From 64 tiles and 64 K (channel, tile) items on -- 8 images, whole VGG-16 stack: 1.607 ms against 1.619 ms
+// with the kernel kept to 1024 tiles and more; one image: 0.381 against 0.382 ms the other way round, which is why the
+// item count is part of the rule.  $FASTCONV_IT_WIDE_MIN=<tiles> replaces the rule by a plain threshold.
 static bool it_wide(const WinoGeom &g) {
     static int v = -1;
     if (v < 0) {
@@ -397,7 +397,7 @@ static bool it_wide(const WinoGeom &g) {
         v = e && atoi(e) > 0 ? atoi(e) : 0;
     }
     if (v > 0) return g.tiles >= v;
-    return g.tiles >= 1024 || (g.tiles >= 512 && (long long)g.tiles * g.icp >= 256 * 1024);
+    return g.tiles >= 64 && (long long)g.tiles * g.icp >= 64 * 1024;
 }
 
 int launch_input_transform_rowmajor(fc_context *ctx, const float *d_in, float *d_V, const WinoGeom &g) {
